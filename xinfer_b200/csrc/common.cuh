@@ -1,0 +1,63 @@
+// Shared device helpers for the engine's kernels (sm_100a only).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+// Bits of the device-side error word that kernels set instead of faulting.
+#define XB_ERR_BAD_TOKEN 1   // a token id outside [0, vocab)
+#define XB_ERR_BAD_PAGE 2    // a block-table entry outside [0, num_pages)
+#define XB_ERR_WAIT 4        // a bounded wait on an mbarrier gave up
+#define XB_ERR_BAD_ROW 8     // a requested row outside [0, tokens)
+
+// Element type codes shared with the Python side.
+#define XB_F32 0
+#define XB_BF16 1
+
+#define XB_EXPORT extern "C" __attribute__((visibility("default")))
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  The order of the
+// additions is fixed by the thread layout, so the result does not depend on what else runs.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floats */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+// Last CUDA error of a launch as an int for the caller (0 = ok).
+static inline int xb_launch_status() { return (int)cudaGetLastError(); }

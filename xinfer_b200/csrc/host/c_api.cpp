@@ -1,0 +1,212 @@
+// C interface of the host runtime (loaded from Python with ctypes): cache manager, scheduler and
+// the assembly of a step's metadata into one packed int32 buffer that a single copy sends to the
+// device.
+#include <algorithm>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "cache_manager.h"
+#include "scheduler.h"
+
+#define XB_API extern "C" __attribute__((visibility("default")))
+
+using namespace xb;
+
+// ---- cache manager -------------------------------------------------------------------------
+XB_API void* xb_cm_create(int n_groups, const int* page_sizes, const int* num_pages, const int* windows,
+                          int max_requests) {
+    if (n_groups <= 0 || max_requests <= 0) return nullptr;
+    std::vector<GroupSpec> groups(n_groups);
+    for (int g = 0; g < n_groups; ++g) {
+        if (page_sizes[g] <= 0 || num_pages[g] <= 0) return nullptr;
+        groups[g].page_size = page_sizes[g];
+        groups[g].num_pages = num_pages[g];
+        groups[g].window = windows[g];
+    }
+    return new CacheManager(groups, max_requests);
+}
+XB_API void xb_cm_destroy(void* h) { delete static_cast<CacheManager*>(h); }
+XB_API int xb_cm_open(void* h) { return static_cast<CacheManager*>(h)->open_request(); }
+XB_API int xb_cm_close(void* h, int slot) { return static_cast<CacheManager*>(h)->close_request(slot) ? 1 : 0; }
+XB_API int xb_cm_is_live(void* h, int slot) { return static_cast<CacheManager*>(h)->is_live(slot) ? 1 : 0; }
+XB_API int xb_cm_length(void* h, int slot) { return static_cast<CacheManager*>(h)->length(slot); }
+XB_API int xb_cm_can_extend(void* h, int slot, int new_len) { return static_cast<CacheManager*>(h)->can_extend(slot, new_len) ? 1 : 0; }
+XB_API int xb_cm_extend(void* h, int slot, int new_len) { return static_cast<CacheManager*>(h)->extend(slot, new_len) ? 1 : 0; }
+XB_API int xb_cm_advance(void* h, int slot, int new_len) { return static_cast<CacheManager*>(h)->advance(slot, new_len) ? 1 : 0; }
+XB_API int xb_cm_free_pages(void* h, int g) { return static_cast<CacheManager*>(h)->free_pages(g); }
+XB_API int xb_cm_table_size(void* h, int slot, int g) { return static_cast<CacheManager*>(h)->table_size(slot, g); }
+XB_API int xb_cm_copy_table(void* h, int slot, int g, int32_t* out, int cap) { return static_cast<CacheManager*>(h)->copy_table(slot, g, out, cap); }
+XB_API int xb_cm_live_requests(void* h) { return static_cast<CacheManager*>(h)->live_requests(); }
+XB_API int xb_cm_consistent(void* h, char* why, int cap) {
+    std::string s;
+    const bool ok = static_cast<CacheManager*>(h)->consistent(&s);
+    if (why && cap > 0) {
+        std::strncpy(why, s.c_str(), cap - 1);
+        why[cap - 1] = 0;
+    }
+    return ok ? 1 : 0;
+}
+
+// ---- step metadata ---------------------------------------------------------------------------
+// Packs, for B entries (slot, count, tokens) whose start is the slot's cached length:
+//   token_ids[Tp] positions[Tp] req_of_token[Tp] q_start[Bp+1] start_pos[Bp] slots[Bp]
+//   logit_rows[Rp] and, per group, block_table[Bp, stride_g]
+// Tp/Bp are T and B padded up to pad_tokens / pad_entries (padding tokens belong to request -1
+// and are skipped by the kernels); every array starts on a 16-byte boundary.  `strides` holds a
+// wanted row length per group (0: as long as the longest table here, rounded up to 8).
+// offsets_out[0..6] = array offsets in int32 units, [7 + g] = table offset of group g,
+// [7 + G + g] = stride of group g, and the return value is the number of int32 used
+// (negative on error: -1 capacity, -2 slot not live, -3 pages missing, -4 bad want).
+XB_API long long xb_assemble(void* h, int B, const int* slots, const int* counts, const int* tokens,
+                             int R, const int* want_entry, const int* want_offset, int pad_tokens,
+                             int pad_entries, const int* strides, int32_t* out, long long capacity,
+                             long long* offsets_out) {
+    CacheManager* cm = static_cast<CacheManager*>(h);
+    const int G = cm->num_groups();
+    int T = 0;
+    for (int b = 0; b < B; ++b) {
+        if (!cm->is_live(slots[b]) || counts[b] <= 0) return -2;
+        T += counts[b];
+    }
+    const int Tp = std::max(T, pad_tokens), Bp = std::max(B, pad_entries), Rp = std::max(R, 1);
+    auto up4 = [](long long x) { return (x + 3) / 4 * 4; };
+    std::vector<int> stride(G);
+    for (int g = 0; g < G; ++g) {
+        int longest = 1;
+        const int ps = cm->group(g).page_size;
+        for (int b = 0; b < B; ++b) {
+            const int new_len = cm->length(slots[b]) + counts[b];
+            if (cm->table_size(slots[b], g) * ps < new_len) return -3;
+            longest = std::max(longest, (new_len + ps - 1) / ps);
+        }
+        stride[g] = (longest + 7) / 8 * 8;
+        if (strides && strides[g] > 0) {
+            if (strides[g] < longest) return -1;
+            stride[g] = strides[g];
+        }
+    }
+    long long off = 0;
+    long long o_tok = off; off = up4(off + Tp);
+    long long o_pos = off; off = up4(off + Tp);
+    long long o_req = off; off = up4(off + Tp);
+    long long o_qs = off; off = up4(off + Bp + 1);
+    long long o_sp = off; off = up4(off + Bp);
+    long long o_sl = off; off = up4(off + Bp);
+    long long o_rows = off; off = up4(off + Rp);
+    std::vector<long long> o_tab(G);
+    for (int g = 0; g < G; ++g) {
+        o_tab[g] = off;
+        off = up4(off + (long long)Bp * stride[g]);
+    }
+    if (off > capacity) return -1;
+    int t = 0;
+    for (int b = 0; b < B; ++b) {
+        const int start = cm->length(slots[b]);
+        out[o_qs + b] = t;
+        out[o_sp + b] = start;
+        out[o_sl + b] = slots[b];
+        for (int i = 0; i < counts[b]; ++i, ++t) {
+            out[o_tok + t] = tokens[t];
+            out[o_pos + t] = start + i;
+            out[o_req + t] = b;
+        }
+    }
+    for (int b = B; b <= Bp; ++b) out[o_qs + b] = T;
+    for (int b = B; b < Bp; ++b) {
+        out[o_sp + b] = 0;
+        out[o_sl + b] = -1;
+    }
+    for (; t < Tp; ++t) {
+        out[o_tok + t] = 0;
+        out[o_pos + t] = 0;
+        out[o_req + t] = -1;
+    }
+    for (int r = 0; r < R; ++r) {
+        const int e = want_entry[r];
+        if (e < 0 || e >= B || want_offset[r] < 0 || want_offset[r] >= counts[e]) return -4;
+        out[o_rows + r] = out[o_qs + e] + want_offset[r];
+    }
+    for (int r = R; r < Rp; ++r) out[o_rows + r] = 0;
+    for (int g = 0; g < G; ++g) {
+        for (int b = 0; b < Bp; ++b) {
+            int32_t* row = out + o_tab[g] + (long long)b * stride[g];
+            int n = 0;
+            if (b < B) n = cm->copy_table(slots[b], g, row, stride[g]);
+            for (int i = std::max(n, 0); i < stride[g]; ++i) row[i] = -1;
+        }
+    }
+    offsets_out[0] = o_tok; offsets_out[1] = o_pos; offsets_out[2] = o_req; offsets_out[3] = o_qs;
+    offsets_out[4] = o_sp; offsets_out[5] = o_sl; offsets_out[6] = o_rows;
+    for (int g = 0; g < G; ++g) {
+        offsets_out[7 + g] = o_tab[g];
+        offsets_out[7 + G + g] = stride[g];
+    }
+    return off;
+}
+
+// ---- scheduler ---------------------------------------------------------------------------------
+struct SchedHandle {
+    Scheduler sched;
+    std::vector<StepEntry> last;
+    SchedHandle(CacheManager* c, const SchedulerConfig& cfg) : sched(c, cfg) {}
+};
+
+XB_API void* xb_sched_create(void* cm, int max_num_seqs, int max_batched_tokens, int prefill_chunk,
+                             int max_model_len, const int* eos_ids, int n_eos) {
+    if (!cm || max_num_seqs <= 0 || max_batched_tokens <= 0 || prefill_chunk <= 0 || max_model_len <= 1) return nullptr;
+    SchedulerConfig cfg;
+    cfg.max_num_seqs = max_num_seqs;
+    cfg.max_num_batched_tokens = max_batched_tokens;
+    cfg.prefill_chunk_size = prefill_chunk;
+    cfg.max_model_len = max_model_len;
+    if (n_eos > 0) cfg.eos_token_ids.assign(eos_ids, eos_ids + n_eos);
+    return new SchedHandle(static_cast<CacheManager*>(cm), cfg);
+}
+XB_API void xb_sched_destroy(void* h) { delete static_cast<SchedHandle*>(h); }
+XB_API int xb_sched_add(void* h, long long req_id, const int* prompt, int n, int max_tokens, int ignore_eos,
+                        const int* stop_ids, int n_stop) {
+    return (int)static_cast<SchedHandle*>(h)->sched.add(req_id, prompt, n, max_tokens, ignore_eos != 0, stop_ids, n_stop);
+}
+XB_API int xb_sched_abort(void* h, long long req_id) { return static_cast<SchedHandle*>(h)->sched.abort(req_id) ? 1 : 0; }
+
+// Returns the number of entries (or -1 if the arrays are too small) and keeps them for commit.
+XB_API int xb_sched_schedule(void* h, int cap_entries, long long* req_ids, int* slots, int* starts,
+                             int* counts, int* wants, int cap_tokens, int* tokens, int* n_tokens) {
+    SchedHandle* s = static_cast<SchedHandle*>(h);
+    std::vector<int32_t> toks;
+    s->last = s->sched.schedule(&toks);
+    if ((int)s->last.size() > cap_entries || (int)toks.size() > cap_tokens) return -1;
+    for (size_t i = 0; i < s->last.size(); ++i) {
+        req_ids[i] = s->last[i].req_id;
+        slots[i] = s->last[i].slot;
+        starts[i] = s->last[i].start;
+        counts[i] = s->last[i].count;
+        wants[i] = s->last[i].want ? 1 : 0;
+    }
+    std::copy(toks.begin(), toks.end(), tokens);
+    *n_tokens = (int)toks.size();
+    return (int)s->last.size();
+}
+XB_API void xb_sched_commit(void* h, const int* sampled, int n_sampled) {
+    SchedHandle* s = static_cast<SchedHandle*>(h);
+    std::vector<int32_t> v(sampled, sampled + (n_sampled > 0 ? n_sampled : 0));
+    s->sched.commit(s->last, v);
+    s->last.clear();
+}
+XB_API int xb_sched_drain_finished(void* h, long long* out, int cap) {
+    auto v = static_cast<SchedHandle*>(h)->sched.drain_finished();
+    const int n = std::min((int)v.size(), cap);
+    for (int i = 0; i < n; ++i) out[i] = v[i];
+    return n;
+}
+XB_API int xb_sched_num_waiting(void* h) { return static_cast<SchedHandle*>(h)->sched.num_waiting(); }
+XB_API int xb_sched_num_running(void* h) { return static_cast<SchedHandle*>(h)->sched.num_running(); }
+XB_API int xb_sched_preemptions(void* h) { return static_cast<SchedHandle*>(h)->sched.preemptions(); }
+XB_API int xb_sched_finish_reason(void* h, long long id) { return static_cast<SchedHandle*>(h)->sched.finish_reason(id); }
+XB_API int xb_sched_output_length(void* h, long long id) { return static_cast<SchedHandle*>(h)->sched.output_length(id); }
+XB_API int xb_sched_copy_output(void* h, long long id, int* out, int cap) { return static_cast<SchedHandle*>(h)->sched.copy_output(id, out, cap); }
+XB_API int xb_sched_prompt_length(void* h, long long id) { return static_cast<SchedHandle*>(h)->sched.prompt_length(id); }
+XB_API int xb_sched_num_drawn(void* h, long long id) { return static_cast<SchedHandle*>(h)->sched.num_drawn(id); }
+XB_API int xb_sched_copy_tail(void* h, long long id, int* out, int n) { return static_cast<SchedHandle*>(h)->sched.copy_tail(id, out, n); }
+XB_API int xb_sched_release(void* h, long long id) { return static_cast<SchedHandle*>(h)->sched.release(id) ? 1 : 0; }

@@ -1,0 +1,200 @@
+"""The Python entry point, in the manner of the reference's package (xinfer.pyi:191-238,
+src/py/mod.rs:28-152): ``Engine(econfig, dtype)`` with ``generate_sync`` and ``generate_stream``.
+Prompts are lists of token ids (the reference takes chat messages and tokenises them; templates
+and tokenisers are outside this engine).
+
+One loop iteration = schedule -> step -> sample -> commit, as the reference's
+prepare_step / run_forward / finish_step (src/core/engine.rs:1034, 1085, 1363).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Dict, Iterator, List, Optional, Sequence, Tuple, Union
+
+import numpy as np
+import torch
+
+from ..config import EngineConfig
+from ..sampling import SamplingParams
+from ..sampling.sampler import PENALTY_HISTORY, Sampler
+from .runner import ModelRunner, StepError, StepInput
+from .scheduler import Scheduler, SchedulerError
+
+
+@dataclass
+class GenerationOutput:
+    """Fields as in the reference (src/core/mod.rs:13-30); ``decode_output`` holds token ids."""
+
+    seq_id: int
+    prompt_length: int
+    prompt_start_time: int    # milliseconds since the epoch
+    decode_start_time: int
+    decode_finish_time: int
+    decoded_length: int
+    decode_output: List[int]
+    finish_reason: Optional[str] = None
+
+
+@dataclass
+class StreamItem:
+    """``datatype`` is "TOKEN_ID" (data: int), "DONE" (data: (seq_id, prompt_length,
+    decoded_length, decode_ms)) or "ERROR" (data: str), after src/py/mod.rs:178-279."""
+
+    datatype: str
+    data: object
+
+
+@dataclass
+class _Live:
+    params: SamplingParams
+    seed: int
+    prompt_len: int
+    t_start: float
+    t_first: float = 0.0
+    streamed: int = 0
+
+
+def _ms(t: float) -> int:
+    return int(t * 1000)
+
+
+class Engine:
+    def __init__(self, econfig: EngineConfig, dtype: str = "bf16"):
+        econfig.validate()
+        self.econfig = econfig
+        self.runner = ModelRunner(
+            econfig.model_dir(), dtype, block_size=econfig.block_size, num_blocks=econfig.num_blocks,
+            max_num_seqs=econfig.max_num_seqs, kv_fraction=econfig.kv_fraction, device=econfig.device,
+            max_model_len=econfig.max_model_len)
+        self.max_model_len = self.runner.max_model_len
+        budget = min(econfig.max_num_batched_tokens, max(self.runner.kv_cache_tokens(), 1))
+        self.scheduler = Scheduler(
+            self.runner.cache, max_num_seqs=econfig.max_num_seqs, max_num_batched_tokens=budget,
+            prefill_chunk_size=econfig.prefill_chunk_size, max_model_len=self.max_model_len,
+            eos_token_ids=self.runner.plan.eos_token_ids)
+        self.sampler = Sampler(self.runner.device, econfig.max_num_seqs)
+        self.seed = 0 if econfig.seed is None else int(econfig.seed)
+        self._next_id = 0
+        self._live: Dict[int, _Live] = {}
+        self._done: Dict[int, GenerationOutput] = {}
+        self.use_graphs = not econfig.disable_cuda_graph
+        # counters (the reference logs the same two throughputs, src/core/engine.rs:1584-1716)
+        self.stats = {"steps": 0, "prompt_tokens": 0, "decoded_tokens": 0, "preemptions": 0}
+
+    # ---- admission ------------------------------------------------------------------------------
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
+        params = params or SamplingParams()
+        params.validate()
+        prompt = [int(t) for t in prompt]
+        V = self.runner.plan.vocab_size
+        if any(t < 0 or t >= V for t in prompt):
+            raise ValueError(f"prompt token ids must lie in [0, {V})")
+        max_tokens = params.max_tokens or self.econfig.max_tokens or 16384
+        seq_id = self._next_id
+        self._next_id += 1
+        self.scheduler.add(seq_id, prompt, max_tokens, params.ignore_eos, params.stop_token_ids)
+        seed = params.seed if params.seed is not None else (self.seed * 0x9E3779B97F4A7C15 + seq_id + 1)
+        self._live[seq_id] = _Live(params, int(seed) & 0xFFFFFFFFFFFFFFFF, len(prompt), time.time())
+        return seq_id
+
+    # ---- one iteration --------------------------------------------------------------------------------
+    def step(self) -> List[int]:
+        """Schedule and run one batch; returns the ids of requests that ended with it."""
+        entries = self.scheduler.schedule()
+        ended = self.scheduler.drain_finished()  # requests the scheduler had to abort
+        if entries:
+            inputs = []
+            wanted = []
+            for e in entries:
+                if e.start == 0:
+                    self.runner.prepare_slot(e.slot)
+                inputs.append(StepInput(e.slot, e.tokens, [len(e.tokens) - 1] if e.want else []))
+                if e.want:
+                    wanted.append(e)
+                if e.start < self._live[e.req_id].prompt_len:
+                    self.stats["prompt_tokens"] += min(len(e.tokens), self._live[e.req_id].prompt_len - e.start)
+            logits = self.runner.step(inputs, allow_graph=self.use_graphs)
+            sampled: List[int] = []
+            if wanted:
+                lives = [self._live[e.req_id] for e in wanted]
+                hist = None
+                if any(l.params.has_penalties for l in lives):
+                    hist = [self.scheduler.tail(e.req_id, PENALTY_HISTORY) if l.params.has_penalties else ()
+                            for e, l in zip(wanted, lives)]
+                toks = self.sampler.sample(logits, [l.params for l in lives], [l.seed for l in lives],
+                                           [self.scheduler.num_drawn(e.req_id) for e in wanted], hist)
+                self.runner.queue_error_check()
+                sampled = self.sampler.to_host(toks).tolist()
+                self.runner.raise_if_error()
+                now = time.time()
+                for l in lives:
+                    if not l.t_first:
+                        l.t_first = now
+                self.stats["decoded_tokens"] += len(sampled)
+            ended += self.scheduler.commit(sampled)
+            self.stats["steps"] += 1
+        self.stats["preemptions"] = self.scheduler.preemptions
+        for seq_id in ended:
+            self._finish(seq_id)
+        return ended
+
+    def _finish(self, seq_id: int) -> None:
+        live = self._live.pop(seq_id, None)
+        if live is None:
+            return
+        out = self.scheduler.output(seq_id)
+        now = time.time()
+        self._done[seq_id] = GenerationOutput(
+            seq_id=seq_id, prompt_length=live.prompt_len, prompt_start_time=_ms(live.t_start),
+            decode_start_time=_ms(live.t_first or now), decode_finish_time=_ms(now),
+            decoded_length=len(out), decode_output=out, finish_reason=self.scheduler.finish_reason(seq_id))
+        self.scheduler.release(seq_id)
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    # ---- the reference's calls ----------------------------------------------------------------------------
+    def generate_sync(self, params: Union[SamplingParams, Sequence[SamplingParams]],
+                      prompts: Sequence[Sequence[int]]) -> List[GenerationOutput]:
+        """Generate for every prompt (continuous batching) and return the outputs in prompt order."""
+        if isinstance(params, SamplingParams):
+            params = [params] * len(prompts)
+        if len(params) != len(prompts):
+            raise ValueError(f"{len(params)} sampling params for {len(prompts)} prompts")
+        ids = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
+        while any(i in self._live for i in ids):
+            before = (self.stats["steps"], len(self._live))
+            self.step()
+            if (self.stats["steps"], len(self._live)) == before and not self.has_work():
+                break
+        return [self._done.pop(i) for i in ids]
+
+    def generate_stream(self, params: SamplingParams, prompt: Sequence[int]) -> Tuple[int, int, Iterator[StreamItem]]:
+        """Returns (seq_id, prompt_length, iterator of StreamItem)."""
+        seq_id = self.add_request(prompt, params)
+        live = self._live[seq_id]
+
+        def stream() -> Iterator[StreamItem]:
+            try:
+                while seq_id in self._live:
+                    self.step()
+                    src = self._done[seq_id].decode_output if seq_id in self._done else self.scheduler.output(seq_id)
+                    for tok in src[live.streamed:]:
+                        yield StreamItem("TOKEN_ID", int(tok))
+                    live.streamed = len(src)
+                out = self._done.pop(seq_id)
+                yield StreamItem("DONE", (seq_id, out.prompt_length, out.decoded_length,
+                                          out.decode_finish_time - out.decode_start_time))
+            except (StepError, SchedulerError) as e:
+                self.scheduler.abort(seq_id)
+                yield StreamItem("ERROR", str(e))
+
+        return seq_id, len(prompt), stream()
+
+    def get_available_kv_tokens(self) -> int:
+        return self.runner.available_kv_tokens()
+
+    def get_num_cached_tokens(self) -> int:
+        """Tokens held by a prefix cache; this engine keeps none."""
+        return 0

@@ -1,0 +1,303 @@
+"""The model runner: owns the model, the cache manager with its device pages, per-request state
+and the ONE step function everything else drives (generation, trace replay, the benchmark).
+
+``step(entries)`` takes a batch of (request slot, its next tokens, wanted positions): portions of
+prompts beside single decoded tokens, cut anywhere.  It takes the pages those tokens need, runs
+only those tokens as one batch against the cache and returns float32 logits at the wanted
+positions.  The reference's counterpart is ``ModelRunner::run`` (src/core/runner.rs:1018), which
+runs either prompt chunks or decode tokens, never both, and returns sampled ids
+(prepare_prefill :1303-1563, prepare_decode :1565-1750).
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import kernels
+from ..cache.manager import CacheError, CacheGroup, CacheManager, StateSlots
+from ..config import ConfigError, load_config
+from ..models.decoder import DecoderModel
+from ..native import host_lib
+from ..parts import LayerCache, StepContext, Workspace
+from ..weights.loader import WeightStore
+
+
+class StepError(RuntimeError):
+    pass
+
+
+@dataclass
+class StepInput:
+    slot: int                 # the request's slot, from ``open_request``
+    tokens: Sequence[int]     # its next tokens (a prompt portion, or one decoded token)
+    want: Sequence[int] = ()  # positions among these tokens whose logits are wanted
+
+
+def _dtype_of(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        if name in (torch.float32, torch.bfloat16):
+            return name
+        raise ConfigError(f"dtype {name} is not supported (bfloat16 or float32)")
+    key = str(name).lower()
+    if key in ("bf16", "bfloat16"):
+        return torch.bfloat16
+    if key in ("f32", "fp32", "float32"):
+        return torch.float32
+    raise ConfigError(f"dtype '{name}' is not supported (bf16/bfloat16 or f32/float32)")
+
+
+class _MetaBuffers:
+    """A small ring of pinned staging buffers with a device twin each; a buffer is reused only
+    after the copy that read it has finished."""
+
+    def __init__(self, device, depth: int = 3):
+        self.device = device
+        self.depth = depth
+        self.cap = 0
+        self.host: List[torch.Tensor] = []
+        self.dev: List[torch.Tensor] = []
+        self.events: List[Optional[torch.cuda.Event]] = []
+        self.i = 0
+
+    def reserve(self, n: int) -> None:
+        if n <= self.cap:
+            return
+        torch.cuda.synchronize(self.device)
+        self.cap = max(n, 2 * self.cap, 4096)
+        self.host = [torch.empty(self.cap, dtype=torch.int32, pin_memory=True) for _ in range(self.depth)]
+        self.dev = [torch.empty(self.cap, dtype=torch.int32, device=self.device) for _ in range(self.depth)]
+        self.events = [None] * self.depth
+
+    def next(self) -> Tuple[torch.Tensor, torch.Tensor, int]:
+        self.i = (self.i + 1) % self.depth
+        ev = self.events[self.i]
+        if ev is not None:
+            ev.synchronize()
+        return self.host[self.i], self.dev[self.i], self.i
+
+    def sent(self, i: int) -> None:
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+
+
+class ModelRunner:
+    def __init__(self, model_dir: str, dtype="bfloat16", *, block_size: int = 16,
+                 num_blocks: Optional[int] = None, max_num_seqs: int = 32,
+                 kv_fraction: float = 0.7, device="cuda:0", max_model_len: Optional[int] = None,
+                 model: Optional[DecoderModel] = None, plan=None):
+        if not torch.cuda.is_available():
+            raise StepError("no CUDA device: this engine runs on a B200 (sm_100a) only and has no CPU path")
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        cap = torch.cuda.get_device_capability(self.device)
+        if cap[0] != 10:
+            raise StepError(f"device {self.device} has compute capability {cap[0]}.{cap[1]}; the kernels are built for sm_100a")
+        self.dtype = _dtype_of(dtype)
+        kernels.kernels_lib()  # build / load now, loudly
+        if model is None:
+            entry, cfg = load_config(model_dir)
+            self.config = cfg
+            plan = entry.plan_of(cfg)
+            model = DecoderModel(plan, self.dtype, self.device)
+            store = WeightStore(model_dir)
+            try:
+                model.load(store)
+            finally:
+                store.close()
+        self.model = model
+        self.plan = model.plan
+        self.block_size = int(block_size)
+        self.max_num_seqs = int(max_num_seqs)
+        self.max_model_len = int(max_model_len or self.plan.max_positions)
+        self.workspace = Workspace(self.device)
+        self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._err_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+        self._build_caches(num_blocks, kv_fraction)
+        self._meta = _MetaBuffers(self.device)
+        self._lib = host_lib()
+        self.steps_run = 0
+
+    # ---- caches --------------------------------------------------------------------------------------
+    def _build_caches(self, num_blocks: Optional[int], kv_fraction: float) -> None:
+        needs = self.model.cache_needs()
+        runs = self.plan.runs
+        # runs that own pages, grouped by how long keys are kept
+        keys: List[Optional[int]] = []
+        run_group: Dict[int, int] = {}
+        for pos, (run, need) in enumerate(zip(runs, needs)):
+            if need is None or run.cache_from is not None:
+                continue
+            if need.window not in keys:
+                keys.append(need.window)
+            run_group[pos] = keys.index(need.window)
+        esize = 4 if self.dtype == torch.float32 else 2
+        page_bytes = [0] * max(len(keys), 1)
+        for pos, g in run_group.items():
+            page_bytes[g] += 2 * needs[pos].kv_heads * needs[pos].head_dim * self.block_size * esize
+        if num_blocks is None:
+            free, _ = torch.cuda.mem_get_info(self.device)
+            budget = int(free * kv_fraction)
+            total = sum(page_bytes) or 1
+            num_blocks = max(budget // total, 1)
+            # no group needs more pages than every request at full length
+            num_blocks = min(num_blocks, self.max_num_seqs * ((self.max_model_len + self.block_size - 1) // self.block_size))
+        self.num_blocks = int(num_blocks)
+        groups = [CacheGroup(self.block_size, self.num_blocks, w) for w in keys] or [CacheGroup(self.block_size, 1, None)]
+        self.cache = CacheManager(groups, self.max_num_seqs)
+        self.layer_caches: List[Optional[LayerCache]] = [None] * len(runs)
+        for pos, g in run_group.items():
+            n = needs[pos]
+            shape = (self.num_blocks, n.kv_heads, self.block_size, n.head_dim)
+            self.layer_caches[pos] = LayerCache(torch.zeros(shape, dtype=self.dtype, device=self.device),
+                                                torch.zeros(shape, dtype=self.dtype, device=self.device),
+                                                g, self.block_size)
+        for pos, run in enumerate(runs):
+            if run.cache_from is not None and needs[pos] is not None and self.layer_caches[run.cache_from] is None:
+                raise StepError(f"layer run {pos} reads the cache of run {run.cache_from}, which has none")
+        # fixed-size per-request state
+        self.state = StateSlots(self.max_num_seqs, self.device)
+        self.layer_states: List[Optional[Dict[str, torch.Tensor]]] = []
+        for pos, need in enumerate(self.model.state_needs()):
+            if not need:
+                self.layer_states.append(None)
+                continue
+            self.layer_states.append({name: self.state.add(f"run{pos}.{name}", shape, dt)
+                                      for name, (shape, dt) in need.items()})
+
+    def kv_cache_tokens(self) -> int:
+        return self.num_blocks * self.block_size
+
+    def available_kv_tokens(self) -> int:
+        return min(self.cache.free_pages(g) for g in range(len(self.cache.groups))) * self.block_size
+
+    # ---- requests ----------------------------------------------------------------------------------
+    def open_request(self) -> int:
+        slot = self.cache.open_request()
+        self.state.clear_slot(slot)
+        return slot
+
+    def close_request(self, slot: int) -> None:
+        self.cache.close_request(slot)
+
+    def prepare_slot(self, slot: int) -> None:
+        """Clear a slot's per-request state (for callers that open slots through the scheduler)."""
+        self.state.clear_slot(slot)
+
+    # ---- the step --------------------------------------------------------------------------------------
+    def step(self, entries: Sequence[StepInput], *, pad_entries: int = 0, pad_tokens: int = 0,
+             strides: Optional[Sequence[int]] = None, allow_graph: bool = False) -> torch.Tensor:
+        """Run one batch; returns float32 logits ``[wanted, vocab]`` on the device (a view of a
+        reused buffer: copy what must outlive the next step)."""
+        ctx = self.prepare(entries, pad_entries=pad_entries, pad_tokens=pad_tokens, strides=strides)
+        logits = self.model.forward(ctx, self.layer_caches, self.layer_states)
+        self.finish(entries)
+        return logits
+
+    def prepare(self, entries: Sequence[StepInput], *, pad_entries: int = 0, pad_tokens: int = 0,
+                strides: Optional[Sequence[int]] = None) -> StepContext:
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        B = len(entries)
+        counts = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=B)
+        if (counts <= 0).any():
+            raise StepError("every entry of a step must bring at least one token")
+        slots = np.fromiter((e.slot for e in entries), dtype=np.int32, count=B)
+        if len(set(slots.tolist())) != B:
+            raise StepError("a request may appear only once in a step")
+        T = int(counts.sum())
+        tokens = np.empty(T, dtype=np.int32)
+        want_e: List[int] = []
+        want_o: List[int] = []
+        t = 0
+        V = self.plan.vocab_size
+        starts = np.empty(B, dtype=np.int32)
+        for b, e in enumerate(entries):
+            n = int(counts[b])
+            tokens[t:t + n] = np.asarray(e.tokens, dtype=np.int64)
+            t += n
+            for w in e.want:
+                if not (0 <= int(w) < n):
+                    raise StepError(f"entry {b} wants logits at {w}, but brings {n} tokens")
+                want_e.append(b)
+                want_o.append(int(w))
+            if not self.cache.is_live(int(slots[b])):
+                raise StepError(f"entry {b}: slot {int(slots[b])} is not an open request")
+            start = self.cache.length(int(slots[b]))
+            starts[b] = start
+            if start + n > self.max_model_len:
+                raise StepError(f"entry {b}: {start + n} tokens exceed the longest sequence {self.max_model_len}")
+            if not self.cache.extend(int(slots[b]), start + n):
+                raise StepError(f"entry {b}: the page pool has no room for {n} more tokens "
+                                f"(free pages {[self.cache.free_pages(g) for g in range(len(self.cache.groups))]})")
+        if tokens.min() < 0 or tokens.max() >= V:
+            raise StepError(f"token ids must lie in [0, {V}); got {int(tokens.min())}..{int(tokens.max())}")
+        R = len(want_e)
+        G = len(self.cache.groups)
+        Bp, Tp = max(B, pad_entries), max(T, pad_tokens)
+        longest = int((starts + counts).max())
+        max_stride = max((longest + self.block_size - 1) // self.block_size + 8, max(strides) if strides else 0)
+        need = 3 * (Tp + 4) + 3 * (Bp + 5) + R + 8 + G * (Bp * max_stride + 4) + 64
+        self._meta.reserve(need)
+        host, dev, which = self._meta.next()
+        offs = (ctypes.c_longlong * (7 + 2 * G))()
+        we = np.asarray(want_e, dtype=np.int32)
+        wo = np.asarray(want_o, dtype=np.int32)
+        st = np.asarray(strides, dtype=np.int32) if strides is not None else None
+        used = self._lib.xb_assemble(
+            self.cache.handle, B, slots.ctypes.data, counts.ctypes.data, tokens.ctypes.data, R,
+            we.ctypes.data if R else None, wo.ctypes.data if R else None, int(pad_tokens), int(pad_entries),
+            st.ctypes.data if st is not None else None, host.data_ptr(), host.numel(), offs)
+        if used < 0:
+            raise StepError({-1: "step metadata does not fit its buffer", -2: "a slot is not live",
+                             -3: "pages are missing for an entry", -4: "a wanted position is out of range"}.get(used, f"assemble failed ({used})"))
+        dev[:used].copy_(host[:used], non_blocking=True)
+        self._meta.sent(which)
+
+        def view(k, n):
+            return dev[offs[k]: offs[k] + n]
+
+        q_start_h = host[offs[3]: offs[3] + Bp + 1].numpy().copy()
+        ctx = StepContext(
+            dtype=self.dtype, device=self.device, num_tokens=Tp, num_entries=Bp,
+            token_ids=view(0, Tp), positions=view(1, Tp), req_of_token=view(2, Tp),
+            q_start=view(3, Bp + 1), start_pos=view(4, Bp), slots=view(5, Bp),
+            logit_rows=view(6, max(R, 1)), num_logit_rows=R,
+            tables=[dev[offs[7 + g]: offs[7 + g] + Bp * offs[7 + G + g]] for g in range(G)],
+            strides=[int(offs[7 + G + g]) for g in range(G)],
+            err=self.err, workspace=self.workspace,
+            h_q_start=q_start_h, h_start_pos=starts.copy(), h_slots=slots.copy(),
+            real_tokens=T, real_entries=B, max_context=longest, all_single=bool((counts == 1).all()),
+        )
+        return ctx
+
+    def finish(self, entries: Sequence[StepInput]) -> None:
+        for e in entries:
+            self.cache.advance(e.slot, self.cache.length(e.slot) + len(e.tokens))
+        self.steps_run += 1
+
+    # ---- errors the kernels reported ---------------------------------------------------------------------
+    def queue_error_check(self) -> None:
+        """Queue the copy of the device error word; ``raise_if_error`` reads it after the caller's
+        next synchronisation (so a step costs one synchronisation, not two)."""
+        self._err_host.copy_(self.err, non_blocking=True)
+
+    def raise_if_error(self) -> None:
+        word = int(self._err_host[0])
+        if word:
+            self._err_host[0] = 0
+            self.err.zero_()
+            raise StepError("a kernel reported: " + kernels.describe_error(word))
+
+    def check_errors(self) -> None:
+        """Synchronises and raises if any kernel has set the device error word since the last check."""
+        self._err_host.copy_(self.err, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        word = int(self._err_host[0])
+        if word:
+            self.err.zero_()
+            raise StepError("a kernel reported: " + kernels.describe_error(word))

@@ -1,0 +1,209 @@
+"""Python faces of the CUDA kernels.  Each wrapper checks devices, dtypes, shapes and contiguity,
+launches on the current torch stream and raises on a launch error.  Nothing here computes on the
+CPU or through a library: a missing extension or a CPU tensor is an error.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import numpy as np
+import torch
+
+from .native import kernels_lib
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, not {dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise KernelError(f"{name}: expected a tensor, got {type(t).__name__}")
+    if not t.is_cuda:
+        raise KernelError(f"{name}: tensor is on {t.device}; the kernels run on a CUDA device only")
+    if not t.is_contiguous():
+        raise KernelError(f"{name}: tensor must be contiguous (shape {tuple(t.shape)}, strides {t.stride()})")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name}: expected {dtype}, got {t.dtype}")
+    if shape is not None:
+        if len(shape) != t.dim() or any(s is not None and s != d for s, d in zip(shape, t.shape)):
+            raise KernelError(f"{name}: expected shape {tuple(shape)}, got {tuple(t.shape)}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ok(status: int, what: str) -> None:
+    if status != 0:
+        raise KernelError(f"{what}: CUDA error {status} at launch")
+
+
+# device-side error word -------------------------------------------------------------------------
+ERR_BAD_TOKEN, ERR_BAD_PAGE, ERR_WAIT, ERR_BAD_ROW = 1, 2, 4, 8
+
+
+def describe_error(word: int) -> str:
+    parts = []
+    if word & ERR_BAD_TOKEN:
+        parts.append("a token id outside the vocabulary")
+    if word & ERR_BAD_PAGE:
+        parts.append("a block-table entry outside the page pool")
+    if word & ERR_WAIT:
+        parts.append("a bounded wait inside a kernel gave up")
+    if word & ERR_BAD_ROW:
+        parts.append("a requested row outside the step's tokens")
+    return "; ".join(parts) or "no error"
+
+
+# ---- wrappers --------------------------------------------------------------------------------------
+def embedding(out, table, ids, err):
+    T, H = out.shape
+    _need(out, "out", table.dtype, (T, H))
+    _need(table, "table", None, (None, H))
+    _need(ids, "ids", torch.int32)
+    if ids.numel() < T:
+        raise KernelError(f"ids holds {ids.numel()} entries for {T} tokens")
+    _need(err, "err", torch.int32)
+    _ok(kernels_lib().xb_embedding(dtype_code(table.dtype), out.data_ptr(), table.data_ptr(), ids.data_ptr(),
+                                   T, H, table.shape[0], err.data_ptr(), _stream()), "embedding")
+
+
+def rmsnorm(out, x, weight, eps, err, *, branch=None, sum_out=None, rows=None, weight_offset=0.0):
+    """out = norm(s) * (offset + w) with s = x (+ branch), optionally gathered at ``rows``;
+    ``sum_out`` receives s (it may be x itself when no rows are given)."""
+    dim = x.shape[-1]
+    n = out.shape[0]
+    _need(x, "x", None, (None, dim))
+    _need(out, "out", x.dtype, (n, dim))
+    _need(weight, "weight", torch.float32, (dim,))
+    if branch is not None:
+        _need(branch, "branch", x.dtype, tuple(x.shape))
+    if sum_out is not None:
+        _need(sum_out, "sum_out", x.dtype, (n, dim))
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        if rows.numel() < n:
+            raise KernelError(f"rows holds {rows.numel()} entries for {n} output rows")
+    elif n != x.shape[0]:
+        raise KernelError(f"out has {n} rows, x has {x.shape[0]} and no row list was given")
+    _ok(kernels_lib().xb_rmsnorm(dtype_code(x.dtype), out.data_ptr(), _ptr(sum_out), x.data_ptr(), _ptr(branch),
+                                 _ptr(rows), weight.data_ptr(), n, dim, x.shape[0], float(eps),
+                                 float(weight_offset), err.data_ptr(), _stream()), "rmsnorm")
+
+
+def add(out, x, branch):
+    _need(x, "x")
+    _need(branch, "branch", x.dtype, tuple(x.shape))
+    _need(out, "out", x.dtype, tuple(x.shape))
+    _ok(kernels_lib().xb_add(dtype_code(x.dtype), out.data_ptr(), x.data_ptr(), branch.data_ptr(), x.numel(), _stream()), "add")
+
+
+def gemm_plain(out, a, w):
+    """out[M, N] = a[M, K] . w[N, K]^T with float32 FMA accumulation (no tensor cores)."""
+    M, K = a.shape
+    N = w.shape[0]
+    _need(a, "a", None, (M, K))
+    _need(w, "w", None, (N, K))
+    _need(out, "out", None, (M, N))
+    _ok(kernels_lib().xb_gemm_plain(dtype_code(a.dtype), dtype_code(w.dtype), dtype_code(out.dtype), out.data_ptr(),
+                                    a.data_ptr(), w.data_ptr(), M, N, K, _stream()), "gemm_plain")
+
+
+def rope_table(cos_t, sin_t, inv_freq):
+    max_pos, half = cos_t.shape
+    _need(cos_t, "cos", torch.float32, (max_pos, half))
+    _need(sin_t, "sin", torch.float32, (max_pos, half))
+    _need(inv_freq, "inv_freq", torch.float32, (half,))
+    _ok(kernels_lib().xb_rope_table(cos_t.data_ptr(), sin_t.data_ptr(), inv_freq.data_ptr(), max_pos, half, _stream()), "rope_table")
+
+
+def qk_norm_rope_write(q_out, k_cache, v_cache, qkv, q_w, k_w, cos_t, sin_t, positions, req_of_token,
+                       block_table, table_stride, nh, nkv, d, rot, interleaved, eps, write_kv, err):
+    T = qkv.shape[0]
+    _need(qkv, "qkv", None, (T, (nh + 2 * nkv) * d))
+    _need(q_out, "q_out", qkv.dtype, (T, nh, d))
+    if write_kv:
+        _need(k_cache, "k_cache", qkv.dtype, (None, nkv, None, d))
+        _need(v_cache, "v_cache", qkv.dtype, tuple(k_cache.shape))
+    num_pages = k_cache.shape[0] if k_cache is not None else 0
+    page_size = k_cache.shape[2] if k_cache is not None else 1
+    for name, w_ in (("q_norm", q_w), ("k_norm", k_w)):
+        if w_ is not None:
+            _need(w_, name, torch.float32, (d,))
+    max_pos = 0
+    if cos_t is not None:
+        _need(cos_t, "cos", torch.float32, (None, rot // 2))
+        _need(sin_t, "sin", torch.float32, tuple(cos_t.shape))
+        max_pos = cos_t.shape[0]
+    _ok(kernels_lib().xb_qk_norm_rope_write(
+        dtype_code(qkv.dtype), q_out.data_ptr(), _ptr(k_cache), _ptr(v_cache), qkv.data_ptr(), _ptr(q_w), _ptr(k_w),
+        _ptr(cos_t), _ptr(sin_t), positions.data_ptr(), req_of_token.data_ptr(), block_table.data_ptr(),
+        int(table_stride), T, nh, nkv, d, rot, int(bool(interleaved)), page_size, num_pages, max_pos, float(eps),
+        int(bool(write_kv)), err.data_ptr(), _stream()), "qk_norm_rope_write")
+
+
+def attention_plain(out, q, k_cache, v_cache, positions, req_of_token, block_table, table_stride, window, scale, err):
+    T, nh, d = q.shape
+    _need(q, "q", None, (T, nh, d))
+    _need(out, "out", q.dtype, (T, nh, d))
+    _need(k_cache, "k_cache", q.dtype, (None, None, None, d))
+    _need(v_cache, "v_cache", q.dtype, tuple(k_cache.shape))
+    num_pages, nkv, page_size, _ = k_cache.shape
+    if nh % nkv:
+        raise KernelError(f"{nh} query heads do not divide into {nkv} key/value heads")
+    if d > 512:
+        raise KernelError(f"head size {d} is larger than the plain attention kernel's limit of 512")
+    _ok(kernels_lib().xb_attention_plain(
+        dtype_code(q.dtype), out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr(),
+        req_of_token.data_ptr(), block_table.data_ptr(), int(table_stride), T, nh, nkv, d, page_size, num_pages,
+        int(window or 0), float(scale), err.data_ptr(), _stream()), "attention_plain")
+
+
+def swiglu(out, gate_up):
+    T, two_i = gate_up.shape
+    _need(gate_up, "gate_up", None, (T, two_i))
+    _need(out, "out", gate_up.dtype, (T, two_i // 2))
+    _ok(kernels_lib().xb_swiglu(dtype_code(gate_up.dtype), out.data_ptr(), gate_up.data_ptr(), T, two_i // 2, _stream()), "swiglu")
+
+
+def widen_bf16(out, x):
+    _need(x, "x", torch.bfloat16)
+    _need(out, "out", torch.float32, tuple(x.shape))
+    _ok(kernels_lib().xb_widen_bf16(out.data_ptr(), x.data_ptr(), x.numel(), _stream()), "widen_bf16")
+
+
+SAMPLE_PARAMS = np.dtype([
+    ("temperature", np.float32), ("top_k", np.int32), ("top_p", np.float32),
+    ("seed_lo", np.uint32), ("seed_hi", np.uint32), ("draw", np.uint32),
+    ("frequency_penalty", np.float32), ("presence_penalty", np.float32),
+    ("history_offset", np.int32), ("history_len", np.int32),
+])
+
+
+def sample(out_tokens, logits, params_dev, history_dev, apply_penalties: bool):
+    R, V = logits.shape
+    _need(logits, "logits", torch.float32, (R, V))
+    _need(out_tokens, "out_tokens", torch.int32)
+    _need(params_dev, "params", torch.uint8)
+    lib = kernels_lib()
+    if lib.xb_sample_params_size() != SAMPLE_PARAMS.itemsize:
+        raise KernelError("the sampler's parameter record differs between Python and CUDA")
+    if params_dev.numel() < R * SAMPLE_PARAMS.itemsize or out_tokens.numel() < R:
+        raise KernelError("sampler buffers are smaller than the number of rows")
+    _ok(lib.xb_sample(out_tokens.data_ptr(), logits.data_ptr(), params_dev.data_ptr(), _ptr(history_dev), R, V,
+                      int(bool(apply_penalties)), _stream()), "sample")

@@ -1,0 +1,205 @@
+"""Interfaces of the parts a decoder block is put together from, their registries, and the
+step context they are handed.  A part knows its own sizes and constants (its spec) and the step's
+metadata; it never sees a model configuration or the model it sits in.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple, Type
+
+import numpy as np
+import torch
+
+from ..config.plan import PartSpec
+from ..weights.loader import WeightSpec, WeightStore
+
+
+class Workspace:
+    """Named scratch buffers that live across layers and steps.  A buffer is grown when a larger
+    shape is asked for; with ``frozen`` set (while a CUDA graph holds pointers into it) growing
+    is an error."""
+
+    def __init__(self, device):
+        self.device = device
+        self._bufs: Dict[str, torch.Tensor] = {}
+        self.frozen = False
+
+    def get(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        buf = self._bufs.get(name)
+        if buf is None or buf.dtype != dtype or buf.numel() < n:
+            if self.frozen and buf is not None:
+                raise RuntimeError(f"workspace buffer '{name}' would have to grow while a CUDA graph uses it")
+            cap = n if buf is None or buf.dtype != dtype else max(n, buf.numel())
+            buf = torch.empty(max(cap, 1), dtype=dtype, device=self.device)
+            self._bufs[name] = buf
+        return buf[:n].view(*shape)
+
+    def bytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self._bufs.values())
+
+
+@dataclass
+class StepContext:
+    """Everything a part may know about the running step."""
+
+    dtype: torch.dtype
+    device: torch.device
+    num_tokens: int            # rows in the activations (including padding tokens)
+    num_entries: int           # requests in the batch (including padding entries)
+    # device int32 arrays (views into the step's packed metadata)
+    token_ids: torch.Tensor    # [T]
+    positions: torch.Tensor    # [T]   absolute position of each token in its request
+    req_of_token: torch.Tensor # [T]   index of the token's entry in this batch, -1 for padding
+    q_start: torch.Tensor      # [B+1] first token of each entry
+    start_pos: torch.Tensor    # [B]   tokens already cached for each entry
+    slots: torch.Tensor        # [B]   request slot of each entry (row of per-request state)
+    logit_rows: torch.Tensor   # [R]   rows whose logits are wanted
+    num_logit_rows: int
+    tables: List[torch.Tensor] # per cache group: [B, stride] page ids, -1 where none
+    strides: List[int]
+    err: torch.Tensor          # int32[1] device error word
+    workspace: Workspace
+    # host copies for parts that loop over entries on the host
+    h_q_start: np.ndarray = None
+    h_start_pos: np.ndarray = None
+    h_slots: np.ndarray = None
+    real_tokens: int = 0       # tokens that are not padding
+    real_entries: int = 0
+    # longest context (start + count) of any entry, and whether every entry brings one token
+    max_context: int = 0
+    all_single: bool = False
+
+
+@dataclass(frozen=True)
+class PagedCacheNeed:
+    """What a mixer wants from the paged cache: per token, ``kv_heads x head_dim`` keys and the
+    same of values; ``window`` None keeps all tokens."""
+
+    kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass
+class LayerCache:
+    """The pages of one layer run: K and V ``[num_pages, kv_heads, page_size, head_dim]`` and
+    the index of the cache group whose block tables address them."""
+
+    k: torch.Tensor
+    v: torch.Tensor
+    group: int
+    page_size: int
+
+
+class Part:
+    """Base of all parts.  Subclasses set ``kind`` and implement the class method
+    ``weight_specs(spec, prefix)`` and the methods ``load`` and ``forward``."""
+
+    kind: str = ""
+
+    def __init__(self, spec: PartSpec, prefix: str, dtype: torch.dtype, device):
+        self.spec = spec
+        self.prefix = prefix
+        self.dtype = dtype
+        self.device = device
+
+    @classmethod
+    def weight_specs(cls, spec: PartSpec, prefix: str) -> List[WeightSpec]:
+        return []
+
+    def load(self, store: WeightStore) -> None:
+        pass
+
+
+class Mixer(Part):
+    """Mixes information across the tokens of a request.
+
+    ``cache_need()``: pages it wants (or None).  ``state_need()``: fixed-size per-request state,
+    a dict name -> (shape, dtype), one row per request slot (or None).
+    ``forward(x, ctx, cache, state)`` takes the normed activations ``[T, hidden]`` and returns
+    ``[T, hidden]``; it must write this step's keys/values (or state) before reading them, and it
+    must give the same result however the request's tokens were cut into steps.
+    ``writes_cache`` False means this run reads pages another run wrote.
+    """
+
+    def cache_need(self) -> Optional[PagedCacheNeed]:
+        return None
+
+    def state_need(self) -> Optional[Dict[str, Tuple[Tuple[int, ...], torch.dtype]]]:
+        return None
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCache],
+                state: Optional[Dict[str, torch.Tensor]], writes_cache: bool = True) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    """Acts on every token alone: ``forward(x, ctx)`` takes and returns ``[T, hidden]``."""
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Norm(Part):
+    """``forward(out, x, ctx, branch=None, sum_out=None, rows=None)``: out = norm(x (+ branch)),
+    optionally on gathered rows; ``sum_out`` receives x + branch."""
+
+    def forward(self, out, x, ctx, branch=None, sum_out=None, rows=None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Position information for a mixer's queries and keys.  Either it offers rotary tables that
+    the attention kernel applies while it writes the cache (``rotary()`` returns them), or it
+    rewrites q and k itself in ``apply``."""
+
+    def rotary(self):
+        return None
+
+    def apply(self, q: torch.Tensor, k: torch.Tensor, ctx: StepContext) -> None:
+        pass
+
+
+_REGISTRIES: Dict[str, Dict[str, Type[Part]]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position": {}}
+
+
+def _register(family: str, kind: str, cls: Type[Part], replace: bool) -> None:
+    reg = _REGISTRIES[family]
+    if kind in reg and not replace:
+        raise ValueError(f"{family} kind '{kind}' is already registered")
+    reg[kind] = cls
+
+
+def register_mixer(kind: str, cls: Type[Mixer], *, replace: bool = False) -> None:
+    _register("mixer", kind, cls, replace)
+
+
+def register_feed_forward(kind: str, cls: Type[FeedForward], *, replace: bool = False) -> None:
+    _register("feed_forward", kind, cls, replace)
+
+
+def register_norm(kind: str, cls: Type[Norm], *, replace: bool = False) -> None:
+    _register("norm", kind, cls, replace)
+
+
+def register_position_encoding(kind: str, cls: Type[PositionEncoding], *, replace: bool = False) -> None:
+    _register("position", kind, cls, replace)
+
+
+def unregister(family: str, kind: str) -> None:
+    _REGISTRIES[family].pop(kind, None)
+
+
+def part_class(family: str, kind: str) -> Type[Part]:
+    try:
+        return _REGISTRIES[family][kind]
+    except KeyError:
+        known = ", ".join(sorted(_REGISTRIES[family])) or "none"
+        raise ValueError(f"no {family} of kind '{kind}' is registered (known: {known})") from None
+
+
+def build_part(family: str, spec: PartSpec, prefix: str, dtype: torch.dtype, device) -> Part:
+    return part_class(family, spec.kind)(spec, prefix, dtype, device)

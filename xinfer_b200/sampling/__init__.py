@@ -1,0 +1,11 @@
+"""Sampling: per-request options and the device sampler."""
+from .params import SamplingParams
+
+__all__ = ["SamplingParams", "Sampler"]
+
+
+def __getattr__(name):
+    if name == "Sampler":
+        from .sampler import Sampler
+        return Sampler
+    raise AttributeError(name)

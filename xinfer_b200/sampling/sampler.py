@@ -1,0 +1,73 @@
+"""Device-side sampling for a batch of logits rows: one launch for penalties, one for the draw
+(greedy, temperature, top-k, top-p, top-k then top-p; src/utils/logits_processor.rs:258-344)."""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import kernels
+from .params import SamplingParams
+
+# tokens that the penalties count: the most recent ones of the request, as many as the reference
+# tracks (src/core/runner.rs:1887-1912)
+PENALTY_HISTORY = 128
+
+
+class Sampler:
+    def __init__(self, device, max_rows: int):
+        self.device = device
+        self.max_rows = max_rows
+        rec = kernels.SAMPLE_PARAMS.itemsize
+        self._params_host = torch.zeros(max_rows * rec, dtype=torch.uint8, pin_memory=True)
+        self._params_dev = torch.zeros(max_rows * rec, dtype=torch.uint8, device=device)
+        self._hist_host = torch.zeros(max_rows * PENALTY_HISTORY, dtype=torch.int32, pin_memory=True)
+        self._hist_dev = torch.zeros(max_rows * PENALTY_HISTORY, dtype=torch.int32, device=device)
+        self._out_dev = torch.zeros(max_rows, dtype=torch.int32, device=device)
+        self._out_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=True)
+        self._params_np = self._params_host.numpy().view(kernels.SAMPLE_PARAMS)
+        self._hist_np = self._hist_host.numpy()
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
+               draws: Sequence[int], histories: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+        """One token per logits row, as an int32 device tensor (a view of a reused buffer).
+        ``seeds[r]`` / ``draws[r]``: the request's seed and how many tokens it has drawn before.
+        ``histories[r]``: the request's recent tokens, used when it has penalties."""
+        R = logits.shape[0]
+        if R > self.max_rows:
+            raise ValueError(f"{R} rows exceed the sampler's capacity {self.max_rows}")
+        rec = self._params_np
+        any_pen = False
+        off = 0
+        for r, p in enumerate(params):
+            rec[r]["temperature"] = 0.0 if p.greedy else float(p.temperature)
+            rec[r]["top_k"] = int(p.top_k) if p.top_k and p.top_k > 0 else 0
+            rec[r]["top_p"] = float(p.top_p) if p.top_p is not None else 1.0
+            s = int(seeds[r]) & 0xFFFFFFFFFFFFFFFF
+            rec[r]["seed_lo"], rec[r]["seed_hi"] = s & 0xFFFFFFFF, s >> 32
+            rec[r]["draw"] = int(draws[r]) & 0xFFFFFFFF
+            rec[r]["frequency_penalty"] = float(p.frequency_penalty or 0.0)
+            rec[r]["presence_penalty"] = float(p.presence_penalty or 0.0)
+            rec[r]["history_offset"] = off
+            n = 0
+            if p.has_penalties and histories is not None:
+                h = list(histories[r])[-PENALTY_HISTORY:]
+                n = len(h)
+                self._hist_np[off:off + n] = h
+                any_pen = any_pen or n > 0
+            rec[r]["history_len"] = n
+            off += n
+        nb = R * kernels.SAMPLE_PARAMS.itemsize
+        self._params_dev[:nb].copy_(self._params_host[:nb], non_blocking=True)
+        if any_pen:
+            self._hist_dev[:off].copy_(self._hist_host[:off], non_blocking=True)
+        kernels.sample(self._out_dev, logits, self._params_dev, self._hist_dev, any_pen)
+        return self._out_dev[:R]
+
+    def to_host(self, tokens_dev: torch.Tensor) -> np.ndarray:
+        """Copy sampled ids to the host (synchronises the stream)."""
+        n = tokens_dev.shape[0]
+        self._out_host[:n].copy_(tokens_dev, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self._out_host[:n].numpy().copy()

@@ -1,0 +1,78 @@
+"""Random-weights mode: from a configuration and a seed to a model folder (config.json and
+model.safetensors), or to tensors drawn straight on a device.
+
+The reference always loads files; it has no such mode.  Each tensor is drawn from a generator
+seeded by (seed, tensor name), so a tensor's values do not depend on the order in which tensors
+are produced or on which other tensors exist.  Linear and embedding weights ~ N(0, std), norm
+weights ~ 1 + N(0, norm_std).
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import os
+from typing import Any, Callable, Dict, List, Mapping, Optional, Sequence
+
+import torch
+
+from .loader import WeightSpec
+from .safetensors_io import write_safetensors
+
+
+def _seed_of(seed: int, name: str) -> int:
+    h = hashlib.sha256(f"{int(seed)}:{name}".encode("utf-8")).digest()
+    return int.from_bytes(h[:8], "little") & ((1 << 63) - 1)
+
+
+def draw(spec: WeightSpec, seed: int, std: float, norm_std: float, dtype: torch.dtype,
+         device="cpu") -> torch.Tensor:
+    """One tensor.  The stream differs between CPU and CUDA generators: a folder written on the
+    CPU and tensors drawn on the GPU with the same seed are different models."""
+    g = torch.Generator(device=device)
+    g.manual_seed(_seed_of(seed, spec.name))
+    shape = tuple(spec.shape)
+    if spec.init in ("linear", "embedding"):
+        t = torch.randn(shape, generator=g, dtype=torch.float32, device=device).mul_(std)
+    elif spec.init == "norm":
+        t = torch.randn(shape, generator=g, dtype=torch.float32, device=device).mul_(norm_std).add_(1.0)
+    elif spec.init == "zeros":
+        t = torch.zeros(shape, dtype=torch.float32, device=device)
+    elif spec.init == "ones":
+        t = torch.ones(shape, dtype=torch.float32, device=device)
+    else:
+        raise ValueError(f"weight '{spec.name}' has unknown init kind '{spec.init}'")
+    return t.to(dtype)
+
+
+def write_random_model(model_dir: str, config_dict: Mapping[str, Any], seed: int,
+                       dtype: torch.dtype = torch.bfloat16, std: Optional[float] = None,
+                       norm_std: Optional[float] = None,
+                       override: Optional[Callable[[str, torch.Tensor], torch.Tensor]] = None) -> str:
+    """Write ``config.json`` and ``model.safetensors`` for the architecture that
+    ``config_dict['architectures'][0]`` names.  ``override(name, tensor)`` may return a changed
+    tensor (tests use it to plant weights that make one key or one page stand out)."""
+    from ..config import config_from_dict
+    from ..models.decoder import model_weight_specs
+
+    entry, cfg = config_from_dict(config_dict)
+    plan = entry.plan_of(cfg)
+    specs = model_weight_specs(plan)
+    std = plan.init_std if std is None else std
+    norm_std = plan.norm_init_std if norm_std is None else norm_std
+    os.makedirs(model_dir, exist_ok=True)
+    by_name = {s.name: s for s in specs}
+
+    def produce(name: str) -> torch.Tensor:
+        t = draw(by_name[name], seed, std, norm_std, dtype)
+        if override is not None:
+            t2 = override(name, t)
+            if t2 is not None:
+                t = t2.to(dtype)
+        return t
+
+    write_safetensors(os.path.join(model_dir, "model.safetensors"),
+                      [(s.name, tuple(s.shape), dtype) for s in specs], produce,
+                      metadata={"format": "pt", "seed": str(int(seed))})
+    with open(os.path.join(model_dir, "config.json"), "w", encoding="utf-8") as f:
+        json.dump(dict(config_dict), f, indent=1)
+    return model_dir
