@@ -1,0 +1,137 @@
+"""Configuration and registry (no GPU)."""
+import json
+import os
+
+import pytest
+
+from helpers import TINY
+from xinfer_b200.config import (ConfigError, EngineConfig, Qwen3Config, config_from_dict,
+                                known_architectures, load_config, register_architecture,
+                                unregister_architecture)
+from xinfer_b200.config.plan import (AttentionSpec, BlockSpec, FeedForwardSpec, LayerRun, ModelPlan,
+                                     NormSpec)
+
+
+def test_reads_every_key_from_config_json():
+    for name, (raw, _) in TINY.items():
+        entry, cfg = config_from_dict(raw)
+        assert entry.name == "Qwen3ForCausalLM"
+        for key in ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers",
+                    "num_attention_heads", "num_key_value_heads", "head_dim", "rms_norm_eps",
+                    "rope_theta", "max_position_embeddings", "tie_word_embeddings", "sliding_window"):
+            assert getattr(cfg, key) == raw[key], (name, key)
+
+
+def test_defaults():
+    raw = dict(TINY["A"][0])
+    del raw["head_dim"], raw["rope_theta"], raw["tie_word_embeddings"], raw["sliding_window"]
+    cfg = Qwen3Config.from_dict(raw)
+    assert cfg.head_dim == raw["hidden_size"] // raw["num_attention_heads"]
+    assert cfg.rope_theta == 10000.0
+    assert cfg.tie_word_embeddings is False
+    assert cfg.sliding_window is None
+    assert cfg.eos_token_id == (255,)
+    assert Qwen3Config.from_dict(TINY["B"][0]).eos_token_id == (3, 5)
+
+
+@pytest.mark.parametrize("change, fragment", [
+    (dict(vocab_size=None), "vocab_size"),
+    (dict(num_attention_heads=5), "multiple of num_key_value_heads"),
+    (dict(hidden_act="gelu"), "hidden_act"),
+    (dict(rms_norm_eps=0), "rms_norm_eps"),
+    (dict(attention_bias=True), "attention_bias"),
+    (dict(rope_scaling={"rope_type": "yarn", "factor": 4.0}), "rope_scaling"),
+    (dict(sliding_window=-3), "sliding_window"),
+    (dict(hidden_size="64"), "hidden_size"),
+    (dict(head_dim=15), "head_dim"),
+    (dict(eos_token_id="x"), "eos_token_id"),
+])
+def test_errors_name_the_key(change, fragment):
+    raw = dict(TINY["A"][0])
+    raw.update(change)
+    with pytest.raises(ConfigError) as e:
+        Qwen3Config.from_dict(raw)
+    assert fragment in str(e.value)
+
+
+def test_missing_keys_are_listed_together():
+    raw = dict(TINY["A"][0])
+    del raw["vocab_size"], raw["rms_norm_eps"]
+    with pytest.raises(ConfigError) as e:
+        Qwen3Config.from_dict(raw)
+    assert "vocab_size" in str(e.value) and "rms_norm_eps" in str(e.value)
+
+
+def test_registry_unknown_and_malformed():
+    raw = dict(TINY["A"][0], architectures=["NoSuchModel"])
+    with pytest.raises(ConfigError) as e:
+        config_from_dict(raw)
+    assert "NoSuchModel" in str(e.value) and "Qwen3ForCausalLM" in str(e.value)
+    with pytest.raises(ConfigError):
+        config_from_dict(dict(TINY["A"][0], architectures=["a", "b"]))
+    with pytest.raises(ConfigError):
+        config_from_dict({k: v for k, v in TINY["A"][0].items() if k != "architectures"})
+
+
+def test_register_another_architecture():
+    def plan_of(cfg):
+        return Qwen3Config.from_dict(cfg).plan()
+    register_architecture("ToyForTest", lambda raw: dict(raw), plan_of)
+    try:
+        assert "ToyForTest" in known_architectures()
+        with pytest.raises(ValueError):
+            register_architecture("ToyForTest", lambda raw: raw, plan_of)
+        entry, cfg = config_from_dict(dict(TINY["A"][0], architectures=["ToyForTest"]))
+        assert entry.plan_of(cfg).vocab_size == 256
+    finally:
+        unregister_architecture("ToyForTest")
+    assert "ToyForTest" not in known_architectures()
+
+
+def test_plan_carries_every_constant():
+    for name, (raw, _) in TINY.items():
+        cfg = Qwen3Config.from_dict(raw)
+        plan = cfg.plan()
+        assert len(plan.blocks) == raw["num_hidden_layers"] == len(plan.runs)
+        assert [r.block for r in plan.runs] == list(range(raw["num_hidden_layers"]))
+        b = plan.blocks[-1]
+        assert b.mixer.num_heads == raw["num_attention_heads"] and b.mixer.num_kv_heads == raw["num_key_value_heads"]
+        assert b.mixer.head_dim == raw["head_dim"] and b.mixer.window == raw["sliding_window"]
+        assert b.mixer.scale == pytest.approx(raw["head_dim"] ** -0.5)
+        assert b.mixer.rope.theta == raw["rope_theta"] and b.mixer.rope.max_positions == raw["max_position_embeddings"]
+        assert b.mixer.qk_norm and b.mixer.qk_norm_eps == raw["rms_norm_eps"]
+        assert b.norm_in.eps == raw["rms_norm_eps"] == plan.final_norm.eps
+        assert b.feed_forward.intermediate == raw["intermediate_size"]
+        assert (plan.head_name is None) == bool(raw["tie_word_embeddings"])
+
+
+def test_plan_validation_of_the_run_list():
+    plan = Qwen3Config.from_dict(TINY["A"][0]).plan()
+    import dataclasses
+    ok = dataclasses.replace(plan, runs=(LayerRun(0), LayerRun(1), LayerRun(1), LayerRun(0, cache_from=0)))
+    ok.validate()
+    for bad in ((LayerRun(0), LayerRun(5)), (LayerRun(0, cache_from=0),), (LayerRun(0), LayerRun(1, cache_from=1)),
+                (LayerRun(0), LayerRun(1, cache_from=0), LayerRun(0, cache_from=1))):
+        with pytest.raises(ValueError):
+            dataclasses.replace(plan, runs=bad).validate()
+
+
+def test_load_config_from_folder(tmp_path):
+    with pytest.raises(ConfigError):
+        load_config(str(tmp_path))
+    (tmp_path / "config.json").write_text("{not json")
+    with pytest.raises(ConfigError):
+        load_config(str(tmp_path))
+    (tmp_path / "config.json").write_text(json.dumps(TINY["B"][0]))
+    entry, cfg = load_config(str(tmp_path))
+    assert cfg.num_key_value_heads == 1 and cfg.to_dict()["model_type"] == "qwen3"
+
+
+def test_engine_config_validation():
+    EngineConfig(weight_path="x").validate()
+    assert EngineConfig(model_id="m").model_dir() == "m"
+    with pytest.raises(ValueError):
+        EngineConfig().model_dir()
+    for bad in (dict(block_size=0), dict(max_num_seqs=-1), dict(kv_fraction=0.0), dict(num_blocks=0)):
+        with pytest.raises(ValueError):
+            EngineConfig(weight_path="x", **bad).validate()

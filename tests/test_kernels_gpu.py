@@ -1,0 +1,288 @@
+"""Each CUDA kernel alone against a plain PyTorch float32 restatement of the same operation, at
+sizes other than the engine's tiny models (odd widths, head sizes in steps of 16, groups of
+2/4/6/8, vocabularies that are no power of two)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def err_word():
+    return torch.zeros(1, dtype=torch.int32, device=dev())
+
+
+def tol(dtype, scale=1.0):
+    return (2e-5 if dtype == torch.float32 else 1.6e-2) * scale
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(dev())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H,V", [(1, 24, 5), (37, 100, 331), (64, 4096, 1000)])
+def test_embedding(dtype, T, H, V):
+    from xinfer_b200 import kernels
+    table = rnd(V, H, dtype=dtype)
+    ids = torch.randint(0, V, (T,), dtype=torch.int32, device=dev())
+    out = torch.empty(T, H, dtype=dtype, device=dev())
+    e = err_word()
+    kernels.embedding(out, table, ids, e)
+    assert torch.equal(out, table[ids.long()]) and int(e) == 0
+    ids[T // 2] = V  # out of range: flagged, never read
+    kernels.embedding(out, table, ids, e)
+    assert int(e) == kernels.ERR_BAD_TOKEN and torch.count_nonzero(out[T // 2]) == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,dim,eps,offset", [(1, 16, 1e-6, 0.0), (33, 100, 1e-5, 0.0), (7, 5120, 3e-6, 1.0), (5, 8200, 1e-6, 0.0)])
+def test_rmsnorm_plain_fused_and_gathered(dtype, rows, dim, eps, offset):
+    from xinfer_b200 import kernels
+    x, br = rnd(rows, dim, dtype=dtype, seed=1), rnd(rows, dim, dtype=dtype, seed=2)
+    w = rnd(dim, seed=3) * 0.1 + 1
+    e = err_word()
+
+    def ref(s):
+        s = s.float()
+        return s * torch.rsqrt((s * s).mean(-1, keepdim=True) + eps) * (offset + w)
+    out = torch.empty_like(x)
+    kernels.rmsnorm(out, x, w, eps, e, weight_offset=offset)
+    assert (out.float() - ref(x)).abs().max() <= tol(dtype, 4)
+    # fused residual sum: the sum is formed in float32, rounded to the storage type, then normed
+    xs = x.clone()
+    kernels.rmsnorm(out, xs, w, eps, e, branch=br, sum_out=xs, weight_offset=offset)
+    s = (x.float() + br.float()).to(dtype)
+    assert torch.equal(xs, s)
+    assert (out.float() - ref(s)).abs().max() <= tol(dtype, 4)
+    # gathered rows (with the sum, as the final norm uses it)
+    idx = torch.tensor([rows - 1, 0, rows // 2], dtype=torch.int32, device=dev())
+    g = torch.empty(3, dim, dtype=dtype, device=dev())
+    kernels.rmsnorm(g, x, w, eps, e, branch=br, rows=idx, weight_offset=offset)
+    assert (g.float() - ref(s[idx.long()])).abs().max() <= tol(dtype, 4)
+    assert int(e) == 0
+    idx[1] = rows
+    kernels.rmsnorm(g, x, w, eps, e, rows=idx)
+    assert int(e) == kernels.ERR_BAD_ROW
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (33, 100, 70), (130, 257, 129), (3, 1000, 4096)])
+def test_gemm_plain_is_true_float32_and_row_independent(M, N, K):
+    from xinfer_b200 import kernels
+    a, w = rnd(M, K, seed=4), rnd(N, K, seed=5)
+    out = torch.empty(M, N, device=dev())
+    kernels.gemm_plain(out, a, w)
+    ref = (a.double() @ w.double().t())
+    assert (out.double() - ref).abs().max() <= 1e-6 * K ** 0.5 * float(ref.abs().max())
+    # a row's result does not depend on the other rows of the batch
+    one = torch.empty(1, N, device=dev())
+    kernels.gemm_plain(one, a[M // 2: M // 2 + 1].contiguous(), w)
+    assert torch.equal(one[0], out[M // 2])
+    # mixed storage types
+    ab, wb = a.bfloat16(), w.bfloat16()
+    o2 = torch.empty(M, N, device=dev())
+    kernels.gemm_plain(o2, ab, wb)
+    assert (o2.double() - ab.double() @ wb.double().t()).abs().max() <= 1e-6 * K ** 0.5 * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,I", [(1, 8), (13, 48), (37, 11008 // 16 + 3)])
+def test_swiglu(dtype, T, I):
+    from xinfer_b200 import kernels
+    gu = rnd(T, 2 * I, dtype=dtype, scale=3.0)
+    out = torch.empty(T, I, dtype=dtype, device=dev())
+    kernels.swiglu(out, gu)
+    g, u = gu[:, :I].float(), gu[:, I:].float()
+    ref = (g / (1 + torch.exp(-g)) * u).to(dtype)
+    # within one unit in the last place of the storage type (the reference's own probe bound,
+    # tests/probes/compare_attention_misc_probe.py:73-87)
+    ulp = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -22
+    assert ((out.float() - ref.float()).abs() <= ulp * ref.float().abs().clamp_min(1e-3)).all()
+
+
+def make_cache(num_pages, nkv, ps, d, dtype):
+    k = torch.zeros(num_pages, nkv, ps, d, dtype=dtype, device=dev())
+    return k, torch.zeros_like(k)
+
+
+def meta(entries, ps, num_pages, seed=0):
+    """entries: list of (start, count).  Pages are dealt in a shuffled order."""
+    rng = np.random.default_rng(seed)
+    pages = rng.permutation(num_pages).tolist()
+    B = len(entries)
+    stride = max((s + c + ps - 1) // ps for s, c in entries) + 1
+    table = np.full((B, stride), -1, np.int32)
+    pos, req = [], []
+    for b, (s, c) in enumerate(entries):
+        for i in range((s + c + ps - 1) // ps):
+            table[b, i] = pages.pop()
+        pos += list(range(s, s + c))
+        req += [b] * c
+    to = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device=dev())
+    return to(pos), to(req), to(table.reshape(-1)), stride, table
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d,rot,inter,ps", [(4, 2, 16, 16, False, 16), (6, 1, 48, 48, False, 8), (8, 8, 128, 64, True, 4), (10, 5, 80, 80, False, 16)])
+def test_qk_norm_rope_write(dtype, nh, nkv, d, rot, inter, ps):
+    from xinfer_b200 import kernels
+    entries = [(0, 9), (21, 1), (5, 14)]
+    T = sum(c for _, c in entries)
+    num_pages, max_pos, eps, theta = 30, 64, 1e-5, 10000.0
+    pos, req, table, stride, table_np = meta(entries, ps, num_pages)
+    qkv = rnd(T, (nh + 2 * nkv) * d, dtype=dtype, seed=6)
+    qw, kw = rnd(d, seed=7) * 0.2 + 1, rnd(d, seed=8) * 0.2 + 1
+    inv = torch.tensor((1.0 / theta ** (np.arange(0, rot, 2) / rot)).astype(np.float32), device=dev())
+    cos, sin = torch.empty(max_pos, rot // 2, device=dev()), torch.empty(max_pos, rot // 2, device=dev())
+    kernels.rope_table(cos, sin, inv)
+    ang = torch.arange(max_pos, device=dev()).float()[:, None] * inv[None, :]
+    assert (cos - torch.cos(ang)).abs().max() < 2e-6 and (sin - torch.sin(ang)).abs().max() < 2e-6
+    kc, vc = make_cache(num_pages, nkv, ps, d, dtype)
+    q_out = torch.empty(T, nh, d, dtype=dtype, device=dev())
+    e = err_word()
+    kernels.qk_norm_rope_write(q_out, kc, vc, qkv, qw, kw, cos, sin, pos, req, table, stride, nh, nkv, d, rot, inter, eps, True, e)
+    assert int(e) == 0
+
+    def ref_rot(x, w):  # x [T, heads, d] float32
+        x = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w
+        c, s = torch.cos(ang[pos.long()])[:, None, :], torch.sin(ang[pos.long()])[:, None, :]
+        y = x.clone()
+        if inter:
+            a, b = x[..., 0:rot:2], x[..., 1:rot:2]
+            y[..., 0:rot:2], y[..., 1:rot:2] = a * c - b * s, a * s + b * c
+        else:
+            a, b = x[..., : rot // 2], x[..., rot // 2: rot]
+            y[..., : rot // 2], y[..., rot // 2: rot] = a * c - b * s, a * s + b * c
+        return y
+    x = qkv.float()
+    q_ref = ref_rot(x[:, : nh * d].view(T, nh, d), qw)
+    k_ref = ref_rot(x[:, nh * d:(nh + nkv) * d].view(T, nkv, d), kw)
+    v_ref = x[:, (nh + nkv) * d:].view(T, nkv, d)
+    t_ = tol(dtype, 4)
+    assert (q_out.float() - q_ref).abs().max() <= t_
+    posl, reql = pos.tolist(), req.tolist()
+    for t in range(T):
+        page, off = table_np[reql[t], posl[t] // ps], posl[t] % ps
+        assert (kc[page, :, off].float() - k_ref[t]).abs().max() <= t_
+        assert torch.equal(vc[page, :, off].float(), v_ref[t])
+    # nothing else in the cache was touched
+    written = kc.float().abs().sum(-1).ne(0).sum().item()
+    assert written == T * nkv
+    # a table entry outside the pool is flagged and skipped, never written through
+    bad = table.clone()
+    bad[0] = num_pages + 3
+    before = kc.clone()
+    kernels.qk_norm_rope_write(q_out, kc, vc, qkv, qw, kw, cos, sin, pos, req, bad, stride, nh, nkv, d, rot, inter, eps, True, e)
+    assert int(e) == kernels.ERR_BAD_PAGE
+
+
+def attention_ref(q, k_all, v_all, start, window, scale):
+    """q [n, nh, d] at positions start..start+n-1 over keys [ctx, nkv, d] (float64)."""
+    n, nh, d = q.shape
+    nkv = k_all.shape[1]
+    out = torch.zeros(n, nh, d, dtype=torch.float64)
+    for i in range(n):
+        p = start + i
+        lo = 0 if not window else max(0, p - window + 1)
+        for h in range(nh):
+            g = h // (nh // nkv)
+            s = (k_all[lo:p + 1, g] @ q[i, h]) * scale
+            out[i, h] = torch.softmax(s, 0) @ v_all[lo:p + 1, g]
+    return out
+
+
+def attention_case(kernel, dtype, nh, nkv, d, ps, entries, window, plant=None, seed=0, want_out=False):
+    """Fill a cache through shuffled pages, run `kernel`, compare with the dense reference."""
+    from xinfer_b200 import kernels
+    num_pages = sum((s + c + ps - 1) // ps for s, c in entries) + 3
+    pos, req, table, stride, table_np = meta(entries, ps, num_pages, seed)
+    kc, vc = make_cache(num_pages, nkv, ps, d, dtype)
+    kc.fill_(float("nan"))   # anything read beyond a request's keys poisons the result
+    vc.fill_(float("nan"))
+    T = sum(c for _, c in entries)
+    q = rnd(T, nh, d, dtype=dtype, seed=seed + 9)
+    ks, vs = [], []
+    for b, (s, c) in enumerate(entries):
+        k = rnd(s + c, nkv, d, dtype=dtype, seed=seed + 20 + b)
+        v = rnd(s + c, nkv, d, dtype=dtype, seed=seed + 40 + b)
+        if plant is not None:
+            plant(b, s, c, q, k, v)
+        ks.append(k)
+        vs.append(v)
+        for j in range(s + c):
+            kc[table_np[b, j // ps], :, j % ps] = k[j]
+            vc[table_np[b, j // ps], :, j % ps] = v[j]
+    out = torch.full((T, nh, d), float("nan"), dtype=dtype, device=dev())
+    e = err_word()
+    scale = 1.0 / math.sqrt(d)
+    kernel(out, q, kc, vc, pos, req, table, stride, window, scale, e, entries)
+    assert int(e) == 0
+    t0 = 0
+    worst = 0.0
+    for b, (s, c) in enumerate(entries):
+        ref = attention_ref(q[t0:t0 + c].double().cpu(), ks[b].double().cpu(), vs[b].double().cpu(), s, window, scale)
+        diff = (out[t0:t0 + c].double().cpu() - ref).abs().max().item()
+        assert diff == diff, f"entry {b}: NaN in the output (a key beyond the request's range was read)"
+        worst = max(worst, diff)
+        t0 += c
+    return (worst, out) if want_out else worst
+
+
+def plain_kernel(out, q, kc, vc, pos, req, table, stride, window, scale, e, entries):
+    from xinfer_b200 import kernels
+    kernels.attention_plain(out, q, kc, vc, pos, req, table, stride, window, scale, e)
+
+
+CASES = [
+    # nh, nkv, d, page, entries (start, count), window
+    (4, 2, 16, 16, [(0, 1)], None),
+    (4, 2, 16, 16, [(0, 17), (16, 1), (15, 2)], None),
+    (6, 1, 32, 8, [(0, 40), (63, 1), (5, 7), (64, 1)], None),
+    (8, 2, 64, 16, [(33, 31), (0, 3)], 20),
+    (8, 1, 128, 16, [(300, 1), (0, 70)], None),
+    (6, 3, 48, 4, [(10, 25), (36, 1)], 5),
+    (16, 2, 80, 16, [(0, 33)], 16),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d,ps,entries,window", CASES)
+def test_attention_plain(dtype, nh, nkv, d, ps, entries, window):
+    worst = attention_case(plain_kernel, dtype, nh, nkv, d, ps, entries, window)
+    assert worst <= tol(dtype, 2), worst
+
+
+def far_key_checks(kernel, dtype):
+    """One key far back gets a score that dominates and a value unlike all others: if a kernel
+    skipped it (or read past the window's edge) the output would be wrong by O(1), not by
+    rounding.  Checked for a key far behind, for the oldest key inside a window and for the
+    newest key outside it."""
+    window = 50
+    nh, nkv, d, ps = 2, 1, 32, 16
+    for win, start, far, visible in ((None, 300, 3, True), (window, 120, 120 - window + 1, True),
+                                     (window, 120, 120 - window, False)):
+        def plant(b, s, c, q, k, v, far=far):
+            qd = q[0, 0, :].float()
+            k[far] = 0
+            k[far, 0] = (qd / qd.norm() * 60).to(k.dtype)     # head 0's query points at it
+            v[far] = 7.0
+        worst, out = attention_case(kernel, dtype, nh, nkv, d, ps, [(start, 1)], win, plant=plant, seed=5, want_out=True)
+        assert worst <= tol(dtype, 8), (win, far, worst)
+        if visible:
+            assert (out[0, 0].float() - 7.0).abs().max() < 0.1, "the planted key must decide head 0"
+        else:
+            assert (out[0, 0].float() - 7.0).abs().min() > 3.0, "a key behind the window must not be seen"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_plain_sees_one_far_key_and_the_windows_edge(dtype):
+    far_key_checks(plain_kernel, dtype)

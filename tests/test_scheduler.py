@@ -1,0 +1,207 @@
+"""The scheduler's decisions, with a fake step that makes up tokens (no GPU)."""
+import random
+
+import pytest
+
+from xinfer_b200.cache import CacheGroup, CacheManager
+from xinfer_b200.engine.scheduler import Scheduler, SchedulerError
+
+
+def make(pages=64, page=16, seqs=4, budget=64, chunk=32, max_len=512, eos=(), window=None):
+    cm = CacheManager([CacheGroup(page, pages, window)], max_requests=seqs)
+    return cm, Scheduler(cm, max_num_seqs=seqs, max_num_batched_tokens=budget, prefill_chunk_size=chunk,
+                         max_model_len=max_len, eos_token_ids=eos)
+
+
+def run(sched, token_of=lambda e, step: 7, max_steps=10_000):
+    """Drive to completion; returns (list of batches, {id: finish step})."""
+    batches, ended = [], {}
+    for step in range(max_steps):
+        if not sched.has_work():
+            break
+        entries = sched.schedule()
+        for i in sched.drain_finished():
+            ended[i] = step
+        if not entries:
+            continue
+        batches.append(entries)
+        for i in sched.commit([token_of(e, step) for e in entries if e.want]):
+            ended[i] = step
+    assert not sched.has_work()
+    return batches, ended
+
+
+def test_prompt_is_cut_under_chunk_and_budget_then_decoded():
+    cm, s = make(budget=40, chunk=32)
+    s.add(0, list(range(100)), max_tokens=3)
+    batches, ended = run(s)
+    sizes = [len(b[0].tokens) for b in batches]
+    assert sizes == [32, 32, 32, 4, 1, 1]
+    assert [b[0].start for b in batches] == [0, 32, 64, 96, 100, 101]
+    assert [b[0].want for b in batches] == [False, False, False, True, True, True]
+    assert batches[0][0].tokens.tolist() == list(range(32))
+    assert s.output(0) == [7, 7, 7] and s.finish_reason(0) == "length"
+    assert cm.live_requests() == 0 and cm.free_pages() == 64
+    s.release(0)
+
+
+def test_decodes_come_first_and_share_a_step_with_prompt_portions():
+    cm, s = make(budget=24, chunk=16)
+    s.add(0, [1] * 10, max_tokens=8)
+    e = s.schedule()
+    assert [(x.req_id, len(x.tokens), x.want) for x in e] == [(0, 10, True)]
+    s.commit([9])
+    s.add(1, [2] * 40, max_tokens=2)
+    e = s.schedule()
+    # one decode token of request 0, then a portion of request 1 cut by the chunk size
+    assert [(x.req_id, len(x.tokens), x.start, x.want) for x in e] == [(0, 1, 10, True), (1, 16, 0, False)]
+    s.commit([9])
+    e = s.schedule()
+    assert [(x.req_id, len(x.tokens), x.start) for x in e] == [(0, 1, 11), (1, 16, 16)]
+    s.commit([9])
+    e = s.schedule()
+    assert [(x.req_id, len(x.tokens), x.start, x.want) for x in e] == [(0, 1, 12, True), (1, 8, 32, True)]
+    total = sum(len(x.tokens) for x in e)
+    assert total <= 24
+
+
+def test_token_budget_cuts_a_portion_down():
+    cm, s = make(budget=20, chunk=16, seqs=4)
+    for i in range(3):
+        s.add(i, [i] * 12, max_tokens=1)
+    e = s.schedule()
+    assert [(x.req_id, len(x.tokens)) for x in e] == [(0, 12), (1, 8)]
+    s.commit([5])   # request 0 finishes (max_tokens 1)
+    e = s.schedule()
+    assert [(x.req_id, len(x.tokens), x.start) for x in e] == [(1, 4, 8), (2, 12, 0)]
+
+
+def test_max_num_seqs_limits_admission():
+    cm, s = make(seqs=2, budget=64)
+    for i in range(4):
+        s.add(i, [1, 2, 3], max_tokens=2)
+    e = s.schedule()
+    assert [x.req_id for x in e] == [0, 1] and s.num_waiting == 2
+    _, ended = run(s)
+    assert sorted(ended) == [0, 1, 2, 3]
+
+
+def test_finish_rules():
+    cm, s = make(eos=(99,), max_len=12)
+    s.add(0, [1, 2, 3], max_tokens=50)                          # ends on EOS, which stays out
+    s.add(1, [1, 2, 3], max_tokens=50, ignore_eos=True)         # ignores EOS, ends at max_model_len
+    s.add(2, [1, 2, 3], max_tokens=50, stop_token_ids=[42])     # ends on its own stop token
+    s.add(3, [1, 2, 3], max_tokens=2)
+
+    def tok(e, step):
+        if e.req_id == 0:
+            return 99 if step == 2 else 5
+        if e.req_id == 2:
+            return 42 if step == 1 else 5
+        return 99 if e.req_id == 1 else 5
+    run(s, tok)
+    assert s.output(0) == [5, 5] and s.finish_reason(0) == "stop"
+    assert s.finish_reason(1) == "length" and len(s.output(1)) == 9 and s.prompt_length(1) == 3
+    assert s.output(2) == [5] and s.finish_reason(2) == "stop"
+    assert s.output(3) == [5, 5] and s.finish_reason(3) == "length"
+    assert s.num_drawn(0) == 3 and s.num_drawn(3) == 2
+    assert cm.free_pages() == 64
+
+
+def test_add_errors():
+    cm, s = make(pages=4, page=16, max_len=128)
+    with pytest.raises(SchedulerError, match="empty"):
+        s.add(0, [], 4)
+    with pytest.raises(SchedulerError, match="too long"):
+        s.add(0, [1] * 128, 4)
+    with pytest.raises(SchedulerError, match="never fit"):
+        s.add(0, [1] * 60, 10)       # 70 tokens need 5 pages, the pool has 4
+    s.add(0, [1] * 50, 10)
+    with pytest.raises(SchedulerError, match="exists"):
+        s.add(0, [1], 1)
+
+
+def test_out_of_pages_preempts_the_newest_and_recomputes_it():
+    # 6 pages of 4 tokens: two requests of 8 prompt tokens fit, but not both growing to 14
+    cm, s = make(pages=6, page=4, seqs=2, budget=64, chunk=64, max_len=64)
+    s.add(0, list(range(10, 18)), max_tokens=6)
+    s.add(1, list(range(20, 28)), max_tokens=6)
+    log = []
+
+    def tok(e, step):
+        log.append((step, e.req_id, e.start, len(e.tokens)))
+        return 100 + e.req_id
+    batches, ended = run(s, tok)
+    assert s.preemptions >= 1
+    assert s.output(0) == [100] * 6 and s.output(1) == [101] * 6
+    assert ended[0] < ended[1]                       # the older request was never disturbed
+    # the preempted request came back with its prompt and generated tokens as one portion from 0
+    redo = [b for b in batches for e in b if e.req_id == 1 and e.start == 0]
+    assert len(redo) == 2
+    again = [e for e in redo[1] if e.req_id == 1][0]
+    assert again.tokens.tolist()[:8] == list(range(20, 28)) and set(again.tokens.tolist()[8:]) == {101}
+    assert cm.free_pages() == 6 and cm.live_requests() == 0
+    cm.check_consistent()
+
+
+def test_a_request_alone_that_cannot_grow_is_aborted_not_spun_on():
+    cm, s = make(pages=2, page=4, seqs=1, budget=64, chunk=64, max_len=64)
+    s.add(0, [1] * 6, max_tokens=2)     # fits: 8 tokens = 2 pages
+    run(s)
+    assert s.finish_reason(0) == "length"
+    # a second pool user that takes a page away makes the lone request impossible to grow
+    cm2, s2 = make(pages=3, page=4, seqs=2, budget=64, chunk=64, max_len=64)
+    other = cm2.open_request()
+    assert cm2.extend(other, 4)
+    s2.add(0, [1] * 8, max_tokens=4)
+    _, ended = run(s2)
+    assert s2.finish_reason(0) == "abort" and cm2.free_pages() == 2
+
+
+def test_abort_frees_pages():
+    cm, s = make()
+    s.add(0, [1] * 30, max_tokens=5)
+    s.schedule()
+    s.commit([])
+    assert cm.free_pages() < 64
+    assert s.abort(0) and not s.abort(0)
+    assert cm.free_pages() == 64 and s.finish_reason(0) == "abort" and s.drain_finished() == [0]
+
+
+@pytest.mark.parametrize("seed", range(5))
+def test_random_workloads_finish_and_leave_the_pool_whole(seed):
+    rng = random.Random(seed)
+    page = rng.choice([4, 8, 16])
+    pages = rng.randint(12, 40)
+    window = rng.choice([None, None, 9, 23])
+    cm, s = make(pages=pages, page=page, seqs=rng.randint(2, 5), budget=rng.randint(8, 48),
+                 chunk=rng.randint(4, 32), max_len=200, eos=(1,), window=window)
+    want = {}
+    nxt = 0
+    for step in range(3000):
+        if nxt < 25 and rng.random() < 0.3:
+            n, m = rng.randint(1, 60), rng.randint(1, 30)
+            try:
+                s.add(nxt, [rng.randint(2, 50) for _ in range(n)], m)
+                want[nxt] = (n, m)
+            except SchedulerError:
+                pass
+            nxt += 1
+        if not s.has_work():
+            if nxt >= 25:
+                break
+            continue
+        entries = s.schedule()
+        s.drain_finished()
+        total = sum(len(e.tokens) for e in entries)
+        assert len({e.req_id for e in entries}) == len(entries)
+        for e in entries:
+            assert cm.length(e.slot) == e.start
+            assert len(cm.table(e.slot)) * page >= e.start + len(e.tokens)
+        s.commit([rng.choice([1, 7, 8, 9]) if rng.random() < 0.05 else 7 for e in entries if e.want])
+        cm.check_consistent()
+    assert not s.has_work()
+    for i, (n, m) in want.items():
+        assert s.finish_reason(i) in ("stop", "length")
+        assert len(s.output(i)) <= m
+    assert cm.free_pages() == pages and cm.live_requests() == 0
