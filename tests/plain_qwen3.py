@@ -191,13 +191,13 @@ def _philox4x32_10(c0, c1, c2, c3, k0, k1):
 
 def gumbel_noise(seed: int, draw: int, vocab: int) -> np.ndarray:
     """G_i = -log(-log(u_i)), u_i from Philox keyed by the request's seed with counter
-    (i // 4, draw, tag, 0), word i % 4, mapped to (0, 1) through its top 24 bits."""
+    (i // 4, draw, tag, 0), word i % 4, mapped to (0, 1) through its top 23 bits."""
     n4 = (vocab + 3) // 4
     idx = np.arange(n4, dtype=np.uint32)
     words = _philox4x32_10(idx, np.full(n4, draw, np.uint32), np.full(n4, 0x58494E46, np.uint32),
                            np.zeros(n4, np.uint32), seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
     w = np.stack(words, axis=1).reshape(-1)[:vocab]
-    u = ((w >> np.uint32(8)).astype(np.float32) + np.float32(0.5)) * np.float32(1.0 / 16777216.0)
+    u = ((w >> np.uint32(9)).astype(np.float32) + np.float32(0.5)) * np.float32(1.0 / 8388608.0)
     return (-np.log(-np.log(u))).astype(np.float32)
 
 

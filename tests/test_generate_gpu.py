@@ -1,0 +1,159 @@
+"""Generation through the Python entry point against the plain implementation."""
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from helpers import PAGE_SIZE, TINY, prompts_for
+
+pytestmark = pytest.mark.gpu
+
+
+def engine(folder, dtype, name, **kw):
+    from xinfer_b200 import Engine, EngineConfig
+    opts = dict(weight_path=folder, block_size=PAGE_SIZE[name], num_blocks=64, max_num_seqs=4,
+                max_num_batched_tokens=256, prefill_chunk_size=256, disable_cuda_graph=True)
+    opts.update(kw)
+    return Engine(EngineConfig(**opts), dtype)
+
+
+def test_greedy_float32_equals_plain(model_folders):
+    # tiny configuration A: three prompts of 5 / 11 / 17 tokens, whole, 8 greedy steps each
+    from xinfer_b200 import SamplingParams
+    folder = model_folders("A", torch.float32)
+    cfg, w = plain.load_folder(folder)
+    prompts = prompts_for("A", [5, 11, 17])
+    outs = engine(folder, "f32", "A").generate_sync(SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True), prompts)
+    for p, o in zip(prompts, outs):
+        assert o.decode_output == plain.generate(cfg, w, p, 8)
+        assert (o.prompt_length, o.decoded_length, o.finish_reason) == (len(p), 8, "length")
+        assert o.prompt_start_time <= o.decode_start_time <= o.decode_finish_time
+
+
+def test_portions_of_six_and_temperature_sampling_equal_plain(model_folders):
+    # tiny configuration B: prompts of 1 / 7 / 23 / 40 tokens in portions of 6, temperature 0.8, 10 steps
+    from xinfer_b200 import SamplingParams
+    folder = model_folders("B", torch.float32)
+    cfg, w = plain.load_folder(folder)
+    prompts = prompts_for("B", [1, 7, 23, 40])
+    eng = engine(folder, "f32", "B", prefill_chunk_size=6, max_num_batched_tokens=16)
+    params = [SamplingParams(temperature=0.8, max_tokens=10, ignore_eos=True, seed=50 + i) for i in range(4)]
+    outs = eng.generate_sync(params, prompts)
+    for i, (p, o) in enumerate(zip(prompts, outs)):
+        assert o.decode_output == plain.generate(cfg, w, p, 10, temperature=0.8, seed=50 + i)
+    assert eng.stats["steps"] > 10 + 40 // 6
+
+
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_bfloat16_greedy_follows_the_plain_logits(name, model_folders):
+    """bfloat16 may flip a near-tie, so each generated token is checked against the plain logits
+    of the sequence the engine actually produced: it must be the best token up to the drift."""
+    from xinfer_b200 import SamplingParams
+    folder = model_folders(name, torch.bfloat16)
+    cfg, w = plain.load_folder(folder)
+    prompts = prompts_for(name, [3, 30, 61])
+    outs = engine(folder, "bf16", name).generate_sync(SamplingParams(max_tokens=40, ignore_eos=True), prompts)
+    for p, o in zip(prompts, outs):
+        seq = p + o.decode_output
+        ref = plain.forward(cfg, w, seq)
+        drift = 3.0 * (plain.forward(cfg, w, seq, round_to=torch.bfloat16) - ref).abs().max().item()
+        for i, tok in enumerate(o.decode_output):
+            row = ref[len(p) + i - 1]
+            assert row[tok] >= row.max() - 2 * drift, (i, tok)
+
+
+def test_long_decoding_and_first_tokens(model_folders):
+    from xinfer_b200 import SamplingParams
+    folder = model_folders("C", torch.float32)     # window 37: pages behind the window are given back
+    cfg, w = plain.load_folder(folder)
+    prompts = prompts_for("C", [1, 2, 9])
+    eng = engine(folder, "f32", "C", num_blocks=12)  # 192 tokens of pages for 3 requests growing to ~300 each
+    outs = eng.generate_sync(SamplingParams(max_tokens=300, ignore_eos=True), prompts)
+    for p, o in zip(prompts, outs):
+        assert o.decoded_length == 300
+        seq = p + o.decode_output
+        ref = plain.forward(cfg, w, seq)
+        for i, tok in enumerate(o.decode_output):   # teacher-forced: each token is the plain argmax
+            row = ref[len(p) + i - 1]
+            assert row[tok] >= row.max() - 1e-5, (i, tok)
+    assert eng.stats["preemptions"] == 0
+    eng.runner.cache.check_consistent()
+    assert eng.runner.cache.live_requests() == 0
+
+
+def test_top_k_top_p_and_penalties_equal_plain(model_folders):
+    from xinfer_b200 import SamplingParams
+    folder = model_folders("A", torch.float32)
+    cfg, w = plain.load_folder(folder)
+    p = prompts_for("A", [12])[0]
+    eng = engine(folder, "f32", "A")
+    for kw in (dict(top_k=5), dict(top_p=0.7), dict(top_k=12, top_p=0.8)):
+        o = eng.generate_sync(SamplingParams(temperature=1.1, max_tokens=12, ignore_eos=True, seed=9, **kw), [p])[0]
+        assert o.decode_output == plain.generate(cfg, w, p, 12, temperature=1.1, seed=9,
+                                                 top_k=kw.get("top_k", 0), top_p=kw.get("top_p", 1.0)), kw
+    o = eng.generate_sync(SamplingParams(temperature=0.9, max_tokens=20, ignore_eos=True, seed=4,
+                                         frequency_penalty=1.5, presence_penalty=0.5), [p])[0]
+    ids = list(p)
+    for n in range(20):
+        logits = plain.apply_penalties(plain.forward(cfg, w, ids)[-1].numpy(), ids[-128:], 1.5, 0.5)
+        ids.append(plain.sample(logits, 0.9, seed=4, draw=n))
+    assert o.decode_output == ids[len(p):]
+
+
+def test_eos_stop_tokens_and_stream(model_folders):
+    from xinfer_b200 import SamplingParams
+    folder = model_folders("A", torch.float32)
+    cfg, w = plain.load_folder(folder)
+    p = prompts_for("A", [10])[0]
+    free = plain.generate(cfg, w, p, 12)
+    eng = engine(folder, "f32", "A")
+    stop = free[5]
+    o = eng.generate_sync(SamplingParams(max_tokens=12, ignore_eos=True, stop_token_ids=[stop]), [p])[0]
+    assert o.decode_output == free[: free.index(stop)] and o.finish_reason == "stop"
+    seq_id, plen, stream = eng.generate_stream(SamplingParams(max_tokens=12, ignore_eos=True), p)
+    items = list(stream)
+    assert plen == 10 and [i.data for i in items if i.datatype == "TOKEN_ID"] == free
+    assert items[-1].datatype == "DONE" and items[-1].data[:3] == (seq_id, 10, 12)
+    assert eng.get_available_kv_tokens() == 64 * 16 and eng.get_num_cached_tokens() == 0
+
+
+def test_scarce_pages_preempt_and_still_give_the_same_tokens(model_folders):
+    from xinfer_b200 import SamplingParams
+    folder = model_folders("B", torch.float32)
+    cfg, w = plain.load_folder(folder)
+    prompts = prompts_for("B", [30, 26, 22, 18], seed=3)
+    sp = [SamplingParams(temperature=0.7, max_tokens=40, ignore_eos=True, seed=i) for i in range(4)]
+    roomy = engine(folder, "f32", "B", num_blocks=64).generate_sync(sp, prompts)
+    tight_engine = engine(folder, "f32", "B", num_blocks=20)     # 160 tokens for 4 requests that grow to ~260
+    tight = tight_engine.generate_sync(sp, prompts)
+    assert tight_engine.stats["preemptions"] > 0
+    for a, b, p, s in zip(roomy, tight, prompts, sp):
+        assert a.decode_output == b.decode_output
+        assert a.decode_output == plain.generate(cfg, w, p, 40, temperature=0.7, seed=s.seed)
+    tight_engine.runner.cache.check_consistent()
+    assert tight_engine.runner.cache.free_pages() == 20
+
+
+def test_bad_requests_are_refused(model_folders):
+    from xinfer_b200 import SamplingParams
+    from xinfer_b200.engine.scheduler import SchedulerError
+    folder = model_folders("A", torch.float32)
+    eng = engine(folder, "f32", "A", num_blocks=4, max_model_len=128)
+    with pytest.raises(ValueError):
+        eng.generate_sync(SamplingParams(max_tokens=2), [[1, 2, 999]])
+    with pytest.raises(SchedulerError, match="never fit"):
+        eng.generate_sync(SamplingParams(max_tokens=60), [[1] * 30])
+    with pytest.raises(SchedulerError, match="too long"):
+        eng.generate_sync(SamplingParams(max_tokens=2), [[1] * 128])
+    assert eng.generate_sync(SamplingParams(max_tokens=3, ignore_eos=True), [[1, 2, 3]])[0].decoded_length == 3
+
+
+def test_command_line(model_folders, capsys):
+    from xinfer_b200.cli import main
+    folder = model_folders("A", torch.float32)
+    cfg, w = plain.load_folder(folder)
+    assert main(["--m", folder, "--dtype", "f32", "--prompts", "5,6,7|9,10", "--max-tokens", "4", "--ignore-eos",
+                 "--disable-cuda-graph", "--num-blocks", "16"]) == 0
+    out = capsys.readouterr().out
+    want = ",".join(str(t) for t in plain.generate(cfg, w, [5, 6, 7], 4))
+    assert want in out and "Prompt tokens: 5" in out and "Decoded tokens: 8" in out

@@ -21,7 +21,7 @@ AddStatus Scheduler::add(int64_t req_id, const int32_t* prompt, int n, int max_t
         int most = total;
         if (s.window > 0) {
             // a windowed group holds at most one portion plus the window behind it
-            const int portion = std::min(cfg_.prefill_chunk_size, cfg_.max_num_batched_tokens);
+            const int portion = std::min(std::min(cfg_.prefill_chunk_size, cfg_.max_num_batched_tokens), n);
             most = std::min(total, s.window + portion + s.page_size);
         }
         if ((most + s.page_size - 1) / s.page_size > s.num_pages) return ADD_NEVER_FITS;

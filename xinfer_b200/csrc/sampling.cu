@@ -28,7 +28,7 @@ __device__ __forceinline__ float gumbel_of(uint32_t seed_lo, uint32_t seed_hi, u
     uint32_t r[4];
     philox4x32_10((uint32_t)i >> 2, draw, 0x58494e46u, 0u, seed_lo, seed_hi, r);
     const uint32_t w = r[i & 3];
-    const float u = ((float)(w >> 8) + 0.5f) * (1.0f / 16777216.0f);  // in (0, 1), exact in float32
+    const float u = ((float)(w >> 9) + 0.5f) * (1.0f / 8388608.0f);  // in (0, 1), exact in float32
     return -logf(-logf(u));
 }
 

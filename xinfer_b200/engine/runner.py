@@ -85,6 +85,101 @@ class _MetaBuffers:
         self.events[i] = ev
 
 
+class StepAssembler:
+    """Turns a batch of ``StepInput`` into a ``StepContext``: takes the pages the tokens need,
+    packs the step's metadata natively into a pinned buffer and sends it with one copy."""
+
+    def __init__(self, cache: CacheManager, *, vocab_size: int, max_model_len: int, dtype: torch.dtype,
+                 device, workspace: Optional[Workspace] = None, err: Optional[torch.Tensor] = None):
+        self.cache = cache
+        self.vocab_size = int(vocab_size)
+        self.max_model_len = int(max_model_len)
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.block_size = cache.groups[0].page_size
+        self.workspace = workspace if workspace is not None else Workspace(self.device)
+        self.err = err if err is not None else torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._meta = _MetaBuffers(self.device)
+        self._lib = host_lib()
+
+    def prepare(self, entries: Sequence[StepInput], *, pad_entries: int = 0, pad_tokens: int = 0,
+                strides: Optional[Sequence[int]] = None) -> StepContext:
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        B = len(entries)
+        counts = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=B)
+        if (counts <= 0).any():
+            raise StepError("every entry of a step must bring at least one token")
+        slots = np.fromiter((e.slot for e in entries), dtype=np.int32, count=B)
+        if len(set(slots.tolist())) != B:
+            raise StepError("a request may appear only once in a step")
+        T = int(counts.sum())
+        tokens = np.empty(T, dtype=np.int32)
+        want_e: List[int] = []
+        want_o: List[int] = []
+        t = 0
+        V = self.vocab_size
+        starts = np.empty(B, dtype=np.int32)
+        for b, e in enumerate(entries):
+            n = int(counts[b])
+            tokens[t:t + n] = np.asarray(e.tokens, dtype=np.int64)
+            t += n
+            for w in e.want:
+                if not (0 <= int(w) < n):
+                    raise StepError(f"entry {b} wants logits at {w}, but brings {n} tokens")
+                want_e.append(b)
+                want_o.append(int(w))
+            if not self.cache.is_live(int(slots[b])):
+                raise StepError(f"entry {b}: slot {int(slots[b])} is not an open request")
+            start = self.cache.length(int(slots[b]))
+            starts[b] = start
+            if start + n > self.max_model_len:
+                raise StepError(f"entry {b}: {start + n} tokens exceed the longest sequence {self.max_model_len}")
+            if not self.cache.extend(int(slots[b]), start + n):
+                raise StepError(f"entry {b}: the page pool has no room for {n} more tokens "
+                                f"(free pages {[self.cache.free_pages(g) for g in range(len(self.cache.groups))]})")
+        if tokens.min() < 0 or tokens.max() >= V:
+            raise StepError(f"token ids must lie in [0, {V}); got {int(tokens.min())}..{int(tokens.max())}")
+        R = len(want_e)
+        G = len(self.cache.groups)
+        Bp, Tp = max(B, pad_entries), max(T, pad_tokens)
+        longest = int((starts + counts).max())
+        max_stride = max((longest + self.block_size - 1) // self.block_size + 8, max(strides) if strides else 0)
+        need = 3 * (Tp + 4) + 3 * (Bp + 5) + R + 8 + G * (Bp * max_stride + 4) + 64
+        self._meta.reserve(need)
+        host, dev, which = self._meta.next()
+        offs = (ctypes.c_longlong * (7 + 2 * G))()
+        we = np.asarray(want_e, dtype=np.int32)
+        wo = np.asarray(want_o, dtype=np.int32)
+        st = np.asarray(strides, dtype=np.int32) if strides is not None else None
+        used = self._lib.xb_assemble(
+            self.cache.handle, B, slots.ctypes.data, counts.ctypes.data, tokens.ctypes.data, R,
+            we.ctypes.data if R else None, wo.ctypes.data if R else None, int(pad_tokens), int(pad_entries),
+            st.ctypes.data if st is not None else None, host.data_ptr(), host.numel(), offs)
+        if used < 0:
+            raise StepError({-1: "step metadata does not fit its buffer", -2: "a slot is not live",
+                             -3: "pages are missing for an entry", -4: "a wanted position is out of range"}.get(used, f"assemble failed ({used})"))
+        dev[:used].copy_(host[:used], non_blocking=True)
+        self._meta.sent(which)
+
+        def view(k, n):
+            return dev[offs[k]: offs[k] + n]
+
+        q_start_h = host[offs[3]: offs[3] + Bp + 1].numpy().copy()
+        ctx = StepContext(
+            dtype=self.dtype, device=self.device, num_tokens=Tp, num_entries=Bp,
+            token_ids=view(0, Tp), positions=view(1, Tp), req_of_token=view(2, Tp),
+            q_start=view(3, Bp + 1), start_pos=view(4, Bp), slots=view(5, Bp),
+            logit_rows=view(6, max(R, 1)), num_logit_rows=R,
+            tables=[dev[offs[7 + g]: offs[7 + g] + Bp * offs[7 + G + g]] for g in range(G)],
+            strides=[int(offs[7 + G + g]) for g in range(G)],
+            err=self.err, workspace=self.workspace,
+            h_q_start=q_start_h, h_start_pos=starts.copy(), h_slots=slots.copy(),
+            real_tokens=T, real_entries=B, max_context=longest, all_single=bool((counts == 1).all()),
+        )
+        return ctx
+
+
 class ModelRunner:
     def __init__(self, model_dir: str, dtype="bfloat16", *, block_size: int = 16,
                  num_blocks: Optional[int] = None, max_num_seqs: int = 32,
@@ -118,8 +213,8 @@ class ModelRunner:
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._err_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
         self._build_caches(num_blocks, kv_fraction)
-        self._meta = _MetaBuffers(self.device)
-        self._lib = host_lib()
+        self.assembler = StepAssembler(self.cache, vocab_size=self.plan.vocab_size, max_model_len=self.max_model_len,
+                                       dtype=self.dtype, device=self.device, workspace=self.workspace, err=self.err)
         self.steps_run = 0
 
     # ---- caches --------------------------------------------------------------------------------------
@@ -200,80 +295,7 @@ class ModelRunner:
 
     def prepare(self, entries: Sequence[StepInput], *, pad_entries: int = 0, pad_tokens: int = 0,
                 strides: Optional[Sequence[int]] = None) -> StepContext:
-        if not entries:
-            raise StepError("a step needs at least one entry")
-        B = len(entries)
-        counts = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=B)
-        if (counts <= 0).any():
-            raise StepError("every entry of a step must bring at least one token")
-        slots = np.fromiter((e.slot for e in entries), dtype=np.int32, count=B)
-        if len(set(slots.tolist())) != B:
-            raise StepError("a request may appear only once in a step")
-        T = int(counts.sum())
-        tokens = np.empty(T, dtype=np.int32)
-        want_e: List[int] = []
-        want_o: List[int] = []
-        t = 0
-        V = self.plan.vocab_size
-        starts = np.empty(B, dtype=np.int32)
-        for b, e in enumerate(entries):
-            n = int(counts[b])
-            tokens[t:t + n] = np.asarray(e.tokens, dtype=np.int64)
-            t += n
-            for w in e.want:
-                if not (0 <= int(w) < n):
-                    raise StepError(f"entry {b} wants logits at {w}, but brings {n} tokens")
-                want_e.append(b)
-                want_o.append(int(w))
-            if not self.cache.is_live(int(slots[b])):
-                raise StepError(f"entry {b}: slot {int(slots[b])} is not an open request")
-            start = self.cache.length(int(slots[b]))
-            starts[b] = start
-            if start + n > self.max_model_len:
-                raise StepError(f"entry {b}: {start + n} tokens exceed the longest sequence {self.max_model_len}")
-            if not self.cache.extend(int(slots[b]), start + n):
-                raise StepError(f"entry {b}: the page pool has no room for {n} more tokens "
-                                f"(free pages {[self.cache.free_pages(g) for g in range(len(self.cache.groups))]})")
-        if tokens.min() < 0 or tokens.max() >= V:
-            raise StepError(f"token ids must lie in [0, {V}); got {int(tokens.min())}..{int(tokens.max())}")
-        R = len(want_e)
-        G = len(self.cache.groups)
-        Bp, Tp = max(B, pad_entries), max(T, pad_tokens)
-        longest = int((starts + counts).max())
-        max_stride = max((longest + self.block_size - 1) // self.block_size + 8, max(strides) if strides else 0)
-        need = 3 * (Tp + 4) + 3 * (Bp + 5) + R + 8 + G * (Bp * max_stride + 4) + 64
-        self._meta.reserve(need)
-        host, dev, which = self._meta.next()
-        offs = (ctypes.c_longlong * (7 + 2 * G))()
-        we = np.asarray(want_e, dtype=np.int32)
-        wo = np.asarray(want_o, dtype=np.int32)
-        st = np.asarray(strides, dtype=np.int32) if strides is not None else None
-        used = self._lib.xb_assemble(
-            self.cache.handle, B, slots.ctypes.data, counts.ctypes.data, tokens.ctypes.data, R,
-            we.ctypes.data if R else None, wo.ctypes.data if R else None, int(pad_tokens), int(pad_entries),
-            st.ctypes.data if st is not None else None, host.data_ptr(), host.numel(), offs)
-        if used < 0:
-            raise StepError({-1: "step metadata does not fit its buffer", -2: "a slot is not live",
-                             -3: "pages are missing for an entry", -4: "a wanted position is out of range"}.get(used, f"assemble failed ({used})"))
-        dev[:used].copy_(host[:used], non_blocking=True)
-        self._meta.sent(which)
-
-        def view(k, n):
-            return dev[offs[k]: offs[k] + n]
-
-        q_start_h = host[offs[3]: offs[3] + Bp + 1].numpy().copy()
-        ctx = StepContext(
-            dtype=self.dtype, device=self.device, num_tokens=Tp, num_entries=Bp,
-            token_ids=view(0, Tp), positions=view(1, Tp), req_of_token=view(2, Tp),
-            q_start=view(3, Bp + 1), start_pos=view(4, Bp), slots=view(5, Bp),
-            logit_rows=view(6, max(R, 1)), num_logit_rows=R,
-            tables=[dev[offs[7 + g]: offs[7 + g] + Bp * offs[7 + G + g]] for g in range(G)],
-            strides=[int(offs[7 + G + g]) for g in range(G)],
-            err=self.err, workspace=self.workspace,
-            h_q_start=q_start_h, h_start_pos=starts.copy(), h_slots=slots.copy(),
-            real_tokens=T, real_entries=B, max_context=longest, all_single=bool((counts == 1).all()),
-        )
-        return ctx
+        return self.assembler.prepare(entries, pad_entries=pad_entries, pad_tokens=pad_tokens, strides=strides)
 
     def finish(self, entries: Sequence[StepInput]) -> None:
         for e in entries:
