@@ -1,0 +1,282 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput at Qwen3-8B layer sizes with random weights, on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+
+Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 and the context length
+of the configuration (a "step" is one decode step of the whole batch), timed on the device with
+CUDA events around exactly K steps; ``e2e`` is the same through the Python entry point
+(``Engine.step``: host token ids in through pinned memory every step, sampled ids read back every
+step).  ``prefill`` times one step of 2,048 prompt tokens; ``roofline`` divides the bytes a decode
+step must read (every weight once, the cache of the live requests) by its time; ``points`` holds
+decode at batch 1 and 64.  Peaks come from MEASURED_PEAKS.json beside this file when present.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# Layer sizes of the headline configuration (Qwen3-8B shape).
+CONFIG = dict(
+    architectures=["Qwen3ForCausalLM"], vocab_size=151936, hidden_size=4096, intermediate_size=12288,
+    num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+    rms_norm_eps=1e-6, rope_theta=1000000.0, max_position_embeddings=40960,
+    tie_word_embeddings=False, sliding_window=None,
+)
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+PAGE = 16
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=float(p["hbm_gbs"]), bf16_tflops=float(p["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.time(), line.strip()))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, t0: float, t1: float):
+        mhz, mx, reasons = [], 0, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for t, line in self.samples:
+            if t < t0 or t > t1 + 0.2:
+                continue
+            parts = [p.strip() for p in line.split(",")]
+            try:
+                mhz.append(float(parts[0]))
+                mx = max(mx, float(parts[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def reference_arm():
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "the reference is a Rust crate (no setup.py/pyproject.toml; pip: 'not installable'); "
+                      "no Rust toolchain and no network on this machine"}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=CONFIG["num_hidden_layers"],
+                    help="run fewer layers than the configuration has (reported in config)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=CONTEXT)
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print("bench.py: this engine runs on one GPU; --gpus must be 1")
+        return 2
+    steps, warmup = max(args.steps, 1), max(args.warmup, 3)
+
+    import numpy as np
+    import torch
+    from xinfer_b200 import kernels
+    from xinfer_b200.config import EngineConfig
+    from xinfer_b200.engine.llm import Engine
+    from xinfer_b200.engine.runner import ModelRunner, StepInput
+    from xinfer_b200.sampling import SamplingParams
+
+    pk = peaks()
+    cfg = dict(CONFIG, num_hidden_layers=args.layers)
+    max_b = args.batch if args.no_points else max(args.batch, 64)
+    pages_per_req = (args.context + PAGE - 1) // PAGE + 1
+    t_load = time.time()
+    runner = ModelRunner.random(cfg, seed=0, dtype="bfloat16", block_size=PAGE, num_blocks=max_b * pages_per_req,
+                                max_num_seqs=max_b, max_model_len=args.context + 64)
+    torch.cuda.synchronize()
+    load_s = time.time() - t_load
+    rng = np.random.default_rng(0)
+    V = cfg["vocab_size"]
+    use_graph = not args.no_graph
+
+    def fill(batch: int, ctx: int):
+        """Open `batch` requests and prefill each to `ctx` tokens through the step function."""
+        slots = [runner.open_request() for _ in range(batch)]
+        chunk = 4096
+        for s in slots:
+            at = 0
+            while at < ctx:
+                n = min(chunk, ctx - at)
+                runner.step([StepInput(s, rng.integers(0, V, size=n), [])])
+                at += n
+        runner.check_errors()
+        return slots
+
+    def decode_device(slots, n_steps: int, n_warm: int):
+        """K decode steps, kernel time only: token ids come from the host each step, no read-back."""
+        toks = rng.integers(0, V, size=(n_steps + n_warm, len(slots)))
+        for i in range(n_warm):
+            runner.step([StepInput(s, toks[i, j:j + 1], [0]) for j, s in enumerate(slots)], allow_graph=use_graph)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches = 0
+        t0 = time.time()
+        e0.record()
+        for i in range(n_warm, n_warm + n_steps):
+            runner.step([StepInput(s, toks[i, j:j + 1], [0]) for j, s in enumerate(slots)], allow_graph=use_graph)
+            launches += runner.last_launches
+        e1.record()
+        torch.cuda.synchronize()
+        t1 = time.time()
+        runner.check_errors()
+        return e0.elapsed_time(e1) / n_steps, launches, (t0, t1)
+
+    def close(slots):
+        for s in slots:
+            runner.close_request(s)
+
+    clocks = ClockSampler()
+    clocks.start()
+
+    # ---- prefill: one step of 2,048 prompt tokens ------------------------------------------------------
+    pre_ms = []
+    for i in range(3 + 3):
+        s = runner.open_request()
+        ids = rng.integers(0, V, size=PREFILL_TOKENS)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        runner.step([StepInput(s, ids, [PREFILL_TOKENS - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            pre_ms.append(e0.elapsed_time(e1))
+        runner.close_request(s)
+    runner.check_errors()
+    pre = min(pre_ms)
+    L, H, I = cfg["num_hidden_layers"], cfg["hidden_size"], cfg["intermediate_size"]
+    nh, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    layer_params = H * (nh + 2 * nkv) * d + nh * d * H + 3 * H * I
+    T = PREFILL_TOKENS
+    flops = 2.0 * T * layer_params * L + 2.0 * V * H + L * 4.0 * nh * d * (T * (T + 1) / 2)
+    prefill = {"value": round(T / (pre / 1e3), 1), "tokens": T, "ms": round(pre, 3),
+               "frac": round(flops / (pre / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # ---- decode at the headline batch --------------------------------------------------------------------
+    B = args.batch
+    ctx0 = args.context - steps - warmup - 2
+    slots = fill(B, ctx0)
+    ms, launches, (t0, t1) = decode_device(slots, steps, warmup)
+    ck = clocks.summary(t0, t1)
+    value = B / (ms / 1e3)
+    weight_bytes = (layer_params * L + V * H) * 2 + (2 * L + 1) * H * 4 + L * 2 * d * 4
+    ctx_mid = ctx0 + warmup + steps / 2
+    kv_bytes = runner.kv_bytes_per_token * ctx_mid * B
+    achieved = (weight_bytes + kv_bytes) / (ms / 1e3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / pk["hbm_gbs"], 4)}
+    close(slots)
+
+    # ---- the same through the Python entry point ----------------------------------------------------------
+    econfig = EngineConfig(weight_path="(random)", block_size=PAGE, max_num_seqs=max_b, max_num_batched_tokens=8192,
+                           prefill_chunk_size=4096, max_model_len=args.context + 64, disable_cuda_graph=not use_graph)
+    engine = Engine(econfig, "bf16", runner=runner)
+    n_e2e = min(steps, 64)
+    prompt_len = args.context - n_e2e - warmup - 2
+    sp = SamplingParams(temperature=0.0, max_tokens=n_e2e + warmup, ignore_eos=True)
+    for _ in range(B):
+        engine.add_request(rng.integers(0, V, size=prompt_len).tolist(), sp)
+    while any(engine.scheduler.output(i) == [] for i in list(engine._live)):   # prompts, first tokens
+        engine.step()
+    for _ in range(warmup - 1):
+        engine.step()
+    torch.cuda.synchronize()
+    tw0 = time.time()
+    done_before = engine.stats["decoded_tokens"]
+    h2d = 0
+    for _ in range(n_e2e):
+        engine.step()
+        h2d += runner.assembler.h2d_bytes + B * kernels.SAMPLE_PARAMS.itemsize
+    torch.cuda.synchronize()
+    tw1 = time.time()
+    e2e_tokens = engine.stats["decoded_tokens"] - done_before
+    e2e = {"value": round(e2e_tokens / (tw1 - tw0), 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d // n_e2e,
+           "d2h_bytes_per_step": B * 4 + 4}
+    while engine.has_work():
+        engine.step()
+
+    # ---- batch 1 and 64 -----------------------------------------------------------------------------------
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            k = min(steps, 32)
+            sl = fill(b, args.context - k - warmup - 2)
+            m, _, _ = decode_device(sl, k, warmup)
+            points[f"decode_b{b}"] = round(b / (m / 1e3), 1)
+            close(sl)
+    clocks.stop()
+
+    out = {
+        "metric": "decode tok/s at batch 8 (Qwen3-8B shape, context 4096)", "value": round(value, 1), "unit": "tokens/s",
+        "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights, seeded uniform token ids)",
+        "impl": "ours",
+        "config": {"model": "Qwen3-8B shape", "layers": cfg["num_hidden_layers"], "layers_of_config": CONFIG["num_hidden_layers"],
+                   "hidden": H, "heads": nh, "kv_heads": nkv, "head_dim": d, "intermediate": I, "vocab": V,
+                   "global_batch": B, "seq_len": args.context, "page_size": PAGE, "parallelism": "1 GPU",
+                   "cuda_graph": use_graph, "l2": "inputs larger than L2 (weights read every step)",
+                   "peaks": pk["source"], "load_s": round(load_s, 1)},
+        "clocks": ck, "e2e": e2e, "gpu_launches": int(launches), "prefill": prefill, "roofline": roofline, "points": points,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -52,7 +52,8 @@ XB_API int xb_cm_consistent(void* h, char* why, int cap) {
 // Packs, for B entries (slot, count, tokens) whose start is the slot's cached length:
 //   token_ids[Tp] positions[Tp] req_of_token[Tp] q_start[Bp+1] start_pos[Bp] slots[Bp]
 //   logit_rows[Rp] and, per group, block_table[Bp, stride_g]
-// Tp/Bp are T and B padded up to pad_tokens / pad_entries (padding tokens belong to request -1
+// Tp/Bp/Rp are T, B and R padded up to pad_tokens / pad_entries / pad_rows (padding rows read
+// row 0; padding tokens belong to request -1
 // and are skipped by the kernels); every array starts on a 16-byte boundary.  `strides` holds a
 // wanted row length per group (0: as long as the longest table here, rounded up to 8).
 // offsets_out[0..6] = array offsets in int32 units, [7 + g] = table offset of group g,
@@ -60,7 +61,7 @@ XB_API int xb_cm_consistent(void* h, char* why, int cap) {
 // (negative on error: -1 capacity, -2 slot not live, -3 pages missing, -4 bad want).
 XB_API long long xb_assemble(void* h, int B, const int* slots, const int* counts, const int* tokens,
                              int R, const int* want_entry, const int* want_offset, int pad_tokens,
-                             int pad_entries, const int* strides, int32_t* out, long long capacity,
+                             int pad_entries, int pad_rows, const int* strides, int32_t* out, long long capacity,
                              long long* offsets_out) {
     CacheManager* cm = static_cast<CacheManager*>(h);
     const int G = cm->num_groups();
@@ -69,7 +70,7 @@ XB_API long long xb_assemble(void* h, int B, const int* slots, const int* counts
         if (!cm->is_live(slots[b]) || counts[b] <= 0) return -2;
         T += counts[b];
     }
-    const int Tp = std::max(T, pad_tokens), Bp = std::max(B, pad_entries), Rp = std::max(R, 1);
+    const int Tp = std::max(T, pad_tokens), Bp = std::max(B, pad_entries), Rp = std::max(std::max(R, pad_rows), 1);
     auto up4 = [](long long x) { return (x + 3) / 4 * 4; };
     std::vector<int> stride(G);
     for (int g = 0; g < G; ++g) {

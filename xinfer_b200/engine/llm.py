@@ -60,10 +60,12 @@ def _ms(t: float) -> int:
 
 
 class Engine:
-    def __init__(self, econfig: EngineConfig, dtype: str = "bf16"):
+    def __init__(self, econfig: EngineConfig, dtype: str = "bf16", runner: Optional[ModelRunner] = None):
+        """``runner``: a prepared model runner (for instance ``ModelRunner.random``) to use instead
+        of loading ``econfig``'s model folder."""
         econfig.validate()
         self.econfig = econfig
-        self.runner = ModelRunner(
+        self.runner = runner if runner is not None else ModelRunner(
             econfig.model_dir(), dtype, block_size=econfig.block_size, num_blocks=econfig.num_blocks,
             max_num_seqs=econfig.max_num_seqs, kv_fraction=econfig.kv_fraction, device=econfig.device,
             max_model_len=econfig.max_model_len)

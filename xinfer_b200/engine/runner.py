@@ -7,20 +7,24 @@ only those tokens as one batch against the cache and returns float32 logits at t
 positions.  The reference's counterpart is ``ModelRunner::run`` (src/core/runner.rs:1018), which
 runs either prompt chunks or decode tokens, never both, and returns sampled ids
 (prepare_prefill :1303-1563, prepare_decode :1565-1750).
+
+Steps in which every request brings exactly one token and wants its logits may be replayed from a
+CUDA graph (one per padded batch size and block-table width), as the reference captures its
+decode step per batch size (src/utils/graph.rs:400-420, 689-711).
 """
 from __future__ import annotations
 
 import ctypes
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Any, Dict, List, Mapping, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
 
 from .. import kernels
 from ..cache.manager import CacheError, CacheGroup, CacheManager, StateSlots
-from ..config import ConfigError, load_config
-from ..models.decoder import DecoderModel
+from ..config import ConfigError, config_from_dict, load_config
+from ..models.decoder import DecoderModel, model_weight_specs
 from ..native import host_lib
 from ..parts import LayerCache, StepContext, Workspace
 from ..weights.loader import WeightStore
@@ -101,9 +105,13 @@ class StepAssembler:
         self.err = err if err is not None else torch.zeros(1, dtype=torch.int32, device=self.device)
         self._meta = _MetaBuffers(self.device)
         self._lib = host_lib()
+        self.h2d_bytes = 0   # bytes of the last step's metadata copy
 
     def prepare(self, entries: Sequence[StepInput], *, pad_entries: int = 0, pad_tokens: int = 0,
-                strides: Optional[Sequence[int]] = None) -> StepContext:
+                pad_rows: int = 0, strides: Optional[Sequence[int]] = None,
+                into: Optional[torch.Tensor] = None, workspace: Optional[Workspace] = None) -> StepContext:
+        """``into``: a device buffer that must receive the metadata (a CUDA graph reads it at a
+        fixed address); otherwise a buffer of the ring is used."""
         if not entries:
             raise StepError("a step needs at least one entry")
         B = len(entries)
@@ -120,32 +128,34 @@ class StepAssembler:
         t = 0
         V = self.vocab_size
         starts = np.empty(B, dtype=np.int32)
+        cache = self.cache
         for b, e in enumerate(entries):
             n = int(counts[b])
-            tokens[t:t + n] = np.asarray(e.tokens, dtype=np.int64)
+            tokens[t:t + n] = e.tokens
             t += n
             for w in e.want:
                 if not (0 <= int(w) < n):
                     raise StepError(f"entry {b} wants logits at {w}, but brings {n} tokens")
                 want_e.append(b)
                 want_o.append(int(w))
-            if not self.cache.is_live(int(slots[b])):
-                raise StepError(f"entry {b}: slot {int(slots[b])} is not an open request")
-            start = self.cache.length(int(slots[b]))
+            slot = int(slots[b])
+            if not cache.is_live(slot):
+                raise StepError(f"entry {b}: slot {slot} is not an open request")
+            start = cache.length(slot)
             starts[b] = start
             if start + n > self.max_model_len:
                 raise StepError(f"entry {b}: {start + n} tokens exceed the longest sequence {self.max_model_len}")
-            if not self.cache.extend(int(slots[b]), start + n):
+            if not cache.extend(slot, start + n):
                 raise StepError(f"entry {b}: the page pool has no room for {n} more tokens "
-                                f"(free pages {[self.cache.free_pages(g) for g in range(len(self.cache.groups))]})")
+                                f"(free pages {[cache.free_pages(g) for g in range(len(cache.groups))]})")
         if tokens.min() < 0 or tokens.max() >= V:
             raise StepError(f"token ids must lie in [0, {V}); got {int(tokens.min())}..{int(tokens.max())}")
         R = len(want_e)
-        G = len(self.cache.groups)
-        Bp, Tp = max(B, pad_entries), max(T, pad_tokens)
+        G = len(cache.groups)
+        Bp, Tp, Rp = max(B, pad_entries), max(T, pad_tokens), max(R, pad_rows, 1)
         longest = int((starts + counts).max())
         max_stride = max((longest + self.block_size - 1) // self.block_size + 8, max(strides) if strides else 0)
-        need = 3 * (Tp + 4) + 3 * (Bp + 5) + R + 8 + G * (Bp * max_stride + 4) + 64
+        need = 3 * (Tp + 4) + 3 * (Bp + 5) + Rp + 8 + G * (Bp * max_stride + 4) + 64
         self._meta.reserve(need)
         host, dev, which = self._meta.next()
         offs = (ctypes.c_longlong * (7 + 2 * G))()
@@ -153,38 +163,56 @@ class StepAssembler:
         wo = np.asarray(want_o, dtype=np.int32)
         st = np.asarray(strides, dtype=np.int32) if strides is not None else None
         used = self._lib.xb_assemble(
-            self.cache.handle, B, slots.ctypes.data, counts.ctypes.data, tokens.ctypes.data, R,
+            cache.handle, B, slots.ctypes.data, counts.ctypes.data, tokens.ctypes.data, R,
             we.ctypes.data if R else None, wo.ctypes.data if R else None, int(pad_tokens), int(pad_entries),
-            st.ctypes.data if st is not None else None, host.data_ptr(), host.numel(), offs)
+            int(pad_rows), st.ctypes.data if st is not None else None, host.data_ptr(), host.numel(), offs)
         if used < 0:
             raise StepError({-1: "step metadata does not fit its buffer", -2: "a slot is not live",
                              -3: "pages are missing for an entry", -4: "a wanted position is out of range"}.get(used, f"assemble failed ({used})"))
+        if into is not None:
+            if into.numel() < used:
+                raise StepError("the graph's metadata buffer is smaller than the step's metadata")
+            dev = into
         dev[:used].copy_(host[:used], non_blocking=True)
         self._meta.sent(which)
+        self.h2d_bytes = int(used) * 4
 
         def view(k, n):
             return dev[offs[k]: offs[k] + n]
 
-        q_start_h = host[offs[3]: offs[3] + Bp + 1].numpy().copy()
-        ctx = StepContext(
+        return StepContext(
             dtype=self.dtype, device=self.device, num_tokens=Tp, num_entries=Bp,
             token_ids=view(0, Tp), positions=view(1, Tp), req_of_token=view(2, Tp),
             q_start=view(3, Bp + 1), start_pos=view(4, Bp), slots=view(5, Bp),
-            logit_rows=view(6, max(R, 1)), num_logit_rows=R,
+            logit_rows=view(6, Rp), num_logit_rows=max(R, pad_rows),
             tables=[dev[offs[7 + g]: offs[7 + g] + Bp * offs[7 + G + g]] for g in range(G)],
             strides=[int(offs[7 + G + g]) for g in range(G)],
-            err=self.err, workspace=self.workspace,
-            h_q_start=q_start_h, h_start_pos=starts.copy(), h_slots=slots.copy(),
+            err=self.err, workspace=workspace if workspace is not None else self.workspace,
+            h_q_start=host[offs[3]: offs[3] + Bp + 1].numpy().copy(), h_start_pos=starts, h_slots=slots,
             real_tokens=T, real_entries=B, max_context=longest, all_single=bool((counts == 1).all()),
         )
-        return ctx
+
+
+@dataclass
+class _DecodeGraph:
+    graph: torch.cuda.CUDAGraph
+    meta: torch.Tensor          # the device metadata buffer the graph reads
+    logits: torch.Tensor        # [bucket, vocab] float32, written by the graph
+    launches: int               # kernels of ours inside the graph
+
+
+def _bucket(n: int, cap: int) -> int:
+    b = 1
+    while b < n:
+        b *= 2
+    return min(b, max(cap, n))
 
 
 class ModelRunner:
-    def __init__(self, model_dir: str, dtype="bfloat16", *, block_size: int = 16,
+    def __init__(self, model_dir: Optional[str], dtype="bfloat16", *, block_size: int = 16,
                  num_blocks: Optional[int] = None, max_num_seqs: int = 32,
                  kv_fraction: float = 0.7, device="cuda:0", max_model_len: Optional[int] = None,
-                 model: Optional[DecoderModel] = None, plan=None):
+                 model: Optional[DecoderModel] = None):
         if not torch.cuda.is_available():
             raise StepError("no CUDA device: this engine runs on a B200 (sm_100a) only and has no CPU path")
         self.device = torch.device(device)
@@ -196,9 +224,7 @@ class ModelRunner:
         kernels.kernels_lib()  # build / load now, loudly
         if model is None:
             entry, cfg = load_config(model_dir)
-            self.config = cfg
-            plan = entry.plan_of(cfg)
-            model = DecoderModel(plan, self.dtype, self.device)
+            model = DecoderModel(entry.plan_of(cfg), self.dtype, self.device)
             store = WeightStore(model_dir)
             try:
                 model.load(store)
@@ -216,6 +242,23 @@ class ModelRunner:
         self.assembler = StepAssembler(self.cache, vocab_size=self.plan.vocab_size, max_model_len=self.max_model_len,
                                        dtype=self.dtype, device=self.device, workspace=self.workspace, err=self.err)
         self.steps_run = 0
+        self.last_launches = 0      # kernels of ours launched by the last step
+        self.last_used_graph = False
+        self._graphs: Dict[Tuple[int, Tuple[int, ...]], _DecodeGraph] = {}
+        self._graph_workspace: Optional[Workspace] = None
+        self._graph_pool = None
+
+    @classmethod
+    def random(cls, config_dict: Mapping[str, Any], seed: int, dtype="bfloat16", **kw) -> "ModelRunner":
+        """A runner over a model with random weights drawn on the device (nothing is written)."""
+        from ..weights.random_init import RandomWeightStore
+        device = kw.get("device", "cuda:0")
+        entry, cfg = config_from_dict(config_dict)
+        plan = entry.plan_of(cfg)
+        model = DecoderModel(plan, _dtype_of(dtype), device)
+        torch.cuda.set_device(torch.device(device))
+        model.load(RandomWeightStore(model_weight_specs(plan), seed, plan.init_std, plan.norm_init_std))
+        return cls(None, dtype, model=model, **kw)
 
     # ---- caches --------------------------------------------------------------------------------------
     def _build_caches(self, num_blocks: Optional[int], kv_fraction: float) -> None:
@@ -242,6 +285,7 @@ class ModelRunner:
             # no group needs more pages than every request at full length
             num_blocks = min(num_blocks, self.max_num_seqs * ((self.max_model_len + self.block_size - 1) // self.block_size))
         self.num_blocks = int(num_blocks)
+        self.kv_bytes_per_token = sum(page_bytes) // self.block_size
         groups = [CacheGroup(self.block_size, self.num_blocks, w) for w in keys] or [CacheGroup(self.block_size, 1, None)]
         self.cache = CacheManager(groups, self.max_num_seqs)
         self.layer_caches: List[Optional[LayerCache]] = [None] * len(runs)
@@ -263,6 +307,7 @@ class ModelRunner:
                 continue
             self.layer_states.append({name: self.state.add(f"run{pos}.{name}", shape, dt)
                                       for name, (shape, dt) in need.items()})
+        self.has_state = any(s is not None for s in self.layer_states)
 
     def kv_cache_tokens(self) -> int:
         return self.num_blocks * self.block_size
@@ -284,23 +329,83 @@ class ModelRunner:
         self.state.clear_slot(slot)
 
     # ---- the step --------------------------------------------------------------------------------------
-    def step(self, entries: Sequence[StepInput], *, pad_entries: int = 0, pad_tokens: int = 0,
-             strides: Optional[Sequence[int]] = None, allow_graph: bool = False) -> torch.Tensor:
+    def step(self, entries: Sequence[StepInput], *, allow_graph: bool = False) -> torch.Tensor:
         """Run one batch; returns float32 logits ``[wanted, vocab]`` on the device (a view of a
         reused buffer: copy what must outlive the next step)."""
-        ctx = self.prepare(entries, pad_entries=pad_entries, pad_tokens=pad_tokens, strides=strides)
+        if allow_graph and self._graph_eligible(entries):
+            return self._step_graph(entries)
+        before = kernels.launch_count()
+        ctx = self.assembler.prepare(entries)
         logits = self.model.forward(ctx, self.layer_caches, self.layer_states)
         self.finish(entries)
+        self.last_launches = kernels.launch_count() - before
+        self.last_used_graph = False
         return logits
-
-    def prepare(self, entries: Sequence[StepInput], *, pad_entries: int = 0, pad_tokens: int = 0,
-                strides: Optional[Sequence[int]] = None) -> StepContext:
-        return self.assembler.prepare(entries, pad_entries=pad_entries, pad_tokens=pad_tokens, strides=strides)
 
     def finish(self, entries: Sequence[StepInput]) -> None:
         for e in entries:
             self.cache.advance(e.slot, self.cache.length(e.slot) + len(e.tokens))
         self.steps_run += 1
+
+    # ---- decode steps from a CUDA graph ---------------------------------------------------------------
+    def _graph_eligible(self, entries: Sequence[StepInput]) -> bool:
+        if self.has_state or self.dtype != torch.bfloat16:
+            return False
+        for e in entries:
+            if len(e.tokens) != 1 or len(e.want) != 1:
+                return False
+        return True
+
+    def _graph_strides(self, entries: Sequence[StepInput]) -> Tuple[int, ...]:
+        longest = max(self.cache.length(e.slot) for e in entries) + 1
+        pages = (longest + self.block_size - 1) // self.block_size
+        s = 64
+        while s < pages:
+            s *= 2
+        return tuple(s for _ in self.cache.groups)
+
+    def _step_graph(self, entries: Sequence[StepInput]) -> torch.Tensor:
+        B = len(entries)
+        bucket = _bucket(B, self.max_num_seqs)
+        strides = self._graph_strides(entries)
+        key = (bucket, strides)
+        g = self._graphs.get(key)
+        if g is None:
+            g = self._capture(entries, bucket, strides)
+            self._graphs[key] = g
+        self.assembler.prepare(entries, pad_entries=bucket, pad_tokens=bucket, pad_rows=bucket, strides=strides,
+                               into=g.meta, workspace=self._graph_workspace)
+        g.graph.replay()
+        self.finish(entries)
+        self.last_launches = g.launches
+        self.last_used_graph = True
+        return g.logits[:B]
+
+    def _capture(self, entries: Sequence[StepInput], bucket: int, strides: Tuple[int, ...]) -> _DecodeGraph:
+        if self._graph_workspace is None:
+            self._graph_workspace = Workspace(self.device)
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        ws = self._graph_workspace
+        cap = 3 * (bucket + 4) + 3 * (bucket + 5) + bucket + 8 + sum(bucket * s + 4 for s in strides) + 64
+        meta = torch.zeros(cap, dtype=torch.int32, device=self.device)
+        kw = dict(pad_entries=bucket, pad_tokens=bucket, pad_rows=bucket, strides=strides, workspace=ws)
+        # size every buffer for the largest bucket first, so that no later capture moves them
+        if not getattr(ws, "sized", False):
+            ws.frozen = False
+            top = _bucket(self.max_num_seqs, self.max_num_seqs)
+            big = self.assembler.prepare(entries, pad_entries=top, pad_tokens=top, pad_rows=top, strides=strides, workspace=ws)
+            self.model.forward(big, self.layer_caches, self.layer_states)
+            ws.sized = True
+            ws.frozen = True
+        ctx = self.assembler.prepare(entries, into=meta, **kw)
+        self.model.forward(ctx, self.layer_caches, self.layer_states)   # warm-up on this stream
+        torch.cuda.current_stream().synchronize()
+        graph = torch.cuda.CUDAGraph()
+        before = kernels.launch_count()
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            logits = self.model.forward(ctx, self.layer_caches, self.layer_states)
+        launches = kernels.launch_count() - before
+        return _DecodeGraph(graph, meta, logits, launches)
 
     # ---- errors the kernels reported ---------------------------------------------------------------------
     def queue_error_check(self) -> None:
@@ -319,7 +424,4 @@ class ModelRunner:
         """Synchronises and raises if any kernel has set the device error word since the last check."""
         self._err_host.copy_(self.err, non_blocking=True)
         torch.cuda.current_stream().synchronize()
-        word = int(self._err_host[0])
-        if word:
-            self.err.zero_()
-            raise StepError("a kernel reported: " + kernels.describe_error(word))
+        self.raise_if_error()

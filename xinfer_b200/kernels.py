@@ -48,9 +48,19 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def _ok(status: int, what: str) -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this engine launched so far by this process (captured launches included)."""
+    return _launches
+
+
+def _ok(status: int, what: str, n: int = 1) -> None:
+    global _launches
     if status != 0:
         raise KernelError(f"{what}: CUDA error {status} at launch")
+    _launches += n
 
 
 # device-side error word -------------------------------------------------------------------------
@@ -206,4 +216,4 @@ def sample(out_tokens, logits, params_dev, history_dev, apply_penalties: bool):
     if params_dev.numel() < R * SAMPLE_PARAMS.itemsize or out_tokens.numel() < R:
         raise KernelError("sampler buffers are smaller than the number of rows")
     _ok(lib.xb_sample(out_tokens.data_ptr(), logits.data_ptr(), params_dev.data_ptr(), _ptr(history_dev), R, V,
-                      int(bool(apply_penalties)), _stream()), "sample")
+                      int(bool(apply_penalties)), _stream()), "sample", 2 if apply_penalties else 1)

@@ -76,3 +76,36 @@ def write_random_model(model_dir: str, config_dict: Mapping[str, Any], seed: int
     with open(os.path.join(model_dir, "config.json"), "w", encoding="utf-8") as f:
         json.dump(dict(config_dict), f, indent=1)
     return model_dir
+
+
+class RandomWeightStore:
+    """Stands where a ``WeightStore`` stands, but draws every tensor on the target device instead
+    of reading a file: a model of any size with random weights and nothing written to disk."""
+
+    def __init__(self, specs: Sequence[WeightSpec], seed: int, std: float = 0.02, norm_std: float = 0.1):
+        self.specs = {s.name: s for s in specs}
+        self.seed = int(seed)
+        self.std = std
+        self.norm_std = norm_std
+
+    def names(self) -> List[str]:
+        return sorted(self.specs)
+
+    def check(self, specs: Sequence[WeightSpec]) -> None:
+        from .loader import WeightError
+        want = {s.name: tuple(s.shape) for s in specs}
+        missing = sorted(n for n in want if n not in self.specs)
+        unexpected = sorted(n for n in self.specs if n not in want)
+        wrong = [(n, self.specs[n].shape, want[n]) for n in sorted(want) if n in self.specs and tuple(self.specs[n].shape) != want[n]]
+        if missing or unexpected or wrong:
+            raise WeightError(missing, unexpected, wrong)
+
+    def get(self, name: str, device, compute_dtype: torch.dtype) -> torch.Tensor:
+        spec = self.specs[name]
+        target = torch.float32 if compute_dtype == torch.float32 else torch.bfloat16
+        dev = torch.device(device)
+        gen_dev = dev if dev.type == "cuda" else "cpu"
+        return draw(spec, self.seed, self.std, self.norm_std, target, device=gen_dev).to(dev).contiguous()
+
+    def close(self) -> None:
+        pass
