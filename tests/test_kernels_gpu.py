@@ -286,3 +286,72 @@ def far_key_checks(kernel, dtype):
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_attention_plain_sees_one_far_key_and_the_windows_edge(dtype):
     far_key_checks(plain_kernel, dtype)
+
+
+# ---- the tensor-core attention kernels (bfloat16) through the backend that picks them -------------
+def tiled_kernel(out, q, kc, vc, pos, req, table, stride, window, scale, e, entries):
+    from types import SimpleNamespace
+    from xinfer_b200.parts import LayerCache, Workspace
+    from xinfer_b200.parts import attention_backend
+    counts = [c for _, c in entries]
+    q_start = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    to = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device=dev())
+    ctx = SimpleNamespace(positions=pos, req_of_token=req, q_start=to(q_start), start_pos=to([s for s, _ in entries]),
+                          num_entries=len(entries), num_tokens=int(q_start[-1]), h_q_start=q_start, real_entries=len(entries),
+                          max_context=max(s + c for s, c in entries), fixed_shapes=False, scratch={},
+                          workspace=Workspace(dev()), err=e)
+    cache = LayerCache(kc, vc, 0, kc.shape[2])
+    attention_backend.attend(out, q, cache, ctx, table, stride, window, scale)
+
+
+TILED_CASES = CASES + [
+    (32, 8, 128, 16, [(0, 200), (1000, 1), (130, 3), (64, 64), (511, 2)], None),     # 8B head layout, mixed batch
+    (16, 8, 128, 16, [(0, 70), (700, 1)], 100),
+    (4, 4, 16, 8, [(0, 65), (3, 130)], None),
+    (12, 2, 96, 16, [(250, 1), (256, 1), (255, 1), (0, 1)], None),                  # range edges of the decode kernel
+    (40, 2, 32, 16, [(513, 1), (20, 150)], 300),                                   # 20 query heads per kv head: two row tiles
+    (5, 5, 256, 16, [(0, 90), (300, 1)], None),
+    (8, 2, 112, 32, [(77, 4), (0, 5), (1023, 1)], 512),
+]
+
+
+@pytest.mark.parametrize("nh,nkv,d,ps,entries,window", TILED_CASES)
+def test_attention_tiled_bf16(nh, nkv, d, ps, entries, window):
+    worst = attention_case(tiled_kernel, torch.bfloat16, nh, nkv, d, ps, entries, window)
+    assert worst <= tol(torch.bfloat16, 2), worst
+
+
+def test_attention_tiled_sees_one_far_key_and_the_windows_edge():
+    far_key_checks(tiled_kernel, torch.bfloat16)
+
+
+def test_attention_tiled_far_key_in_a_long_prompt_portion():
+    """The same planted key, but seen from the prefill kernel: a 70-token portion starting at 400."""
+    nh, nkv, d, ps = 4, 2, 64, 16
+    for win, far, visible in ((None, 5, True), (128, 400 + 69 - 128 + 1, True), (128, 400 + 69 - 128, False)):
+        def plant(b, s, c, q, k, v, far=far):
+            qd = q[69, 0, :].float()                   # the last query of the portion, head 0
+            k[far] = 0
+            k[far, 0] = (qd / qd.norm() * 60).to(k.dtype)
+            v[far] = 7.0
+        worst, out = attention_case(tiled_kernel, torch.bfloat16, nh, nkv, d, ps, [(400, 70)], win, plant=plant, seed=11, want_out=True)
+        assert worst <= tol(torch.bfloat16, 8), (win, far, worst)
+        if visible:
+            assert (out[69, 0].float() - 7.0).abs().max() < 0.1
+        else:
+            assert (out[69, 0].float() - 7.0).abs().min() > 3.0
+
+
+def test_attention_tiled_refuses_what_it_cannot_do():
+    from xinfer_b200 import kernels
+    assert not kernels.attn_tiled_supported(torch.bfloat16, 40)
+    assert not kernels.attn_tiled_supported(torch.bfloat16, 272)
+    assert not kernels.attn_tiled_supported(torch.float32, 64)
+    q = torch.zeros(2, 4, 40, dtype=torch.bfloat16, device=dev())
+    kc = torch.zeros(4, 2, 16, 40, dtype=torch.bfloat16, device=dev())
+    z = torch.zeros(4, dtype=torch.int32, device=dev())
+    with pytest.raises(kernels.KernelError, match="head size"):
+        kernels.attn_prefill_bf16(q.clone(), q, kc, kc.clone(), z, z, 1, z, 4, None, 1.0, 4, 1, err_word())
+    # head size 40 still runs: the backend hands it to the plain kernel
+    worst = attention_case(tiled_kernel, torch.bfloat16, 4, 2, 40, 16, [(0, 30), (50, 1)], None)
+    assert worst <= tol(torch.bfloat16, 2)

@@ -1,0 +1,536 @@
+// bfloat16 attention over the paged cache on tensor cores (mma.sync m16n8k16, float32 scores,
+// softmax and accumulation), for head sizes that are multiples of 16 up to 256.
+//
+//  * attn_prefill_kernel: one CTA per (64 queries of one request's portion, query head); keys and
+//    values stream through shared memory in tiles of 64 positions fetched page by page with
+//    cp.async; causal mask, optional window, running softmax.
+//  * attn_decode_kernel: for requests that bring only a few tokens.  One CTA per (token, key/value
+//    head, range of 256 key positions): the query heads that share the key/value head form the rows
+//    of the tile, four warps take 16 keys each of every 64-key tile.  Ranges are cut at absolute
+//    positions, so a token's partition never depends on what else is in the batch.  With more
+//    than one range the CTAs write normalised partial outputs and (max, sum) to scratch memory and
+//    attn_combine_kernel merges them.
+//
+// Cache layout: [num_pages, kv_heads, page_size, head_dim]; any page size.
+// Keys a query at position p may see: max(0, p - window + 1) .. p  (window <= 0: from 0).
+// Rows of a tile that lie outside a request's keys are zero-filled, never read from memory, so
+// stale or poisoned pages cannot reach a result.
+#include "common.cuh"
+
+namespace {
+
+constexpr int KT = 64;        // key positions per shared-memory tile
+constexpr int QT = 64;        // queries per CTA in the prefill kernel
+constexpr int THREADS = 128;  // four warps
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Byte offset of 16-byte chunk c of row r in a [rows][DP] bf16 tile whose chunks are XOR-swizzled
+// with the row, so that ldmatrix reads of 8 rows hit 8 different banks groups.
+template <int DP>
+__device__ __forceinline__ uint32_t tile_off(int r, int c) { return (uint32_t)(r * DP * 2 + ((c ^ (r & 7)) << 4)); }
+
+// Fetch rows key0 .. key0+KT-1 of key/value head g into a tile; rows outside [lo, hi] and columns
+// beyond d are zero-filled.
+template <int DP>
+__device__ __forceinline__ void load_kv_tile(uint32_t tile, const __nv_bfloat16* __restrict__ cache,
+                                             const int* __restrict__ table, int num_pages, int nkv, int g,
+                                             int ps, int d, int key0, int lo, int hi, int* err) {
+    constexpr int CPR = DP / 8;
+    for (int idx = threadIdx.x; idx < KT * CPR; idx += THREADS) {
+        const int r = idx / CPR, c = idx % CPR;
+        const int j = key0 + r;
+        bool ok = j >= lo && j <= hi && c * 8 < d;
+        const __nv_bfloat16* src = cache;
+        if (ok) {
+            const int page = table[j / ps];
+            if (page < 0 || page >= num_pages) {
+                ok = false;
+                atomicOr(err, XB_ERR_BAD_PAGE);
+            } else {
+                src = cache + (((size_t)page * nkv + g) * ps + (j % ps)) * d + c * 8;
+            }
+        }
+        cp_async16(tile + tile_off<DP>(r, c), src, ok ? 16 : 0);
+    }
+}
+
+// Fetch `rows` query rows (row r = query vector at qbase + r * row_stride elements when valid[r])
+template <int DP, int ROWS>
+__device__ __forceinline__ void load_q_tile(uint32_t tile, const __nv_bfloat16* __restrict__ qbase,
+                                            size_t row_stride, int valid_rows, int d) {
+    constexpr int CPR = DP / 8;
+    for (int idx = threadIdx.x; idx < ROWS * CPR; idx += THREADS) {
+        const int r = idx / CPR, c = idx % CPR;
+        const bool ok = r < valid_rows && c * 8 < d;
+        cp_async16(tile + tile_off<DP>(r, c), ok ? qbase + r * row_stride + c * 8 : qbase, ok ? 16 : 0);
+    }
+}
+
+// S[16 x NK keys] += Q[16 x DP] . K[NK x DP]^T for one warp.  q_tile/k_tile: shared addresses of
+// the tiles, q_row0/k_row0 the first row of the warp's slice.
+template <int DP, int NK>
+__device__ __forceinline__ void warp_qk(float (&s)[NK / 8][4], uint32_t q_tile, int q_row0, uint32_t k_tile, int k_row0) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int ks = 0; ks < DP / 16; ++ks) {
+        uint32_t a[4];
+        ldmatrix_x4(a, q_tile + tile_off<DP>(q_row0 + (lane & 15), ks * 2 + (lane >> 4)));
+#pragma unroll
+        for (int nb = 0; nb < NK / 16; ++nb) {
+            uint32_t b[4];
+            const int mid = lane >> 3;
+            ldmatrix_x4(b, k_tile + tile_off<DP>(k_row0 + nb * 16 + (mid >> 1) * 8 + (lane & 7), ks * 2 + (mid & 1)));
+            mma_bf16(s[nb * 2], a, b[0], b[1]);
+            mma_bf16(s[nb * 2 + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+// O[16 x DP] += P[16 x NK] . V[NK x DP] for one warp; P comes from the score accumulators.
+template <int DP, int NK>
+__device__ __forceinline__ void warp_pv(float (&o)[DP / 8][4], const float (&p)[NK / 8][4], uint32_t v_tile, int v_row0) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int kb = 0; kb < NK / 16; ++kb) {
+        uint32_t a[4];
+        a[0] = pack_bf16(p[kb * 2][0], p[kb * 2][1]);
+        a[1] = pack_bf16(p[kb * 2][2], p[kb * 2][3]);
+        a[2] = pack_bf16(p[kb * 2 + 1][0], p[kb * 2 + 1][1]);
+        a[3] = pack_bf16(p[kb * 2 + 1][2], p[kb * 2 + 1][3]);
+#pragma unroll
+        for (int nb = 0; nb < DP / 16; ++nb) {
+            uint32_t b[4];
+            const int mid = lane >> 3;
+            ldmatrix_x4_trans(b, v_tile + tile_off<DP>(v_row0 + kb * 16 + (mid & 1) * 8 + (lane & 7), nb * 2 + (mid >> 1)));
+            mma_bf16(o[nb * 2], a, b[0], b[1]);
+            mma_bf16(o[nb * 2 + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+// Which token the z-th "small" token of the batch is: tokens of entries that bring at most
+// dec_max tokens, in batch order.  -1 if there is none.
+__device__ __forceinline__ int small_token(int z, const int* __restrict__ q_start, int num_entries, int dec_max, int direct) {
+    if (direct) return z < q_start[num_entries] ? z : -1;
+    int acc = 0;
+    for (int b = 0; b < num_entries; ++b) {
+        const int n = q_start[b + 1] - q_start[b];
+        if (n > 0 && n <= dec_max) {
+            if (z < acc + n) return q_start[b] + z - acc;
+            acc += n;
+        }
+    }
+    return -1;
+}
+
+// ------------------------------------------------------------------------------------------------
+// prefill
+// ------------------------------------------------------------------------------------------------
+template <int DP>
+__global__ void __launch_bounds__(THREADS)
+attn_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ q,
+                    const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
+                    const int* __restrict__ q_start, const int* __restrict__ start_pos, int num_entries,
+                    const int* __restrict__ block_table, int table_stride, int nh, int nkv, int d, int ps,
+                    int num_pages, int window, float scale_log2, int dec_max, int* err) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ int s_entry, s_tile;
+    constexpr int TILE_BYTES = KT * DP * 2;
+    const uint32_t q_tile = smem_addr(smem_raw);
+    const uint32_t kv_base = q_tile + QT * DP * 2;  // stages: [K0][V0][K1][V1]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.y, g = h / (nh / nkv);
+
+    if (threadIdx.x == 0) {
+        int acc = 0, found = -1, tile = 0;
+        for (int b = 0; b < num_entries; ++b) {
+            const int n = q_start[b + 1] - q_start[b];
+            if (n > dec_max) {
+                const int nt = (n + QT - 1) / QT;
+                if ((int)blockIdx.x < acc + nt) {
+                    found = b;
+                    tile = blockIdx.x - acc;
+                    break;
+                }
+                acc += nt;
+            }
+        }
+        s_entry = found;
+        s_tile = tile;
+    }
+    __syncthreads();
+    const int b = s_entry;
+    if (b < 0) return;
+    const int n = q_start[b + 1] - q_start[b];
+    const int row0 = s_tile * QT;                     // first query of this tile within the portion
+    const int rows = min(QT, n - row0);
+    const int t0 = q_start[b] + row0;                 // its token index
+    const int p0 = start_pos[b] + row0;               // its position
+    const int last_key = p0 + rows - 1;               // newest key any row of the tile may see
+    const int first_key = window > 0 ? max(0, p0 - window + 1) : 0;
+    const int* table = block_table + (size_t)b * table_stride;
+
+    load_q_tile<DP, QT>(q_tile, q + ((size_t)t0 * nh + h) * d, (size_t)nh * d, rows, d);
+    const int kt_first = first_key / KT, kt_last = last_key / KT;
+    load_kv_tile<DP>(kv_base, kc, table, num_pages, nkv, g, ps, d, kt_first * KT, first_key, last_key, err);
+    load_kv_tile<DP>(kv_base + TILE_BYTES, vc, table, num_pages, nkv, g, ps, d, kt_first * KT, first_key, last_key, err);
+    cp_async_commit();
+
+    float o[DP / 8][4];
+#pragma unroll
+    for (int i = 0; i < DP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const int pr[2] = {p0 + warp * 16 + (lane >> 2), p0 + warp * 16 + (lane >> 2) + 8};  // positions of this lane's two rows
+
+    for (int kt = kt_first; kt <= kt_last; ++kt) {
+        const int stage = (kt - kt_first) & 1;
+        if (kt < kt_last) {
+            const uint32_t nxt = kv_base + (stage ^ 1) * 2 * TILE_BYTES;
+            load_kv_tile<DP>(nxt, kc, table, num_pages, nkv, g, ps, d, (kt + 1) * KT, first_key, last_key, err);
+            load_kv_tile<DP>(nxt + TILE_BYTES, vc, table, num_pages, nkv, g, ps, d, (kt + 1) * KT, first_key, last_key, err);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const uint32_t k_tile = kv_base + stage * 2 * TILE_BYTES, v_tile = k_tile + TILE_BYTES;
+        const int key0 = kt * KT;
+        // rows of this warp see nothing of the tile: keys all newer than its last row, or all older than its window
+        const int w_last = p0 + warp * 16 + 15, w_first = p0 + warp * 16;
+        const bool skip = key0 > w_last || (window > 0 && key0 + KT - 1 < w_first - window + 1);
+        if (!skip) {
+            float s[KT / 8][4];
+#pragma unroll
+            for (int i = 0; i < KT / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+            warp_qk<DP, KT>(s, q_tile, warp * 16, k_tile, 0);
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < KT / 8; ++i) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = key0 + i * 8 + (lane & 3) * 2 + (e & 1);
+                    const int p = pr[e >> 1];
+                    const bool ok = j <= p && j <= last_key && (window <= 0 || j > p - window);
+                    const float v = ok ? s[i][e] * scale_log2 : -INFINITY;
+                    s[i][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                const float m_new = fmaxf(m[r], mx[r]);
+                const float m_use = m_new == -INFINITY ? 0.f : m_new;
+                const float corr = exp2f(m[r] - m_use);
+                m[r] = m_new;
+                l[r] *= corr;
+#pragma unroll
+                for (int i = 0; i < DP / 8; ++i) {
+                    o[i][r * 2] *= corr;
+                    o[i][r * 2 + 1] *= corr;
+                }
+                float sum = 0.f;
+#pragma unroll
+                for (int i = 0; i < KT / 8; ++i) {
+                    const float a = exp2f(s[i][r * 2] - m_use), c = exp2f(s[i][r * 2 + 1] - m_use);
+                    s[i][r * 2] = a;
+                    s[i][r * 2 + 1] = c;
+                    sum += a + c;
+                }
+                l[r] += sum;
+            }
+            warp_pv<DP, KT>(o, s, v_tile, 0);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+        const int row = warp * 16 + (lane >> 2) + r * 8;
+        if (row >= rows) continue;
+        const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+        __nv_bfloat16* dst = out + ((size_t)(t0 + row) * nh + h) * d;
+#pragma unroll
+        for (int i = 0; i < DP / 8; ++i) {
+            const int c = i * 8 + (lane & 3) * 2;
+            if (c < d) *reinterpret_cast<uint32_t*>(dst + c) = pack_bf16(o[i][r * 2] * inv, o[i][r * 2 + 1] * inv);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// decode (few tokens per request), split over key ranges
+// ------------------------------------------------------------------------------------------------
+template <int DP>
+__global__ void __launch_bounds__(THREADS)
+attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                   const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
+                   const __nv_bfloat16* __restrict__ vc, const int* __restrict__ positions,
+                   const int* __restrict__ req_of_token, const int* __restrict__ q_start, int num_entries,
+                   const int* __restrict__ block_table, int table_stride, int nh, int nkv, int d, int ps,
+                   int num_pages, int window, float scale_log2, int dec_max, int direct, int split,
+                   int num_splits, int* err) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ float s_m[4][16], s_l[4][16];
+    constexpr int TILE_BYTES = KT * DP * 2;
+    const uint32_t q_tile = smem_addr(smem_raw);
+    const uint32_t kv_base = q_tile + 16 * DP * 2;
+    float* o_all = reinterpret_cast<float*>(smem_raw + 16 * DP * 2);  // reused after the loop: [4][16][DP]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = nh / nkv;
+    const int qtiles = (G + 15) / 16;
+    const int g = blockIdx.y / qtiles, qt = blockIdx.y % qtiles;
+    const int t = small_token(blockIdx.z, q_start, num_entries, dec_max, direct);
+    if (t < 0) return;
+    const int b = req_of_token[t];
+    if (b < 0) return;
+    const int pos = positions[t];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int k_begin = max(lo, (int)blockIdx.x * split), k_end = min(pos, ((int)blockIdx.x + 1) * split - 1);
+    if (k_begin > k_end) return;
+    const int* table = block_table + (size_t)b * table_stride;
+    const int h0 = g * G + qt * 16;
+    const int rows = min(16, G - qt * 16);
+
+    load_q_tile<DP, 16>(q_tile, q + ((size_t)t * nh + h0) * d, (size_t)d, rows, d);
+    const int kt_first = k_begin / KT, kt_last = k_end / KT;
+    load_kv_tile<DP>(kv_base, kc, table, num_pages, nkv, g, ps, d, kt_first * KT, k_begin, k_end, err);
+    load_kv_tile<DP>(kv_base + TILE_BYTES, vc, table, num_pages, nkv, g, ps, d, kt_first * KT, k_begin, k_end, err);
+    cp_async_commit();
+
+    float o[DP / 8][4];
+#pragma unroll
+    for (int i = 0; i < DP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    for (int kt = kt_first; kt <= kt_last; ++kt) {
+        const int stage = (kt - kt_first) & 1;
+        if (kt < kt_last) {
+            const uint32_t nxt = kv_base + (stage ^ 1) * 2 * TILE_BYTES;
+            load_kv_tile<DP>(nxt, kc, table, num_pages, nkv, g, ps, d, (kt + 1) * KT, k_begin, k_end, err);
+            load_kv_tile<DP>(nxt + TILE_BYTES, vc, table, num_pages, nkv, g, ps, d, (kt + 1) * KT, k_begin, k_end, err);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const uint32_t k_tile = kv_base + stage * 2 * TILE_BYTES, v_tile = k_tile + TILE_BYTES;
+        const int key0 = kt * KT + warp * 16;  // this warp's 16 keys of the tile
+        if (key0 <= k_end && key0 + 15 >= k_begin) {
+            float s[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+            warp_qk<DP, 16>(s, q_tile, 0, k_tile, warp * 16);
+            float mx = -INFINITY;  // every row of the tile is the same token: one key range for all
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = key0 + i * 8 + (lane & 3) * 2 + (e & 1);
+                    s[i][e] = (j >= k_begin && j <= k_end) ? s[i][e] * scale_log2 : -INFINITY;
+                }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                mx = fmaxf(fmaxf(s[0][r * 2], s[0][r * 2 + 1]), fmaxf(s[1][r * 2], s[1][r * 2 + 1]));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                const float m_new = fmaxf(m[r], mx);
+                const float m_use = m_new == -INFINITY ? 0.f : m_new;
+                const float corr = exp2f(m[r] - m_use);
+                m[r] = m_new;
+                l[r] *= corr;
+#pragma unroll
+                for (int i = 0; i < DP / 8; ++i) {
+                    o[i][r * 2] *= corr;
+                    o[i][r * 2 + 1] *= corr;
+                }
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const float a = exp2f(s[i][r * 2] - m_use), c = exp2f(s[i][r * 2 + 1] - m_use);
+                    s[i][r * 2] = a;
+                    s[i][r * 2 + 1] = c;
+                    l[r] += a + c;
+                }
+            }
+            warp_pv<DP, 16>(o, s, v_tile, warp * 16);
+        }
+        __syncthreads();
+    }
+    // merge the four warps (each saw its own keys)
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+        const int row = (lane >> 2) + r * 8;
+        if ((lane & 3) == 0) {
+            s_m[warp][row] = m[r];
+            s_l[warp][row] = l[r];
+        }
+#pragma unroll
+        for (int i = 0; i < DP / 8; ++i) {
+            const int c = i * 8 + (lane & 3) * 2;
+            float* dst = o_all + ((size_t)warp * 16 + row) * DP + c;
+            dst[0] = o[i][r * 2];
+            dst[1] = o[i][r * 2 + 1];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < rows * d; idx += THREADS) {
+        const int row = idx / d, c = idx % d;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, s_m[w][row]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float f = s_m[w][row] == -INFINITY ? 0.f : exp2f(s_m[w][row] - M);
+            L += s_l[w][row] * f;
+            O += o_all[((size_t)w * 16 + row) * DP + c] * f;
+        }
+        const float val = L > 0.f ? O / L : 0.f;
+        const int h = h0 + row;
+        if (num_splits == 1) {
+            out[((size_t)t * nh + h) * d + c] = __float2bfloat16_rn(val);
+        } else {
+            const size_t slot = ((size_t)blockIdx.z * nh + h) * num_splits + blockIdx.x;  // by the token's rank among the small ones
+            part_o[slot * d + c] = val;
+            if (c == 0) {
+                part_ml[slot * 2] = M;
+                part_ml[slot * 2 + 1] = L;
+            }
+        }
+    }
+}
+
+// out[t, h] = sum_s w_s O_s / sum_s w_s with w_s = L_s * 2^(M_s - max M) over the key ranges the
+// token's keys touch (the same ranges the decode kernel worked on).  One warp per (token, head).
+__global__ void attn_combine_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
+                                    const float* __restrict__ part_ml, const int* __restrict__ positions,
+                                    const int* __restrict__ req_of_token, const int* __restrict__ q_start,
+                                    int num_entries, int nh, int d, int window, int dec_max, int direct,
+                                    int split, int num_splits) {
+    const int lane = threadIdx.x & 31;
+    const int h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (h >= nh) return;
+    const int t = small_token(blockIdx.x, q_start, num_entries, dec_max, direct);
+    if (t < 0 || req_of_token[t] < 0) return;
+    const int pos = positions[t];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int s0 = lo / split, s1 = pos / split;
+    const size_t base = ((size_t)blockIdx.x * nh + h) * num_splits;
+    float M = -INFINITY;
+    for (int s = s0; s <= s1; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+    float W = 0.f;
+    for (int s = s0; s <= s1; ++s) W += part_ml[(base + s) * 2 + 1] * exp2f(part_ml[(base + s) * 2] - M);
+    const float inv = W > 0.f ? 1.f / W : 0.f;
+    for (int c = lane; c < d; c += 32) {
+        float acc = 0.f;
+        for (int s = s0; s <= s1; ++s)
+            acc += part_o[(base + s) * d + c] * (part_ml[(base + s) * 2 + 1] * exp2f(part_ml[(base + s) * 2] - M));
+        out[((size_t)t * nh + h) * d + c] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+template <int DP>
+int launch_prefill(void* out, const void* q, const void* kc, const void* vc, const int* q_start, const int* start_pos,
+                   int num_entries, const int* table, int stride, int nh, int nkv, int d, int ps, int num_pages,
+                   int window, float scale_log2, int dec_max, int tiles, int* err, cudaStream_t stream) {
+    const size_t smem = (size_t)QT * DP * 2 + 4 * KT * DP * 2;
+    cudaFuncSetAttribute(attn_prefill_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attn_prefill_kernel<DP><<<dim3(tiles, nh), THREADS, smem, stream>>>(
+        (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, q_start,
+        start_pos, num_entries, table, stride, nh, nkv, d, ps, num_pages, window, scale_log2, dec_max, err);
+    return xb_launch_status();
+}
+
+template <int DP>
+int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const void* kc, const void* vc,
+                  const int* positions, const int* req_of_token, const int* q_start, int num_entries, const int* table,
+                  int stride, int nh, int nkv, int d, int ps, int num_pages, int window, float scale_log2, int dec_max,
+                  int direct, int split, int num_splits, int tokens, int* err, cudaStream_t stream) {
+    const size_t kv = 4 * (size_t)KT * DP * 2, merge = 4 * 16 * (size_t)DP * 4;
+    const size_t smem = 16 * DP * 2 + (kv > merge ? kv : merge);
+    cudaFuncSetAttribute(attn_decode_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const int qtiles = (nh / nkv + 15) / 16;
+    attn_decode_kernel<DP><<<dim3(num_splits, nkv * qtiles, tokens), THREADS, smem, stream>>>(
+        (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc,
+        positions, req_of_token, q_start, num_entries, table, stride, nh, nkv, d, ps, num_pages, window, scale_log2,
+        dec_max, direct, split, num_splits, err);
+    return xb_launch_status();
+}
+
+}  // namespace
+
+// Key positions per range of the decode kernel (a multiple of the 64-key tile).
+XB_EXPORT int xb_attn_decode_split() { return 256; }
+
+// Portions of more than dec_max tokens; `tiles` = sum over those portions of ceil(tokens / 64).
+XB_EXPORT int xb_attn_prefill_bf16(void* out, const void* q, const void* kc, const void* vc, const int* q_start,
+                                   const int* start_pos, int num_entries, const int* table, int stride, int nh,
+                                   int nkv, int d, int ps, int num_pages, int window, float scale, int dec_max,
+                                   int tiles, int* err, cudaStream_t stream) {
+    if (tiles <= 0) return 0;
+    if (d % 16 || d > 256 || nh % nkv) return (int)cudaErrorInvalidValue;
+    const float sl2 = scale * 1.4426950408889634f;
+#define XB_GO(DP) return launch_prefill<DP>(out, q, kc, vc, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, num_pages, window, sl2, dec_max, tiles, err, stream)
+    if (d <= 64) XB_GO(64);
+    if (d <= 128) XB_GO(128);
+    XB_GO(256);
+#undef XB_GO
+}
+
+// Tokens of portions of at most dec_max tokens (`tokens` of them; direct != 0: every token of the
+// batch is one).  part_o: [tokens, nh, num_splits, d] float32, part_ml: [tokens, nh, num_splits, 2]; both may
+// be null when num_splits == 1.  num_splits = ceil(longest context / xb_attn_decode_split()).
+XB_EXPORT int xb_attn_decode_bf16(void* out, float* part_o, float* part_ml, const void* q, const void* kc,
+                                  const void* vc, const int* positions, const int* req_of_token, const int* q_start,
+                                  int num_entries, const int* table, int stride, int nh, int nkv, int d, int ps,
+                                  int num_pages, int window, float scale, int dec_max, int direct, int num_splits,
+                                  int tokens, int* err, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (d % 16 || d > 256 || nh % nkv || num_splits < 1) return (int)cudaErrorInvalidValue;
+    if (num_splits > 1 && (!part_o || !part_ml)) return (int)cudaErrorInvalidValue;
+    const float sl2 = scale * 1.4426950408889634f;
+    const int split = xb_attn_decode_split();
+    int rc;
+#define XB_GO(DP) rc = launch_decode<DP>(out, part_o, part_ml, q, kc, vc, positions, req_of_token, q_start, num_entries, table, stride, nh, nkv, d, ps, num_pages, window, sl2, dec_max, direct, split, num_splits, tokens, err, stream)
+    if (d <= 64) XB_GO(64);
+    else if (d <= 128) XB_GO(128);
+    else XB_GO(256);
+#undef XB_GO
+    if (rc != 0 || num_splits == 1) return rc;
+    attn_combine_kernel<<<dim3(tokens, (nh + 3) / 4), 128, 0, stream>>>(
+        (__nv_bfloat16*)out, part_o, part_ml, positions, req_of_token, q_start, num_entries, nh, d, window, dec_max,
+        direct, split, num_splits);
+    return xb_launch_status();
+}

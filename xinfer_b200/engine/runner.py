@@ -190,6 +190,7 @@ class StepAssembler:
             err=self.err, workspace=workspace if workspace is not None else self.workspace,
             h_q_start=host[offs[3]: offs[3] + Bp + 1].numpy().copy(), h_start_pos=starts, h_slots=slots,
             real_tokens=T, real_entries=B, max_context=longest, all_single=bool((counts == 1).all()),
+            fixed_shapes=into is not None,
         )
 
 
@@ -393,8 +394,17 @@ class ModelRunner:
         if not getattr(ws, "sized", False):
             ws.frozen = False
             top = _bucket(self.max_num_seqs, self.max_num_seqs)
-            big = self.assembler.prepare(entries, pad_entries=top, pad_tokens=top, pad_rows=top, strides=strides, workspace=ws)
+            widest = 64
+            while widest * self.block_size < self.max_model_len:
+                widest *= 2
+            wide = tuple(widest for _ in strides)
+            tmp = torch.zeros(3 * (top + 4) + 3 * (top + 5) + top + 8 + sum(top * s + 4 for s in wide) + 64,
+                              dtype=torch.int32, device=self.device)
+            big = self.assembler.prepare(entries, pad_entries=top, pad_tokens=top, pad_rows=top, strides=wide,
+                                         into=tmp, workspace=ws)
             self.model.forward(big, self.layer_caches, self.layer_states)
+            torch.cuda.current_stream().synchronize()
+            del tmp
             ws.sized = True
             ws.frozen = True
         ctx = self.assembler.prepare(entries, into=meta, **kw)

@@ -217,3 +217,58 @@ def sample(out_tokens, logits, params_dev, history_dev, apply_penalties: bool):
         raise KernelError("sampler buffers are smaller than the number of rows")
     _ok(lib.xb_sample(out_tokens.data_ptr(), logits.data_ptr(), params_dev.data_ptr(), _ptr(history_dev), R, V,
                       int(bool(apply_penalties)), _stream()), "sample", 2 if apply_penalties else 1)
+
+
+# ---- bfloat16 attention on tensor cores ------------------------------------------------------------
+def attn_tiled_supported(dtype, head_dim: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256
+
+
+def attn_decode_split() -> int:
+    return kernels_lib().xb_attn_decode_split()
+
+
+def attn_prefill_bf16(out, q, k_cache, v_cache, q_start, start_pos, num_entries, block_table, table_stride,
+                      window, scale, dec_max, tiles, err):
+    """Portions of more than ``dec_max`` tokens; ``tiles`` = sum of ceil(tokens / 64) over them."""
+    T, nh, d = q.shape
+    _need(q, "q", torch.bfloat16, (T, nh, d))
+    _need(out, "out", torch.bfloat16, (T, nh, d))
+    _need(k_cache, "k_cache", torch.bfloat16, (None, None, None, d))
+    _need(v_cache, "v_cache", torch.bfloat16, tuple(k_cache.shape))
+    num_pages, nkv, ps, _ = k_cache.shape
+    if not attn_tiled_supported(q.dtype, d) or nh % nkv:
+        raise KernelError(f"tiled attention needs bfloat16, a head size in steps of 16 up to 256 and heads divisible "
+                          f"by key/value heads; got head size {d}, {nh}/{nkv} heads")
+    _ok(kernels_lib().xb_attn_prefill_bf16(
+        out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), q_start.data_ptr(), start_pos.data_ptr(),
+        int(num_entries), block_table.data_ptr(), int(table_stride), nh, nkv, d, ps, num_pages, int(window or 0),
+        float(scale), int(dec_max), int(tiles), err.data_ptr(), _stream()), "attn_prefill_bf16")
+
+
+def attn_decode_bf16(out, part_o, part_ml, q, k_cache, v_cache, positions, req_of_token, q_start, num_entries,
+                     block_table, table_stride, window, scale, dec_max, direct, num_splits, tokens, err):
+    """Tokens of portions of at most ``dec_max`` tokens (``tokens`` of them).  ``part_o`` /
+    ``part_ml``: float32 scratch of at least tokens*heads*num_splits*head_dim and
+    tokens*heads*num_splits*2 elements when ``num_splits`` > 1."""
+    T, nh, d = q.shape
+    _need(q, "q", torch.bfloat16, (T, nh, d))
+    _need(out, "out", torch.bfloat16, (T, nh, d))
+    _need(k_cache, "k_cache", torch.bfloat16, (None, None, None, d))
+    _need(v_cache, "v_cache", torch.bfloat16, tuple(k_cache.shape))
+    num_pages, nkv, ps, _ = k_cache.shape
+    if not attn_tiled_supported(q.dtype, d) or nh % nkv:
+        raise KernelError(f"tiled attention needs bfloat16, a head size in steps of 16 up to 256 and heads divisible "
+                          f"by key/value heads; got head size {d}, {nh}/{nkv} heads")
+    if tokens > 65535:
+        raise KernelError(f"{tokens} small-portion tokens exceed the decode kernel's grid limit of 65535")
+    if num_splits > 1:
+        _need(part_o, "part_o", torch.float32)
+        _need(part_ml, "part_ml", torch.float32)
+        if part_o.numel() < tokens * nh * num_splits * d or part_ml.numel() < tokens * nh * num_splits * 2:
+            raise KernelError("attention scratch buffers are too small for the number of key ranges")
+    _ok(kernels_lib().xb_attn_decode_bf16(
+        out.data_ptr(), _ptr(part_o), _ptr(part_ml), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+        positions.data_ptr(), req_of_token.data_ptr(), q_start.data_ptr(), int(num_entries), block_table.data_ptr(),
+        int(table_stride), nh, nkv, d, ps, num_pages, int(window or 0), float(scale), int(dec_max), int(bool(direct)),
+        int(num_splits), int(tokens), err.data_ptr(), _stream()), "attn_decode_bf16", 2 if num_splits > 1 else 1)

@@ -91,4 +91,7 @@ def _declare_kernels(lib):
     _sig(lib, "xb_widen_bf16", I, [P, P, L, P])
     _sig(lib, "xb_sample", I, [P, P, P, P, I, I, I, P])
     _sig(lib, "xb_sample_params_size", I, [])
-    # optional symbols of later kernels are declared where they are wrapped (kernels.py)
+    _sig(lib, "xb_attn_decode_split", I, [])
+    _sig(lib, "xb_attn_prefill_bf16", I, [P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, I, P, P])
+    _sig(lib, "xb_attn_decode_bf16", I,
+         [P, P, P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, I, I, I, P, P])

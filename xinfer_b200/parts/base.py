@@ -33,7 +33,8 @@ class Workspace:
             if self.frozen and buf is not None:
                 raise RuntimeError(f"workspace buffer '{name}' would have to grow while a CUDA graph uses it")
             cap = n if buf is None or buf.dtype != dtype else max(n, buf.numel())
-            buf = torch.empty(max(cap, 1), dtype=dtype, device=self.device)
+            # zero-filled: rows that padding tokens never write must stay finite
+            buf = torch.zeros(max(cap, 1), dtype=dtype, device=self.device)
             self._bufs[name] = buf
         return buf[:n].view(*shape)
 
@@ -71,6 +72,11 @@ class StepContext:
     # longest context (start + count) of any entry, and whether every entry brings one token
     max_context: int = 0
     all_single: bool = False
+    # the step is (or will be) replayed from a CUDA graph: launch sizes must come from the padded
+    # shapes, never from this step's actual lengths
+    fixed_shapes: bool = False
+    # values parts compute once per step and share between layers
+    scratch: Dict[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)
