@@ -16,6 +16,17 @@ def dev():
     return torch.device("cuda:0")
 
 
+@pytest.fixture(params=[True, False], ids=["vectorized", "plain"])
+def both_families(request):
+    """Norm, gate and q/k preparation exist as plain kernels and as 16-byte-access bfloat16
+    kernels; the tests that use this fixture check both."""
+    from xinfer_b200 import kernels
+    old = kernels.vectorized
+    kernels.vectorized = request.param
+    yield request.param
+    kernels.vectorized = old
+
+
 def err_word():
     return torch.zeros(1, dtype=torch.int32, device=dev())
 
@@ -46,7 +57,7 @@ def test_embedding(dtype, T, H, V):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("rows,dim,eps,offset", [(1, 16, 1e-6, 0.0), (33, 100, 1e-5, 0.0), (7, 5120, 3e-6, 1.0), (5, 8200, 1e-6, 0.0)])
-def test_rmsnorm_plain_fused_and_gathered(dtype, rows, dim, eps, offset):
+def test_rmsnorm_plain_fused_and_gathered(dtype, rows, dim, eps, offset, both_families):
     from xinfer_b200 import kernels
     x, br = rnd(rows, dim, dtype=dtype, seed=1), rnd(rows, dim, dtype=dtype, seed=2)
     w = rnd(dim, seed=3) * 0.1 + 1
@@ -95,8 +106,8 @@ def test_gemm_plain_is_true_float32_and_row_independent(M, N, K):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T,I", [(1, 8), (13, 48), (37, 11008 // 16 + 3)])
-def test_swiglu(dtype, T, I):
+@pytest.mark.parametrize("T,I", [(1, 8), (13, 48), (37, 11008 // 16 + 3), (5, 12288)])
+def test_swiglu(dtype, T, I, both_families):
     from xinfer_b200 import kernels
     gu = rnd(T, 2 * I, dtype=dtype, scale=3.0)
     out = torch.empty(T, I, dtype=dtype, device=dev())
@@ -132,8 +143,8 @@ def meta(entries, ps, num_pages, seed=0):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("nh,nkv,d,rot,inter,ps", [(4, 2, 16, 16, False, 16), (6, 1, 48, 48, False, 8), (8, 8, 128, 64, True, 4), (10, 5, 80, 80, False, 16)])
-def test_qk_norm_rope_write(dtype, nh, nkv, d, rot, inter, ps):
+@pytest.mark.parametrize("nh,nkv,d,rot,inter,ps", [(4, 2, 16, 16, False, 16), (6, 1, 48, 48, False, 8), (8, 8, 128, 64, True, 4), (10, 5, 80, 80, False, 16), (32, 8, 128, 128, False, 16), (3, 3, 256, 256, True, 16), (5, 1, 64, 32, False, 16)])
+def test_qk_norm_rope_write(dtype, nh, nkv, d, rot, inter, ps, both_families):
     from xinfer_b200 import kernels
     entries = [(0, 9), (21, 1), (5, 14)]
     T = sum(c for _, c in entries)

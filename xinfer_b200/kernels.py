@@ -50,6 +50,10 @@ def _stream() -> int:
 
 _launches = 0
 
+# Use the 16-byte-access bfloat16 kernels for norm / gate / q-k preparation where sizes allow;
+# tests switch this off to compare them with the plain kernels.
+vectorized = True
+
 
 def launch_count() -> int:
     """Kernels of this engine launched so far by this process (captured launches included)."""
@@ -111,6 +115,11 @@ def rmsnorm(out, x, weight, eps, err, *, branch=None, sum_out=None, rows=None, w
             raise KernelError(f"rows holds {rows.numel()} entries for {n} output rows")
     elif n != x.shape[0]:
         raise KernelError(f"out has {n} rows, x has {x.shape[0]} and no row list was given")
+    if vectorized and x.dtype == torch.bfloat16 and dim % 8 == 0 and dim <= 32768:
+        _ok(kernels_lib().xb_rmsnorm_bf16(out.data_ptr(), _ptr(sum_out), x.data_ptr(), _ptr(branch), _ptr(rows),
+                                          weight.data_ptr(), n, dim, x.shape[0], float(eps), float(weight_offset),
+                                          err.data_ptr(), _stream()), "rmsnorm_bf16")
+        return
     _ok(kernels_lib().xb_rmsnorm(dtype_code(x.dtype), out.data_ptr(), _ptr(sum_out), x.data_ptr(), _ptr(branch),
                                  _ptr(rows), weight.data_ptr(), n, dim, x.shape[0], float(eps),
                                  float(weight_offset), err.data_ptr(), _stream()), "rmsnorm")
@@ -160,6 +169,14 @@ def qk_norm_rope_write(q_out, k_cache, v_cache, qkv, q_w, k_w, cos_t, sin_t, pos
         _need(cos_t, "cos", torch.float32, (None, rot // 2))
         _need(sin_t, "sin", torch.float32, tuple(cos_t.shape))
         max_pos = cos_t.shape[0]
+    if (vectorized and qkv.dtype == torch.bfloat16 and d % 16 == 0 and d <= 512
+            and (cos_t is None or interleaved or rot == d)):
+        _ok(kernels_lib().xb_qk_norm_rope_write_bf16(
+            q_out.data_ptr(), _ptr(k_cache), _ptr(v_cache), qkv.data_ptr(), _ptr(q_w), _ptr(k_w), _ptr(cos_t), _ptr(sin_t),
+            positions.data_ptr(), req_of_token.data_ptr(), block_table.data_ptr(), int(table_stride), T, nh, nkv, d, rot,
+            int(bool(interleaved)), page_size, num_pages, max_pos, float(eps), int(bool(write_kv)), err.data_ptr(),
+            _stream()), "qk_norm_rope_write_bf16")
+        return
     _ok(kernels_lib().xb_qk_norm_rope_write(
         dtype_code(qkv.dtype), q_out.data_ptr(), _ptr(k_cache), _ptr(v_cache), qkv.data_ptr(), _ptr(q_w), _ptr(k_w),
         _ptr(cos_t), _ptr(sin_t), positions.data_ptr(), req_of_token.data_ptr(), block_table.data_ptr(),
@@ -188,6 +205,9 @@ def swiglu(out, gate_up):
     T, two_i = gate_up.shape
     _need(gate_up, "gate_up", None, (T, two_i))
     _need(out, "out", gate_up.dtype, (T, two_i // 2))
+    if vectorized and gate_up.dtype == torch.bfloat16 and two_i % 16 == 0:
+        _ok(kernels_lib().xb_swiglu_bf16(out.data_ptr(), gate_up.data_ptr(), T, two_i // 2, _stream()), "swiglu_bf16")
+        return
     _ok(kernels_lib().xb_swiglu(dtype_code(gate_up.dtype), out.data_ptr(), gate_up.data_ptr(), T, two_i // 2, _stream()), "swiglu")
 
 
