@@ -309,6 +309,7 @@ def tiled_kernel(out, q, kc, vc, pos, req, table, stride, window, scale, e, entr
     to = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device=dev())
     ctx = SimpleNamespace(positions=pos, req_of_token=req, q_start=to(q_start), start_pos=to([s for s, _ in entries]),
                           num_entries=len(entries), num_tokens=int(q_start[-1]), h_q_start=q_start, real_entries=len(entries),
+                          h_start_pos=np.asarray([s for s, _ in entries], dtype=np.int32),
                           max_context=max(s + c for s, c in entries), fixed_shapes=False, scratch={},
                           workspace=Workspace(dev()), err=e)
     cache = LayerCache(kc, vc, 0, kc.shape[2])
@@ -362,7 +363,25 @@ def test_attention_tiled_refuses_what_it_cannot_do():
     kc = torch.zeros(4, 2, 16, 40, dtype=torch.bfloat16, device=dev())
     z = torch.zeros(4, dtype=torch.int32, device=dev())
     with pytest.raises(kernels.KernelError, match="head size"):
-        kernels.attn_prefill_bf16(q.clone(), q, kc, kc.clone(), z, z, 1, z, 4, None, 1.0, 4, 1, err_word())
+        kernels.attn_prefill_bf16(q.clone(), q, kc, kc.clone(), z, z, 1, z, 4, None, 1.0, 4, 1, 64, err_word())
     # head size 40 still runs: the backend hands it to the plain kernel
     worst = attention_case(tiled_kernel, torch.bfloat16, 4, 2, 40, 16, [(0, 30), (50, 1)], None)
     assert worst <= tol(torch.bfloat16, 2)
+
+
+@pytest.mark.parametrize("warps", [4, 8])
+def test_attention_prefill_tile_sizes(warps, monkeypatch):
+    from xinfer_b200.parts import attention_backend
+    monkeypatch.setattr(attention_backend, "PREFILL_WARPS", warps)
+    for nh, nkv, d, ps, entries, window in [(8, 2, 128, 16, [(0, 300), (100, 129), (5, 64)], None), (4, 1, 64, 8, [(37, 200)], 90)]:
+        worst = attention_case(tiled_kernel, torch.bfloat16, nh, nkv, d, ps, entries, window)
+        assert worst <= tol(torch.bfloat16, 2), worst
+
+
+def test_decode_split_choice():
+    from xinfer_b200.parts.attention_backend import decode_split
+    for bound, pairs in [(1, 1), (4096, 8), (4096, 64), (4096, 512), (40000, 8), (100, 4096)]:
+        split, n = decode_split(bound, pairs)
+        assert split % 64 == 0 and split >= 64 and (n - 1) * split < bound <= n * split
+    assert decode_split(4096, 512) == (2048, 2)
+    assert decode_split(4096, 8)[0] == 64

@@ -1,14 +1,14 @@
 // bfloat16 attention over the paged cache on tensor cores (mma.sync m16n8k16, float32 scores,
 // softmax and accumulation), for head sizes that are multiples of 16 up to 256.
 //
-//  * attn_prefill_kernel: one CTA per (64 queries of one request's portion, query head); keys and
+//  * attn_prefill_kernel: one CTA per (128 queries of one request's portion, query head); keys and
 //    values stream through shared memory in tiles of 64 positions fetched page by page with
 //    cp.async; causal mask, optional window, running softmax.
 //  * attn_decode_kernel: for requests that bring only a few tokens.  One CTA per (token, key/value
-//    head, range of 256 key positions): the query heads that share the key/value head form the rows
+//    head, range of key positions): the query heads that share the key/value head form the rows
 //    of the tile, four warps take 16 keys each of every 64-key tile.  Ranges are cut at absolute
-//    positions, so a token's partition never depends on what else is in the batch.  With more
-//    than one range the CTAs write normalised partial outputs and (max, sum) to scratch memory and
+//    positions (multiples of the range length the host picks for the launch).  With more than one
+//    range the CTAs write normalised partial outputs and (max, sum) to scratch memory and
 //    attn_combine_kernel merges them.
 //
 // Cache layout: [num_pages, kv_heads, page_size, head_dim]; any page size.
@@ -19,9 +19,7 @@
 
 namespace {
 
-constexpr int KT = 64;        // key positions per shared-memory tile
-constexpr int QT = 64;        // queries per CTA in the prefill kernel
-constexpr int THREADS = 128;  // four warps
+constexpr int KT = 64;  // key positions per shared-memory tile
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -51,49 +49,82 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // Byte offset of 16-byte chunk c of row r in a [rows][DP] bf16 tile whose chunks are XOR-swizzled
-// with the row, so that ldmatrix reads of 8 rows hit 8 different banks groups.
+// with the row, so that the 8 rows an ldmatrix reads lie in 8 different bank groups.
 template <int DP>
 __device__ __forceinline__ uint32_t tile_off(int r, int c) { return (uint32_t)(r * DP * 2 + ((c ^ (r & 7)) << 4)); }
 
-// Fetch rows key0 .. key0+KT-1 of key/value head g into a tile; rows outside [lo, hi] and columns
-// beyond d are zero-filled.
-template <int DP>
-__device__ __forceinline__ void load_kv_tile(uint32_t tile, const __nv_bfloat16* __restrict__ cache,
-                                             const int* __restrict__ table, int num_pages, int nkv, int g,
-                                             int ps, int d, int key0, int lo, int hi, int* err) {
-    constexpr int CPR = DP / 8;
-    for (int idx = threadIdx.x; idx < KT * CPR; idx += THREADS) {
-        const int r = idx / CPR, c = idx % CPR;
+// Where a CTA finds the page ids of the positions it reads: a copy in shared memory when the
+// range is short enough, else the block table itself.  pages[i] is the page of positions
+// (first + i) * page_size ...
+struct PageView {
+    const int* pages;
+    int first;
+};
+
+template <int NT>
+__device__ __forceinline__ PageView stage_pages(int* s_pages, int cap, const int* __restrict__ table,
+                                                int page_lo, int page_hi) {
+    PageView v;
+    const int n = page_hi - page_lo + 1;
+    if (n > cap) {
+        v.pages = table;
+        v.first = 0;
+        return v;
+    }
+    for (int i = threadIdx.x; i < n; i += NT) s_pages[i] = table[page_lo + i];
+    v.pages = s_pages;
+    v.first = page_lo;
+    return v;  // the caller synchronises before the first load
+}
+
+// Fetch rows key0 .. key0+KT-1 of key/value head g into a K tile and a V tile; rows outside
+// [lo, hi] and columns beyond d are zero-filled; a page id outside the pool is flagged and its
+// rows zero-filled.
+template <int DP, int NT>
+__device__ __forceinline__ void load_kv_tiles(uint32_t k_tile, uint32_t v_tile, const __nv_bfloat16* __restrict__ kc,
+                                              const __nv_bfloat16* __restrict__ vc, PageView pv, int num_pages,
+                                              int nkv, int g, int ps, int ps_shift, int d, int key0, int lo,
+                                              int hi, int* err) {
+    constexpr int CPR = DP / 8;     // 16-byte chunks per row
+    constexpr int RPP = NT / CPR;   // rows per pass
+    const int c = threadIdx.x % CPR, r0 = threadIdx.x / CPR;
+    const bool col_ok = c * 8 < d;
+#pragma unroll
+    for (int i = 0; i < KT / RPP; ++i) {
+        const int r = r0 + i * RPP;
         const int j = key0 + r;
-        bool ok = j >= lo && j <= hi && c * 8 < d;
-        const __nv_bfloat16* src = cache;
+        bool ok = col_ok && j >= lo && j <= hi;
+        size_t off = 0;
         if (ok) {
-            const int page = table[j / ps];
+            const int pi = ps_shift >= 0 ? (j >> ps_shift) : (j / ps);
+            const int in = ps_shift >= 0 ? (j & (ps - 1)) : (j - pi * ps);
+            const int page = pv.pages[pi - pv.first];
             if (page < 0 || page >= num_pages) {
                 ok = false;
                 atomicOr(err, XB_ERR_BAD_PAGE);
             } else {
-                src = cache + (((size_t)page * nkv + g) * ps + (j % ps)) * d + c * 8;
+                off = (((size_t)page * nkv + g) * ps + in) * d + c * 8;
             }
         }
-        cp_async16(tile + tile_off<DP>(r, c), src, ok ? 16 : 0);
+        const uint32_t o = tile_off<DP>(r, c);
+        cp_async16(k_tile + o, kc + off, ok ? 16 : 0);
+        cp_async16(v_tile + o, vc + off, ok ? 16 : 0);
     }
 }
 
-// Fetch `rows` query rows (row r = query vector at qbase + r * row_stride elements when valid[r])
-template <int DP, int ROWS>
+// Fetch ROWS query rows (row r at qbase + r * row_stride elements while r < valid_rows).
+template <int DP, int ROWS, int NT>
 __device__ __forceinline__ void load_q_tile(uint32_t tile, const __nv_bfloat16* __restrict__ qbase,
                                             size_t row_stride, int valid_rows, int d) {
     constexpr int CPR = DP / 8;
-    for (int idx = threadIdx.x; idx < ROWS * CPR; idx += THREADS) {
+    for (int idx = threadIdx.x; idx < ROWS * CPR; idx += NT) {
         const int r = idx / CPR, c = idx % CPR;
         const bool ok = r < valid_rows && c * 8 < d;
         cp_async16(tile + tile_off<DP>(r, c), ok ? qbase + r * row_stride + c * 8 : qbase, ok ? 16 : 0);
     }
 }
 
-// S[16 x NK keys] += Q[16 x DP] . K[NK x DP]^T for one warp.  q_tile/k_tile: shared addresses of
-// the tiles, q_row0/k_row0 the first row of the warp's slice.
+// S[16 x NK keys] += Q[16 x DP] . K[NK x DP]^T for one warp.
 template <int DP, int NK>
 __device__ __forceinline__ void warp_qk(float (&s)[NK / 8][4], uint32_t q_tile, int q_row0, uint32_t k_tile, int k_row0) {
     const int lane = threadIdx.x & 31;
@@ -150,20 +181,22 @@ __device__ __forceinline__ int small_token(int z, const int* __restrict__ q_star
 }
 
 // ------------------------------------------------------------------------------------------------
-// prefill
+// prefill: NW warps, 16 queries each
 // ------------------------------------------------------------------------------------------------
-template <int DP>
-__global__ void __launch_bounds__(THREADS)
+template <int DP, int NW>
+__global__ void __launch_bounds__(NW * 32)
 attn_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ q,
                     const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
                     const int* __restrict__ q_start, const int* __restrict__ start_pos, int num_entries,
                     const int* __restrict__ block_table, int table_stride, int nh, int nkv, int d, int ps,
-                    int num_pages, int window, float scale_log2, int dec_max, int* err) {
+                    int ps_shift, int num_pages, int window, float scale_log2, int dec_max, int page_cap, int* err) {
+    constexpr int NT = NW * 32, QT = NW * 16;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ int s_entry, s_tile;
     constexpr int TILE_BYTES = KT * DP * 2;
     const uint32_t q_tile = smem_addr(smem_raw);
     const uint32_t kv_base = q_tile + QT * DP * 2;  // stages: [K0][V0][K1][V1]
+    int* s_pages = reinterpret_cast<int*>(smem_raw + QT * DP * 2 + 4 * TILE_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.y, g = h / (nh / nkv);
 
@@ -175,7 +208,7 @@ attn_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __rest
                 const int nt = (n + QT - 1) / QT;
                 if ((int)blockIdx.x < acc + nt) {
                     found = b;
-                    tile = blockIdx.x - acc;
+                    tile = nt - 1 - ((int)blockIdx.x - acc);  // a portion's last (longest) tiles come first
                     break;
                 }
                 acc += nt;
@@ -195,11 +228,13 @@ attn_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __rest
     const int last_key = p0 + rows - 1;               // newest key any row of the tile may see
     const int first_key = window > 0 ? max(0, p0 - window + 1) : 0;
     const int* table = block_table + (size_t)b * table_stride;
-
-    load_q_tile<DP, QT>(q_tile, q + ((size_t)t0 * nh + h) * d, (size_t)nh * d, rows, d);
     const int kt_first = first_key / KT, kt_last = last_key / KT;
-    load_kv_tile<DP>(kv_base, kc, table, num_pages, nkv, g, ps, d, kt_first * KT, first_key, last_key, err);
-    load_kv_tile<DP>(kv_base + TILE_BYTES, vc, table, num_pages, nkv, g, ps, d, kt_first * KT, first_key, last_key, err);
+    const PageView pv = stage_pages<NT>(s_pages, page_cap, table, (kt_first * KT) / ps, last_key / ps);
+    __syncthreads();
+
+    load_q_tile<DP, QT, NT>(q_tile, q + ((size_t)t0 * nh + h) * d, (size_t)nh * d, rows, d);
+    load_kv_tiles<DP, NT>(kv_base, kv_base + TILE_BYTES, kc, vc, pv, num_pages, nkv, g, ps, ps_shift, d,
+                          kt_first * KT, first_key, last_key, err);
     cp_async_commit();
 
     float o[DP / 8][4];
@@ -212,8 +247,8 @@ attn_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __rest
         const int stage = (kt - kt_first) & 1;
         if (kt < kt_last) {
             const uint32_t nxt = kv_base + (stage ^ 1) * 2 * TILE_BYTES;
-            load_kv_tile<DP>(nxt, kc, table, num_pages, nkv, g, ps, d, (kt + 1) * KT, first_key, last_key, err);
-            load_kv_tile<DP>(nxt + TILE_BYTES, vc, table, num_pages, nkv, g, ps, d, (kt + 1) * KT, first_key, last_key, err);
+            load_kv_tiles<DP, NT>(nxt, nxt + TILE_BYTES, kc, vc, pv, num_pages, nkv, g, ps, ps_shift, d,
+                                  (kt + 1) * KT, first_key, last_key, err);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -222,7 +257,7 @@ attn_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __rest
         __syncthreads();
         const uint32_t k_tile = kv_base + stage * 2 * TILE_BYTES, v_tile = k_tile + TILE_BYTES;
         const int key0 = kt * KT;
-        // rows of this warp see nothing of the tile: keys all newer than its last row, or all older than its window
+        // this warp's rows see nothing of the tile: keys all newer than its last row, or all older than its window
         const int w_last = p0 + warp * 16 + 15, w_first = p0 + warp * 16;
         const bool skip = key0 > w_last || (window > 0 && key0 + KT - 1 < w_first - window + 1);
         if (!skip) {
@@ -230,15 +265,21 @@ attn_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __rest
 #pragma unroll
             for (int i = 0; i < KT / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
             warp_qk<DP, KT>(s, q_tile, warp * 16, k_tile, 0);
+            // masks are needed only where the tile touches the diagonal, the window's edge or the end
+            const bool need_mask = key0 + KT - 1 > w_first || key0 + KT - 1 > last_key ||
+                                   (window > 0 && key0 < w_last - window + 1);
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
             for (int i = 0; i < KT / 8; ++i) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const int j = key0 + i * 8 + (lane & 3) * 2 + (e & 1);
-                    const int p = pr[e >> 1];
-                    const bool ok = j <= p && j <= last_key && (window <= 0 || j > p - window);
-                    const float v = ok ? s[i][e] * scale_log2 : -INFINITY;
+                    float v = s[i][e] * scale_log2;
+                    if (need_mask) {
+                        const int j = key0 + i * 8 + (lane & 3) * 2 + (e & 1);
+                        const int p = pr[e >> 1];
+                        const bool ok = j <= p && j <= last_key && (window <= 0 || j > p - window);
+                        v = ok ? v : -INFINITY;
+                    }
                     s[i][e] = v;
                     mx[e >> 1] = fmaxf(mx[e >> 1], v);
                 }
@@ -291,20 +332,23 @@ attn_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __rest
 // decode (few tokens per request), split over key ranges
 // ------------------------------------------------------------------------------------------------
 template <int DP>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(128)
 attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
                    const __nv_bfloat16* __restrict__ vc, const int* __restrict__ positions,
                    const int* __restrict__ req_of_token, const int* __restrict__ q_start, int num_entries,
                    const int* __restrict__ block_table, int table_stride, int nh, int nkv, int d, int ps,
-                   int num_pages, int window, float scale_log2, int dec_max, int direct, int split,
-                   int num_splits, int* err) {
+                   int ps_shift, int num_pages, int window, float scale_log2, int dec_max, int direct, int split,
+                   int num_splits, int page_cap, int* err) {
+    constexpr int NT = 128;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ float s_m[4][16], s_l[4][16];
     constexpr int TILE_BYTES = KT * DP * 2;
+    constexpr int KV_BYTES = 4 * TILE_BYTES, MERGE_BYTES = 4 * 16 * DP * 4;
     const uint32_t q_tile = smem_addr(smem_raw);
     const uint32_t kv_base = q_tile + 16 * DP * 2;
     float* o_all = reinterpret_cast<float*>(smem_raw + 16 * DP * 2);  // reused after the loop: [4][16][DP]
+    int* s_pages = reinterpret_cast<int*>(smem_raw + 16 * DP * 2 + (KV_BYTES > MERGE_BYTES ? KV_BYTES : MERGE_BYTES));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = nh / nkv;
     const int qtiles = (G + 15) / 16;
@@ -320,11 +364,13 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
     const int* table = block_table + (size_t)b * table_stride;
     const int h0 = g * G + qt * 16;
     const int rows = min(16, G - qt * 16);
-
-    load_q_tile<DP, 16>(q_tile, q + ((size_t)t * nh + h0) * d, (size_t)d, rows, d);
     const int kt_first = k_begin / KT, kt_last = k_end / KT;
-    load_kv_tile<DP>(kv_base, kc, table, num_pages, nkv, g, ps, d, kt_first * KT, k_begin, k_end, err);
-    load_kv_tile<DP>(kv_base + TILE_BYTES, vc, table, num_pages, nkv, g, ps, d, kt_first * KT, k_begin, k_end, err);
+    const PageView pv = stage_pages<NT>(s_pages, page_cap, table, (kt_first * KT) / ps, k_end / ps);
+    __syncthreads();
+
+    load_q_tile<DP, 16, NT>(q_tile, q + ((size_t)t * nh + h0) * d, (size_t)d, rows, d);
+    load_kv_tiles<DP, NT>(kv_base, kv_base + TILE_BYTES, kc, vc, pv, num_pages, nkv, g, ps, ps_shift, d,
+                          kt_first * KT, k_begin, k_end, err);
     cp_async_commit();
 
     float o[DP / 8][4];
@@ -336,8 +382,8 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
         const int stage = (kt - kt_first) & 1;
         if (kt < kt_last) {
             const uint32_t nxt = kv_base + (stage ^ 1) * 2 * TILE_BYTES;
-            load_kv_tile<DP>(nxt, kc, table, num_pages, nkv, g, ps, d, (kt + 1) * KT, k_begin, k_end, err);
-            load_kv_tile<DP>(nxt + TILE_BYTES, vc, table, num_pages, nkv, g, ps, d, (kt + 1) * KT, k_begin, k_end, err);
+            load_kv_tiles<DP, NT>(nxt, nxt + TILE_BYTES, kc, vc, pv, num_pages, nkv, g, ps, ps_shift, d,
+                                  (kt + 1) * KT, k_begin, k_end, err);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -351,7 +397,7 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
 #pragma unroll
             for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
             warp_qk<DP, 16>(s, q_tile, 0, k_tile, warp * 16);
-            float mx = -INFINITY;  // every row of the tile is the same token: one key range for all
+            // every row of the tile is the same token: one key range for all rows
 #pragma unroll
             for (int i = 0; i < 2; ++i)
 #pragma unroll
@@ -361,7 +407,7 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
                 }
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
-                mx = fmaxf(fmaxf(s[0][r * 2], s[0][r * 2 + 1]), fmaxf(s[1][r * 2], s[1][r * 2 + 1]));
+                float mx = fmaxf(fmaxf(s[0][r * 2], s[0][r * 2 + 1]), fmaxf(s[1][r * 2], s[1][r * 2 + 1]));
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
                 const float m_new = fmaxf(m[r], mx);
@@ -396,16 +442,18 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
             s_m[warp][row] = m[r];
             s_l[warp][row] = l[r];
         }
+        if (row < rows) {
 #pragma unroll
-        for (int i = 0; i < DP / 8; ++i) {
-            const int c = i * 8 + (lane & 3) * 2;
-            float* dst = o_all + ((size_t)warp * 16 + row) * DP + c;
-            dst[0] = o[i][r * 2];
-            dst[1] = o[i][r * 2 + 1];
+            for (int i = 0; i < DP / 8; ++i) {
+                const int c = i * 8 + (lane & 3) * 2;
+                float* dst = o_all + ((size_t)warp * 16 + row) * DP + c;
+                dst[0] = o[i][r * 2];
+                dst[1] = o[i][r * 2 + 1];
+            }
         }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < rows * d; idx += THREADS) {
+    for (int idx = threadIdx.x; idx < rows * d; idx += NT) {
         const int row = idx / d, c = idx % d;
         float M = -INFINITY;
 #pragma unroll
@@ -461,15 +509,26 @@ __global__ void attn_combine_kernel(__nv_bfloat16* __restrict__ out, const float
     }
 }
 
-template <int DP>
+int shift_of(int ps) {
+    for (int s = 0; s < 31; ++s)
+        if ((1 << s) == ps) return s;
+    return -1;
+}
+
+constexpr int PAGE_CAP_MAX = 8192;  // page ids a CTA may stage in shared memory (32 KB)
+
+template <int DP, int NW>
 int launch_prefill(void* out, const void* q, const void* kc, const void* vc, const int* q_start, const int* start_pos,
                    int num_entries, const int* table, int stride, int nh, int nkv, int d, int ps, int num_pages,
-                   int window, float scale_log2, int dec_max, int tiles, int* err, cudaStream_t stream) {
-    const size_t smem = (size_t)QT * DP * 2 + 4 * KT * DP * 2;
-    cudaFuncSetAttribute(attn_prefill_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    attn_prefill_kernel<DP><<<dim3(tiles, nh), THREADS, smem, stream>>>(
+                   int window, float scale_log2, int dec_max, int tiles, int max_context, int* err, cudaStream_t stream) {
+    int page_cap = (max_context + ps - 1) / ps + 2;
+    if (page_cap > PAGE_CAP_MAX) page_cap = 0;
+    const size_t smem = (size_t)NW * 16 * DP * 2 + 4 * KT * DP * 2 + (size_t)page_cap * 4;
+    cudaFuncSetAttribute(attn_prefill_kernel<DP, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attn_prefill_kernel<DP, NW><<<dim3(tiles, nh), NW * 32, smem, stream>>>(
         (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, q_start,
-        start_pos, num_entries, table, stride, nh, nkv, d, ps, num_pages, window, scale_log2, dec_max, err);
+        start_pos, num_entries, table, stride, nh, nkv, d, ps, shift_of(ps), num_pages, window, scale_log2, dec_max,
+        page_cap, err);
     return xb_launch_status();
 }
 
@@ -479,49 +538,55 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const
                   int stride, int nh, int nkv, int d, int ps, int num_pages, int window, float scale_log2, int dec_max,
                   int direct, int split, int num_splits, int tokens, int* err, cudaStream_t stream) {
     const size_t kv = 4 * (size_t)KT * DP * 2, merge = 4 * 16 * (size_t)DP * 4;
-    const size_t smem = 16 * DP * 2 + (kv > merge ? kv : merge);
+    int page_cap = (split + KT) / ps + 2;
+    if (page_cap > PAGE_CAP_MAX) page_cap = 0;
+    const size_t smem = 16 * DP * 2 + (kv > merge ? kv : merge) + (size_t)page_cap * 4;
     cudaFuncSetAttribute(attn_decode_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     const int qtiles = (nh / nkv + 15) / 16;
-    attn_decode_kernel<DP><<<dim3(num_splits, nkv * qtiles, tokens), THREADS, smem, stream>>>(
+    attn_decode_kernel<DP><<<dim3(num_splits, nkv * qtiles, tokens), 128, smem, stream>>>(
         (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc,
-        positions, req_of_token, q_start, num_entries, table, stride, nh, nkv, d, ps, num_pages, window, scale_log2,
-        dec_max, direct, split, num_splits, err);
+        positions, req_of_token, q_start, num_entries, table, stride, nh, nkv, d, ps, shift_of(ps), num_pages, window,
+        scale_log2, dec_max, direct, split, num_splits, page_cap, err);
     return xb_launch_status();
 }
 
 }  // namespace
 
-// Key positions per range of the decode kernel (a multiple of the 64-key tile).
-XB_EXPORT int xb_attn_decode_split() { return 256; }
-
-// Portions of more than dec_max tokens; `tiles` = sum over those portions of ceil(tokens / 64).
+// Portions of more than dec_max tokens, `warps` * 16 queries per CTA (warps = 4 or 8); `tiles` =
+// sum over those portions of ceil(tokens / (warps * 16)); max_context = the longest
+// start + tokens among them.
 XB_EXPORT int xb_attn_prefill_bf16(void* out, const void* q, const void* kc, const void* vc, const int* q_start,
                                    const int* start_pos, int num_entries, const int* table, int stride, int nh,
                                    int nkv, int d, int ps, int num_pages, int window, float scale, int dec_max,
-                                   int tiles, int* err, cudaStream_t stream) {
+                                   int tiles, int max_context, int warps, int* err, cudaStream_t stream) {
     if (tiles <= 0) return 0;
-    if (d % 16 || d > 256 || nh % nkv) return (int)cudaErrorInvalidValue;
+    if (d % 16 || d > 256 || nh % nkv || ps <= 0 || (warps != 4 && warps != 8)) return (int)cudaErrorInvalidValue;
     const float sl2 = scale * 1.4426950408889634f;
-#define XB_GO(DP) return launch_prefill<DP>(out, q, kc, vc, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, num_pages, window, sl2, dec_max, tiles, err, stream)
-    if (d <= 64) XB_GO(64);
-    if (d <= 128) XB_GO(128);
-    XB_GO(256);
+#define XB_GO(DP, NW) return launch_prefill<DP, NW>(out, q, kc, vc, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, num_pages, window, sl2, dec_max, tiles, max_context, err, stream)
+    if (warps == 4) {
+        if (d <= 64) XB_GO(64, 4);
+        if (d <= 128) XB_GO(128, 4);
+        XB_GO(256, 4);
+    }
+    if (d <= 64) XB_GO(64, 8);
+    if (d <= 128) XB_GO(128, 8);
+    XB_GO(256, 4);  // 8 warps of a 256-wide head would not fit shared memory
 #undef XB_GO
 }
 
 // Tokens of portions of at most dec_max tokens (`tokens` of them; direct != 0: every token of the
-// batch is one).  part_o: [tokens, nh, num_splits, d] float32, part_ml: [tokens, nh, num_splits, 2]; both may
-// be null when num_splits == 1.  num_splits = ceil(longest context / xb_attn_decode_split()).
+// batch is one).  Keys are cut into ranges of `split` positions (a multiple of 64) at absolute
+// positions; num_splits = ceil(longest context / split).  part_o: [tokens, nh, num_splits, d]
+// float32, part_ml: [tokens, nh, num_splits, 2]; both may be null when num_splits == 1.
 XB_EXPORT int xb_attn_decode_bf16(void* out, float* part_o, float* part_ml, const void* q, const void* kc,
                                   const void* vc, const int* positions, const int* req_of_token, const int* q_start,
                                   int num_entries, const int* table, int stride, int nh, int nkv, int d, int ps,
-                                  int num_pages, int window, float scale, int dec_max, int direct, int num_splits,
-                                  int tokens, int* err, cudaStream_t stream) {
+                                  int num_pages, int window, float scale, int dec_max, int direct, int split,
+                                  int num_splits, int tokens, int* err, cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    if (d % 16 || d > 256 || nh % nkv || num_splits < 1) return (int)cudaErrorInvalidValue;
+    if (d % 16 || d > 256 || nh % nkv || num_splits < 1 || split < KT || split % KT || ps <= 0) return (int)cudaErrorInvalidValue;
     if (num_splits > 1 && (!part_o || !part_ml)) return (int)cudaErrorInvalidValue;
     const float sl2 = scale * 1.4426950408889634f;
-    const int split = xb_attn_decode_split();
     int rc;
 #define XB_GO(DP) rc = launch_decode<DP>(out, part_o, part_ml, q, kc, vc, positions, req_of_token, q_start, num_entries, table, stride, nh, nkv, d, ps, num_pages, window, sl2, dec_max, direct, split, num_splits, tokens, err, stream)
     if (d <= 64) XB_GO(64);

@@ -244,13 +244,16 @@ def attn_tiled_supported(dtype, head_dim: int) -> bool:
     return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256
 
 
-def attn_decode_split() -> int:
-    return kernels_lib().xb_attn_decode_split()
+def attn_prefill_queries(head_dim: int, warps: int = 8) -> int:
+    """Queries one CTA of the prefill kernel takes (256-wide heads always use 4 warps)."""
+    return 16 * (4 if head_dim > 128 else warps)
 
 
 def attn_prefill_bf16(out, q, k_cache, v_cache, q_start, start_pos, num_entries, block_table, table_stride,
-                      window, scale, dec_max, tiles, err):
-    """Portions of more than ``dec_max`` tokens; ``tiles`` = sum of ceil(tokens / 64) over them."""
+                      window, scale, dec_max, tiles, max_context, err, warps: int = 8):
+    """Portions of more than ``dec_max`` tokens; ``tiles`` = sum over them of
+    ceil(tokens / attn_prefill_queries(head_dim, warps)); ``max_context`` = their longest
+    start + tokens."""
     T, nh, d = q.shape
     _need(q, "q", torch.bfloat16, (T, nh, d))
     _need(out, "out", torch.bfloat16, (T, nh, d))
@@ -263,12 +266,14 @@ def attn_prefill_bf16(out, q, k_cache, v_cache, q_start, start_pos, num_entries,
     _ok(kernels_lib().xb_attn_prefill_bf16(
         out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), q_start.data_ptr(), start_pos.data_ptr(),
         int(num_entries), block_table.data_ptr(), int(table_stride), nh, nkv, d, ps, num_pages, int(window or 0),
-        float(scale), int(dec_max), int(tiles), err.data_ptr(), _stream()), "attn_prefill_bf16")
+        float(scale), int(dec_max), int(tiles), int(max_context), 4 if d > 128 else int(warps), err.data_ptr(),
+        _stream()), "attn_prefill_bf16")
 
 
 def attn_decode_bf16(out, part_o, part_ml, q, k_cache, v_cache, positions, req_of_token, q_start, num_entries,
-                     block_table, table_stride, window, scale, dec_max, direct, num_splits, tokens, err):
-    """Tokens of portions of at most ``dec_max`` tokens (``tokens`` of them).  ``part_o`` /
+                     block_table, table_stride, window, scale, dec_max, direct, split, num_splits, tokens, err):
+    """Tokens of portions of at most ``dec_max`` tokens (``tokens`` of them); keys are cut into
+    ``num_splits`` ranges of ``split`` positions (a multiple of 64).  ``part_o`` /
     ``part_ml``: float32 scratch of at least tokens*heads*num_splits*head_dim and
     tokens*heads*num_splits*2 elements when ``num_splits`` > 1."""
     T, nh, d = q.shape
@@ -291,4 +296,4 @@ def attn_decode_bf16(out, part_o, part_ml, q, k_cache, v_cache, positions, req_o
         out.data_ptr(), _ptr(part_o), _ptr(part_ml), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
         positions.data_ptr(), req_of_token.data_ptr(), q_start.data_ptr(), int(num_entries), block_table.data_ptr(),
         int(table_stride), nh, nkv, d, ps, num_pages, int(window or 0), float(scale), int(dec_max), int(bool(direct)),
-        int(num_splits), int(tokens), err.data_ptr(), _stream()), "attn_decode_bf16", 2 if num_splits > 1 else 1)
+        int(split), int(num_splits), int(tokens), err.data_ptr(), _stream()), "attn_decode_bf16", 2 if num_splits > 1 else 1)

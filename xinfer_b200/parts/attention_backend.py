@@ -14,6 +14,9 @@ from .. import kernels
 
 # portions up to this many tokens are treated token by token by the decode kernel
 DEC_MAX = 4
+# CTAs the decode kernel should at least be cut into (a few per SM of a 148-SM part)
+DECODE_TARGET_CTAS = 592
+PREFILL_WARPS = 8
 
 _enabled = True
 
@@ -24,19 +27,32 @@ def set_tiled(flag: bool) -> None:
     _enabled = bool(flag)
 
 
-def _plan(ctx):
+def decode_split(bound: int, pairs: int) -> tuple:
+    """Range length (a multiple of 64) and number of ranges for keys up to ``bound`` when
+    ``pairs`` (token, key/value head) pairs share the machine: few pairs are cut finely so that
+    every SM gets work, many pairs are left whole so that nothing has to be merged."""
+    want = max((DECODE_TARGET_CTAS + pairs - 1) // max(pairs, 1), 1)
+    split = max(((bound + want - 1) // want + 63) // 64 * 64, 64)
+    return split, max((bound + split - 1) // split, 1)
+
+
+def _plan(ctx, head_dim: int):
     """Per-step launch figures, computed once and shared by all layers of the step."""
-    plan = ctx.scratch.get("attn_plan")
+    key = ("attn_plan", head_dim)
+    plan = ctx.scratch.get(key)
     if plan is None:
         if ctx.fixed_shapes:
             # a captured step: every token is its own one-token portion; sizes come from the padding
-            plan = dict(tiles=0, small=ctx.num_tokens, direct=True, bound=None)
+            plan = dict(tiles=0, small=ctx.num_tokens, direct=True, bound=None, prefill_bound=0)
         else:
             counts = np.diff(ctx.h_q_start[: ctx.real_entries + 1])
             small = counts <= DEC_MAX
-            plan = dict(tiles=int(((counts[~small] + 63) // 64).sum()), small=int(counts[small].sum()),
-                        direct=bool(small.all()), bound=int(ctx.max_context))
-        ctx.scratch["attn_plan"] = plan
+            per = kernels.attn_prefill_queries(head_dim, PREFILL_WARPS)
+            ends = ctx.h_start_pos[: ctx.real_entries] + counts
+            plan = dict(tiles=int(((counts[~small] + per - 1) // per).sum()), small=int(counts[small].sum()),
+                        direct=bool(small.all()), bound=int(ends[small].max()) if small.any() else 0,
+                        prefill_bound=int(ends[~small].max()) if (~small).any() else 0)
+        ctx.scratch[key] = plan
     return plan
 
 
@@ -46,18 +62,19 @@ def attend(out, q, cache, ctx, table, stride, window, scale) -> None:
         kernels.attention_plain(out, q, cache.k, cache.v, ctx.positions, ctx.req_of_token, table, stride,
                                 window, scale, ctx.err)
         return
-    plan = _plan(ctx)
+    plan = _plan(ctx, d)
     if plan["tiles"]:
         kernels.attn_prefill_bf16(out, q, cache.k, cache.v, ctx.q_start, ctx.start_pos, ctx.num_entries, table, stride,
-                                  window, scale, DEC_MAX, plan["tiles"], ctx.err)
+                                  window, scale, DEC_MAX, plan["tiles"], plan["prefill_bound"], ctx.err, warps=PREFILL_WARPS)
     if plan["small"]:
+        nkv = cache.k.shape[1]
         bound = plan["bound"] if plan["bound"] is not None else stride * cache.page_size
-        split = kernels.attn_decode_split()
-        num_splits = max((bound + split - 1) // split, 1)
+        pairs = plan["small"] * nkv * ((nh // nkv + 15) // 16)
+        split, num_splits = decode_split(bound, pairs)
         part_o = part_ml = None
         if num_splits > 1:
             part_o = ctx.workspace.get("attn.part_o", (plan["small"] * nh * num_splits * d,), torch.float32)
             part_ml = ctx.workspace.get("attn.part_ml", (plan["small"] * nh * num_splits * 2,), torch.float32)
         kernels.attn_decode_bf16(out, part_o, part_ml, q, cache.k, cache.v, ctx.positions, ctx.req_of_token, ctx.q_start,
-                                 ctx.num_entries, table, stride, window, scale, DEC_MAX, plan["direct"], num_splits,
+                                 ctx.num_entries, table, stride, window, scale, DEC_MAX, plan["direct"], split, num_splits,
                                  plan["small"], ctx.err)
