@@ -1,0 +1,336 @@
+// Matrix product for few tokens (decode): out[M, N] = x[M, K] . W[N, K]^T, bfloat16 in, float32
+// accumulation, on the 5th-generation tensor cores.
+//
+// The product is bound by reading W once, so the kernel is built around streaming W:
+//   * "swap AB": the 128 rows of a W tile are the M side of tcgen05.mma, the (padded) tokens the
+//     N side, so the accumulator D[128 features, tokens] lives in tensor memory (TMEM);
+//   * one thread issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of [128 x 64] W tiles and
+//     [tokens x 64] x tiles into a ring of shared-memory stages guarded by mbarriers; one thread
+//     issues the MMAs and releases stages with tcgen05.commit; all four warps read the accumulator
+//     back with tcgen05.ld for the epilogue;
+//   * K is split over the CTAs of a thread-block cluster; their partial tiles are summed through
+//     distributed shared memory in rank order (deterministic, no scratch in global memory).
+// Every wait on an mbarrier is bounded: on expiry the kernel sets XB_ERR_WAIT in the error word,
+// skips the remaining work, frees its TMEM and returns.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int TILE_N = 128;   // W rows (output features) per CTA
+constexpr int TILE_K = 64;    // K elements per stage (one 128-byte swizzle row)
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity; false (and the error bit) when it expires.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    atomicOr(err, XB_ERR_WAIT);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+// Shared-memory operand descriptor: K-major tile of 128-byte rows, 128-byte swizzle, 8-row groups
+// 1024 bytes apart (start address, leading and stride byte offsets in 16-byte units; version 1).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;                  // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;        // stride byte offset: next 8-row group
+    d |= (uint64_t)1 << 46;                  // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;                  // layout type: SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t umma_idesc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+// grid: (ceil(N / 128), splits); cluster (1, splits, 1).  mp: tokens padded to 16/32/64/128/256.
+template <typename TO>
+__global__ void __launch_bounds__(128)
+gemm_skinny_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                      TO* __restrict__ out, int M, int N, int K, int mp, int k_per_split, int stages, int* err) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long bars[2 * 16 + 1];
+    __shared__ uint32_t s_tmem;
+    // the dynamic window is aligned to 1024 bytes by hand (the swizzle repeats every 1024 bytes)
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t w_bytes = TILE_N * TILE_K * 2, x_bytes = (uint32_t)mp * TILE_K * 2;
+    const uint32_t stage_bytes = w_bytes + x_bytes;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * TILE_N;
+    const int k_begin = blockIdx.y * k_per_split;
+    const int k_end = min(K, k_begin + k_per_split);
+    const int iters = k_end > k_begin ? (k_end - k_begin + TILE_K - 1) / TILE_K : 0;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[16]), accum = smem_u32(&bars[32]);
+    const uint32_t tmem_cols = mp < 32 ? 32u : (uint32_t)mp;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+
+    if (threadIdx.x == 0) {
+        // ---- producer: stream W and x tiles -------------------------------------------------------
+        for (int it = 0; it < iters; ++it) {
+            const int s = it % stages;
+            if (it >= stages && !mbar_wait(empty0 + 8 * s, ((it / stages) & 1) ^ 1, err)) break;
+            const uint32_t dst = base + s * stage_bytes;
+            mbar_expect_tx(full0 + 8 * s, stage_bytes);
+            tma_load_2d(dst, &map_w, k_begin + it * TILE_K, n0, full0 + 8 * s);
+            tma_load_2d(dst + w_bytes, &map_x, k_begin + it * TILE_K, 0, full0 + 8 * s);
+        }
+    } else if (threadIdx.x == 32) {
+        // ---- MMA issuer -------------------------------------------------------------------------------
+        const uint32_t idesc = umma_idesc(mp);
+        bool ok = true;
+        for (int it = 0; it < iters && ok; ++it) {
+            const int s = it % stages;
+            ok = mbar_wait(full0 + 8 * s, (it / stages) & 1, err);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a = base + s * stage_bytes;
+            const uint64_t adesc = umma_desc(a), bdesc = umma_desc(a + w_bytes);
+#pragma unroll
+            for (int kk = 0; kk < TILE_K / 16; ++kk)   // 16 K elements = 32 bytes further along the swizzle row
+                umma_bf16(tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc, (it | kk) ? 1u : 0u);
+            umma_commit(empty0 + 8 * s);   // the stage is free once these MMAs have read it
+        }
+        umma_commit(accum);                 // arrives when every MMA issued so far is complete
+    }
+    // ---- epilogue: all four warps ----------------------------------------------------------------------
+    __syncwarp();
+    const bool ready = mbar_wait(accum, 0, err);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int row = warp * 32 + lane;         // TMEM lane = row of D = output feature n0 + row
+    const int n = n0 + row;
+    const uint32_t csize = cluster_size(), crank = cluster_rank();
+    float* part = reinterpret_cast<float*>(base_ptr);   // [mp][128] float32, over the (now idle) stages
+    for (int c0 = 0; c0 < mp; c0 += 16) {
+        float v[16];
+        if (ready && iters > 0) {
+            tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = 0.f;
+        }
+        if (csize == 1) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int m = c0 + i;
+                if (m < M && n < N) out[(size_t)m * N + n] = from_f32<TO>(v[i]);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) part[(c0 + i) * TILE_N + row] = v[i];
+        }
+    }
+    if (csize > 1) {
+        cluster_sync();   // every CTA of the cluster has written its partial tile
+        const uint32_t part_addr = base;
+        for (int m = (int)crank; m < M; m += (int)csize) {
+            float acc = 0.f;
+            for (uint32_t r = 0; r < csize; ++r) acc += ld_cluster_f32(part_addr + (uint32_t)(m * TILE_N + row) * 4u, r);
+            if (n < N) out[(size_t)m * N + n] = from_f32<TO>(acc);
+        }
+        cluster_sync();   // nobody leaves while a neighbour still reads its shared memory
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
+    }
+}
+
+// ---- host side: tensor maps (cached) and the launch ---------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr;
+    long long rows, cols;
+    int box_rows;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        return std::hash<const void*>()(k.ptr) ^ (std::hash<long long>()(k.rows) * 31) ^ (std::hash<long long>()(k.cols) * 131) ^ (size_t)k.box_rows * 7919;
+    }
+};
+
+// A [rows, cols] row-major bfloat16 matrix seen through boxes of [box_rows x 64] with 128-byte swizzle.
+bool tensor_map_2d(CUtensorMap* out, const void* ptr, long long rows, long long cols, int box_rows) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    const MapKey key{ptr, rows, cols, box_rows};
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return true;
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUtensorMap m;
+    const CUresult rc = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return false;
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = m;
+    *out = m;
+    return true;
+}
+
+template <typename TO>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int M, int N, int K, int mp, int splits,
+           int k_per_split, int stages, size_t smem, int* err, cudaStream_t stream) {
+    cudaFuncSetAttribute(gemm_skinny_tc_kernel<TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((N + TILE_N - 1) / TILE_N, splits, 1);
+    cfg.blockDim = dim3(128, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = splits;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t rc = cudaLaunchKernelEx(&cfg, gemm_skinny_tc_kernel<TO>, mw, mx, (TO*)out, M, N, K, mp, k_per_split, stages, err);
+    return rc != cudaSuccess ? (int)rc : xb_launch_status();
+}
+
+}  // namespace
+
+// out[M, N] (bfloat16 when out_f32 == 0, else float32) = x[M, K] . w[N, K]^T for M <= 256.
+// K must be a multiple of 8 (rows 16-byte aligned); `splits` in 1..8 CTAs share K through a
+// cluster (0: chosen here).  Returns cudaErrorNotSupported for shapes it does not take.
+XB_EXPORT int xb_gemm_skinny_tc(void* out, int out_f32, const void* x, const void* w, int M, int N, int K, int splits,
+                                int* err, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 256 || K % 8 || K < TILE_K || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return (int)cudaErrorNotSupported;
+    int mp = 16;
+    while (mp < M) mp *= 2;
+    const int k_tiles = (K + TILE_K - 1) / TILE_K;
+    const int n_tiles = (N + TILE_N - 1) / TILE_N;
+    if (splits <= 0) {
+        // enough CTAs to fill 148 SMs, at least 4 K tiles per CTA, at most 8 CTAs per cluster
+        splits = 1;
+        while (splits < 8 && n_tiles * splits < 148 && k_tiles / (splits * 2) >= 4) splits *= 2;
+    }
+    if (splits > 8) splits = 8;
+    int tiles_per_split = (k_tiles + splits - 1) / splits;
+    while (splits > 1 && (splits - 1) * tiles_per_split >= k_tiles) --splits;   // no empty split
+    tiles_per_split = (k_tiles + splits - 1) / splits;
+    const size_t stage_bytes = (size_t)TILE_N * TILE_K * 2 + (size_t)mp * TILE_K * 2;
+    // few tokens: stages small enough for two CTAs per SM, so that a wave holds every CTA
+    const size_t budget = mp <= 64 ? 100 * 1024 : 200 * 1024;
+    int stages = (int)(budget / stage_bytes);
+    if (stages > 12) stages = 12;
+    if (stages > tiles_per_split) stages = tiles_per_split < 2 ? 2 : tiles_per_split;
+    size_t smem = stages * stage_bytes;
+    const size_t part = (size_t)mp * TILE_N * 4;
+    if (splits > 1 && smem < part) smem = part;
+    smem += 1024;  // room to align the window to 1024 bytes
+    CUtensorMap mw, mx;
+    if (!tensor_map_2d(&mw, w, N, K, TILE_N) || !tensor_map_2d(&mx, x, M, K, mp)) return (int)cudaErrorNotSupported;
+    if (out_f32) return launch<float>(mw, mx, out, M, N, K, mp, splits, tiles_per_split * TILE_K, stages, smem, err, stream);
+    return launch<__nv_bfloat16>(mw, mx, out, M, N, K, mp, splits, tiles_per_split * TILE_K, stages, smem, err, stream);
+}

@@ -297,3 +297,26 @@ def attn_decode_bf16(out, part_o, part_ml, q, k_cache, v_cache, positions, req_o
         positions.data_ptr(), req_of_token.data_ptr(), q_start.data_ptr(), int(num_entries), block_table.data_ptr(),
         int(table_stride), nh, nkv, d, ps, num_pages, int(window or 0), float(scale), int(dec_max), int(bool(direct)),
         int(split), int(num_splits), int(tokens), err.data_ptr(), _stream()), "attn_decode_bf16", 2 if num_splits > 1 else 1)
+
+
+# ---- matrix product for few tokens on tcgen05 tensor cores ---------------------------------------------
+ERR_NOT_SUPPORTED = 801  # cudaErrorNotSupported
+
+
+def gemm_skinny_tc(out, x, w, err, splits: int = 0) -> bool:
+    """out[M, N] = x[M, K] . w[N, K]^T for M <= 256 with TMA-fed tcgen05 MMAs (bfloat16 in, float32
+    accumulation; ``out`` bfloat16 or float32).  Returns False, having done nothing, for shapes
+    the kernel does not take (K not a multiple of 8, K < 64, M > 256)."""
+    M, K = x.shape
+    N = w.shape[0]
+    _need(x, "x", torch.bfloat16, (M, K))
+    _need(w, "w", torch.bfloat16, (N, K))
+    _need(out, "out", None, (M, N))
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError(f"out must be bfloat16 or float32, not {out.dtype}")
+    rc = kernels_lib().xb_gemm_skinny_tc(out.data_ptr(), int(out.dtype == torch.float32), x.data_ptr(), w.data_ptr(),
+                                         M, N, K, int(splits), err.data_ptr(), _stream())
+    if rc == ERR_NOT_SUPPORTED:
+        return False
+    _ok(rc, "gemm_skinny_tc")
+    return True
