@@ -481,30 +481,44 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
 }
 
 // out[t, h] = sum_s w_s O_s / sum_s w_s with w_s = L_s * 2^(M_s - max M) over the key ranges the
-// token's keys touch (the same ranges the decode kernel worked on).  One warp per (token, head).
-__global__ void attn_combine_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
-                                    const float* __restrict__ part_ml, const int* __restrict__ positions,
-                                    const int* __restrict__ req_of_token, const int* __restrict__ q_start,
-                                    int num_entries, int nh, int d, int window, int dec_max, int direct,
-                                    int split, int num_splits) {
-    const int lane = threadIdx.x & 31;
-    const int h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (h >= nh) return;
+// token's keys touch (the same ranges the decode kernel worked on).  One block per (token, head):
+// the weights are formed once in shared memory (at most XB_MAX_SPLITS ranges), then every thread
+// sums its columns over the ranges in range order.
+constexpr int MAX_SPLITS = 1024;
+
+__global__ void __launch_bounds__(128)
+attn_combine_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
+                    const float* __restrict__ part_ml, const int* __restrict__ positions,
+                    const int* __restrict__ req_of_token, const int* __restrict__ q_start, int num_entries,
+                    int nh, int d, int window, int dec_max, int direct, int split, int num_splits) {
+    __shared__ float s_w[MAX_SPLITS];
+    __shared__ float s_red[33];
+    const int h = blockIdx.y;
     const int t = small_token(blockIdx.x, q_start, num_entries, dec_max, direct);
     if (t < 0 || req_of_token[t] < 0) return;
     const int pos = positions[t];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int s0 = lo / split, s1 = pos / split;
-    const size_t base = ((size_t)blockIdx.x * nh + h) * num_splits;
+    const int ns = s1 - s0 + 1;
+    const size_t base = ((size_t)blockIdx.x * nh + h) * num_splits + s0;
+    float mloc = -INFINITY;
+    for (int i = threadIdx.x; i < ns; i += blockDim.x) mloc = fmaxf(mloc, part_ml[(base + i) * 2]);
+    mloc = warp_max(mloc);
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = mloc;
+    __syncthreads();
     float M = -INFINITY;
-    for (int s = s0; s <= s1; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-    float W = 0.f;
-    for (int s = s0; s <= s1; ++s) W += part_ml[(base + s) * 2 + 1] * exp2f(part_ml[(base + s) * 2] - M);
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) M = fmaxf(M, s_red[w]);
+    for (int i = threadIdx.x; i < ns; i += blockDim.x)
+        s_w[i] = part_ml[(base + i) * 2 + 1] * exp2f(part_ml[(base + i) * 2] - M);
+    __syncthreads();
+    float W = 0.f;   // summed in range order by every thread: the same value everywhere
+    for (int i = 0; i < ns; ++i) W += s_w[i];
     const float inv = W > 0.f ? 1.f / W : 0.f;
-    for (int c = lane; c < d; c += 32) {
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
         float acc = 0.f;
-        for (int s = s0; s <= s1; ++s)
-            acc += part_o[(base + s) * d + c] * (part_ml[(base + s) * 2 + 1] * exp2f(part_ml[(base + s) * 2] - M));
+        const float* src = part_o + base * d + c;
+#pragma unroll 8
+        for (int i = 0; i < ns; ++i) acc += src[(size_t)i * d] * s_w[i];
         out[((size_t)t * nh + h) * d + c] = __float2bfloat16_rn(acc * inv);
     }
 }
@@ -586,6 +600,7 @@ XB_EXPORT int xb_attn_decode_bf16(void* out, float* part_o, float* part_ml, cons
     if (tokens <= 0) return 0;
     if (d % 16 || d > 256 || nh % nkv || num_splits < 1 || split < KT || split % KT || ps <= 0) return (int)cudaErrorInvalidValue;
     if (num_splits > 1 && (!part_o || !part_ml)) return (int)cudaErrorInvalidValue;
+    if (num_splits > MAX_SPLITS) return (int)cudaErrorInvalidValue;
     const float sl2 = scale * 1.4426950408889634f;
     int rc;
 #define XB_GO(DP) rc = launch_decode<DP>(out, part_o, part_ml, q, kc, vc, positions, req_of_token, q_start, num_entries, table, stride, nh, nkv, d, ps, num_pages, window, sl2, dec_max, direct, split, num_splits, tokens, err, stream)
@@ -594,7 +609,7 @@ XB_EXPORT int xb_attn_decode_bf16(void* out, float* part_o, float* part_ml, cons
     else XB_GO(256);
 #undef XB_GO
     if (rc != 0 || num_splits == 1) return rc;
-    attn_combine_kernel<<<dim3(tokens, (nh + 3) / 4), 128, 0, stream>>>(
+    attn_combine_kernel<<<dim3(tokens, nh), 128, 0, stream>>>(
         (__nv_bfloat16*)out, part_o, part_ml, positions, req_of_token, q_start, num_entries, nh, d, window, dec_max,
         direct, split, num_splits);
     return xb_launch_status();

@@ -99,5 +99,5 @@ class DecoderModel:
             return logits
         y = ws.get("model.final", (R, H), self.dtype)
         self.final_norm.forward(y, x, ctx, branch=pending, rows=ctx.logit_rows)
-        linear(logits, y, self.head)
+        linear(logits, y, self.head, ctx.err)
         return logits

@@ -66,7 +66,7 @@ class Attention(Mixer):
         nh, nkv, d = s.num_heads, s.num_kv_heads, s.head_dim
         ws = ctx.workspace
         qkv = ws.get("attn.qkv", (T, (nh + 2 * nkv) * d), self.dtype)
-        linear(qkv, x, self.w_qkv)
+        linear(qkv, x, self.w_qkv, ctx.err)
         rot = self.position.rotary() if self.position is not None else None
         if self.position is not None and rot is None:
             q_view = qkv[:, : nh * d].view(T, nh, d)
@@ -83,7 +83,7 @@ class Attention(Mixer):
         from . import attention_backend
         attention_backend.attend(o, q, cache, ctx, table, stride, s.window, s.scale)
         out = ws.get("attn.out", (T, s.hidden), self.dtype)
-        linear(out, o.view(T, nh * d), self.w_o)
+        linear(out, o.view(T, nh * d), self.w_o, ctx.err)
         return out
 
 

@@ -31,7 +31,7 @@ def decode_split(bound: int, pairs: int) -> tuple:
     """Range length (a multiple of 64) and number of ranges for keys up to ``bound`` when
     ``pairs`` (token, key/value head) pairs share the machine: few pairs are cut finely so that
     every SM gets work, many pairs are left whole so that nothing has to be merged."""
-    want = max((DECODE_TARGET_CTAS + pairs - 1) // max(pairs, 1), 1)
+    want = min(max((DECODE_TARGET_CTAS + pairs - 1) // max(pairs, 1), 1), 1024)   # the merge takes at most 1024 ranges
     split = max(((bound + want - 1) // want + 63) // 64 * 64, 64)
     return split, max((bound + split - 1) // split, 1)
 

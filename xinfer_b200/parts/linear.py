@@ -1,8 +1,8 @@
 """Dense projection ``y = x . W^T`` with ``W`` stored ``[out, in]`` (src/models/layers/linear.rs:76-124).
 
-float32: the engine's own FMA kernel (true 32-bit, no tensor-core mode).  bfloat16: the library
-matrix product, as in the reference (cuBLAS through its tensor library), until a hand-written
-tcgen05 kernel takes a shape over (see ``gemm_backend``).
+float32: the engine's own FMA kernel (true 32-bit, no tensor-core mode).  bfloat16: the engine's
+tcgen05 kernel for steps of few tokens, else the library matrix product, as in the reference
+(cuBLAS through its tensor library); see ``gemm_backend``.
 """
 from __future__ import annotations
 
@@ -13,11 +13,12 @@ import torch
 from .. import kernels
 
 
-def linear(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    """out[M, N] = x[M, K] . weight[N, K]^T.  ``out`` may be float32 for bfloat16 inputs."""
+def linear(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, err: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[M, N] = x[M, K] . weight[N, K]^T.  ``out`` may be float32 for bfloat16 inputs.
+    ``err``: the step's device error word (kernels with bounded waits report there)."""
     if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
         from . import gemm_backend
-        if gemm_backend.try_fast(out, x, weight):
+        if gemm_backend.try_fast(out, x, weight, err):
             return out
         if out.dtype == torch.bfloat16:
             torch.mm(x, weight.t(), out=out)

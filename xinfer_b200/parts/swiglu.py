@@ -46,11 +46,11 @@ class SwiGLU(FeedForward):
         T = x.shape[0]
         ws = ctx.workspace
         gu = ws.get("ffn.gate_up", (T, 2 * s.intermediate), self.dtype)
-        linear(gu, x, self.w_gate_up)
+        linear(gu, x, self.w_gate_up, ctx.err)
         act = ws.get("ffn.act", (T, s.intermediate), self.dtype)
         kernels.swiglu(act, gu)
         out = ws.get("ffn.out", (T, s.hidden), self.dtype)
-        linear(out, act, self.w_down)
+        linear(out, act, self.w_down, ctx.err)
         return out
 
 
