@@ -383,5 +383,6 @@ def test_decode_split_choice():
     for bound, pairs in [(1, 1), (4096, 8), (4096, 64), (4096, 512), (40000, 8), (100, 4096)]:
         split, n = decode_split(bound, pairs)
         assert split % 64 == 0 and split >= 64 and (n - 1) * split < bound <= n * split
-    assert decode_split(4096, 512) == (2048, 2)
-    assert decode_split(4096, 8)[0] == 64
+    assert decode_split(4096, 8)[1] >= 16              # few pairs: cut finely
+    assert decode_split(4096, 64)[1] * 64 <= 444       # one wave holds every CTA
+    assert decode_split(64, 5000) == (64, 1)

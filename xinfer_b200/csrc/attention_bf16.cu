@@ -8,8 +8,8 @@
 //    head, range of key positions): the query heads that share the key/value head form the rows
 //    of the tile, four warps take 16 keys each of every 64-key tile.  Ranges are cut at absolute
 //    positions (multiples of the range length the host picks for the launch).  With more than one
-//    range the CTAs write normalised partial outputs and (max, sum) to scratch memory and
-//    attn_combine_kernel merges them.
+//    range the CTAs write normalised partial outputs and (max, sum) to scratch memory, and the
+//    CTA that finishes last for a (token, key/value head) merges them in range order.
 //
 // Cache layout: [num_pages, kv_heads, page_size, head_dim]; any page size.
 // Keys a query at position p may see: max(0, p - window + 1) .. p  (window <= 0: from 0).
@@ -339,7 +339,7 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
                    const int* __restrict__ req_of_token, const int* __restrict__ q_start, int num_entries,
                    const int* __restrict__ block_table, int table_stride, int nh, int nkv, int d, int ps,
                    int ps_shift, int num_pages, int window, float scale_log2, int dec_max, int direct, int split,
-                   int num_splits, int page_cap, int* err) {
+                   int num_splits, int page_cap, int* __restrict__ tickets, int* err) {
     constexpr int NT = 128;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ float s_m[4][16], s_l[4][16];
@@ -478,48 +478,46 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
             }
         }
     }
-}
-
-// out[t, h] = sum_s w_s O_s / sum_s w_s with w_s = L_s * 2^(M_s - max M) over the key ranges the
-// token's keys touch (the same ranges the decode kernel worked on).  One block per (token, head):
-// the weights are formed once in shared memory (at most XB_MAX_SPLITS ranges), then every thread
-// sums its columns over the ranges in range order.
-constexpr int MAX_SPLITS = 1024;
-
-__global__ void __launch_bounds__(128)
-attn_combine_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
-                    const float* __restrict__ part_ml, const int* __restrict__ positions,
-                    const int* __restrict__ req_of_token, const int* __restrict__ q_start, int num_entries,
-                    int nh, int d, int window, int dec_max, int direct, int split, int num_splits) {
-    __shared__ float s_w[MAX_SPLITS];
-    __shared__ float s_red[33];
-    const int h = blockIdx.y;
-    const int t = small_token(blockIdx.x, q_start, num_entries, dec_max, direct);
-    if (t < 0 || req_of_token[t] < 0) return;
-    const int pos = positions[t];
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int s0 = lo / split, s1 = pos / split;
+    if (num_splits == 1) return;
+    // The CTA that finishes last among the ranges of this (token, key/value head) merges them:
+    //   out[h] = sum_s w_s O_s / sum_s w_s,  w_s = L_s * 2^(M_s - max M),  in range order.
+    __shared__ int s_last;
+    const int s0 = lo / split, s1 = pos / split;   // the ranges this token's keys touch
     const int ns = s1 - s0 + 1;
-    const size_t base = ((size_t)blockIdx.x * nh + h) * num_splits + s0;
-    float mloc = -INFINITY;
-    for (int i = threadIdx.x; i < ns; i += blockDim.x) mloc = fmaxf(mloc, part_ml[(base + i) * 2]);
-    mloc = warp_max(mloc);
-    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = mloc;
+    __threadfence();
     __syncthreads();
-    float M = -INFINITY;
-    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) M = fmaxf(M, s_red[w]);
-    for (int i = threadIdx.x; i < ns; i += blockDim.x)
-        s_w[i] = part_ml[(base + i) * 2 + 1] * exp2f(part_ml[(base + i) * 2] - M);
+    if (threadIdx.x == 0) {
+        int* ticket = tickets + (size_t)blockIdx.z * gridDim.y + blockIdx.y;
+        const int mine = atomicAdd(ticket, 1);
+        s_last = mine == ns - 1;
+        if (s_last) *ticket = 0;   // ready for the next launch
+    }
     __syncthreads();
-    float W = 0.f;   // summed in range order by every thread: the same value everywhere
-    for (int i = 0; i < ns; ++i) W += s_w[i];
-    const float inv = W > 0.f ? 1.f / W : 0.f;
-    for (int c = threadIdx.x; c < d; c += blockDim.x) {
-        float acc = 0.f;
-        const float* src = part_o + base * d + c;
+    if (!s_last) return;
+    __threadfence();
+    for (int row = warp; row < rows; row += 4) {
+        const int h = h0 + row;
+        const size_t base = ((size_t)blockIdx.z * nh + h) * num_splits + s0;
+        float mloc = -INFINITY;
+        for (int i = lane; i < ns; i += 32) mloc = fmaxf(mloc, __ldcg(part_ml + (base + i) * 2));
+        const float M = warp_max(mloc);
+        float wloc = 0.f;
+        for (int i = lane; i < ns; i += 32)
+            wloc += __ldcg(part_ml + (base + i) * 2 + 1) * exp2f(__ldcg(part_ml + (base + i) * 2) - M);
+        const float W = warp_sum(wloc);
+        const float inv = W > 0.f ? 1.f / W : 0.f;
+        for (int c4 = lane * 4; c4 < d; c4 += 128) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 8
-        for (int i = 0; i < ns; ++i) acc += src[(size_t)i * d] * s_w[i];
-        out[((size_t)t * nh + h) * d + c] = __float2bfloat16_rn(acc * inv);
+            for (int i = 0; i < ns; ++i) {
+                const float w = __ldcg(part_ml + (base + i) * 2 + 1) * exp2f(__ldcg(part_ml + (base + i) * 2) - M);
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(part_o + (base + i) * d + c4));
+                acc.x += v.x * w; acc.y += v.y * w; acc.z += v.z * w; acc.w += v.w * w;
+            }
+            __nv_bfloat16* dst = out + ((size_t)t * nh + h) * d + c4;
+            *reinterpret_cast<uint32_t*>(dst) = pack_bf16(acc.x * inv, acc.y * inv);
+            *reinterpret_cast<uint32_t*>(dst + 2) = pack_bf16(acc.z * inv, acc.w * inv);
+        }
     }
 }
 
@@ -550,7 +548,7 @@ template <int DP>
 int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const void* kc, const void* vc,
                   const int* positions, const int* req_of_token, const int* q_start, int num_entries, const int* table,
                   int stride, int nh, int nkv, int d, int ps, int num_pages, int window, float scale_log2, int dec_max,
-                  int direct, int split, int num_splits, int tokens, int* err, cudaStream_t stream) {
+                  int direct, int split, int num_splits, int tokens, int* tickets, int* err, cudaStream_t stream) {
     const size_t kv = 4 * (size_t)KT * DP * 2, merge = 4 * 16 * (size_t)DP * 4;
     int page_cap = (split + KT) / ps + 2;
     if (page_cap > PAGE_CAP_MAX) page_cap = 0;
@@ -560,7 +558,7 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const
     attn_decode_kernel<DP><<<dim3(num_splits, nkv * qtiles, tokens), 128, smem, stream>>>(
         (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc,
         positions, req_of_token, q_start, num_entries, table, stride, nh, nkv, d, ps, shift_of(ps), num_pages, window,
-        scale_log2, dec_max, direct, split, num_splits, page_cap, err);
+        scale_log2, dec_max, direct, split, num_splits, page_cap, tickets, err);
     return xb_launch_status();
 }
 
@@ -590,27 +588,24 @@ XB_EXPORT int xb_attn_prefill_bf16(void* out, const void* q, const void* kc, con
 
 // Tokens of portions of at most dec_max tokens (`tokens` of them; direct != 0: every token of the
 // batch is one).  Keys are cut into ranges of `split` positions (a multiple of 64) at absolute
-// positions; num_splits = ceil(longest context / split).  part_o: [tokens, nh, num_splits, d]
-// float32, part_ml: [tokens, nh, num_splits, 2]; both may be null when num_splits == 1.
+// positions; num_splits = ceil(longest context / split).  Scratch, needed when num_splits > 1:
+// part_o [tokens, nh, num_splits, d] float32, part_ml [tokens, nh, num_splits, 2] float32 and
+// tickets [tokens * kv heads * ceil(group / 16)] int32, zero before the first launch (the kernel
+// leaves them zero).
 XB_EXPORT int xb_attn_decode_bf16(void* out, float* part_o, float* part_ml, const void* q, const void* kc,
                                   const void* vc, const int* positions, const int* req_of_token, const int* q_start,
                                   int num_entries, const int* table, int stride, int nh, int nkv, int d, int ps,
                                   int num_pages, int window, float scale, int dec_max, int direct, int split,
-                                  int num_splits, int tokens, int* err, cudaStream_t stream) {
+                                  int num_splits, int tokens, int* tickets, int* err, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (d % 16 || d > 256 || nh % nkv || num_splits < 1 || split < KT || split % KT || ps <= 0) return (int)cudaErrorInvalidValue;
-    if (num_splits > 1 && (!part_o || !part_ml)) return (int)cudaErrorInvalidValue;
-    if (num_splits > MAX_SPLITS) return (int)cudaErrorInvalidValue;
+    if (num_splits > 1 && (!part_o || !part_ml || !tickets)) return (int)cudaErrorInvalidValue;
     const float sl2 = scale * 1.4426950408889634f;
     int rc;
-#define XB_GO(DP) rc = launch_decode<DP>(out, part_o, part_ml, q, kc, vc, positions, req_of_token, q_start, num_entries, table, stride, nh, nkv, d, ps, num_pages, window, sl2, dec_max, direct, split, num_splits, tokens, err, stream)
+#define XB_GO(DP) rc = launch_decode<DP>(out, part_o, part_ml, q, kc, vc, positions, req_of_token, q_start, num_entries, table, stride, nh, nkv, d, ps, num_pages, window, sl2, dec_max, direct, split, num_splits, tokens, tickets, err, stream)
     if (d <= 64) XB_GO(64);
     else if (d <= 128) XB_GO(128);
     else XB_GO(256);
 #undef XB_GO
-    if (rc != 0 || num_splits == 1) return rc;
-    attn_combine_kernel<<<dim3(tokens, nh), 128, 0, stream>>>(
-        (__nv_bfloat16*)out, part_o, part_ml, positions, req_of_token, q_start, num_entries, nh, d, window, dec_max,
-        direct, split, num_splits);
-    return xb_launch_status();
+    return rc;
 }

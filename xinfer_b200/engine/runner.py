@@ -400,9 +400,16 @@ class ModelRunner:
             wide = tuple(widest for _ in strides)
             tmp = torch.zeros(3 * (top + 4) + 3 * (top + 5) + top + 8 + sum(top * s + 4 for s in wide) + 64,
                               dtype=torch.int32, device=self.device)
-            big = self.assembler.prepare(entries, pad_entries=top, pad_tokens=top, pad_rows=top, strides=wide,
-                                         into=tmp, workspace=ws)
-            self.model.forward(big, self.layer_caches, self.layer_states)
+            # every bucket once (scratch sizes are not monotonic in the batch size), largest first
+            sizes = []
+            b = top
+            while b >= 1:
+                sizes.append(b)
+                b //= 2
+            for b in sizes:
+                big = self.assembler.prepare(entries[:b], pad_entries=b, pad_tokens=b, pad_rows=b, strides=wide,
+                                             into=tmp, workspace=ws)
+                self.model.forward(big, self.layer_caches, self.layer_states)
             torch.cuda.current_stream().synchronize()
             del tmp
             ws.sized = True

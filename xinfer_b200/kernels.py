@@ -271,9 +271,10 @@ def attn_prefill_bf16(out, q, k_cache, v_cache, q_start, start_pos, num_entries,
 
 
 def attn_decode_bf16(out, part_o, part_ml, q, k_cache, v_cache, positions, req_of_token, q_start, num_entries,
-                     block_table, table_stride, window, scale, dec_max, direct, split, num_splits, tokens, err):
+                     block_table, table_stride, window, scale, dec_max, direct, split, num_splits, tokens, err, tickets=None):
     """Tokens of portions of at most ``dec_max`` tokens (``tokens`` of them); keys are cut into
-    ``num_splits`` ranges of ``split`` positions (a multiple of 64).  ``part_o`` /
+    ``num_splits`` ranges of ``split`` positions (a multiple of 64).  ``tickets``: int32 scratch of
+    tokens * kv_heads * ceil(group / 16) zeros (left zero), needed with ``num_splits`` > 1.  ``part_o`` /
     ``part_ml``: float32 scratch of at least tokens*heads*num_splits*head_dim and
     tokens*heads*num_splits*2 elements when ``num_splits`` > 1."""
     T, nh, d = q.shape
@@ -292,11 +293,14 @@ def attn_decode_bf16(out, part_o, part_ml, q, k_cache, v_cache, positions, req_o
         _need(part_ml, "part_ml", torch.float32)
         if part_o.numel() < tokens * nh * num_splits * d or part_ml.numel() < tokens * nh * num_splits * 2:
             raise KernelError("attention scratch buffers are too small for the number of key ranges")
+        _need(tickets, "tickets", torch.int32)
+        if tickets.numel() < tokens * nkv * ((nh // nkv + 15) // 16):
+            raise KernelError("the attention ticket buffer is too small")
     _ok(kernels_lib().xb_attn_decode_bf16(
         out.data_ptr(), _ptr(part_o), _ptr(part_ml), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
         positions.data_ptr(), req_of_token.data_ptr(), q_start.data_ptr(), int(num_entries), block_table.data_ptr(),
         int(table_stride), nh, nkv, d, ps, num_pages, int(window or 0), float(scale), int(dec_max), int(bool(direct)),
-        int(split), int(num_splits), int(tokens), err.data_ptr(), _stream()), "attn_decode_bf16", 2 if num_splits > 1 else 1)
+        int(split), int(num_splits), int(tokens), _ptr(tickets), err.data_ptr(), _stream()), "attn_decode_bf16")
 
 
 # ---- matrix product for few tokens on tcgen05 tensor cores ---------------------------------------------

@@ -98,4 +98,4 @@ def _declare_kernels(lib):
     _sig(lib, "xb_gemm_skinny_tc", I, [P, I, P, P, I, I, I, I, P, P])
     _sig(lib, "xb_attn_prefill_bf16", I, [P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, I, I, I, P, P])
     _sig(lib, "xb_attn_decode_bf16", I,
-         [P, P, P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, I, I, I, I, P, P])
+         [P, P, P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, I, I, I, I, P, P, P])

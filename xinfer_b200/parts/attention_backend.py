@@ -14,8 +14,11 @@ from .. import kernels
 
 # portions up to this many tokens are treated token by token by the decode kernel
 DEC_MAX = 4
-# CTAs the decode kernel should at least be cut into (a few per SM of a 148-SM part)
-DECODE_TARGET_CTAS = 592
+# CTAs of the decode kernel that are resident at once (three per SM of a 148-SM part): key ranges
+# are cut so that one wave holds them all
+DECODE_RESIDENT_CTAS = 444
+# what starting a CTA of the decode kernel costs, in key positions of work
+DECODE_CTA_OVERHEAD = 96
 PREFILL_WARPS = 8
 
 _enabled = True
@@ -29,11 +32,24 @@ def set_tiled(flag: bool) -> None:
 
 def decode_split(bound: int, pairs: int) -> tuple:
     """Range length (a multiple of 64) and number of ranges for keys up to ``bound`` when
-    ``pairs`` (token, key/value head) pairs share the machine: few pairs are cut finely so that
-    every SM gets work, many pairs are left whole so that nothing has to be merged."""
-    want = min(max((DECODE_TARGET_CTAS + pairs - 1) // max(pairs, 1), 1), 1024)   # the merge takes at most 1024 ranges
-    split = max(((bound + want - 1) // want + 63) // 64 * 64, 64)
-    return split, max((bound + split - 1) // split, 1)
+    ``pairs`` (token, key/value head) pairs share the machine.  Each CTA costs its range plus a
+    fixed start-up (about ``DECODE_CTA_OVERHEAD`` keys' worth); CTAs run in waves of
+    ``DECODE_RESIDENT_CTAS``.  The cheapest cut wins: few pairs are cut finely so that every SM
+    gets work, many pairs coarsely so that little has to be merged and the last wave is full."""
+    pairs = max(pairs, 1)
+    best = None
+    tiles = max((bound + 63) // 64, 1)
+    for per in range(1, tiles + 1):                # 64-key tiles per range
+        n = (tiles + per - 1) // per
+        if n > 1024:
+            continue
+        if best is not None and per > 1 and (tiles + per - 2) // (per - 1) == n:
+            continue                               # same number of ranges as the shorter cut
+        waves = (pairs * n + DECODE_RESIDENT_CTAS - 1) // DECODE_RESIDENT_CTAS
+        cost = waves * (per * 64 + DECODE_CTA_OVERHEAD)
+        if best is None or cost < best[0]:
+            best = (cost, per * 64, n)
+    return best[1], best[2]
 
 
 def _plan(ctx, head_dim: int):
@@ -71,10 +87,11 @@ def attend(out, q, cache, ctx, table, stride, window, scale) -> None:
         bound = plan["bound"] if plan["bound"] is not None else stride * cache.page_size
         pairs = plan["small"] * nkv * ((nh // nkv + 15) // 16)
         split, num_splits = decode_split(bound, pairs)
-        part_o = part_ml = None
+        part_o = part_ml = tickets = None
         if num_splits > 1:
             part_o = ctx.workspace.get("attn.part_o", (plan["small"] * nh * num_splits * d,), torch.float32)
             part_ml = ctx.workspace.get("attn.part_ml", (plan["small"] * nh * num_splits * 2,), torch.float32)
+            tickets = ctx.workspace.get("attn.tickets", (pairs,), torch.int32)   # zero-filled when made, left zero
         kernels.attn_decode_bf16(out, part_o, part_ml, q, cache.k, cache.v, ctx.positions, ctx.req_of_token, ctx.q_start,
                                  ctx.num_entries, table, stride, window, scale, DEC_MAX, plan["direct"], split, num_splits,
-                                 plan["small"], ctx.err)
+                                 plan["small"], ctx.err, tickets)
