@@ -537,6 +537,7 @@ int launch_prefill(void* out, const void* q, const void* kc, const void* vc, con
     if (page_cap > PAGE_CAP_MAX) page_cap = 0;
     const size_t smem = (size_t)NW * 16 * DP * 2 + 4 * KT * DP * 2 + (size_t)page_cap * 4;
     cudaFuncSetAttribute(attn_prefill_kernel<DP, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(attn_prefill_kernel<DP, NW>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     attn_prefill_kernel<DP, NW><<<dim3(tiles, nh), NW * 32, smem, stream>>>(
         (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, q_start,
         start_pos, num_entries, table, stride, nh, nkv, d, ps, shift_of(ps), num_pages, window, scale_log2, dec_max,
@@ -554,6 +555,7 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const
     if (page_cap > PAGE_CAP_MAX) page_cap = 0;
     const size_t smem = 16 * DP * 2 + (kv > merge ? kv : merge) + (size_t)page_cap * 4;
     cudaFuncSetAttribute(attn_decode_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(attn_decode_kernel<DP>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     const int qtiles = (nh / nkv + 15) / 16;
     attn_decode_kernel<DP><<<dim3(num_splits, nkv * qtiles, tokens), 128, smem, stream>>>(
         (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc,
