@@ -327,8 +327,28 @@ TILED_CASES = CASES + [
 ]
 
 
+@pytest.fixture(params=[True, False], ids=["tcgen05", "mma_sync"])
+def prefill_family(request, monkeypatch):
+    """Long portions run on the tcgen05 kernel where it takes the sizes, else on the mma.sync
+    kernel; tests with this fixture run both."""
+    from xinfer_b200.parts import attention_backend
+    monkeypatch.setattr(attention_backend, "PREFILL_TC", request.param)
+    return request.param
+
+
 @pytest.mark.parametrize("nh,nkv,d,ps,entries,window", TILED_CASES)
-def test_attention_tiled_bf16(nh, nkv, d, ps, entries, window):
+def test_attention_tiled_bf16(nh, nkv, d, ps, entries, window, prefill_family):
+    worst = attention_case(tiled_kernel, torch.bfloat16, nh, nkv, d, ps, entries, window)
+    assert worst <= tol(torch.bfloat16, 2), worst
+
+
+@pytest.mark.parametrize("nh,nkv,d,ps,entries,window", [
+    (2, 1, 128, 16, [(0, 128)], None), (2, 1, 128, 16, [(0, 200)], None), (4, 2, 64, 8, [(37, 300), (0, 129)], None),
+    (4, 4, 96, 32, [(1000, 260)], 200), (2, 2, 16, 64, [(5, 150)], None), (8, 2, 128, 128, [(100, 500), (0, 6)], 333),
+    (3, 1, 48, 16, [(600, 700)], None)])
+def test_attention_prefill_tcgen05(nh, nkv, d, ps, entries, window, monkeypatch):
+    from xinfer_b200.parts import attention_backend
+    monkeypatch.setattr(attention_backend, "PREFILL_TC", True)
     worst = attention_case(tiled_kernel, torch.bfloat16, nh, nkv, d, ps, entries, window)
     assert worst <= tol(torch.bfloat16, 2), worst
 
@@ -337,7 +357,7 @@ def test_attention_tiled_sees_one_far_key_and_the_windows_edge():
     far_key_checks(tiled_kernel, torch.bfloat16)
 
 
-def test_attention_tiled_far_key_in_a_long_prompt_portion():
+def test_attention_tiled_far_key_in_a_long_prompt_portion(prefill_family):
     """The same planted key, but seen from the prefill kernel: a 70-token portion starting at 400."""
     nh, nkv, d, ps = 4, 2, 64, 16
     for win, far, visible in ((None, 5, True), (128, 400 + 69 - 128 + 1, True), (128, 400 + 69 - 128, False)):

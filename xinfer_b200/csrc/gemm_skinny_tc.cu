@@ -23,7 +23,7 @@ namespace {
 
 constexpr int TILE_N = 128;   // W rows (output features) per CTA
 constexpr int TILE_K = 64;    // K elements per stage (one 128-byte swizzle row)
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr long long WAIT_CYCLES = 400000000LL;  // about 0.2 s: a wait that long has failed
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -35,7 +35,8 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 }
 // Bounded wait for the phase with the given parity; false (and the error bit) when it expires.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    const long long t0 = clock64();
+    for (;;) {
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -43,6 +44,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* er
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
         if (ok) return true;
+        if (clock64() - t0 > WAIT_CYCLES) break;
     }
     atomicOr(err, XB_ERR_WAIT);
     return false;

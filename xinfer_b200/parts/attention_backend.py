@@ -20,6 +20,9 @@ DECODE_RESIDENT_CTAS = 444
 # what starting a CTA of the decode kernel costs, in key positions of work
 DECODE_CTA_OVERHEAD = 96
 PREFILL_WARPS = 8
+# portions of many tokens go to the tcgen05 kernel where it takes the sizes (head size <= 128,
+# page size a power of two >= 8), else to the mma.sync kernel
+PREFILL_TC = True
 
 _enabled = True
 
@@ -79,7 +82,11 @@ def attend(out, q, cache, ctx, table, stride, window, scale) -> None:
                                 window, scale, ctx.err)
         return
     plan = _plan(ctx, d)
-    if plan["tiles"]:
+    took = False
+    if plan["tiles"] and PREFILL_TC and kernels.attn_prefill_queries(d, PREFILL_WARPS) == 128:
+        took = kernels.attn_prefill_tc(out, q, cache.k, cache.v, ctx.q_start, ctx.start_pos, ctx.num_entries, table, stride,
+                                       window, scale, DEC_MAX, plan["tiles"], ctx.err)
+    if plan["tiles"] and not took:
         kernels.attn_prefill_bf16(out, q, cache.k, cache.v, ctx.q_start, ctx.start_pos, ctx.num_entries, table, stride,
                                   window, scale, DEC_MAX, plan["tiles"], plan["prefill_bound"], ctx.err, warps=PREFILL_WARPS)
     if plan["small"]:
