@@ -611,3 +611,63 @@ XB_EXPORT int xb_attn_decode_bf16(void* out, float* part_o, float* part_ml, cons
 #undef XB_GO
     return rc;
 }
+
+// ------------------------------------------------------------------------------------------------
+// The same decode attention for callers that cannot allocate (see no_alloc.h): the scratch that
+// xb_attn_decode_bf16 takes from its caller lives in a fixed device array of this module.
+// ------------------------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+namespace {
+// Device memory that belongs to the loaded module.  In host code this name is only a handle for
+// cudaGetSymbolAddress, never an address a kernel may be given.
+static __device__ __align__(256) unsigned char xb_noalloc_scratch[XB_NOALLOC_SCRATCH_BYTES];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+unsigned char* g_noalloc_base[NOALLOC_MAX_DEVICES] = {};
+
+size_t noalloc_align(size_t n) { return (n + 255) & ~(size_t)255; }
+}  // namespace
+
+// Bytes of the built-in array a call with these sizes would use (tickets, (max, sum) pairs, partials).
+XB_EXPORT long long xb_attn_decode_bf16_noalloc_need(int nh, int nkv, int d, int num_splits, int tokens) {
+    if (num_splits <= 1 || tokens <= 0 || nkv <= 0) return 0;
+    const size_t pairs = (size_t)tokens * nkv * ((nh / nkv + 15) / 16);
+    const size_t slots = (size_t)tokens * nh * num_splits;
+    return (long long)(noalloc_align(pairs * sizeof(int)) + noalloc_align(slots * 2 * sizeof(float)) + slots * d * sizeof(float));
+}
+
+XB_EXPORT int xb_attn_decode_bf16_noalloc(void* out, const void* q, const void* kc, const void* vc, const int* positions,
+                                          const int* req_of_token, const int* q_start, int num_entries,
+                                          const int* table, int stride, int nh, int nkv, int d, int ps, int num_pages,
+                                          int window, float scale, int dec_max, int direct, int split, int num_splits,
+                                          int tokens, int* err, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (nkv <= 0 || nh % nkv) return (int)cudaErrorInvalidValue;
+    if ((size_t)xb_attn_decode_bf16_noalloc_need(nh, nkv, d, num_splits, tokens) > (size_t)XB_NOALLOC_SCRATCH_BYTES)
+        return XB_NOALLOC_TOO_LARGE;
+    // the array's address on the current device, looked up once per device
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return XB_NOALLOC_NO_SYMBOL;
+    if (!g_noalloc_base[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, xb_noalloc_scratch) != cudaSuccess || !p) return XB_NOALLOC_NO_SYMBOL;
+        g_noalloc_base[dev] = static_cast<unsigned char*>(p);
+    }
+    unsigned char* base = g_noalloc_base[dev];
+    int* tickets = nullptr;
+    float *part_ml = nullptr, *part_o = nullptr;
+    if (num_splits > 1) {
+        const size_t pairs = (size_t)tokens * nkv * ((nh / nkv + 15) / 16);
+        const size_t slots = (size_t)tokens * nh * num_splits;
+        tickets = reinterpret_cast<int*>(base);
+        part_ml = reinterpret_cast<float*>(base + noalloc_align(pairs * sizeof(int)));
+        part_o = reinterpret_cast<float*>(base + noalloc_align(pairs * sizeof(int)) + noalloc_align(slots * 2 * sizeof(float)));
+        // the tickets must start at zero whatever an earlier (perhaps failed) call left behind
+        const cudaError_t rc = cudaMemsetAsync(tickets, 0, pairs * sizeof(int), stream);
+        if (rc != cudaSuccess) return (int)rc;
+    }
+    return xb_attn_decode_bf16(out, part_o, part_ml, q, kc, vc, positions, req_of_token, q_start, num_entries, table,
+                               stride, nh, nkv, d, ps, num_pages, window, scale, dec_max, direct, split, num_splits,
+                               tokens, tickets, err, stream);
+}
