@@ -228,8 +228,10 @@ def main() -> int:
                            prefill_chunk_size=4096, max_model_len=args.context + 64, disable_cuda_graph=not use_graph)
     engine = Engine(econfig, "bf16", runner=runner)
     n_e2e = min(steps, 64)
-    prompt_len = args.context - n_e2e - warmup - 2
-    sp = SamplingParams(temperature=0.0, max_tokens=n_e2e + warmup, ignore_eos=True)
+    # prompts are prefilled two per step, so requests start decoding a few steps apart: leave room
+    # for that in the context, and let no request finish inside the timed region
+    prompt_len = args.context - n_e2e - warmup - 16
+    sp = SamplingParams(temperature=0.0, max_tokens=n_e2e + warmup + 64, ignore_eos=True)
     for _ in range(B):
         engine.add_request(rng.integers(0, V, size=prompt_len).tolist(), sp)
     while any(engine.scheduler.output(i) == [] for i in list(engine._live)):   # prompts, first tokens
@@ -248,8 +250,12 @@ def main() -> int:
     e2e_tokens = engine.stats["decoded_tokens"] - done_before
     e2e = {"value": round(e2e_tokens / (tw1 - tw0), 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d // n_e2e,
            "d2h_bytes_per_step": B * 4 + 4}
+    for seq_id in list(engine._live):   # the timed steps are done: drop what is still running
+        engine.scheduler.abort(seq_id)
     while engine.has_work():
         engine.step()
+    for seq_id in engine.scheduler.drain_finished():
+        engine._finish(seq_id)
 
     # ---- batch 1 and 64 -----------------------------------------------------------------------------------
     points = {}
