@@ -340,6 +340,8 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
                    const int* __restrict__ block_table, int table_stride, int nh, int nkv, int d, int ps,
                    int ps_shift, int num_pages, int window, float scale_log2, int dec_max, int direct, int split,
                    int num_splits, int page_cap, int* __restrict__ tickets, int* err) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int NT = 128;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ float s_m[4][16], s_l[4][16];
@@ -557,11 +559,10 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const
     cudaFuncSetAttribute(attn_decode_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaFuncSetAttribute(attn_decode_kernel<DP>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     const int qtiles = (nh / nkv + 15) / 16;
-    attn_decode_kernel<DP><<<dim3(num_splits, nkv * qtiles, tokens), 128, smem, stream>>>(
-        (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc,
-        positions, req_of_token, q_start, num_entries, table, stride, nh, nkv, d, ps, shift_of(ps), num_pages, window,
-        scale_log2, dec_max, direct, split, num_splits, page_cap, tickets, err);
-    return xb_launch_status();
+    return xb_launch(attn_decode_kernel<DP>, dim3(num_splits, nkv * qtiles, tokens), dim3(128), smem, stream,
+                     (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc,
+                     (const __nv_bfloat16*)vc, positions, req_of_token, q_start, num_entries, table, stride, nh, nkv, d, ps,
+                     shift_of(ps), num_pages, window, scale_log2, dec_max, direct, split, num_splits, page_cap, tickets, err);
 }
 
 }  // namespace

@@ -162,6 +162,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     volatile uint32_t* words = reinterpret_cast<volatile uint32_t*>(p_ptr + P_BYTES + 88);  // tmem, entry, tile, dead
     const int warp = threadIdx.x >> 5;
     const int h = blockIdx.x, g = h / (nh / nkv);   // heads vary fastest: every head's longest tiles start first
+    pdl_launch_dependents();
+    pdl_wait();
 
     if (threadIdx.x == 0) {
         if (base & 1023u) atomicOr(err, XB_ERR_WAIT);  // the swizzle needs a 1024-byte aligned window
@@ -537,10 +539,9 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     constexpr size_t smem = (size_t)(DP / 64) * QT * 128 + 2 * 2 * (size_t)(DP / 64) * KT * 128 + QT * 128 + 112;
     cudaFuncSetAttribute(attn_prefill_tc_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaFuncSetAttribute(attn_prefill_tc_kernel<DP>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    attn_prefill_tc_kernel<DP><<<dim3(nh, tiles), 192, smem, stream>>>(
-        mq, mk, mv, (__nv_bfloat16*)out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, ps_shift,
-        num_pages, window, sl2, dec_max, err);
-    return xb_launch_status();
+    return xb_launch(attn_prefill_tc_kernel<DP>, dim3(nh, tiles), dim3(192), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
+                     q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, ps_shift, num_pages, window, sl2,
+                     dec_max, err);
 }
 
 }  // namespace

@@ -61,3 +61,36 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
 
 // Last CUDA error of a launch as an int for the caller (0 = ok).
 static inline int xb_launch_status() { return (int)cudaGetLastError(); }
+
+// Programmatic dependent launch: a kernel launched through xb_launch may be scheduled while the
+// kernel before it in the stream is still running; it calls pdl_wait() before it touches anything
+// that kernel may have written (or still reads), and pdl_launch_dependents() as early as it likes
+// to let the kernel after it do the same.  Both are no-ops in a kernel launched the plain way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <cstdlib>
+static inline bool xb_pdl_enabled() {   // XINFER_B200_PDL=0 switches the overlap off
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("XINFER_B200_PDL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v != 0;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int xb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = xb_pdl_enabled() ? 1 : 0;
+    const cudaError_t rc = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    return rc != cudaSuccess ? (int)rc : xb_launch_status();
+}

@@ -34,6 +34,8 @@ __global__ void rmsnorm_bf16_kernel(__nv_bfloat16* __restrict__ out, __nv_bfloat
                                     const int* __restrict__ rows, const float* __restrict__ w, int dim,
                                     int src_rows, float eps, float offset, int* err) {
     __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     int src = rows ? rows[r] : r;
     if (src < 0 || src >= src_rows) {
@@ -82,6 +84,8 @@ __global__ void rmsnorm_bf16_kernel(__nv_bfloat16* __restrict__ out, __nv_bfloat
 // ---- SiLU gate -----------------------------------------------------------------------------------------
 __global__ void swiglu_bf16_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu,
                                    int inter, size_t nvec) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= nvec) return;
     const int vpr = inter / 8;
@@ -107,6 +111,8 @@ __global__ void qk_norm_rope_write_bf16_kernel(
     const int* __restrict__ req_of_token, const int* __restrict__ block_table, int table_stride, int tokens,
     int nh, int nkv, int d, int rot, int interleaved, int page_size, int num_pages, int max_pos, float eps,
     int write_kv, int* err) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int total_heads = nh + 2 * nkv;
     const int groups_per_block = blockDim.x / LPH;
     const long long item = (long long)blockIdx.x * groups_per_block + threadIdx.x / LPH;
@@ -217,21 +223,20 @@ XB_EXPORT int xb_rmsnorm_bf16(void* out, void* sum_out, const void* x, const voi
     int threads = 32;
     while (threads < nvec && threads < 1024) threads *= 2;
     const int vpt = (nvec + threads - 1) / threads;
-#define XB_GO(V) rmsnorm_bf16_kernel<V><<<nrows, threads, 0, stream>>>((__nv_bfloat16*)out, (__nv_bfloat16*)sum_out, (const __nv_bfloat16*)x, (const __nv_bfloat16*)branch, rows, w, dim, src_rows, eps, offset, err)
+#define XB_GO(V) return xb_launch(rmsnorm_bf16_kernel<V>, dim3(nrows), dim3(threads), 0, stream, (__nv_bfloat16*)out, (__nv_bfloat16*)sum_out, (const __nv_bfloat16*)x, (const __nv_bfloat16*)branch, rows, w, dim, src_rows, eps, offset, err)
     if (vpt <= 1) XB_GO(1);
-    else if (vpt <= 2) XB_GO(2);
-    else if (vpt <= 4) XB_GO(4);
-    else return (int)cudaErrorInvalidValue;
+    if (vpt <= 2) XB_GO(2);
+    if (vpt <= 4) XB_GO(4);
 #undef XB_GO
-    return xb_launch_status();
+    return (int)cudaErrorInvalidValue;
 }
 
 XB_EXPORT int xb_swiglu_bf16(void* out, const void* gu, int tokens, int inter, cudaStream_t stream) {
     if (tokens <= 0 || inter <= 0) return 0;
     if (inter % 8) return (int)cudaErrorInvalidValue;
     const size_t nvec = (size_t)tokens * (inter / 8);
-    swiglu_bf16_kernel<<<(unsigned)((nvec + 255) / 256), 256, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gu, inter, nvec);
-    return xb_launch_status();
+    return xb_launch(swiglu_bf16_kernel, dim3((unsigned)((nvec + 255) / 256)), dim3(256), 0, stream, (__nv_bfloat16*)out,
+                     (const __nv_bfloat16*)gu, inter, nvec);
 }
 
 // Needs d a multiple of 16 (at most 512) and, for the NeoX layout, rot == d.
@@ -245,17 +250,16 @@ XB_EXPORT int xb_qk_norm_rope_write_bf16(
     const int lanes = d / 16;
     const long long items = (long long)tokens * (nh + 2 * nkv);
     const int threads = 128;
-#define XB_GO(LPH)                                                                                          \
-    qk_norm_rope_write_bf16_kernel<LPH><<<(unsigned)((items + threads / LPH - 1) / (threads / LPH)), threads, 0, stream>>>( \
-        (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, (const __nv_bfloat16*)qkv, q_w, k_w,     \
-        cos_t, sin_t, positions, req_of_token, block_table, table_stride, tokens, nh, nkv, d, rot, interleaved,           \
-        page_size, num_pages, max_pos, eps, write_kv, err)
+#define XB_GO(LPH)                                                                                               \
+    return xb_launch(qk_norm_rope_write_bf16_kernel<LPH>, dim3((unsigned)((items + threads / LPH - 1) / (threads / LPH))), \
+                     dim3(threads), 0, stream, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,      \
+                     (const __nv_bfloat16*)qkv, q_w, k_w, cos_t, sin_t, positions, req_of_token, block_table, table_stride,  \
+                     tokens, nh, nkv, d, rot, interleaved, page_size, num_pages, max_pos, eps, write_kv, err)
     if (lanes <= 1) XB_GO(1);
-    else if (lanes <= 2) XB_GO(2);
-    else if (lanes <= 4) XB_GO(4);
-    else if (lanes <= 8) XB_GO(8);
-    else if (lanes <= 16) XB_GO(16);
-    else XB_GO(32);
+    if (lanes <= 2) XB_GO(2);
+    if (lanes <= 4) XB_GO(4);
+    if (lanes <= 8) XB_GO(8);
+    if (lanes <= 16) XB_GO(16);
+    XB_GO(32);
 #undef XB_GO
-    return xb_launch_status();
 }

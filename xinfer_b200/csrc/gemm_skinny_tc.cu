@@ -131,6 +131,7 @@ gemm_skinny_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     const int iters = k_end > k_begin ? (k_end - k_begin + TILE_K - 1) / TILE_K : 0;
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[16]), accum = smem_u32(&bars[32]);
     const uint32_t tmem_cols = mp < 32 ? 32u : (uint32_t)mp;
+    pdl_launch_dependents();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) {
@@ -151,9 +152,19 @@ gemm_skinny_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 
     if (threadIdx.x == 0) {
         // ---- producer: stream W and x tiles -------------------------------------------------------
-        for (int it = 0; it < iters; ++it) {
+        // The weights are never written by a kernel: the first ring of W tiles is requested before
+        // waiting for the kernel that produces x, so that their flight overlaps its tail.
+        const int pre = iters < stages ? iters : stages;
+        for (int it = 0; it < pre; ++it) {
+            mbar_expect_tx(full0 + 8 * it, stage_bytes);
+            tma_load_2d(base + it * stage_bytes, &map_w, k_begin + it * TILE_K, n0, full0 + 8 * it);
+        }
+        pdl_wait();
+        for (int it = 0; it < pre; ++it)
+            tma_load_2d(base + it * stage_bytes + w_bytes, &map_x, k_begin + it * TILE_K, 0, full0 + 8 * it);
+        for (int it = pre; it < iters; ++it) {
             const int s = it % stages;
-            if (it >= stages && !mbar_wait(empty0 + 8 * s, ((it / stages) & 1) ^ 1, err)) break;
+            if (!mbar_wait(empty0 + 8 * s, ((it / stages) & 1) ^ 1, err)) break;
             const uint32_t dst = base + s * stage_bytes;
             mbar_expect_tx(full0 + 8 * s, stage_bytes);
             tma_load_2d(dst, &map_w, k_begin + it * TILE_K, n0, full0 + 8 * s);
@@ -179,6 +190,7 @@ gemm_skinny_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     }
     // ---- epilogue: all four warps ----------------------------------------------------------------------
     __syncwarp();
+    pdl_wait();   // nothing of the kernel before may still read what is written below
     const bool ready = mbar_wait(accum, 0, err);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int row = warp * 32 + lane;         // TMEM lane = row of D = output feature n0 + row
@@ -288,13 +300,15 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int M, int N
     cfg.blockDim = dim3(128, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = splits;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = xb_pdl_enabled() ? 2 : 1;
     const cudaError_t rc = cudaLaunchKernelEx(&cfg, gemm_skinny_tc_kernel<TO>, mw, mx, (TO*)out, M, N, K, mp, k_per_split, stages, err);
     return rc != cudaSuccess ? (int)rc : xb_launch_status();
 }

@@ -13,6 +13,8 @@
 template <typename T>
 __global__ void embedding_kernel(T* __restrict__ out, const T* __restrict__ table,
                                  const int* __restrict__ ids, int hidden, int vocab, int* err) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     T* o = out + (size_t)t * hidden;
@@ -36,10 +38,8 @@ XB_EXPORT int xb_embedding(int dtype, void* out, const void* table, const int* i
                            int hidden, int vocab, int* err, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (dtype == XB_F32)
-        embedding_kernel<float><<<tokens, 256, 0, stream>>>((float*)out, (const float*)table, ids, hidden, vocab, err);
-    else
-        embedding_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)table, ids, hidden, vocab, err);
-    return xb_launch_status();
+        return xb_launch(embedding_kernel<float>, dim3(tokens), dim3(256), 0, stream, (float*)out, (const float*)table, ids, hidden, vocab, err);
+    return xb_launch(embedding_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)table, ids, hidden, vocab, err);
 }
 
 // ------------------------------------------------------------------------------------------
