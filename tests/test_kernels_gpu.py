@@ -329,10 +329,11 @@ TILED_CASES = CASES + [
 
 @pytest.fixture(params=[True, False], ids=["tcgen05", "mma_sync"])
 def prefill_family(request, monkeypatch):
-    """Long portions run on the tcgen05 kernel where it takes the sizes, else on the mma.sync
-    kernel; tests with this fixture run both."""
+    """Long portions and single tokens run on the tcgen05 kernels where they take the sizes, else
+    on the mma.sync kernels; tests with this fixture run both."""
     from xinfer_b200.parts import attention_backend
     monkeypatch.setattr(attention_backend, "PREFILL_TC", request.param)
+    monkeypatch.setattr(attention_backend, "DECODE_TC", request.param)
     return request.param
 
 
@@ -353,8 +354,44 @@ def test_attention_prefill_tcgen05(nh, nkv, d, ps, entries, window, monkeypatch)
     assert worst <= tol(torch.bfloat16, 2), worst
 
 
-def test_attention_tiled_sees_one_far_key_and_the_windows_edge():
+def test_attention_tiled_sees_one_far_key_and_the_windows_edge(prefill_family):
     far_key_checks(tiled_kernel, torch.bfloat16)
+
+
+@pytest.mark.parametrize("nh,nkv,d,ps,entries,window", [
+    (4, 1, 128, 16, [(0, 1)], None),                                            # a single key
+    (32, 8, 128, 16, [(4095, 1), (63, 1), (64, 1), (65, 1), (1, 1), (2049, 1), (700, 1), (127, 1)], None),
+    (8, 2, 64, 8, [(1000, 1), (999, 2), (1001, 3), (5, 4)], None),             # several tokens per small portion
+    (6, 1, 48, 16, [(3000, 1), (129, 1)], 700),                                 # window over several ranges
+    (6, 1, 48, 16, [(3000, 1), (129, 1)], 64),                                  # window of one tile
+    (12, 1, 96, 32, [(513, 1)], None),                                          # 12 heads share the keys: both row sets
+    (16, 1, 16, 64, [(200, 1), (77, 2)], 100),                                  # a full 16-row group, page = tile
+    (3, 3, 112, 128, [(2500, 1), (130, 1)], None),                              # page larger than a tile
+    (2, 2, 80, 16, [(9000, 1)], None),
+])
+def test_attention_decode_tcgen05(nh, nkv, d, ps, entries, window, monkeypatch):
+    """Single tokens (and portions of up to four) over long contexts: ranges, their merge, range
+    edges at multiples of the tile, windows."""
+    from xinfer_b200.parts import attention_backend
+    from xinfer_b200 import kernels
+
+    def not_this_one(*a, **k):
+        raise AssertionError("the mma.sync decode kernel was called")
+    monkeypatch.setattr(attention_backend, "DECODE_TC", True)
+    monkeypatch.setattr(kernels, "attn_decode_bf16", not_this_one)
+    assert attention_backend.decode_tc_takes(nh, nkv, d, ps)
+    worst = attention_case(tiled_kernel, torch.bfloat16, nh, nkv, d, ps, entries, window)
+    assert worst <= tol(torch.bfloat16, 2), worst
+
+
+def test_attention_decode_tcgen05_never_reads_a_poisoned_page(monkeypatch):
+    """Pages the request does not own hold NaN: ranges end inside pages and tiles, and nothing of
+    what lies behind may reach a result."""
+    from xinfer_b200.parts import attention_backend
+    monkeypatch.setattr(attention_backend, "DECODE_TC", True)
+    for start in (0, 15, 16, 63, 64, 100, 1023, 1024):
+        worst = attention_case(tiled_kernel, torch.bfloat16, 8, 2, 128, 16, [(start, 1), (start + 7, 1)], None)
+        assert worst <= tol(torch.bfloat16, 2), (start, worst)
 
 
 def test_attention_tiled_far_key_in_a_long_prompt_portion(prefill_family):
@@ -396,6 +433,17 @@ def test_attention_prefill_tile_sizes(warps, monkeypatch):
     for nh, nkv, d, ps, entries, window in [(8, 2, 128, 16, [(0, 300), (100, 129), (5, 64)], None), (4, 1, 64, 8, [(37, 200)], 90)]:
         worst = attention_case(tiled_kernel, torch.bfloat16, nh, nkv, d, ps, entries, window)
         assert worst <= tol(torch.bfloat16, 2), worst
+
+
+def test_decode_split_choice_tcgen05():
+    from xinfer_b200.parts.attention_backend import decode_split_tc
+    for bound, pairs, ps in [(1, 1, 16), (4096, 8, 16), (4096, 64, 16), (4096, 512, 8), (40000, 8, 16), (100, 4096, 16), (300000, 1, 8)]:
+        split, n = decode_split_tc(bound, pairs, 128, ps)
+        assert split % 64 == 0 and split >= 64 and (n - 1) * split < bound <= n * split
+        assert split // ps + 2 <= 1024, "a range's block-table entries fit the CTA's staging area"
+    assert decode_split_tc(4096, 8)[1] >= 8                # few pairs: cut finely
+    assert decode_split_tc(4096, 64)[1] * 64 <= 296        # one wave holds every CTA
+    assert decode_split_tc(4096, 512) == (4096, 1)         # many pairs: nothing to merge
 
 
 def test_decode_split_choice():

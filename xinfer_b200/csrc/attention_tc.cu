@@ -445,6 +445,430 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// decode: few tokens per request, keys split into ranges
+// ------------------------------------------------------------------------------------------------
+// Which token the z-th "small" token of the batch is: tokens of entries that bring at most dec_max
+// tokens, in batch order.  -1 if there is none.
+__device__ __forceinline__ int small_token_of(int z, const int* __restrict__ q_start, int num_entries, int dec_max, int direct) {
+    if (direct) return z < q_start[num_entries] ? z : -1;
+    int acc = 0;
+    for (int b = 0; b < num_entries; ++b) {
+        const int n = q_start[b + 1] - q_start[b];
+        if (n > 0 && n <= dec_max) {
+            if (z < acc + n) return q_start[b] + z - acc;
+            acc += n;
+        }
+    }
+    return -1;
+}
+
+constexpr int DEC_ROWS = 16;    // query heads of one key/value head a CTA can hold
+constexpr int DEC_STAGES = 3;   // key/value tiles in flight per CTA
+
+// 16 TMEM lanes x 64 columns of float32: lane t of the warp receives, for every block k of 8
+// columns, r[4k], r[4k+1] = row t/4, columns 8k + 2(t%4) and +1, and r[4k+2], r[4k+3] = row t/4 + 8,
+// the same columns (the layout of an MMA accumulator fragment): a row's columns are spread over four lanes.
+__device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// One CTA = one token x one key/value head x one of num_splits ranges of the token's keys (`split` is
+// the longest a range can be: it sizes the staging area of block-table entries).  The query heads of
+// the group are rows 0..G-1 of a 128-row MMA tile (rows from G on hold whatever the shared memory
+// behind the 16-row query and probability tiles holds: rows never mix, and only rows below G are
+// read back).  Warp 0: softmax (each row's 64 scores spread over four lanes) and the epilogue.
+// Warps 1 and 3: TMA producers of keys and of values (a ring each), one lane per page box.  Warp 2: MMA
+// issuer.  Shared memory:
+//   Q [DP/64][16 rows][64]   P[2] [16][64]   stage s: K [DP/64][64 keys][64], V likewise   barriers, pages
+// Tensor memory: S[0] at column 0, S[1] at 64, O at 128.  The scores of tile i+1 are computed while
+// tile i's softmax runs; P is double-buffered, so the softmax warp waits for the
+// tensor cores only when a row's reference maximum has to move (then O is rescaled in TMEM).
+// Ranges of one token are merged by the CTA that finishes last (a ticket per token and key/value
+// head), in range order.
+template <int DP>
+__global__ void __launch_bounds__(128)
+attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                      const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                      float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ positions,
+                      const int* __restrict__ req_of_token, const int* __restrict__ q_start, int num_entries,
+                      const int* __restrict__ block_table, int table_stride, int nh, int nkv, int d, int ps,
+                      int ps_shift, int num_pages, int window, float scale_log2, int dec_max, int direct, int split,
+                      int num_splits, int page_cap, int* __restrict__ tickets, int* err) {
+    constexpr int HALVES = DP / 64;
+    constexpr uint32_t Q_HALF = DEC_ROWS * 128, Q_BYTES = HALVES * Q_HALF, P_ONE = DEC_ROWS * 128, P_BYTES = 2 * P_ONE;
+    constexpr uint32_t KV_HALF = KT * 128, KV_BYTES = HALVES * KV_HALF, STAGE_BYTES = 2 * KV_BYTES;
+    constexpr uint32_t BAR_OFF = Q_BYTES + P_BYTES + DEC_STAGES * STAGE_BYTES;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    const uint32_t base = smem_u32(smem_raw);
+    const uint32_t q_sm = base, p_sm = base + Q_BYTES, kv_sm = p_sm + P_BYTES;
+    unsigned char* p_ptr = smem_raw + Q_BYTES;
+    // barriers, 8 bytes each: k_full[3] k_empty[3] v_full[3] v_empty[3] s_ready[2] s_free[2] p_ready[2] pv_done[2]
+    // q_full; then four words
+    const uint32_t bars = base + BAR_OFF;
+    const uint32_t k_full0 = bars, k_empty0 = bars + 24, v_full0 = bars + 48, v_empty0 = bars + 72;
+    const uint32_t s_ready0 = bars + 96, s_free0 = bars + 112, p_ready0 = bars + 128, pv_done0 = bars + 144, q_full = bars + 160;
+    volatile uint32_t* words = reinterpret_cast<volatile uint32_t*>(smem_raw + BAR_OFF + 168);  // tmem, dead, last, skip
+    int* s_pages = reinterpret_cast<int*>(smem_raw + BAR_OFF + 192);   // this range's part of the block table
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+
+    // what this CTA works on: step metadata only (written before the step's first kernel)
+    const int G = nh / nkv, g = blockIdx.y;
+    const int t = small_token_of(blockIdx.z, q_start, num_entries, dec_max, direct);
+    if (t < 0) return;
+    const int b = req_of_token[t];
+    if (b < 0) return;
+    const int pos = positions[t];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    // the token's own tiles are shared evenly among the grid's ranges, whatever length the grid was sized for
+    const int tile_lo = lo / KT, tile_hi = pos / KT;
+    const int per = (tile_hi - tile_lo + num_splits) / num_splits;   // tiles per range, rounded up
+    const int ns = (tile_hi - tile_lo + per) / per;                  // ranges that hold any
+    if ((int)blockIdx.x >= ns) return;
+    const int kt_first = tile_lo + (int)blockIdx.x * per, kt_last = min(kt_first + per - 1, tile_hi);
+    const int k_begin = max(lo, kt_first * KT), k_end = min(pos, kt_last * KT + KT - 1);
+    const int fresh = pos - dec_max + 1;   // keys before this were written by earlier steps, not by the kernel before this one
+    const int* table = block_table + (size_t)b * table_stride;
+    const int h0 = g * G;
+    const int iters = kt_last - kt_first + 1;
+    const int box_rows = ps < KT ? ps : KT;
+    const int page_first = (kt_first * KT) >> ps_shift;
+    const int staged = min((k_end >> ps_shift) - page_first + 1, page_cap);
+    for (int i = threadIdx.x; i < staged; i += 128) s_pages[i] = table[page_first + i];
+
+    if (threadIdx.x == 0) {
+        if (base & 1023u) atomicOr(err, XB_ERR_WAIT);  // the swizzle needs a 1024-byte aligned window
+        words[1] = 0;
+        words[2] = 0;
+        words[3] = (*reinterpret_cast<volatile int*>(err) & XB_ERR_WAIT) ? 1u : 0u;   // an earlier CTA gave up: do not pile on
+        for (int i = 0; i < 14; ++i) mbar_init(bars + 8 * i, 1);   // k_full, k_empty, v_full, v_empty, s_ready
+        mbar_init(s_free0, 32);
+        mbar_init(s_free0 + 8, 32);
+        mbar_init(p_ready0, 32);
+        mbar_init(p_ready0 + 8, 32);
+        mbar_init(pv_done0, 1);
+        mbar_init(pv_done0 + 8, 1);
+        mbar_init(q_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if ((base & 1023u) || words[3]) return;
+    constexpr uint32_t TMEM_COLS = 256;
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t*>(&words[0]))), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = words[0];
+    const uint32_t tmem_s = tmem, tmem_o = tmem + 128;
+
+    if (warp == 1 || warp == 3) {
+        // ---- producers: warp 1 streams the key pages, warp 3 the value pages, each through its own ring, one
+        // lane per box (page piece x 64-column half): the lanes look their pages up and issue their copies side
+        // by side.  The key ring is freed by Q K^T, the value ring two steps later by P V.
+        const bool is_v = warp == 3;
+        const uint32_t full0 = is_v ? v_full0 : k_full0, empty0 = is_v ? v_empty0 : k_empty0;
+        const CUtensorMap* map = is_v ? &map_v : &map_k;
+        const int boxes = (KT / box_rows) * HALVES;
+        const int bi = lane / HALVES, hf = lane % HALVES;
+        auto issue_tile = [&](int it) {
+            const int s = it % DEC_STAGES, kt = kt_first + it;
+            const uint32_t dst = kv_sm + s * STAGE_BYTES + (is_v ? KV_BYTES : 0u) + hf * KV_HALF + bi * box_rows * 128;
+            const int j = kt * KT + bi * box_rows;
+            int page = -1;
+            if (lane < boxes && j <= k_end && j + box_rows - 1 >= k_begin) {
+                const int idx = (j >> ps_shift) - page_first;
+                page = idx < staged ? s_pages[idx] : table[j >> ps_shift];
+                if (page < 0 || page >= num_pages) {
+                    atomicOr(err, XB_ERR_BAD_PAGE);
+                    page = -1;
+                }
+            }
+            const uint32_t n = __popc(__ballot_sync(0xffffffffu, page >= 0));
+            if (lane == 0) mbar_expect_tx(full0 + 8 * s, n * box_rows * 128);
+            __syncwarp();
+            if (page >= 0) tma_load_2d(dst, map, hf * 64, (page * nkv + g) * ps + (j & (ps - 1)), full0 + 8 * s);
+        };
+        // tiles that hold only keys of earlier steps do not depend on the kernel before this one
+        int pre = 0;
+        while (pre < iters && pre < DEC_STAGES && (kt_first + pre) * KT + KT - 1 < fresh) issue_tile(pre++);
+        pdl_wait();
+        if (!is_v && lane == 0) {
+            mbar_expect_tx(q_full, HALVES * G * 128);
+#pragma unroll
+            for (int h2 = 0; h2 < HALVES; ++h2) tma_load_3d(q_sm + h2 * Q_HALF, &map_q, h2 * 64, h0, t, q_full);
+        }
+        for (int it = pre; it < iters; ++it) {
+            const int s = it % DEC_STAGES;
+            if (it >= DEC_STAGES && !__all_sync(0xffffffffu, mbar_wait(empty0 + 8 * s, ((it / DEC_STAGES) - 1) & 1, err))) {
+                words[1] = 1;
+                break;
+            }
+            issue_tile(it);
+        }
+    } else if (warp == 2) {
+        // ---- MMA issuer: QK(0), then for every tile QK(next) before PV(this) ----------------------------
+        if (lane == 0) {
+            const uint32_t idesc_s = umma_idesc(KT, 0), idesc_o = umma_idesc(DP, 1);
+            const uint64_t dq0 = umma_desc(q_sm, 16, 1024), dk0 = umma_desc(kv_sm, 16, 1024);
+            const uint64_t dp0 = umma_desc(p_sm, 16, 1024), dv0 = umma_desc(kv_sm + KV_BYTES, KV_HALF, 1024);
+            auto issue_qk = [&](int it) -> bool {   // S[it & 1] = Q K^T of tile `it`
+                const int sb = it & 1, s = it % DEC_STAGES;
+                if (!mbar_wait(k_full0 + 8 * s, (it / DEC_STAGES) & 1, err)) return false;
+                if (it >= 2 && !mbar_wait(s_free0 + 8 * sb, ((it >> 1) - 1) & 1, err)) return false;  // S[sb] was read
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t dk = dk0 + (uint64_t)((s * STAGE_BYTES) >> 4);
+#pragma unroll
+                for (int kk = 0; kk < DP / 16; ++kk) {
+                    const uint32_t off = (kk >> 2), inner = (kk & 3) * 32;
+                    umma_bf16(tmem_s + (uint32_t)sb * 64, dq0 + (uint64_t)((off * Q_HALF + inner) >> 4),
+                              dk + (uint64_t)((off * KV_HALF + inner) >> 4), idesc_s, kk ? 1u : 0u);
+                }
+                umma_commit(k_empty0 + 8 * s);   // the key stage is free once these have completed
+                umma_commit(s_ready0 + 8 * sb);
+                return true;
+            };
+            bool ok = mbar_wait(q_full, 0, err) && issue_qk(0);
+            for (int it = 0; it < iters && ok; ++it) {
+                const int s = it % DEC_STAGES, pb = it & 1;
+                if (it + 1 < iters) ok = issue_qk(it + 1);
+                ok = ok && mbar_wait(v_full0 + 8 * s, (it / DEC_STAGES) & 1, err);
+                ok = ok && mbar_wait(p_ready0 + 8 * pb, (it >> 1) & 1, err);   // P written, V rows zeroed, O rescaled
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                // O += P V : A = P [rows x 64 keys] K-major, B = V [64 keys x DP] MN-major (halves 64 columns apart)
+                const uint64_t dp = dp0 + (uint64_t)((pb * P_ONE) >> 4);
+                const uint64_t dv = dv0 + (uint64_t)((s * STAGE_BYTES) >> 4);
+#pragma unroll
+                for (int kk = 0; kk < KT / 16; ++kk)
+                    umma_bf16(tmem_o, dp + (uint64_t)((kk * 32) >> 4), dv + (uint64_t)((kk * 2048) >> 4), idesc_o, (it | kk) ? 1u : 0u);
+                umma_commit(v_empty0 + 8 * s);       // the value stage is free again once these have completed
+                umma_commit(pv_done0 + 8 * pb);      // and so is P[pb]; O holds this tile
+            }
+            if (!ok) words[1] = 1;
+        }
+    } else if (warp == 0) {
+        // ---- softmax: lane t works on rows t/4 and t/4 + 8, a quarter of their columns each -----------------------
+        const int quad = lane & 3, r0 = lane >> 2;
+        const bool two = G > 8;
+        float m_ref[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+        bool alive = true;
+        for (int it = 0; it < iters; ++it) {
+            const int s = it & 1, key0 = (kt_first + it) * KT;
+            if (!__all_sync(0xffffffffu, mbar_wait(s_ready0 + 8 * s, (it >> 1) & 1, err))) {
+                alive = false;
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t raw[32];
+            tmem_ld_16x256b_x8(tmem_s + s * 64, raw);
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(s_free0 + 8 * s);   // S[s] is in registers
+            const bool edge = key0 < k_begin || key0 + KT - 1 > k_end;
+            float corr[2] = {1.f, 1.f};
+            int moved = 0;
+            uint32_t pk[2][8];
+#pragma unroll
+            for (int set = 0; set < 2; ++set) {
+                if (set == 1 && !two) break;
+                float sc[16];
+                float mx2[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        float v = __uint_as_float(raw[4 * k + 2 * set + e]) * scale_log2;
+                        if (edge) {
+                            const int j = key0 + 8 * k + 2 * quad + e;
+                            v = (j >= k_begin && j <= k_end) ? v : -INFINITY;
+                        }
+                        sc[2 * k + e] = v;
+                        mx2[e] = fmaxf(mx2[e], v);
+                    }
+                float mx = fmaxf(mx2[0], mx2[1]);
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                // move the reference maximum only when the row's maximum outgrows it by more than 2^8
+                if (mx > m_ref[set] + RESCALE_STEP) {
+                    corr[set] = m_ref[set] == -INFINITY ? 0.f : exp2f(m_ref[set] - mx);
+                    m_ref[set] = mx;
+                    moved |= (it > 0 && r0 + 8 * set < G) ? 1 : 0;
+                }
+                const float m_use = m_ref[set] == -INFINITY ? 0.f : m_ref[set];
+                float sum2[2] = {0.f, 0.f};
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const float e0 = exp2f(sc[2 * k] - m_use), e1 = exp2f(sc[2 * k + 1] - m_use);
+                    sum2[0] += e0;
+                    sum2[1] += e1;
+                    pk[set][k] = pack_bf16(e0, e1);
+                }
+                float sum = sum2[0] + sum2[1];
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                l[set] = l[set] * corr[set] + sum;
+            }
+            // P[it & 1] belongs to the P V of two tiles ago until that has completed
+            if (it >= 2 && !__all_sync(0xffffffffu, mbar_wait(pv_done0 + 8 * s, ((it >> 1) - 1) & 1, err))) {
+                alive = false;
+                break;
+            }
+#pragma unroll
+            for (int set = 0; set < 2; ++set) {
+                if (set == 1 && !two) break;
+                const int row = r0 + 8 * set;
+                unsigned char* prow = p_ptr + s * P_ONE + row * 128 + quad * 4;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) *reinterpret_cast<uint32_t*>(prow + ((k ^ (row & 7)) << 4)) = pk[set][k];
+            }
+            if (edge) {   // value rows outside the range become zeros (only tiles at the ends of the range)
+                const int st = it % DEC_STAGES;
+                mbar_wait(v_full0 + 8 * st, (it / DEC_STAGES) & 1, err);   // orders these writes after the TMA's
+                unsigned char* v_ptr = smem_raw + Q_BYTES + P_BYTES + st * STAGE_BYTES + KV_BYTES;
+#pragma unroll
+                for (int rr = 0; rr < 2; ++rr) {
+                    const int row = lane + rr * 32, j = key0 + row;
+                    if (j < k_begin || j > k_end) {
+#pragma unroll
+                        for (int hf = 0; hf < HALVES; ++hf) {
+                            uint4* vr = reinterpret_cast<uint4*>(v_ptr + hf * KV_HALF + row * 128);
+#pragma unroll
+                            for (int c8 = 0; c8 < 8; ++c8) vr[c8] = make_uint4(0, 0, 0, 0);
+                        }
+                    }
+                }
+            }
+            if (__any_sync(0xffffffffu, moved)) {
+                // O holds every tile before this one once the last P V has completed; row = lane in this layout
+                if (!__all_sync(0xffffffffu, mbar_wait(pv_done0 + 8 * (s ^ 1), ((it - 1) >> 1) & 1, err))) {
+                    alive = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const float fa = __shfl_sync(0xffffffffu, corr[0], (lane & 7) * 4);
+                const float fb = __shfl_sync(0xffffffffu, corr[1], (lane & 7) * 4);
+                const float f = lane < 8 ? fa : (lane < 16 && two ? fb : 1.f);
+#pragma unroll
+                for (int c0 = 0; c0 < DP; c0 += 32) {
+                    float o[32];
+                    tmem_ld32(tmem_o + c0, o);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] *= f;
+                    tmem_st32(tmem_o + c0, o);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P and zeroed V rows: visible to the MMA
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(p_ready0 + 8 * s);
+        }
+        // ---- O / l -> out, or this range's partial result; row = lane from here on ---------------------------------
+        pdl_wait();
+        if (alive) alive = mbar_wait(pv_done0 + 8 * ((iters - 1) & 1), ((iters - 1) >> 1) & 1, err);
+        alive = __all_sync(0xffffffffu, alive);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const float la = __shfl_sync(0xffffffffu, l[0], (lane & 7) * 4), lb = __shfl_sync(0xffffffffu, l[1], (lane & 7) * 4);
+        const float ma = __shfl_sync(0xffffffffu, m_ref[0], (lane & 7) * 4), mb = __shfl_sync(0xffffffffu, m_ref[1], (lane & 7) * 4);
+        if (alive) {
+            const float l_row = lane < 8 ? la : lb, m_row = lane < 8 ? ma : mb;
+            const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+            const bool valid = lane < G;
+            const int h = h0 + lane;
+            const size_t slot = ((size_t)blockIdx.z * nh + h) * num_splits + blockIdx.x;   // by the token's rank among the small ones
+#pragma unroll
+            for (int c0 = 0; c0 < DP; c0 += 32) {
+                float o[32];
+                tmem_ld32(tmem_o + c0, o);   // warp-wide, whatever `valid` is
+                if (!valid) continue;
+                if (num_splits == 1) {
+                    __nv_bfloat16* dst = out + ((size_t)t * nh + h) * d;
+#pragma unroll
+                    for (int c8 = 0; c8 < 4; ++c8) {
+                        const int c = c0 + c8 * 8;
+                        if (c < d) {
+                            uint4 w;
+                            w.x = pack_bf16(o[c8 * 8] * inv, o[c8 * 8 + 1] * inv);
+                            w.y = pack_bf16(o[c8 * 8 + 2] * inv, o[c8 * 8 + 3] * inv);
+                            w.z = pack_bf16(o[c8 * 8 + 4] * inv, o[c8 * 8 + 5] * inv);
+                            w.w = pack_bf16(o[c8 * 8 + 6] * inv, o[c8 * 8 + 7] * inv);
+                            *reinterpret_cast<uint4*>(dst + c) = w;
+                        }
+                    }
+                } else {
+                    float* dst = part_o + slot * d;
+#pragma unroll
+                    for (int c4 = 0; c4 < 8; ++c4) {
+                        const int c = c0 + c4 * 4;
+                        if (c < d)
+                            *reinterpret_cast<float4*>(dst + c) = make_float4(o[c4 * 4] * inv, o[c4 * 4 + 1] * inv, o[c4 * 4 + 2] * inv, o[c4 * 4 + 3] * inv);
+                    }
+                }
+            }
+            if (valid && num_splits > 1) {
+                part_ml[slot * 2] = m_row;
+                part_ml[slot * 2 + 1] = l_row;
+            }
+        } else {
+            words[1] = 1;
+        }
+    }
+    pdl_wait();
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __threadfence();
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+    if (num_splits == 1) return;
+    // The CTA that finishes last among the ranges of this (token, key/value head) merges them:
+    //   out[h] = sum_s w_s O_s / sum_s w_s,  w_s = L_s * 2^(M_s - max M),  in range order.
+    if (threadIdx.x == 0) {
+        int* ticket = tickets + (size_t)blockIdx.z * gridDim.y + blockIdx.y;
+        const int mine = atomicAdd(ticket, 1);
+        const int last = mine == ns - 1;
+        words[2] = (uint32_t)last;
+        if (last) *ticket = 0;   // ready for the next launch
+    }
+    __syncthreads();
+    if (!words[2]) return;
+    __threadfence();
+    for (int row = warp; row < G; row += 4) {
+        const int h = h0 + row;
+        const size_t pbase = ((size_t)blockIdx.z * nh + h) * num_splits;
+        float mloc = -INFINITY;
+        for (int i = lane; i < ns; i += 32) mloc = fmaxf(mloc, __ldcg(part_ml + (pbase + i) * 2));
+        const float M = warp_max(mloc);
+        float wloc = 0.f;
+        for (int i = lane; i < ns; i += 32)
+            wloc += __ldcg(part_ml + (pbase + i) * 2 + 1) * exp2f(__ldcg(part_ml + (pbase + i) * 2) - M);
+        const float W = warp_sum(wloc);
+        const float inv = W > 0.f ? 1.f / W : 0.f;
+        for (int c4 = lane * 4; c4 < d; c4 += 128) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+            for (int i = 0; i < ns; ++i) {
+                const float w = __ldcg(part_ml + (pbase + i) * 2 + 1) * exp2f(__ldcg(part_ml + (pbase + i) * 2) - M);
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(part_o + (pbase + i) * d + c4));
+                acc.x += v.x * w; acc.y += v.y * w; acc.z += v.z * w; acc.w += v.w * w;
+            }
+            __nv_bfloat16* dst = out + ((size_t)t * nh + h) * d + c4;
+            *reinterpret_cast<uint32_t*>(dst) = pack_bf16(acc.x * inv, acc.y * inv);
+            *reinterpret_cast<uint32_t*>(dst + 2) = pack_bf16(acc.z * inv, acc.w * inv);
+        }
+    }
+}
+
 // ---- host: tensor maps ------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -507,10 +931,10 @@ bool map_rows(CUtensorMap* out, const void* ptr, long long rows, int d, int box_
     return true;
 }
 
-// q [T, nh, d] through boxes [128 tokens x 1 head x 64 columns].
-bool map_q3(CUtensorMap* out, const void* ptr, long long T, int nh, int d) {
+// q [T, nh, d] through boxes [box_tokens x box_heads x 64 columns].
+bool map_q3(CUtensorMap* out, const void* ptr, long long T, int nh, int d, int box_heads, int box_tokens) {
     std::lock_guard<std::mutex> lock(cache_mutex());
-    const Key key{ptr, T, nh, d, -1};
+    const Key key{ptr, T, nh, (long long)d | ((long long)box_heads << 20), -box_tokens};
     auto it = cache().find(key);
     if (it != cache().end()) {
         *out = it->second;
@@ -520,7 +944,7 @@ bool map_q3(CUtensorMap* out, const void* ptr, long long T, int nh, int d) {
     if (!fn) return false;
     const cuuint64_t gdim[3] = {(cuuint64_t)d, (cuuint64_t)nh, (cuuint64_t)T};
     const cuuint64_t gstr[2] = {(cuuint64_t)d * 2, (cuuint64_t)nh * d * 2};
-    const cuuint32_t box[3] = {64, 1, (cuuint32_t)QT};
+    const cuuint32_t box[3] = {64, (cuuint32_t)box_heads, (cuuint32_t)box_tokens};
     const cuuint32_t es[3] = {1, 1, 1};
     CUtensorMap m;
     if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), gdim, gstr, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -544,6 +968,24 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
                      dec_max, err);
 }
 
+template <int DP>
+int launch_decode(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, float* part_o,
+                  float* part_ml, const int* positions, const int* req_of_token, const int* q_start, int num_entries,
+                  const int* table, int stride, int nh, int nkv, int d, int ps, int ps_shift, int num_pages, int window,
+                  float sl2, int dec_max, int direct, int split, int num_splits, int tokens, int* tickets, int* err,
+                  cudaStream_t stream) {
+    // the range's block-table entries are staged in shared memory, up to what still lets two CTAs share an SM
+    int page_cap = (split + KT) / ps + 2;
+    if (page_cap > 1024) page_cap = 1024;
+    const size_t smem = (size_t)(DP / 64) * DEC_ROWS * 128 + 2 * DEC_ROWS * 128 + DEC_STAGES * 2 * (size_t)(DP / 64) * KT * 128 + 192 +
+                        (size_t)page_cap * 4;
+    cudaFuncSetAttribute(attn_decode_tc_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(attn_decode_tc_kernel<DP>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    return xb_launch(attn_decode_tc_kernel<DP>, dim3(num_splits, nkv, tokens), dim3(128), smem, stream, mq, mk, mv,
+                     (__nv_bfloat16*)out, part_o, part_ml, positions, req_of_token, q_start, num_entries, table, stride, nh,
+                     nkv, d, ps, ps_shift, num_pages, window, sl2, dec_max, direct, split, num_splits, page_cap, tickets, err);
+}
+
 }  // namespace
 
 // Portions of more than dec_max tokens, 128 queries per CTA; `tiles` = sum over those portions of
@@ -561,7 +1003,7 @@ XB_EXPORT int xb_attn_prefill_tc(void* out, const void* q, const void* kc, const
     CUtensorMap mq, mk, mv;
     const long long rows = (long long)num_pages * nkv * ps;
     const int box_rows = ps < KT ? ps : KT;
-    if (!map_q3(&mq, q, tokens, nh, d) || !map_rows(&mk, kc, rows, d, box_rows) || !map_rows(&mv, vc, rows, d, box_rows))
+    if (!map_q3(&mq, q, tokens, nh, d, 1, QT) || !map_rows(&mk, kc, rows, d, box_rows) || !map_rows(&mv, vc, rows, d, box_rows))
         return (int)cudaErrorNotSupported;
     const float sl2 = scale * 1.4426950408889634f;
     if (d <= 64)
@@ -569,4 +1011,36 @@ XB_EXPORT int xb_attn_prefill_tc(void* out, const void* q, const void* kc, const
                           window, sl2, dec_max, tiles, err, stream);
     return launch<128>(mq, mk, mv, out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, shift, num_pages,
                        window, sl2, dec_max, tiles, err, stream);
+}
+// Tokens of portions of at most dec_max tokens on the tensor cores: the same arguments, scratch and
+// results as xb_attn_decode_bf16 (`q_rows` = rows of q), except that each token's own keys are cut
+// evenly into at most num_splits ranges (of at most `split` positions, a multiple of 64, which must
+// cover the longest context: num_splits * split >= its length).  Returns cudaErrorNotSupported (having done
+// nothing) for a head size over 128 or not a multiple of 16, a page size that is no power of two
+// >= 8, or more than 16 query heads per key/value head.
+XB_EXPORT int xb_attn_decode_tc(void* out, float* part_o, float* part_ml, const void* q, const void* kc, const void* vc,
+                                const int* positions, const int* req_of_token, const int* q_start, int num_entries,
+                                const int* table, int stride, int q_rows, int nh, int nkv, int d, int ps, int num_pages,
+                                int window, float scale, int dec_max, int direct, int split, int num_splits, int tokens,
+                                int* tickets, int* err, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    int shift = -1;
+    for (int s = 3; s < 20; ++s)
+        if ((1 << s) == ps) shift = s;
+    if (d % 16 || d > 128 || d < 16 || nh % nkv || nh / nkv > DEC_ROWS || shift < 0) return (int)cudaErrorNotSupported;
+    if (split <= 0 || split % KT || num_splits <= 0) return (int)cudaErrorInvalidValue;
+    if (num_splits > 1 && (!part_o || !part_ml || !tickets)) return (int)cudaErrorInvalidValue;
+    CUtensorMap mq, mk, mv;
+    const long long rows = (long long)num_pages * nkv * ps;
+    const int box_rows = ps < KT ? ps : KT;
+    if (!map_q3(&mq, q, q_rows, nh, d, nh / nkv, 1) || !map_rows(&mk, kc, rows, d, box_rows) || !map_rows(&mv, vc, rows, d, box_rows))
+        return (int)cudaErrorNotSupported;
+    const float sl2 = scale * 1.4426950408889634f;
+    if (d <= 64)
+        return launch_decode<64>(mq, mk, mv, out, part_o, part_ml, positions, req_of_token, q_start, num_entries, table, stride,
+                                 nh, nkv, d, ps, shift, num_pages, window, sl2, dec_max, direct, split, num_splits, tokens,
+                                 tickets, err, stream);
+    return launch_decode<128>(mq, mk, mv, out, part_o, part_ml, positions, req_of_token, q_start, num_entries, table, stride,
+                              nh, nkv, d, ps, shift, num_pages, window, sl2, dec_max, direct, split, num_splits, tokens,
+                              tickets, err, stream);
 }

@@ -303,8 +303,47 @@ def attn_decode_bf16(out, part_o, part_ml, q, k_cache, v_cache, positions, req_o
         int(split), int(num_splits), int(tokens), _ptr(tickets), err.data_ptr(), _stream()), "attn_decode_bf16")
 
 
-# ---- matrix product for few tokens on tcgen05 tensor cores ---------------------------------------------
 ERR_NOT_SUPPORTED = 801  # cudaErrorNotSupported
+
+
+def attn_decode_tc(out, part_o, part_ml, q, k_cache, v_cache, positions, req_of_token, q_start, num_entries,
+                   block_table, table_stride, window, scale, dec_max, direct, split, num_splits, tokens, err,
+                   tickets=None) -> bool:
+    """The same work, arguments and scratch as ``attn_decode_bf16`` on tcgen05 tensor cores with
+    TMA-fed pages.  Returns False, having done nothing, for shapes the kernel does not take (a
+    head size over 128, a page size that is no power of two >= 8, more than 16 query heads per
+    key/value head)."""
+    T, nh, d = q.shape
+    _need(q, "q", torch.bfloat16, (T, nh, d))
+    _need(out, "out", torch.bfloat16, (T, nh, d))
+    _need(k_cache, "k_cache", torch.bfloat16, (None, None, None, d))
+    _need(v_cache, "v_cache", torch.bfloat16, tuple(k_cache.shape))
+    num_pages, nkv, ps, _ = k_cache.shape
+    if nh % nkv or d % 16:
+        raise KernelError(f"tiled attention needs a head size in steps of 16 and heads divisible by key/value heads; "
+                          f"got head size {d}, {nh}/{nkv} heads")
+    if tokens > 65535:
+        raise KernelError(f"{tokens} small-portion tokens exceed the decode kernel's grid limit of 65535")
+    if num_splits > 1:
+        _need(part_o, "part_o", torch.float32)
+        _need(part_ml, "part_ml", torch.float32)
+        if part_o.numel() < tokens * nh * num_splits * d or part_ml.numel() < tokens * nh * num_splits * 2:
+            raise KernelError("attention scratch buffers are too small for the number of key ranges")
+        _need(tickets, "tickets", torch.int32)
+        if tickets.numel() < tokens * nkv:
+            raise KernelError("the attention ticket buffer is too small")
+    rc = kernels_lib().xb_attn_decode_tc(
+        out.data_ptr(), _ptr(part_o), _ptr(part_ml), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+        positions.data_ptr(), req_of_token.data_ptr(), q_start.data_ptr(), int(num_entries), block_table.data_ptr(),
+        int(table_stride), T, nh, nkv, d, ps, num_pages, int(window or 0), float(scale), int(dec_max), int(bool(direct)),
+        int(split), int(num_splits), int(tokens), _ptr(tickets), err.data_ptr(), _stream())
+    if rc == ERR_NOT_SUPPORTED:
+        return False
+    _ok(rc, "attn_decode_tc")
+    return True
+
+
+# ---- matrix product for few tokens on tcgen05 tensor cores ---------------------------------------------
 
 
 def gemm_skinny_tc(out, x, w, err, splits: int = 0) -> bool:
