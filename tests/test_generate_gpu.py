@@ -157,3 +157,27 @@ def test_command_line(model_folders, capsys):
     out = capsys.readouterr().out
     want = ",".join(str(t) for t in plain.generate(cfg, w, [5, 6, 7], 4))
     assert want in out and "Prompt tokens: 5" in out and "Decoded tokens: 8" in out
+
+
+@pytest.mark.parametrize("dtype,graphs", [("f32", False), ("bf16", True), ("bf16", False)])
+def test_deciding_the_next_step_ahead_changes_no_token(dtype, graphs, model_folders):
+    """The same requests with and without the next decode step being queued while the current one
+    runs: stop tokens found late, requests ending by length at different steps, sampling with
+    temperature, requests arriving while others decode."""
+    from xinfer_b200 import SamplingParams
+    store = torch.float32 if dtype == "f32" else torch.bfloat16
+    folder = model_folders("B", store)       # configuration B stops on tokens 3 and 5
+    prompts = prompts_for("B", [4, 19, 33, 7, 12, 26], seed=3)
+    params = [SamplingParams(temperature=0.0 if i % 2 else 0.9, top_k=0 if i % 3 else 20, max_tokens=5 + 9 * i,
+                             ignore_eos=(i == 1), seed=7 + i) for i in range(len(prompts))]
+    runs = []
+    for off in (True, False):
+        eng = engine(folder, dtype, "B", disable_run_ahead=off, disable_cuda_graph=not graphs, max_num_seqs=3)
+        outs = eng.generate_sync(params, prompts)     # six requests through three slots
+        runs.append([(o.decode_output, o.finish_reason) for o in outs])
+        assert (eng.stats["steps_decided_ahead"] > 10) == (not off)
+        assert not eng.has_work()
+        eng.runner.cache.check_consistent()
+        assert eng.runner.cache.live_requests() == 0
+    assert runs[0] == runs[1]
+    assert {r for _, r in runs[0]} >= {"length"}

@@ -205,3 +205,124 @@ def test_random_workloads_finish_and_leave_the_pool_whole(seed):
         assert s.finish_reason(i) in ("stop", "length")
         assert len(s.output(i)) <= m
     assert cm.free_pages() == pages and cm.live_requests() == 0
+
+
+# ---- deciding the next step while the current one runs ------------------------------------------------
+def run_ahead(sched, token_of, max_steps=10_000):
+    """Drive to completion the way the engine does: while a step "runs", the next is decided from
+    it; its tokens are made up from what the running step will have sampled."""
+    flights, ended, outputs = [], {}, {}
+    flight = None
+    for step in range(max_steps):
+        if flight is None:
+            if not sched.has_work():
+                break
+            entries = sched.schedule()
+            for i in sched.drain_finished():
+                ended[i] = step
+            if not entries:
+                continue
+            flight = (entries, False)
+        entries, was_ahead = flight
+        flights.append(flight)
+        nxt = sched.schedule_ahead() if all(e.want and len(e.tokens) == 1 for e in entries) else []
+        sampled = [token_of(e, step) for e in entries if e.want]
+        for i in sched.commit(sampled):
+            ended[i] = step
+            outputs[i] = sched.output(i)
+            sched.release(i)
+        flight = (nxt, True) if nxt else None
+        if flight is not None and all(e.req_id in ended for e in nxt):
+            sched.commit([0] * len(nxt))
+            flight = None
+    assert not sched.has_work()
+    return flights, ended, outputs
+
+
+def test_a_decode_step_is_decided_while_the_one_before_runs():
+    cm, s = make(budget=64, chunk=32)
+    s.add(0, [1] * 5, max_tokens=6)
+    s.add(1, [2] * 9, max_tokens=4)
+    assert s.schedule_ahead() == []                       # nothing runs yet
+    e = s.schedule()
+    assert [len(x.tokens) for x in e] == [5, 9]
+    assert s.schedule_ahead() == []                       # the running step is a prompt step
+    s.commit([11, 12])
+    e = s.schedule()
+    assert [(x.req_id, x.start, len(x.tokens)) for x in e] == [(0, 5, 1), (1, 9, 1)]
+    a = s.schedule_ahead()
+    assert [(x.req_id, x.slot, x.start, x.src, x.want) for x in a] == [(0, e[0].slot, 6, 0, True), (1, e[1].slot, 10, 1, True)]
+    assert s.schedule_ahead() == []                       # only one step ahead
+    s.commit([21, 22])                                    # the running step's tokens arrive
+    a2 = s.schedule_ahead()                               # ... and the step after the one decided ahead
+    assert [(x.req_id, x.start) for x in a2] == [(0, 7), (1, 11)]
+    s.commit([31, 32])
+    # request 1 has 3 of its 4 tokens: the step in flight gives the fourth and ends it by length
+    a3 = s.schedule_ahead()
+    assert [(x.req_id, x.start, x.src) for x in a3] == [(0, 8, 0)]
+    assert s.commit([41, 42]) == [1]
+    assert s.output(1) == [12, 22, 32, 42] and s.finish_reason(1) == "length"
+    assert s.commit([51]) == []
+    assert s.output(0) == [11, 21, 31, 41, 51]
+
+
+def test_a_stop_token_found_late_drops_the_token_computed_in_vain():
+    cm, s = make(eos=(99,))
+    s.add(0, [1] * 4, max_tokens=50)
+    s.add(1, [2] * 4, max_tokens=50)
+    s.schedule(); s.commit([5, 6])
+    s.schedule()
+    a = s.schedule_ahead()
+    assert [x.req_id for x in a] == [0, 1]
+    assert s.commit([99, 7]) == [0]                       # request 0 stops; its entry of the next step is void
+    s.release(0)
+    assert s.commit([1234, 8]) == []                      # the void entry's token is skipped, request 1 gets its own
+    assert s.output(1) == [6, 7, 8]
+    assert cm.live_requests() == 1
+    # the step after: only request 1 is left
+    e = s.schedule()
+    assert [(x.req_id, x.start) for x in e] == [(1, 6)]
+
+
+def test_nothing_is_decided_ahead_when_requests_wait_or_pages_are_short():
+    cm, s = make(seqs=1)
+    s.add(0, [1] * 4, max_tokens=9)
+    s.add(1, [2] * 4, max_tokens=9)                       # waits for the only slot
+    s.schedule(); s.commit([5])
+    s.schedule()
+    assert s.schedule_ahead() == []
+    s.commit([5])
+    cm2, s2 = make(pages=4, page=4, seqs=2)
+    s2.add(0, [1] * 7, max_tokens=3)
+    s2.add(1, [2] * 7, max_tokens=3)
+    s2.schedule(); s2.commit([5, 5])                      # 8 tokens known each, 7 cached: all four pages in use
+    e = s2.schedule()
+    assert [(x.start, len(x.tokens)) for x in e] == [(7, 1), (7, 1)]
+    assert s2.schedule_ahead() == []                      # the tokens after these would need a fifth page
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_deciding_ahead_gives_the_same_outputs(seed):
+    rng = random.Random(seed)
+    reqs = [(i, [rng.randrange(50) for _ in range(rng.randrange(1, 40))], rng.randrange(1, 25)) for i in range(7)]
+
+    def tok(e, step):   # a token that depends only on the request and its position: 3 is the stop token
+        return (e.req_id * 7 + (e.start + len(e.tokens)) * 13) % 17
+
+    outs = []
+    for ahead in (False, True):
+        cm, s = make(pages=40, page=4, seqs=4, budget=48, chunk=16, eos=(3,))
+        for i, p, m in reqs:
+            s.add(i, p, max_tokens=m)
+        if ahead:
+            flights, ended, outputs = run_ahead(s, tok)
+            assert any(was for _, was in flights), "some steps must have been decided ahead"
+        else:
+            outputs = {}
+            _, ended = run(s, tok)
+            for i in ended:
+                outputs[i] = s.output(i)
+        assert cm.live_requests() == 0 and cm.free_pages() == 40
+        cm.check_consistent()
+        outs.append(outputs)
+    assert outs[0] == outs[1]

@@ -28,6 +28,9 @@ class EngineConfig:
     max_tokens: Optional[int] = None
     seed: Optional[int] = None
     disable_cuda_graph: bool = False
+    # decide and queue the next decode step while the current one runs (the device then does not
+    # wait for the host between steps); off: every step waits for its tokens before the next is decided
+    disable_run_ahead: bool = False
     device: str = "cuda:0"
 
     def model_dir(self) -> str:

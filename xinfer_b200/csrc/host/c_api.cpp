@@ -149,7 +149,8 @@ XB_API long long xb_assemble(void* h, int B, const int* slots, const int* counts
 // ---- scheduler ---------------------------------------------------------------------------------
 struct SchedHandle {
     Scheduler sched;
-    std::vector<StepEntry> last;
+    std::vector<StepEntry> last;    // scheduled, not yet committed
+    std::vector<StepEntry> ahead;   // the step after `last`, decided while `last` runs
     SchedHandle(CacheManager* c, const SchedulerConfig& cfg) : sched(c, cfg) {}
 };
 
@@ -189,11 +190,30 @@ XB_API int xb_sched_schedule(void* h, int cap_entries, long long* req_ids, int* 
     *n_tokens = (int)toks.size();
     return (int)s->last.size();
 }
+// Commits the oldest uncommitted step; a step decided ahead becomes the one awaiting commit.
 XB_API void xb_sched_commit(void* h, const int* sampled, int n_sampled) {
     SchedHandle* s = static_cast<SchedHandle*>(h);
     std::vector<int32_t> v(sampled, sampled + (n_sampled > 0 ? n_sampled : 0));
     s->sched.commit(s->last, v);
-    s->last.clear();
+    s->last.swap(s->ahead);
+    s->ahead.clear();
+}
+// The step after the uncommitted one (see Scheduler::schedule_ahead).  Returns the number of
+// entries, 0 when it cannot be decided ahead, -1 if the arrays are too small.
+XB_API int xb_sched_schedule_ahead(void* h, int cap_entries, long long* req_ids, int* slots, int* starts, int* src) {
+    SchedHandle* s = static_cast<SchedHandle*>(h);
+    if (!s->ahead.empty()) return 0;
+    std::vector<int> from;
+    std::vector<StepEntry> e = s->sched.schedule_ahead(s->last, &from);
+    if ((int)e.size() > cap_entries) return -1;
+    for (size_t i = 0; i < e.size(); ++i) {
+        req_ids[i] = e[i].req_id;
+        slots[i] = e[i].slot;
+        starts[i] = e[i].start;
+        src[i] = from[i];
+    }
+    s->ahead = e;
+    return (int)e.size();
 }
 XB_API int xb_sched_drain_finished(void* h, long long* out, int cap) {
     auto v = static_cast<SchedHandle*>(h)->sched.drain_finished();

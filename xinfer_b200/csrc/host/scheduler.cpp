@@ -175,9 +175,12 @@ void Scheduler::commit(const std::vector<StepEntry>& entries, const std::vector<
     size_t k = 0;
     for (const StepEntry& e : entries) {
         auto it = reqs_.find(e.req_id);
-        if (it == reqs_.end()) continue;
+        if (it == reqs_.end()) {  // ended and released while this step ran
+            if (e.want) ++k;
+            continue;
+        }
         Request& r = it->second;
-        if (r.finish != NOT_FINISHED || r.slot != e.slot) {  // aborted meanwhile
+        if (r.finish != NOT_FINISHED || r.slot != e.slot) {  // ended or aborted meanwhile
             if (e.want) ++k;
             continue;
         }
@@ -199,6 +202,39 @@ void Scheduler::commit(const std::vector<StepEntry>& entries, const std::vector<
             finish(r, FINISH_LENGTH);
         }
     }
+}
+
+std::vector<StepEntry> Scheduler::schedule_ahead(const std::vector<StepEntry>& prev, std::vector<int>* src) {
+    std::vector<StepEntry> out;
+    src->clear();
+    if (!waiting_.empty() || prev.empty() || prev.size() != running_.size()) return out;
+    int k = 0;
+    for (const StepEntry& e : prev) {
+        const int mine = e.want ? k++ : -1;
+        auto it = reqs_.find(e.req_id);
+        if (it == reqs_.end()) return {};
+        const Request& r = it->second;
+        if (r.finish != NOT_FINISHED || r.slot != e.slot || e.count != 1 || !e.want ||
+            e.start + 1 != (int)r.tokens.size())
+            return {};
+        const int total = (int)r.tokens.size() + 1;   // what the request holds once prev is committed
+        if (total - r.prompt_len >= r.max_tokens || total >= cfg_.max_model_len) continue;  // prev ends it
+        StepEntry a;
+        a.req_id = r.id;
+        a.slot = r.slot;
+        a.start = e.start + 1;
+        a.count = 1;
+        a.want = true;
+        out.push_back(a);
+        src->push_back(mine);
+    }
+    for (const StepEntry& a : out) {
+        if (!cache_->extend(a.slot, a.start + 1)) {
+            src->clear();
+            return {};
+        }
+    }
+    return out;
 }
 
 int Scheduler::finish_reason(int64_t id) const {

@@ -57,6 +57,14 @@ public:
     std::vector<StepEntry> schedule(std::vector<int32_t>* tokens);
     // The step ran.  `sampled` holds one token per entry with want == true, in entry order.
     void commit(const std::vector<StepEntry>& entries, const std::vector<int32_t>& sampled);
+    // The step after `prev`, decided while `prev` still runs (its tokens are not known yet): possible
+    // when nothing waits and `prev` decodes one token for every running request.  Each entry decodes
+    // the token that `prev` will sample for its request; `src` receives, per entry, the index of that
+    // token among prev's sampled tokens.  Requests that `prev` ends by length are left out; one that
+    // ends on a stop token is found out at commit, and its entry of this step is then ignored.
+    // Pages are taken here.  Empty when the step cannot be decided ahead (then nothing has changed
+    // but pages reserved for requests that will need them anyway).
+    std::vector<StepEntry> schedule_ahead(const std::vector<StepEntry>& prev, std::vector<int>* src);
     // Ids that finished (or were aborted) since the last call, in the order they ended.
     std::vector<int64_t> drain_finished();
 

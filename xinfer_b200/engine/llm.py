@@ -59,6 +59,15 @@ def _ms(t: float) -> int:
     return int(t * 1000)
 
 
+@dataclass
+class _Flight:
+    """A batch that is queued on the device."""
+    wanted: list
+    tokens_dev: Optional[torch.Tensor] = None
+    sampler: Optional[Sampler] = None
+    penalties: bool = False
+
+
 class Engine:
     def __init__(self, econfig: EngineConfig, dtype: str = "bf16", runner: Optional[ModelRunner] = None):
         """``runner``: a prepared model runner (for instance ``ModelRunner.random``) to use instead
@@ -75,14 +84,18 @@ class Engine:
             self.runner.cache, max_num_seqs=econfig.max_num_seqs, max_num_batched_tokens=budget,
             prefill_chunk_size=econfig.prefill_chunk_size, max_model_len=self.max_model_len,
             eos_token_ids=self.runner.plan.eos_token_ids)
-        self.sampler = Sampler(self.runner.device, econfig.max_num_seqs)
+        self.samplers = [Sampler(self.runner.device, econfig.max_num_seqs) for _ in range(2)]
+        self.sampler = self.samplers[0]
+        self._sampler_i = 0
+        self._flight: Optional[_Flight] = None    # a batch queued on the device whose tokens are not recorded yet
+        self.run_ahead = not econfig.disable_run_ahead
         self.seed = 0 if econfig.seed is None else int(econfig.seed)
         self._next_id = 0
         self._live: Dict[int, _Live] = {}
         self._done: Dict[int, GenerationOutput] = {}
         self.use_graphs = not econfig.disable_cuda_graph
         # counters (the reference logs the same two throughputs, src/core/engine.rs:1584-1716)
-        self.stats = {"steps": 0, "prompt_tokens": 0, "decoded_tokens": 0, "preemptions": 0}
+        self.stats = {"steps": 0, "prompt_tokens": 0, "decoded_tokens": 0, "preemptions": 0, "steps_decided_ahead": 0}
 
     # ---- admission ------------------------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
@@ -102,44 +115,82 @@ class Engine:
 
     # ---- one iteration --------------------------------------------------------------------------------
     def step(self) -> List[int]:
-        """Schedule and run one batch; returns the ids of requests that ended with it."""
-        entries = self.scheduler.schedule()
-        ended = self.scheduler.drain_finished()  # requests the scheduler had to abort
-        if entries:
-            inputs = []
-            wanted = []
-            for e in entries:
-                if e.start == 0:
-                    self.runner.prepare_slot(e.slot)
-                inputs.append(StepInput(e.slot, e.tokens, [len(e.tokens) - 1] if e.want else []))
-                if e.want:
-                    wanted.append(e)
-                if e.start < self._live[e.req_id].prompt_len:
-                    self.stats["prompt_tokens"] += min(len(e.tokens), self._live[e.req_id].prompt_len - e.start)
-            logits = self.runner.step(inputs, allow_graph=self.use_graphs)
-            sampled: List[int] = []
-            if wanted:
-                lives = [self._live[e.req_id] for e in wanted]
-                hist = None
-                if any(l.params.has_penalties for l in lives):
-                    hist = [self.scheduler.tail(e.req_id, PENALTY_HISTORY) if l.params.has_penalties else ()
-                            for e, l in zip(wanted, lives)]
-                toks = self.sampler.sample(logits, [l.params for l in lives], [l.seed for l in lives],
-                                           [self.scheduler.num_drawn(e.req_id) for e in wanted], hist)
-                self.runner.queue_error_check()
-                sampled = self.sampler.to_host(toks).tolist()
-                self.runner.raise_if_error()
-                now = time.time()
-                for l in lives:
-                    if not l.t_first:
-                        l.t_first = now
-                self.stats["decoded_tokens"] += len(sampled)
-            ended += self.scheduler.commit(sampled)
+        """Run one batch to its end; returns the ids of requests that ended with it.
+
+        While a batch of single decode tokens runs on the device, the next one is decided and
+        queued behind it (its token ids are read on the device from the running batch's sampled
+        tokens), so the device does not wait for the host between decode steps.  A request that
+        the running batch ends on a stop token has then one token computed in vain; its result
+        is dropped."""
+        flight, self._flight = self._flight, None
+        ended: List[int] = []
+        if flight is None:
+            entries = self.scheduler.schedule()
+            ended = self.scheduler.drain_finished()  # requests the scheduler had to abort
+            if entries:
+                flight = self._launch(entries, None)
+        if flight is not None:
+            if self.run_ahead and flight.sampler is not None and not flight.penalties:
+                ahead = self.scheduler.schedule_ahead()
+                if ahead:
+                    self._flight = self._launch(ahead, flight)
+                    self.stats["steps_decided_ahead"] += 1
+            ended += self._retire(flight)
             self.stats["steps"] += 1
         self.stats["preemptions"] = self.scheduler.preemptions
         for seq_id in ended:
             self._finish(seq_id)
+        if self._flight is not None and not any(e.req_id in self._live for e in self._flight.wanted):
+            self._retire(self._flight)   # queued for requests that have all ended meanwhile: nothing to keep
+            self._flight = None
         return ended
+
+    def _launch(self, entries, after: Optional["_Flight"]) -> "_Flight":
+        """Queue a batch and its sampling on the device; nothing waits for it here.  ``after``:
+        the batch still running whose sampled tokens are this batch's token ids."""
+        inputs = []
+        wanted = []
+        for e in entries:
+            if e.start == 0:
+                self.runner.prepare_slot(e.slot)
+            inputs.append(StepInput(e.slot, e.tokens, [len(e.tokens) - 1] if e.want else []))
+            if e.want:
+                wanted.append(e)
+            if e.start < self._live[e.req_id].prompt_len:
+                self.stats["prompt_tokens"] += min(len(e.tokens), self._live[e.req_id].prompt_len - e.start)
+        source = (after.tokens_dev, [e.src for e in entries]) if after is not None else None
+        logits = self.runner.step(inputs, allow_graph=self.use_graphs, tokens_from=source)
+        flight = _Flight(wanted=wanted)
+        if wanted:
+            lives = [self._live[e.req_id] for e in wanted]
+            hist = None
+            flight.penalties = any(l.params.has_penalties for l in lives)
+            if flight.penalties:
+                hist = [self.scheduler.tail(e.req_id, PENALTY_HISTORY) if l.params.has_penalties else ()
+                        for e, l in zip(wanted, lives)]
+            ahead = 1 if after is not None else 0    # tokens of `after` are drawn but not recorded yet
+            self._sampler_i ^= 1
+            sampler = self.samplers[self._sampler_i]   # two sets of buffers: two batches can be in flight
+            flight.tokens_dev = sampler.sample(logits, [l.params for l in lives], [l.seed for l in lives],
+                                               [self.scheduler.num_drawn(e.req_id) + ahead for e in wanted], hist)
+            self.runner.queue_error_check()
+            sampler.start_copy(flight.tokens_dev)
+            flight.sampler = sampler
+        return flight
+
+    def _retire(self, flight: "_Flight") -> List[int]:
+        """Wait for a queued batch's tokens and record them; returns the ids that ended."""
+        sampled: List[int] = []
+        if flight.sampler is not None:
+            sampled = flight.sampler.finish_copy().tolist()
+            self.runner.raise_if_error()
+            now = time.time()
+            for e in flight.wanted:
+                live = self._live.get(e.req_id)
+                if live is not None and not live.t_first:
+                    live.t_first = now
+            self.stats["decoded_tokens"] += sum(1 for e in flight.wanted if e.req_id in self._live)
+        return self.scheduler.commit(sampled)
 
     def _finish(self, seq_id: int) -> None:
         live = self._live.pop(seq_id, None)
@@ -154,7 +205,7 @@ class Engine:
         self.scheduler.release(seq_id)
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._flight is not None
 
     # ---- the reference's calls ----------------------------------------------------------------------------
     def generate_sync(self, params: Union[SamplingParams, Sequence[SamplingParams]],

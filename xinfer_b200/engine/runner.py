@@ -330,13 +330,21 @@ class ModelRunner:
         self.state.clear_slot(slot)
 
     # ---- the step --------------------------------------------------------------------------------------
-    def step(self, entries: Sequence[StepInput], *, allow_graph: bool = False) -> torch.Tensor:
+    def step(self, entries: Sequence[StepInput], *, allow_graph: bool = False,
+             tokens_from: Optional[Tuple[torch.Tensor, Sequence[int]]] = None) -> torch.Tensor:
         """Run one batch; returns float32 logits ``[wanted, vocab]`` on the device (a view of a
-        reused buffer: copy what must outlive the next step)."""
+        reused buffer: copy what must outlive the next step).
+
+        ``tokens_from`` = (int32 device tensor, indices): every entry brings one token whose id is
+        not known on the host yet; entry i's id is read on the device from ``tensor[indices[i]]``
+        (the ids given in the entries are placeholders)."""
+        if tokens_from is not None and any(len(e.tokens) != 1 for e in entries):
+            raise StepError("token ids can be taken from the device only for entries of one token")
         if allow_graph and self._graph_eligible(entries):
-            return self._step_graph(entries)
+            return self._step_graph(entries, tokens_from)
         before = kernels.launch_count()
         ctx = self.assembler.prepare(entries)
+        self._patch_tokens(ctx, len(entries), tokens_from)
         logits = self.model.forward(ctx, self.layer_caches, self.layer_states)
         self.finish(entries)
         self.last_launches = kernels.launch_count() - before
@@ -365,7 +373,33 @@ class ModelRunner:
             s *= 2
         return tuple(s for _ in self.cache.groups)
 
-    def _step_graph(self, entries: Sequence[StepInput]) -> torch.Tensor:
+    def _patch_tokens(self, ctx: StepContext, n: int, tokens_from) -> None:
+        """Overwrite the step's first ``n`` token ids, on the device, with ids a previous step left there."""
+        if tokens_from is None:
+            return
+        src, idx = tokens_from
+        idx = [int(i) for i in idx]
+        if len(idx) != n or src.dtype != torch.int32 or any(i < 0 or i >= src.numel() for i in idx):
+            raise StepError("tokens_from needs an int32 device tensor and one valid index per entry")
+        if idx == list(range(n)):
+            ctx.token_ids[:n].copy_(src[:n])
+            return
+        k = self._patch_i = (getattr(self, "_patch_i", 0) + 1) % 2
+        if not hasattr(self, "_patch_host"):
+            cap = max(self.max_num_seqs, n)
+            self._patch_host = [torch.zeros(cap, dtype=torch.int64, pin_memory=True) for _ in range(2)]
+            self._patch_dev = [torch.zeros(cap, dtype=torch.int64, device=self.device) for _ in range(2)]
+            self._patch_ev = [None, None]
+        if self._patch_ev[k] is not None:
+            self._patch_ev[k].synchronize()   # the copy that last used this pinned buffer has run
+        self._patch_host[k][:n] = torch.tensor(idx, dtype=torch.int64)
+        self._patch_dev[k][:n].copy_(self._patch_host[k][:n], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._patch_ev[k] = ev
+        torch.index_select(src, 0, self._patch_dev[k][:n], out=ctx.token_ids[:n])
+
+    def _step_graph(self, entries: Sequence[StepInput], tokens_from=None) -> torch.Tensor:
         B = len(entries)
         bucket = _bucket(B, self.max_num_seqs)
         strides = self._graph_strides(entries)
@@ -374,8 +408,9 @@ class ModelRunner:
         if g is None:
             g = self._capture(entries, bucket, strides)
             self._graphs[key] = g
-        self.assembler.prepare(entries, pad_entries=bucket, pad_tokens=bucket, pad_rows=bucket, strides=strides,
-                               into=g.meta, workspace=self._graph_workspace)
+        ctx = self.assembler.prepare(entries, pad_entries=bucket, pad_tokens=bucket, pad_rows=bucket, strides=strides,
+                                     into=g.meta, workspace=self._graph_workspace)
+        self._patch_tokens(ctx, B, tokens_from)
         g.graph.replay()
         self.finish(entries)
         self.last_launches = g.launches

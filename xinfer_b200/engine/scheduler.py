@@ -31,6 +31,8 @@ class ScheduledEntry:
     start: int     # tokens already cached
     tokens: np.ndarray
     want: bool     # logits at the last token are wanted (the portion ends the known tokens)
+    # for a step decided ahead: which of the running step's sampled tokens this entry decodes
+    src: Optional[int] = None
 
 
 class Scheduler:
@@ -85,9 +87,23 @@ class Scheduler:
             t += c
         return out
 
+    def schedule_ahead(self) -> List[ScheduledEntry]:
+        """The step after the one that was scheduled and still runs, decided before its tokens are
+        known: one decode token per running request (``tokens`` is a placeholder; ``src`` says
+        which sampled token of the running step takes its place).  Empty when that cannot be done:
+        something waits, the running step is not all decode, pages are short.  A request that the
+        running step ends on a stop token still gets an entry; commit ignores it."""
+        src = np.zeros(self._cap_e, dtype=np.int32)
+        n = self._lib.xb_sched_schedule_ahead(self._h, self._cap_e, self._ids.ctypes.data, self._slots.ctypes.data,
+                                              self._starts.ctypes.data, src.ctypes.data)
+        if n < 0:
+            raise SchedulerError("the scheduled batch exceeds the scheduler's buffers")
+        return [ScheduledEntry(int(self._ids[i]), int(self._slots[i]), int(self._starts[i]),
+                               np.zeros(1, dtype=np.int32), True, int(src[i])) for i in range(n)]
+
     def commit(self, sampled: Sequence[int]) -> List[int]:
-        """Record the step just scheduled; ``sampled`` holds one token per entry that wanted
-        logits, in entry order.  Returns the ids that ended (finished or aborted)."""
+        """Record the oldest scheduled step that is not yet recorded; ``sampled`` holds one token per
+        entry that wanted logits, in entry order.  Returns the ids that ended (finished or aborted)."""
         s = np.asarray(list(sampled), dtype=np.int32)
         self._lib.xb_sched_commit(self._h, s.ctypes.data if len(s) else None, len(s))
         return self.drain_finished()

@@ -67,6 +67,7 @@ def _declare_host(lib):
     _sig(lib, "xb_sched_schedule", c_int,
          [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p])
     _sig(lib, "xb_sched_commit", None, [c_void_p, c_void_p, c_int])
+    _sig(lib, "xb_sched_schedule_ahead", c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
     _sig(lib, "xb_sched_drain_finished", c_int, [c_void_p, c_void_p, c_int])
     for name in ("xb_sched_num_waiting", "xb_sched_num_running", "xb_sched_preemptions"):
         _sig(lib, name, c_int, [c_void_p])

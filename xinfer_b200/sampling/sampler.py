@@ -67,7 +67,18 @@ class Sampler:
 
     def to_host(self, tokens_dev: torch.Tensor) -> np.ndarray:
         """Copy sampled ids to the host (synchronises the stream)."""
+        self.start_copy(tokens_dev)
+        return self.finish_copy()
+
+    def start_copy(self, tokens_dev: torch.Tensor) -> None:
+        """Queue the copy of sampled ids to the host; ``finish_copy`` waits for it alone, so work
+        queued after it keeps running."""
         n = tokens_dev.shape[0]
         self._out_host[:n].copy_(tokens_dev, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return self._out_host[:n].numpy().copy()
+        self._copied = n
+        self._copy_done = torch.cuda.Event()
+        self._copy_done.record()
+
+    def finish_copy(self) -> np.ndarray:
+        self._copy_done.synchronize()
+        return self._out_host[:self._copied].numpy().copy()
