@@ -116,6 +116,12 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
           "r"(__float_as_uint(v[31]))
         : "memory");
 }
+// 2^x on the special-function unit, one instruction (x <= 0 here; -inf gives 0).
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -139,10 +145,11 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // DP: head size padded to 64 or 128.  Shared memory (1024-byte aligned):
 //   Q  [DP/64][128 rows][64]   K stage s [DP/64][64 keys][64]   V stage s likewise   P [128][64]
 // every [rows][64] piece is a tile of 128-byte rows whose 16-byte chunks are XOR-ed with row & 7.
-// Warps 0..3: one query row per thread (softmax).  Warp 4: TMA producer.  Warp 5: MMA issuer.
+// Warps 0..3: one query row per thread (softmax).  Warps 4 and 6: TMA producers of keys and of values.
+// Warp 5: MMA issuer.
 // Tensor memory: S[0] at column 0, S[1] at 64, O at 128.
 template <int DP>
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(224)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                        const int* __restrict__ q_start, const int* __restrict__ start_pos, int num_entries,
@@ -155,11 +162,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t base = smem_u32(smem_raw);
     const uint32_t q_sm = base, kv_sm = base + Q_BYTES, p_sm = kv_sm + 2 * STAGE_BYTES;
     unsigned char* p_ptr = smem_raw + Q_BYTES + 2 * STAGE_BYTES;
-    // barriers, 8 bytes each: full[2] empty[2] s_ready[2] s_free[2] q_full p_ready bar_o; then four words
+    // barriers, 8 bytes each: k_full[2] k_empty[2] v_full[2] v_empty[2] s_ready[2] s_free[2] q_full p_ready bar_o;
+    // then four words
     const uint32_t bars = p_sm + P_BYTES;
-    const uint32_t full0 = bars, empty0 = bars + 16, s_ready0 = bars + 32, s_free0 = bars + 48;
-    const uint32_t q_full = bars + 64, p_ready = bars + 72, bar_o = bars + 80;
-    volatile uint32_t* words = reinterpret_cast<volatile uint32_t*>(p_ptr + P_BYTES + 88);  // tmem, entry, tile, dead
+    const uint32_t k_full0 = bars, k_empty0 = bars + 16, v_full0 = bars + 32, v_empty0 = bars + 48;
+    const uint32_t s_ready0 = bars + 64, s_free0 = bars + 80;
+    const uint32_t q_full = bars + 96, p_ready = bars + 104, bar_o = bars + 112;
+    volatile uint32_t* words = reinterpret_cast<volatile uint32_t*>(p_ptr + P_BYTES + 120);  // tmem, entry, tile, dead
     const int warp = threadIdx.x >> 5;
     const int h = blockIdx.x, g = h / (nh / nkv);   // heads vary fastest: every head's longest tiles start first
     pdl_launch_dependents();
@@ -184,7 +193,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         words[1] = (uint32_t)found;
         words[2] = (uint32_t)tile;
         words[3] = 0;
-        for (int i = 0; i < 6; ++i) mbar_init(bars + 8 * i, 1);   // full, empty, s_ready
+        for (int i = 0; i < 10; ++i) mbar_init(bars + 8 * i, 1);   // k_full, k_empty, v_full, v_empty, s_ready
         mbar_init(s_free0, 128);
         mbar_init(s_free0 + 8, 128);
         mbar_init(q_full, 1);
@@ -218,19 +227,26 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int iters = kt_last - kt_first + 1;
     const int box_rows = ps < KT ? ps : KT;
 
-    if (warp == 4) {
-        // ---- producer: Q once, then the key/value pages of every tile through the two stages ----------
-        if (threadIdx.x == 128) {
-            mbar_expect_tx(q_full, Q_BYTES);
+    if (warp == 4 || warp == 6) {
+        // ---- producers: warp 4 streams Q once and then the key pages, warp 6 the value pages, each through
+        // its own two-stage ring: a key stage is free again after its Q K^T, a value stage only after its
+        // P V, two steps later, so keys can be requested that much earlier
+        const bool is_v = warp == 6;
+        const uint32_t full0 = is_v ? v_full0 : k_full0, empty0 = is_v ? v_empty0 : k_empty0;
+        const CUtensorMap* map = is_v ? &map_v : &map_k;
+        if ((threadIdx.x & 31) == 0) {
+            if (!is_v) {
+                mbar_expect_tx(q_full, Q_BYTES);
 #pragma unroll
-            for (int hf = 0; hf < HALVES; ++hf) tma_load_3d(q_sm + hf * QT * 128, &map_q, hf * 64, h, t0, q_full);
+                for (int hf = 0; hf < HALVES; ++hf) tma_load_3d(q_sm + hf * QT * 128, &map_q, hf * 64, h, t0, q_full);
+            }
             for (int it = 0; it < iters; ++it) {
                 const int s = it & 1, kt = kt_first + it;
                 if (it >= 2 && !mbar_wait(empty0 + 8 * s, ((it >> 1) - 1) & 1, err)) {
                     words[3] = 1;
                     break;
                 }
-                const uint32_t k_dst = kv_sm + s * STAGE_BYTES, v_dst = k_dst + KV_BYTES;
+                const uint32_t dst0 = kv_sm + s * STAGE_BYTES + (is_v ? KV_BYTES : 0u);
                 uint32_t bytes = 0;
                 int pages[KT / 8];
                 for (int i = 0; i < KT / box_rows; ++i) {
@@ -243,7 +259,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         continue;
                     }
                     pages[i] = page;
-                    bytes += 2 * HALVES * box_rows * 128;
+                    bytes += HALVES * box_rows * 128;
                 }
                 mbar_expect_tx(full0 + 8 * s, bytes);
                 for (int i = 0; i < KT / box_rows; ++i) {
@@ -251,10 +267,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     const int j = kt * KT + i * box_rows;
                     const int grow = (pages[i] * nkv + g) * ps + (j & (ps - 1));
 #pragma unroll
-                    for (int hf = 0; hf < HALVES; ++hf) {
-                        tma_load_2d(k_dst + hf * KV_HALF + i * box_rows * 128, &map_k, hf * 64, grow, full0 + 8 * s);
-                        tma_load_2d(v_dst + hf * KV_HALF + i * box_rows * 128, &map_v, hf * 64, grow, full0 + 8 * s);
-                    }
+                    for (int hf = 0; hf < HALVES; ++hf)
+                        tma_load_2d(dst0 + hf * KV_HALF + i * box_rows * 128, map, hf * 64, grow, full0 + 8 * s);
                 }
             }
         }
@@ -267,7 +281,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const uint64_t dp0 = umma_desc(p_sm, 16, 1024), dv0 = umma_desc(kv_sm + KV_BYTES, KV_HALF, 1024);
             auto issue_qk = [&](int it) -> bool {   // S[it & 1] = Q K^T of tile `it`
                 const int sb = it & 1;
-                if (!mbar_wait(full0 + 8 * sb, (it >> 1) & 1, err)) return false;
+                if (!mbar_wait(k_full0 + 8 * sb, (it >> 1) & 1, err)) return false;
                 if (it >= 2 && !mbar_wait(s_free0 + 8 * sb, ((it >> 1) - 1) & 1, err)) return false;  // every row of S[sb] was read
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint64_t dk = dk0 + (uint64_t)((sb * STAGE_BYTES) >> 4);
@@ -277,6 +291,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     umma_bf16(tmem_s + (uint32_t)sb * 64, dq0 + (uint64_t)((off * QT * 128 + inner) >> 4),
                               dk + (uint64_t)((off * KV_HALF + inner) >> 4), idesc_s, kk ? 1u : 0u);
                 }
+                umma_commit(k_empty0 + 8 * sb);   // the key stage is free once these have completed
                 umma_commit(s_ready0 + 8 * sb);
                 return true;
             };
@@ -284,6 +299,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             for (int it = 0; it < iters && ok; ++it) {
                 const int s = it & 1;
                 if (it + 1 < iters) ok = issue_qk(it + 1);
+                ok = ok && mbar_wait(v_full0 + 8 * s, (it >> 1) & 1, err);
                 ok = ok && mbar_wait(p_ready, it & 1, err);   // P written, V rows zeroed, O rescaled
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -292,7 +308,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
                 for (int kk = 0; kk < KT / 16; ++kk)
                     umma_bf16(tmem_o, dp0 + (uint64_t)((kk * 32) >> 4), dv + (uint64_t)((kk * 2048) >> 4), idesc_o, (it | kk) ? 1u : 0u);
-                umma_commit(empty0 + 8 * s);          // stage, P and O are free again once these have completed
+                umma_commit(v_empty0 + 8 * s);        // the value stage, P and O are free again once these have completed
                 if (it + 1 == iters) umma_commit(bar_o);
             }
             if (!ok) words[3] = 1;
@@ -328,45 +344,47 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_arrive(s_free0 + 8 * s);   // this row of S[s] is in registers
             const bool edge = key0 + KT - 1 > p0 || key0 + KT - 1 > last_key || key0 < first_key ||
                               (window > 0 && key0 < p0 + QT - 1 - window + 1);
-            float mx = -INFINITY;
+            // the maximum is taken over the raw scores (the scale is positive); four chains, as a thread
+            // has no one to wait for
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (edge) {
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                float v = sc[i] * scale_log2;
-                if (edge) {
+                for (int i = 0; i < 64; ++i) {
                     const int j = key0 + i;
                     const bool ok = j <= my_pos && j <= last_key && (window <= 0 || j > my_pos - window);
-                    v = ok ? v : -INFINITY;
+                    sc[i] = ok ? sc[i] : -INFINITY;
                 }
-                sc[i] = v;
-                mx = fmaxf(mx, v);
             }
+#pragma unroll
+            for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sc[i]);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
             // move the reference maximum only when the row's maximum outgrows it by more than 2^8
             float corr = 1.f;
             int moved = 0;
             if (mx > m_ref + RESCALE_STEP) {
-                corr = m_ref == -INFINITY ? 0.f : exp2f(m_ref - mx);
+                corr = m_ref == -INFINITY ? 0.f : ex2(m_ref - mx);
                 m_ref = mx;
                 moved = it > 0;
             }
-            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-            float sum = 0.f;
+            const float m_neg = m_ref == -INFINITY ? 0.f : -m_ref;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             uint4 pk[8];
 #pragma unroll
             for (int c8 = 0; c8 < 8; ++c8) {
                 float e[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    e[i] = exp2f(sc[c8 * 8 + i] - m_use);
-                    sum += e[i];
+                    e[i] = ex2(fmaf(sc[c8 * 8 + i], scale_log2, m_neg));   // 2^(s * scale - m), one FMA and one SFU op
+                    sum4[i & 3] += e[i];
                 }
                 pk[c8].x = pack_bf16(e[0], e[1]);
                 pk[c8].y = pack_bf16(e[2], e[3]);
                 pk[c8].z = pack_bf16(e[4], e[5]);
                 pk[c8].w = pack_bf16(e[6], e[7]);
             }
-            l = l * corr + sum;
+            l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             // P and O belong to the previous tile's P V until it has completed
-            if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(empty0 + 8 * (s ^ 1), ((it - 1) >> 1) & 1, err))) {
+            if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(v_empty0 + 8 * (s ^ 1), ((it - 1) >> 1) & 1, err))) {
                 alive = false;
                 break;
             }
@@ -377,7 +395,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // value rows outside the visible keys become zeros (only tiles at the ends of the range)
             if (key0 < first_key || key0 + KT - 1 > last_key) {
                 if (threadIdx.x < KT) {
-                    mbar_wait(full0 + 8 * s, (it >> 1) & 1, err);   // already complete; orders these writes after the TMA's
+                    mbar_wait(v_full0 + 8 * s, (it >> 1) & 1, err);   // orders these writes after the TMA's
                     const int j = key0 + (int)threadIdx.x;
                     if (j < first_key || j > last_key) {
 #pragma unroll
@@ -683,12 +701,12 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             for (int set = 0; set < 2; ++set) {
                 if (set == 1 && !two) break;
                 float sc[16];
-                float mx2[2] = {-INFINITY, -INFINITY};
+                float mx2[2] = {-INFINITY, -INFINITY};   // over the raw scores: the scale is positive
 #pragma unroll
                 for (int k = 0; k < 8; ++k)
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
-                        float v = __uint_as_float(raw[4 * k + 2 * set + e]) * scale_log2;
+                        float v = __uint_as_float(raw[4 * k + 2 * set + e]);
                         if (edge) {
                             const int j = key0 + 8 * k + 2 * quad + e;
                             v = (j >= k_begin && j <= k_end) ? v : -INFINITY;
@@ -699,17 +717,18 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 float mx = fmaxf(mx2[0], mx2[1]);
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                mx *= scale_log2;
                 // move the reference maximum only when the row's maximum outgrows it by more than 2^8
                 if (mx > m_ref[set] + RESCALE_STEP) {
-                    corr[set] = m_ref[set] == -INFINITY ? 0.f : exp2f(m_ref[set] - mx);
+                    corr[set] = m_ref[set] == -INFINITY ? 0.f : ex2(m_ref[set] - mx);
                     m_ref[set] = mx;
                     moved |= (it > 0 && r0 + 8 * set < G) ? 1 : 0;
                 }
-                const float m_use = m_ref[set] == -INFINITY ? 0.f : m_ref[set];
+                const float m_neg = m_ref[set] == -INFINITY ? 0.f : -m_ref[set];
                 float sum2[2] = {0.f, 0.f};
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
-                    const float e0 = exp2f(sc[2 * k] - m_use), e1 = exp2f(sc[2 * k + 1] - m_use);
+                    const float e0 = ex2(fmaf(sc[2 * k], scale_log2, m_neg)), e1 = ex2(fmaf(sc[2 * k + 1], scale_log2, m_neg));
                     sum2[0] += e0;
                     sum2[1] += e1;
                     pk[set][k] = pack_bf16(e0, e1);
@@ -960,10 +979,10 @@ template <int DP>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, const int* q_start,
            const int* start_pos, int num_entries, const int* table, int stride, int nh, int nkv, int d, int ps,
            int ps_shift, int num_pages, int window, float sl2, int dec_max, int tiles, int* err, cudaStream_t stream) {
-    constexpr size_t smem = (size_t)(DP / 64) * QT * 128 + 2 * 2 * (size_t)(DP / 64) * KT * 128 + QT * 128 + 112;
+    constexpr size_t smem = (size_t)(DP / 64) * QT * 128 + 2 * 2 * (size_t)(DP / 64) * KT * 128 + QT * 128 + 144;
     cudaFuncSetAttribute(attn_prefill_tc_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaFuncSetAttribute(attn_prefill_tc_kernel<DP>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    return xb_launch(attn_prefill_tc_kernel<DP>, dim3(nh, tiles), dim3(192), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
+    return xb_launch(attn_prefill_tc_kernel<DP>, dim3(nh, tiles), dim3(224), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
                      q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, ps_shift, num_pages, window, sl2,
                      dec_max, err);
 }

@@ -115,7 +115,8 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t ra
 template <typename TO>
 __global__ void __launch_bounds__(128)
 gemm_skinny_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                      TO* __restrict__ out, int M, int N, int K, int mp, int k_per_split, int stages, int* err) {
+                      TO* __restrict__ out, int M, int N, int K, int mp, int k_per_split, int stages,
+                      const unsigned char* __restrict__ pf_ptr, unsigned long long pf_bytes, int* err) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long bars[2 * 16 + 1];
     __shared__ uint32_t s_tmem;
@@ -169,6 +170,20 @@ gemm_skinny_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             mbar_expect_tx(full0 + 8 * s, stage_bytes);
             tma_load_2d(dst, &map_w, k_begin + it * TILE_K, n0, full0 + 8 * s);
             tma_load_2d(dst + w_bytes, &map_x, k_begin + it * TILE_K, 0, full0 + 8 * s);
+        }
+        // Every load of this CTA is on its way: ask the L2 for this CTA's share of what the next
+        // product will stream first, so that the memory keeps working while this kernel drains and
+        // the next one starts up.
+        if (pf_bytes) {
+            const unsigned long long ctas = (unsigned long long)gridDim.x * gridDim.y;
+            const unsigned long long id = (unsigned long long)blockIdx.y * gridDim.x + blockIdx.x;
+            unsigned long long share = ((pf_bytes / ctas) + 15ull) & ~15ull;
+            unsigned long long at = id * share;
+            const unsigned long long end = at + share < pf_bytes ? at + share : (pf_bytes & ~15ull);
+            for (; at < end; at += 16384ull) {
+                const unsigned int n = (unsigned int)(end - at < 16384ull ? end - at : 16384ull);
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pf_ptr + at), "r"(n) : "memory");
+            }
         }
     } else if (threadIdx.x == 32) {
         // ---- MMA issuer -------------------------------------------------------------------------------
@@ -293,7 +308,8 @@ bool tensor_map_2d(CUtensorMap* out, const void* ptr, long long rows, long long 
 
 template <typename TO>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int M, int N, int K, int mp, int splits,
-           int k_per_split, int stages, size_t smem, int* err, cudaStream_t stream) {
+           int k_per_split, int stages, size_t smem, const void* pf_ptr, unsigned long long pf_bytes, int* err,
+           cudaStream_t stream) {
     cudaFuncSetAttribute(gemm_skinny_tc_kernel<TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((N + TILE_N - 1) / TILE_N, splits, 1);
@@ -309,7 +325,8 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int M, int N
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = xb_pdl_enabled() ? 2 : 1;
-    const cudaError_t rc = cudaLaunchKernelEx(&cfg, gemm_skinny_tc_kernel<TO>, mw, mx, (TO*)out, M, N, K, mp, k_per_split, stages, err);
+    const cudaError_t rc = cudaLaunchKernelEx(&cfg, gemm_skinny_tc_kernel<TO>, mw, mx, (TO*)out, M, N, K, mp, k_per_split, stages,
+                                              (const unsigned char*)pf_ptr, pf_bytes, err);
     return rc != cudaSuccess ? (int)rc : xb_launch_status();
 }
 
@@ -317,9 +334,11 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int M, int N
 
 // out[M, N] (bfloat16 when out_f32 == 0, else float32) = x[M, K] . w[N, K]^T for M <= 256.
 // K must be a multiple of 8 (rows 16-byte aligned); `splits` in 1..8 CTAs share K through a
-// cluster (0: chosen here).  Returns cudaErrorNotSupported for shapes it does not take.
+// cluster (0: chosen here).  `next_w` / `next_bytes`: the first bytes (16-byte aligned) that the
+// product after this one will read, requested into the L2 while this one drains (0: nothing).
+// Returns cudaErrorNotSupported for shapes it does not take.
 XB_EXPORT int xb_gemm_skinny_tc(void* out, int out_f32, const void* x, const void* w, int M, int N, int K, int splits,
-                                int* err, cudaStream_t stream) {
+                                const void* next_w, unsigned long long next_bytes, int* err, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 256 || K % 8 || K < TILE_K || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return (int)cudaErrorNotSupported;
     int mp = 16;
@@ -337,7 +356,15 @@ XB_EXPORT int xb_gemm_skinny_tc(void* out, int out_f32, const void* x, const voi
     tiles_per_split = (k_tiles + splits - 1) / splits;
     const size_t stage_bytes = (size_t)TILE_N * TILE_K * 2 + (size_t)mp * TILE_K * 2;
     // few tokens: stages small enough for two CTAs per SM, so that a wave holds every CTA
-    const size_t budget = mp <= 64 ? 100 * 1024 : 200 * 1024;
+    size_t budget = mp <= 64 ? 100 * 1024 : 200 * 1024;
+    {
+        static int kb = -1;
+        if (kb < 0) {
+            const char* e = getenv("XINFER_B200_GEMM_RING_KB");
+            kb = e ? atoi(e) : 0;
+        }
+        if (kb > 0 && mp <= 64) budget = (size_t)kb * 1024;
+    }
     int stages = (int)(budget / stage_bytes);
     if (stages > 12) stages = 12;
     if (stages > tiles_per_split) stages = tiles_per_split < 2 ? 2 : tiles_per_split;
@@ -347,6 +374,8 @@ XB_EXPORT int xb_gemm_skinny_tc(void* out, int out_f32, const void* x, const voi
     smem += 1024;  // room to align the window to 1024 bytes
     CUtensorMap mw, mx;
     if (!tensor_map_2d(&mw, w, N, K, TILE_N) || !tensor_map_2d(&mx, x, M, K, mp)) return (int)cudaErrorNotSupported;
-    if (out_f32) return launch<float>(mw, mx, out, M, N, K, mp, splits, tiles_per_split * TILE_K, stages, smem, err, stream);
-    return launch<__nv_bfloat16>(mw, mx, out, M, N, K, mp, splits, tiles_per_split * TILE_K, stages, smem, err, stream);
+    if (!next_w || ((uintptr_t)next_w & 15)) next_bytes = 0;
+    if (out_f32)
+        return launch<float>(mw, mx, out, M, N, K, mp, splits, tiles_per_split * TILE_K, stages, smem, next_w, next_bytes, err, stream);
+    return launch<__nv_bfloat16>(mw, mx, out, M, N, K, mp, splits, tiles_per_split * TILE_K, stages, smem, next_w, next_bytes, err, stream);
 }
