@@ -181,3 +181,23 @@ def test_deciding_the_next_step_ahead_changes_no_token(dtype, graphs, model_fold
         assert eng.runner.cache.live_requests() == 0
     assert runs[0] == runs[1]
     assert {r for _, r in runs[0]} >= {"length"}
+
+
+def test_cache_sized_from_free_memory_and_the_command_line(model_folders, tmp_path, capsys):
+    """num_blocks unset: the pool is sized from free device memory x kv_fraction, capped by what
+    max_num_seqs requests of max_model_len tokens can hold; the command line prints what the
+    Python entry point returns."""
+    from xinfer_b200 import SamplingParams
+    from xinfer_b200 import cli
+    folder = model_folders("A", torch.float32)
+    cfg, w = plain.load_folder(folder)
+    eng = engine(folder, "f32", "A", num_blocks=None, kv_fraction=0.01, max_num_seqs=2, max_model_len=200)
+    assert eng.runner.num_blocks == 2 * ((200 + 15) // 16)          # the cap, far below 1 % of a B200
+    assert eng.get_available_kv_tokens() == eng.runner.num_blocks * 16
+    p = prompts_for("A", [9])[0]
+    want = plain.generate(cfg, w, p, 6)
+    assert eng.generate_sync(SamplingParams(max_tokens=6, ignore_eos=True), [p])[0].decode_output == want
+    rc = cli.main(["--m", folder, "--dtype", "f32", "--prompts", ",".join(map(str, p)), "--max-tokens", "6", "--ignore-eos",
+                   "--kv-fraction", "0.01", "--max-model-len", "200"])
+    out = capsys.readouterr().out
+    assert rc == 0 and ",".join(map(str, want)) in out and "Prompt tokens: 9" in out

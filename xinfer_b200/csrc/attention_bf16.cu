@@ -15,7 +15,7 @@
 // Keys a query at position p may see: max(0, p - window + 1) .. p  (window <= 0: from 0).
 // Rows of a tile that lie outside a request's keys are zero-filled, never read from memory, so
 // stale or poisoned pages cannot reach a result.
-#include "common.cuh"
+#include "attention_common.cuh"
 
 namespace {
 
@@ -163,21 +163,6 @@ __device__ __forceinline__ void warp_pv(float (&o)[DP / 8][4], const float (&p)[
             mma_bf16(o[nb * 2 + 1], a, b[2], b[3]);
         }
     }
-}
-
-// Which token the z-th "small" token of the batch is: tokens of entries that bring at most
-// dec_max tokens, in batch order.  -1 if there is none.
-__device__ __forceinline__ int small_token(int z, const int* __restrict__ q_start, int num_entries, int dec_max, int direct) {
-    if (direct) return z < q_start[num_entries] ? z : -1;
-    int acc = 0;
-    for (int b = 0; b < num_entries; ++b) {
-        const int n = q_start[b + 1] - q_start[b];
-        if (n > 0 && n <= dec_max) {
-            if (z < acc + n) return q_start[b] + z - acc;
-            acc += n;
-        }
-    }
-    return -1;
 }
 
 // ------------------------------------------------------------------------------------------------

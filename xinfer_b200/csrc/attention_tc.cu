@@ -17,130 +17,16 @@
 // multiplied, so stale or poisoned pages cannot reach a result.  Every mbarrier wait is bounded
 // (XB_ERR_WAIT in the error word on expiry, then the CTA frees its TMEM and leaves).
 // Head sizes: multiples of 16 up to 128.  Page sizes: powers of two from 8.
-#include <cuda.h>
-
-#include <mutex>
-#include <unordered_map>
-
-#include "common.cuh"
+#include "attention_common.cuh"
+#include "tc_common.cuh"
 
 namespace {
 
+using namespace xbtc;
+
 constexpr int QT = 128;  // queries per CTA
 constexpr int KT = 64;   // keys per tile
-constexpr long long WAIT_CYCLES = 400000000LL;  // about 0.2 s: a wait that long has failed
 constexpr float RESCALE_STEP = 8.f;  // the row maximum moves only when it grows by more than 2^8
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err) {
-    const long long t0 = clock64();
-    for (;;) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-        if (clock64() - t0 > WAIT_CYCLES) break;
-    }
-    atomicOr(err, XB_ERR_WAIT);
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
-}
-// Shared-memory operand descriptor, 128-byte swizzle; byte offsets in 16-byte units, version 1.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
-    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
-    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
-// D float32, A/B bfloat16, A K-major, M = 128, N = n; B K-major or MN-major.
-__device__ __forceinline__ uint32_t umma_idesc(int n, int b_mn_major) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-    uint32_t r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
-          "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
-          "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
-          "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
-          "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])),
-          "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
-          "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
-          "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])),
-          "r"(__float_as_uint(v[31]))
-        : "memory");
-}
-// 2^x on the special-function unit, one instruction (x <= 0 here; -inf gives 0).
-__device__ __forceinline__ float ex2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-
-__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-}
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
 
 // DP: head size padded to 64 or 128.  Shared memory (1024-byte aligned):
 //   Q  [DP/64][128 rows][64]   K stage s [DP/64][64 keys][64]   V stage s likewise   P [128][64]
@@ -466,38 +352,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 // ------------------------------------------------------------------------------------------------
 // decode: few tokens per request, keys split into ranges
 // ------------------------------------------------------------------------------------------------
-// Which token the z-th "small" token of the batch is: tokens of entries that bring at most dec_max
-// tokens, in batch order.  -1 if there is none.
-__device__ __forceinline__ int small_token_of(int z, const int* __restrict__ q_start, int num_entries, int dec_max, int direct) {
-    if (direct) return z < q_start[num_entries] ? z : -1;
-    int acc = 0;
-    for (int b = 0; b < num_entries; ++b) {
-        const int n = q_start[b + 1] - q_start[b];
-        if (n > 0 && n <= dec_max) {
-            if (z < acc + n) return q_start[b] + z - acc;
-            acc += n;
-        }
-    }
-    return -1;
-}
-
 constexpr int DEC_ROWS = 16;    // query heads of one key/value head a CTA can hold
 constexpr int DEC_STAGES = 3;   // key/value tiles in flight per CTA
-
-// 16 TMEM lanes x 64 columns of float32: lane t of the warp receives, for every block k of 8
-// columns, r[4k], r[4k+1] = row t/4, columns 8k + 2(t%4) and +1, and r[4k+2], r[4k+3] = row t/4 + 8,
-// the same columns (the layout of an MMA accumulator fragment): a row's columns are spread over four lanes.
-__device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.16x256b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
 
 // One CTA = one token x one key/value head x one of num_splits ranges of the token's keys (`split` is
 // the longest a range can be: it sizes the staging area of block-table entries).  The query heads of
@@ -541,7 +397,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 
     // what this CTA works on: step metadata only (written before the step's first kernel)
     const int G = nh / nkv, g = blockIdx.y;
-    const int t = small_token_of(blockIdx.z, q_start, num_entries, dec_max, direct);
+    const int t = small_token(blockIdx.z, q_start, num_entries, dec_max, direct);
     if (t < 0) return;
     const int b = req_of_token[t];
     if (b < 0) return;
@@ -889,90 +745,15 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 }
 
 // ---- host: tensor maps ------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    });
-    return fn;
-}
-
-struct Key {
-    const void* ptr;
-    long long a, b, c;
-    int box;
-    bool operator==(const Key& o) const { return ptr == o.ptr && a == o.a && b == o.b && c == o.c && box == o.box; }
-};
-struct KeyHash {
-    size_t operator()(const Key& k) const {
-        return std::hash<const void*>()(k.ptr) ^ (size_t)(k.a * 1000003 + k.b * 10007 + k.c * 101 + k.box);
-    }
-};
-std::unordered_map<Key, CUtensorMap, KeyHash>& cache() {
-    static std::unordered_map<Key, CUtensorMap, KeyHash> c;
-    return c;
-}
-std::mutex& cache_mutex() {
-    static std::mutex m;
-    return m;
-}
-
-// [rows, d] row-major bfloat16 through boxes [box_rows x 64], 128-byte swizzle.
+// [rows, d] row-major bfloat16 (the pages of a cache) through boxes [box_rows x 64].
 bool map_rows(CUtensorMap* out, const void* ptr, long long rows, int d, int box_rows) {
-    std::lock_guard<std::mutex> lock(cache_mutex());
-    const Key key{ptr, rows, d, 0, box_rows};
-    auto it = cache().find(key);
-    if (it != cache().end()) {
-        *out = it->second;
-        return true;
-    }
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return false;
-    const cuuint64_t gdim[2] = {(cuuint64_t)d, (cuuint64_t)rows};
-    const cuuint64_t gstr[1] = {(cuuint64_t)d * 2};
-    const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
-    const cuuint32_t es[2] = {1, 1};
-    CUtensorMap m;
-    if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstr, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return false;
-    if (cache().size() > 4096) cache().clear();
-    cache()[key] = m;
-    *out = m;
-    return true;
+    return tensor_map_2d(out, ptr, rows, d, box_rows);
 }
-
 // q [T, nh, d] through boxes [box_tokens x box_heads x 64 columns].
 bool map_q3(CUtensorMap* out, const void* ptr, long long T, int nh, int d, int box_heads, int box_tokens) {
-    std::lock_guard<std::mutex> lock(cache_mutex());
-    const Key key{ptr, T, nh, (long long)d | ((long long)box_heads << 20), -box_tokens};
-    auto it = cache().find(key);
-    if (it != cache().end()) {
-        *out = it->second;
-        return true;
-    }
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return false;
-    const cuuint64_t gdim[3] = {(cuuint64_t)d, (cuuint64_t)nh, (cuuint64_t)T};
-    const cuuint64_t gstr[2] = {(cuuint64_t)d * 2, (cuuint64_t)nh * d * 2};
-    const cuuint32_t box[3] = {64, (cuuint32_t)box_heads, (cuuint32_t)box_tokens};
-    const cuuint32_t es[3] = {1, 1, 1};
-    CUtensorMap m;
-    if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), gdim, gstr, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return false;
-    if (cache().size() > 4096) cache().clear();
-    cache()[key] = m;
-    *out = m;
-    return true;
+    const long long dims[3] = {d, nh, T}, strides[2] = {d, (long long)nh * d};
+    const int box[3] = {64, box_heads, box_tokens};
+    return tensor_map_bf16(out, ptr, 3, dims, strides, box);
 }
 
 template <int DP>

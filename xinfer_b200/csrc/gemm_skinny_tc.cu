@@ -12,84 +12,15 @@
 //     distributed shared memory in rank order (deterministic, no scratch in global memory).
 // Every wait on an mbarrier is bounded: on expiry the kernel sets XB_ERR_WAIT in the error word,
 // skips the remaining work, frees its TMEM and returns.
-#include <cuda.h>
-
-#include <mutex>
-#include <unordered_map>
-
-#include "common.cuh"
+#include "tc_common.cuh"
 
 namespace {
 
+using namespace xbtc;
+
 constexpr int TILE_N = 128;   // W rows (output features) per CTA
 constexpr int TILE_K = 64;    // K elements per stage (one 128-byte swizzle row)
-constexpr long long WAIT_CYCLES = 400000000LL;  // about 0.2 s: a wait that long has failed
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-// Bounded wait for the phase with the given parity; false (and the error bit) when it expires.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err) {
-    const long long t0 = clock64();
-    for (;;) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-        if (clock64() - t0 > WAIT_CYCLES) break;
-    }
-    atomicOr(err, XB_ERR_WAIT);
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-// Shared-memory operand descriptor: K-major tile of 128-byte rows, 128-byte swizzle, 8-row groups
-// 1024 bytes apart (start address, leading and stride byte offsets in 16-byte units; version 1).
-__device__ __forceinline__ uint64_t umma_desc(uint32_t addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
-    d |= (uint64_t)1 << 16;                  // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)(1024 >> 4) << 32;        // stride byte offset: next 8-row group
-    d |= (uint64_t)1 << 46;                  // descriptor version (Blackwell)
-    d |= (uint64_t)2 << 61;                  // layout type: SWIZZLE_128B
-    return d;
-}
-// Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = n.
-__device__ __forceinline__ uint32_t umma_idesc(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
-    uint32_t r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -106,8 +37,8 @@ __device__ __forceinline__ void cluster_sync() {
 __device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
     uint32_t remote;
     float v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote));
     return v;
 }
 
@@ -233,11 +164,21 @@ gemm_skinny_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     }
     if (csize > 1) {
         cluster_sync();   // every CTA of the cluster has written its partial tile
+        // The tile's M x 128 sums are shared out evenly among the CTAs of the cluster; a thread asks all
+        // ranks for its element at once (the loads are independent) and adds them in rank order.
         const uint32_t part_addr = base;
-        for (int m = (int)crank; m < M; m += (int)csize) {
-            float acc = 0.f;
-            for (uint32_t r = 0; r < csize; ++r) acc += ld_cluster_f32(part_addr + (uint32_t)(m * TILE_N + row) * 4u, r);
-            if (n < N) out[(size_t)m * N + n] = from_f32<TO>(acc);
+        const int total = M * TILE_N;
+        const int per = (total + (int)csize - 1) / (int)csize;
+        const int e_end = min(total, ((int)crank + 1) * per);
+        for (int e = (int)crank * per + (int)threadIdx.x; e < e_end; e += 128) {
+            float v[8];
+#pragma unroll
+            for (uint32_t r = 0; r < 8; ++r) v[r] = r < csize ? ld_cluster_f32(part_addr + (uint32_t)e * 4u, r) : 0.f;
+            float acc = v[0];
+#pragma unroll
+            for (uint32_t r = 1; r < 8; ++r) acc += v[r];
+            const int m = e / TILE_N, col = n0 + e % TILE_N;
+            if (col < N) out[(size_t)m * N + col] = from_f32<TO>(acc);
         }
         cluster_sync();   // nobody leaves while a neighbour still reads its shared memory
     }
@@ -248,64 +189,7 @@ gemm_skinny_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     }
 }
 
-// ---- host side: tensor maps (cached) and the launch ---------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    });
-    return fn;
-}
-
-struct MapKey {
-    const void* ptr;
-    long long rows, cols;
-    int box_rows;
-    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
-};
-struct MapKeyHash {
-    size_t operator()(const MapKey& k) const {
-        return std::hash<const void*>()(k.ptr) ^ (std::hash<long long>()(k.rows) * 31) ^ (std::hash<long long>()(k.cols) * 131) ^ (size_t)k.box_rows * 7919;
-    }
-};
-
-// A [rows, cols] row-major bfloat16 matrix seen through boxes of [box_rows x 64] with 128-byte swizzle.
-bool tensor_map_2d(CUtensorMap* out, const void* ptr, long long rows, long long cols, int box_rows) {
-    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-    static std::mutex mu;
-    std::lock_guard<std::mutex> lock(mu);
-    const MapKey key{ptr, rows, cols, box_rows};
-    auto it = cache.find(key);
-    if (it != cache.end()) {
-        *out = it->second;
-        return true;
-    }
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return false;
-    const cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    CUtensorMap m;
-    const CUresult rc = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (rc != CUDA_SUCCESS) return false;
-    if (cache.size() > 4096) cache.clear();
-    cache[key] = m;
-    *out = m;
-    return true;
-}
-
+// ---- host side: the launch ------------------------------------------------------------------------------
 template <typename TO>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int M, int N, int K, int mp, int splits,
            int k_per_split, int stages, size_t smem, const void* pf_ptr, unsigned long long pf_bytes, int* err,
@@ -356,15 +240,7 @@ XB_EXPORT int xb_gemm_skinny_tc(void* out, int out_f32, const void* x, const voi
     tiles_per_split = (k_tiles + splits - 1) / splits;
     const size_t stage_bytes = (size_t)TILE_N * TILE_K * 2 + (size_t)mp * TILE_K * 2;
     // few tokens: stages small enough for two CTAs per SM, so that a wave holds every CTA
-    size_t budget = mp <= 64 ? 100 * 1024 : 200 * 1024;
-    {
-        static int kb = -1;
-        if (kb < 0) {
-            const char* e = getenv("XINFER_B200_GEMM_RING_KB");
-            kb = e ? atoi(e) : 0;
-        }
-        if (kb > 0 && mp <= 64) budget = (size_t)kb * 1024;
-    }
+    const size_t budget = mp <= 128 ? 100 * 1024 : 200 * 1024;
     int stages = (int)(budget / stage_bytes);
     if (stages > 12) stages = 12;
     if (stages > tiles_per_split) stages = tiles_per_split < 2 ? 2 : tiles_per_split;
