@@ -116,6 +116,8 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--kernels", action="store_true",
+                    help="instead of the step benchmark, time single kernels at serving sizes: one JSON line each")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -123,6 +125,13 @@ def main() -> int:
         print("bench.py: this engine runs on one GPU; --gpus must be 1")
         return 2
     steps, warmup = max(args.steps, 1), max(args.warmup, 3)
+    if args.kernels:
+        from xinfer_b200 import measure
+        pk = peaks()
+        for rec in (measure.decode_gemms(hbm_gbs=pk["hbm_gbs"]) + measure.decode_attention(hbm_gbs=pk["hbm_gbs"])
+                    + measure.prefill_attention(peak_tflops=pk["bf16_tflops"])):
+            print(json.dumps(rec), flush=True)
+        return 0
 
     import numpy as np
     import torch

@@ -1,0 +1,163 @@
+"""Timings of single kernels at serving sizes, with CUDA events, for ``bench.py --kernels``.
+
+Each function returns a list of records (dicts); times are medians over repeated launches.  Decode
+kernels are timed inside a CUDA graph of several launches over different data (larger than the
+L2), the way a decode step runs them; prefill attention is launched directly.
+"""
+from __future__ import annotations
+
+from types import SimpleNamespace
+from typing import Dict, List, Sequence
+
+import numpy as np
+import torch
+
+from . import kernels
+from .parts import LayerCache, Workspace
+from .parts import attention_backend
+
+
+def _graph_time_us(run, per: int, repeats: int = 8) -> float:
+    """Median time of one of the ``per`` launches that ``run`` makes, replayed from a CUDA graph."""
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        run()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            run()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(repeats):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1000.0 / per)
+    return float(sorted(times)[len(times) // 2])
+
+
+def _attention_context(entries, page_size: int, device):
+    """Step metadata for `entries` = [(cached tokens, new tokens)], pages handed out in shuffled order."""
+    to = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device=device)
+    counts = [c for _, c in entries]
+    q_start = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    pages_per = max((s + c + page_size - 1) // page_size for s, c in entries)
+    num_pages = len(entries) * pages_per + 1
+    table = np.random.default_rng(0).permutation(num_pages - 1)[: len(entries) * pages_per].reshape(len(entries), pages_per)
+    pos = np.concatenate([np.arange(s, s + c) for s, c in entries])
+    req = np.concatenate([np.full(c, b) for b, (_, c) in enumerate(entries)])
+    ctx = SimpleNamespace(
+        positions=to(pos), req_of_token=to(req), q_start=to(q_start), start_pos=to([s for s, _ in entries]),
+        num_entries=len(entries), num_tokens=int(q_start[-1]), h_q_start=q_start, real_entries=len(entries),
+        h_start_pos=np.asarray([s for s, _ in entries], dtype=np.int32), max_context=max(s + c for s, c in entries),
+        fixed_shapes=False, scratch={}, workspace=Workspace(device), err=torch.zeros(1, dtype=torch.int32, device=device))
+    return ctx, to(table.astype(np.int32)), pages_per, num_pages
+
+
+def decode_attention(cases: Sequence = ((1, 4096), (8, 4096), (64, 4096), (8, 32768)), *, heads: int = 32,
+                     kv_heads: int = 8, head_dim: int = 128, page_size: int = 16, hbm_gbs: float = 0.0,
+                     device="cuda:0") -> List[Dict]:
+    """One decode token per request over `context` cached tokens, for (batch, context) cases."""
+    out = []
+    for batch, context in cases:
+        ctx, table, stride, num_pages = _attention_context([(context - 1, 1)] * batch, page_size, device)
+        layers = 8 if batch * context <= 8 * 32768 else 2
+        caches = [LayerCache(torch.randn(num_pages, kv_heads, page_size, head_dim, device=device).bfloat16(),
+                             torch.randn(num_pages, kv_heads, page_size, head_dim, device=device).bfloat16(), 0, page_size)
+                  for _ in range(layers)]
+        q = torch.randn(batch, heads, head_dim, device=device).bfloat16()
+        o = torch.empty_like(q)
+        nbytes = batch * context * kv_heads * head_dim * 2 * 2
+        rec = {"kernel": "decode attention", "batch": batch, "context": context, "bytes": nbytes}
+        for name, flag in (("tcgen05_us", True), ("mma_sync_us", False)):
+            attention_backend.DECODE_TC = flag
+            try:
+                rec[name] = round(_graph_time_us(lambda: [attention_backend.attend(o, q, c, ctx, table, stride, None, head_dim ** -0.5)
+                                                          for c in caches], layers), 1)
+            finally:
+                attention_backend.DECODE_TC = True
+        if int(ctx.err):
+            raise RuntimeError("a kernel reported an error: " + kernels.describe_error(int(ctx.err)))
+        rec["gbs"] = round(nbytes / rec["tcgen05_us"] / 1e3, 1)
+        if hbm_gbs:
+            rec["frac_of_hbm"] = round(rec["gbs"] / hbm_gbs, 3)
+        out.append(rec)
+    return out
+
+
+def prefill_attention(cases: Sequence = ((0, 2048), (0, 8192), (24576, 8192)), *, heads: int = 32, kv_heads: int = 8,
+                      head_dim: int = 128, page_size: int = 16, peak_tflops: float = 0.0, device="cuda:0") -> List[Dict]:
+    """One request bringing `new` tokens after `cached` ones, for (cached, new) cases."""
+    out = []
+    for cached, new in cases:
+        ctx, table, stride, num_pages = _attention_context([(cached, new)], page_size, device)
+        cache = LayerCache(torch.randn(num_pages, kv_heads, page_size, head_dim, device=device).bfloat16(),
+                           torch.randn(num_pages, kv_heads, page_size, head_dim, device=device).bfloat16(), 0, page_size)
+        q = torch.randn(new, heads, head_dim, device=device).bfloat16()
+        o = torch.empty_like(q)
+        flops = 4.0 * heads * head_dim * (new * cached + new * (new + 1) / 2)
+        rec = {"kernel": "prefill attention", "cached": cached, "new": new, "flops": flops}
+        for name, flag in (("tcgen05_us", True), ("mma_sync_us", False)):
+            attention_backend.PREFILL_TC = flag
+            try:
+                run = lambda: attention_backend.attend(o, q, cache, ctx, table, stride, None, head_dim ** -0.5)
+                for _ in range(3):
+                    run()
+                torch.cuda.synchronize()
+                times = []
+                for _ in range(7):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    run()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    times.append(e0.elapsed_time(e1) * 1000.0)
+                rec[name] = round(sorted(times)[len(times) // 2], 1)
+            finally:
+                attention_backend.PREFILL_TC = True
+        if int(ctx.err):
+            raise RuntimeError("a kernel reported an error: " + kernels.describe_error(int(ctx.err)))
+        rec["tflops"] = round(flops / rec["tcgen05_us"] / 1e6, 1)
+        if peak_tflops:
+            rec["frac_of_peak"] = round(rec["tflops"] / peak_tflops, 3)
+        out.append(rec)
+    return out
+
+
+def decode_gemms(tokens: Sequence[int] = (1, 8, 32), *, hidden: int = 4096, heads: int = 32, kv_heads: int = 8,
+                 head_dim: int = 128, intermediate: int = 12288, hbm_gbs: float = 0.0, device="cuda:0") -> List[Dict]:
+    """The four matrix products of a layer, one after the other as in a decode step, for M tokens:
+    the streaming tcgen05 kernel and the library product."""
+    shapes = [((heads + 2 * kv_heads) * head_dim, hidden), (hidden, heads * head_dim), (2 * intermediate, hidden),
+              (hidden, intermediate)]
+    layer_bytes = sum(n * k * 2 for n, k in shapes)
+    layers = max(2, int(600e6 / layer_bytes) + 1)      # more weights than the L2 holds
+    ws = [[(torch.randn(n, k, device=device) * 0.02).bfloat16() for n, k in shapes] for _ in range(layers)]
+    err = torch.zeros(1, dtype=torch.int32, device=device)
+    out = []
+    for m in tokens:
+        xs = {k: torch.randn(m, k, device=device).bfloat16() for _, k in shapes}
+        ys = {n: torch.empty(m, n, dtype=torch.bfloat16, device=device) for n, _ in shapes}
+
+        def own():
+            for l in range(layers):
+                for (n, k), w in zip(shapes, ws[l]):
+                    if not kernels.gemm_skinny_tc(ys[n], xs[k], w, err):
+                        raise RuntimeError(f"the streaming kernel does not take M={m}, N={n}, K={k}")
+
+        def lib():
+            for l in range(layers):
+                for (n, k), w in zip(shapes, ws[l]):
+                    torch.mm(xs[k], w.t(), out=ys[n])
+
+        rec = {"kernel": "decode matrix products of a layer", "tokens": m, "bytes": layer_bytes,
+               "tcgen05_us": round(_graph_time_us(own, layers), 1), "library_us": round(_graph_time_us(lib, layers), 1)}
+        rec["gbs"] = round(layer_bytes / rec["tcgen05_us"] / 1e3, 1)
+        if hbm_gbs:
+            rec["frac_of_hbm"] = round(rec["gbs"] / hbm_gbs, 3)
+        out.append(rec)
+    if int(err):
+        raise RuntimeError("a kernel reported an error: " + kernels.describe_error(int(err)))
+    return out
