@@ -190,3 +190,28 @@ def test_layer_order_is_data(model_folders, tmp_path):
     x, _ = layer(x, 0, reuse=kv)
     ref = plain.linear(plain.rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"]), w["model.embed_tokens.weight"])
     assert (whole - ref).abs().max() < 2e-5
+
+
+def test_a_step_reads_token_ids_that_a_sampler_left_on_the_device(model_folders):
+    """A token id -1 - i stands for sampled_tokens[i]: the step's logits equal those of the same
+    step with the ids given by the host; an id beyond the buffer is reported, not followed."""
+    from xinfer_b200.engine.runner import ModelRunner, StepError, StepInput
+    folder = model_folders("A", torch.float32)
+    r = ModelRunner(folder, "float32", block_size=16, num_blocks=16, max_num_seqs=3)
+    a, b = r.open_request(), r.open_request()
+    r.step([StepInput(a, [5, 6, 7], []), StepInput(b, [9], [])])
+    r.sampled_tokens[:3] = torch.tensor([41, 250, 17], dtype=torch.int32)
+    got = r.step([StepInput(a, [r.ahead_token(2)], [0]), StepInput(b, [r.ahead_token(0)], [0])]).cpu().clone()
+    r.check_errors()
+    c, d = r.open_request(), None
+    r.close_request(a); r.close_request(b)
+    a, b = r.open_request(), r.open_request()
+    r.step([StepInput(a, [5, 6, 7], []), StepInput(b, [9], [])])
+    want = r.step([StepInput(a, [17], [0]), StepInput(b, [41], [0])]).cpu().clone()
+    assert torch.equal(got, want)
+    with pytest.raises(StepError, match="token ids"):
+        r.step([StepInput(a, [-5], [0])])                  # beyond the three ids the buffer holds
+    r.sampled_tokens[0] = 100000                            # what the device finds there is checked too
+    r.step([StepInput(a, [r.ahead_token(0)], [0])])
+    with pytest.raises(StepError, match="token id"):
+        r.check_errors()

@@ -8,15 +8,17 @@
 #include "common.cuh"
 
 // ------------------------------------------------------------------------------------------
-// Embedding gather: out[t, :] = table[ids[t], :]
+// Embedding gather: out[t, :] = table[ids[t], :].  An id -1 - i stands for sampled[i], the id a
+// sampler left on the device (the host has not seen it yet).
 // ------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void embedding_kernel(T* __restrict__ out, const T* __restrict__ table,
-                                 const int* __restrict__ ids, int hidden, int vocab, int* err) {
+__global__ void embedding_kernel(T* __restrict__ out, const T* __restrict__ table, const int* __restrict__ ids,
+                                 const int* __restrict__ sampled, int num_sampled, int hidden, int vocab, int* err) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
-    const int id = ids[t];
+    int id = ids[t];
+    if (id < 0 && sampled != nullptr && -1 - id < num_sampled) id = sampled[-1 - id];
     T* o = out + (size_t)t * hidden;
     if (id < 0 || id >= vocab) {
         if (threadIdx.x == 0) atomicOr(err, XB_ERR_BAD_TOKEN);
@@ -34,12 +36,14 @@ __global__ void embedding_kernel(T* __restrict__ out, const T* __restrict__ tabl
     }
 }
 
-XB_EXPORT int xb_embedding(int dtype, void* out, const void* table, const int* ids, int tokens,
-                           int hidden, int vocab, int* err, cudaStream_t stream) {
+XB_EXPORT int xb_embedding(int dtype, void* out, const void* table, const int* ids, const int* sampled, int num_sampled,
+                           int tokens, int hidden, int vocab, int* err, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (dtype == XB_F32)
-        return xb_launch(embedding_kernel<float>, dim3(tokens), dim3(256), 0, stream, (float*)out, (const float*)table, ids, hidden, vocab, err);
-    return xb_launch(embedding_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)table, ids, hidden, vocab, err);
+        return xb_launch(embedding_kernel<float>, dim3(tokens), dim3(256), 0, stream, (float*)out, (const float*)table, ids,
+                         sampled, num_sampled, hidden, vocab, err);
+    return xb_launch(embedding_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, (__nv_bfloat16*)out,
+                     (const __nv_bfloat16*)table, ids, sampled, num_sampled, hidden, vocab, err);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -110,83 +110,194 @@ __global__ void penalties_kernel(float* logits, const SampleParams* params, cons
     }
 }
 
+// Four Gumbel values of the tokens 4g .. 4g+3 from one Philox block.
+__device__ __forceinline__ void gumbel4_of(uint32_t seed_lo, uint32_t seed_hi, uint32_t draw, int g, float out[4]) {
+    uint32_t r[4];
+    philox4x32_10((uint32_t)g, draw, 0x58494e46u, 0u, seed_lo, seed_hi, r);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float u = ((float)(r[e] >> 9) + 0.5f) * (1.0f / 8388608.0f);
+        out[e] = -logf(-logf(u));
+    }
+}
+
+__device__ __forceinline__ unsigned long long key_of(float v, int i) {
+    return ((unsigned long long)float_key(v) << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)i);
+}
+
+#define XB_SAMPLE_CHUNK_SMEM 8192   // values of a chunk that are kept in shared memory
+#define XB_SAMPLE_CHUNKS_MAX 64
+
+// Scratch of the sampler, per row: candidate keys, partial results of the chunks, a candidate
+// counter and a ticket (both zero between launches).
+struct SampleScratch {
+    unsigned long long* cand;   // [rows][XB_TOPK_MAX]
+    Best* part;                 // [rows][XB_SAMPLE_CHUNKS_MAX]
+    int* count;                 // [rows]
+    int* ticket;                // [rows]
+};
+
+// Grid (chunks, rows): a row's vocabulary is cut into chunks of whole Philox blocks (4 tokens); every
+// CTA reduces its chunk - to its best token, or to its k largest - and the CTA that finishes last
+// among a row's chunks (a ticket) makes the draw from those partial results.  Rows with a top-k use
+// at most 1024 / k chunks, so that the candidates of all chunks fit the final sort.
 __global__ void __launch_bounds__(1024)
-sample_kernel(int* __restrict__ out_tokens, const float* __restrict__ logits,
-              const SampleParams* __restrict__ params, int vocab) {
+sample_kernel(int* __restrict__ out_tokens, const float* __restrict__ logits, const SampleParams* __restrict__ params,
+              int vocab, int grid_chunks, SampleScratch sc, const int* __restrict__ err_word) {
+    // the step's error word travels to the host behind the tokens, in the same copy
+    if (err_word != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) out_tokens[gridDim.y] = *err_word;
     __shared__ Best sbest[32];
     __shared__ unsigned int hist[256];
     __shared__ unsigned long long cand_key[XB_TOPK_MAX];
     __shared__ float cand_p[XB_TOPK_MAX];
+    __shared__ float s_vals[XB_SAMPLE_CHUNK_SMEM];
     __shared__ unsigned long long s_prefix;
-    __shared__ int s_need, s_count, s_keep;
+    __shared__ int s_need, s_base, s_keep, s_last;
 
-    const int r = blockIdx.x;
+    const int r = blockIdx.y;
     const SampleParams p = params[r];
     const float* row = logits + (size_t)r * vocab;
     const bool greedy = !(p.temperature >= 1e-7f);
     const bool use_p = p.top_p > 0.f && p.top_p < 1.f;
     const bool truncated = !greedy && (p.top_k > 0 || use_p);
     const float inv_t = greedy ? 1.f : 1.f / p.temperature;
-
-    if (!truncated) {
-        Best b{0.f, -1};
-        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-            float v = row[i];
-            if (!greedy) v = v * inv_t + gumbel_of(p.seed_lo, p.seed_hi, p.draw, i);
-            b = better(b, Best{v, i});
-        }
-        b = block_best(b, sbest);
-        if (threadIdx.x == 0) out_tokens[r] = b.i;
-        return;
-    }
-
-    // ---- the k largest by (value, then lower index): radix select on 64-bit keys ------------
     int k = p.top_k > 0 ? p.top_k : 256;  // top-p alone looks at the 256 largest, as the reference's device sampler does
     if (k > XB_TOPK_MAX) k = XB_TOPK_MAX;
     if (k > vocab) k = vocab;
-    if (threadIdx.x == 0) {
-        s_prefix = 0ull;
-        s_need = k;
-    }
-    __syncthreads();
-    for (int pass = 7; pass >= 0; --pass) {
-        if (threadIdx.x < 256) hist[threadIdx.x] = 0u;
-        __syncthreads();
-        const unsigned long long prefix = s_prefix;
-        const int shift = pass * 8;
-        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-            const unsigned long long key = ((unsigned long long)float_key(row[i]) << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)i);
-            if (pass == 7 || (key >> (shift + 8)) == (prefix >> (shift + 8)))
-                atomicAdd(&hist[(unsigned)(key >> shift) & 255u], 1u);
-        }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            int need = s_need;
-            int bin = 255;
-            for (; bin > 0; --bin) {
-                if ((int)hist[bin] >= need) break;
-                need -= (int)hist[bin];
+
+    // this row's chunks
+    int chunks = truncated ? min(grid_chunks, XB_TOPK_MAX / k) : grid_chunks;
+    if (chunks < 1) chunks = 1;
+    const int chunk_n = ((vocab + chunks - 1) / chunks + 3) & ~3;
+    chunks = (vocab + chunk_n - 1) / chunk_n;
+    if ((int)blockIdx.x >= chunks) return;
+    const int lo = (int)blockIdx.x * chunk_n, hi = min(vocab, lo + chunk_n);
+
+    if (!truncated) {
+        Best b{0.f, -1};
+        for (int g4 = (lo >> 2) + (int)threadIdx.x; g4 * 4 < hi; g4 += blockDim.x) {
+            float noise[4] = {0.f, 0.f, 0.f, 0.f};
+            if (!greedy) gumbel4_of(p.seed_lo, p.seed_hi, p.draw, g4, noise);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = g4 * 4 + e;
+                if (i < hi) {
+                    float v = row[i];
+                    if (!greedy) v = v * inv_t + noise[e];
+                    b = better(b, Best{v, i});
+                }
             }
-            s_need = need;
-            s_prefix = prefix | ((unsigned long long)bin << shift);
+        }
+        b = block_best(b, sbest);
+        if (threadIdx.x == 0) sc.part[(size_t)r * XB_SAMPLE_CHUNKS_MAX + blockIdx.x] = b;
+    } else {
+        // ---- the chunk's k largest by (value, then lower index): radix select on 64-bit keys ------------
+        const int n_chunk = hi - lo;
+        const bool cached = n_chunk <= XB_SAMPLE_CHUNK_SMEM;
+        if (cached)
+            for (int i = threadIdx.x; i < n_chunk; i += blockDim.x) s_vals[i] = row[lo + i];
+        const int kc = min(k, n_chunk);
+        if (threadIdx.x == 0) {
+            s_prefix = 0ull;
+            s_need = kc;
         }
         __syncthreads();
-    }
-    const unsigned long long kth = s_prefix;  // the k-th largest key; keys are unique
-    if (threadIdx.x == 0) s_count = 0;
-    __syncthreads();
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const unsigned long long key = ((unsigned long long)float_key(row[i]) << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)i);
-        if (key >= kth) {
-            const int at = atomicAdd(&s_count, 1);
-            if (at < XB_TOPK_MAX) cand_key[at] = key;
+        for (int pass = 7; pass >= 0; --pass) {
+            if (threadIdx.x < 256) hist[threadIdx.x] = 0u;
+            __syncthreads();
+            const unsigned long long prefix = s_prefix;
+            const int shift = pass * 8;
+            for (int i = lo + (int)threadIdx.x; i < hi; i += blockDim.x) {
+                const unsigned long long key = key_of(cached ? s_vals[i - lo] : row[i], i);
+                if (pass == 7 || (key >> (shift + 8)) == (prefix >> (shift + 8)))
+                    atomicAdd(&hist[(unsigned)(key >> shift) & 255u], 1u);
+            }
+            __syncthreads();
+            if (threadIdx.x < 32) {
+                // the bin in which the count, summed from the top bin down, reaches what is still needed:
+                // lane l holds bins 255 - 8l down to 248 - 8l
+                const int lane = threadIdx.x;
+                unsigned int c[8], sum = 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    c[j] = hist[255 - (8 * lane + j)];
+                    sum += c[j];
+                }
+                unsigned int incl = sum;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const unsigned int t = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += t;
+                }
+                const unsigned int need = (unsigned int)s_need, excl = incl - sum;
+                const bool here = excl < need && (incl >= need || lane == 31);
+                __syncwarp();
+                if (here) {
+                    unsigned int rem = need - excl;
+                    int bin = 0;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int b = 255 - (8 * lane + j);
+                        if (c[j] >= rem || b == 0) {
+                            bin = b;
+                            break;
+                        }
+                        rem -= c[j];
+                    }
+                    s_need = (int)rem;
+                    s_prefix = prefix | ((unsigned long long)bin << shift);
+                }
+            }
+            __syncthreads();
+        }
+        const unsigned long long kth = s_prefix;  // the chunk's kc-th largest key; keys are unique
+        if (threadIdx.x == 0) s_base = atomicAdd(&sc.count[r], kc);   // room for this chunk's candidates
+        __syncthreads();
+        unsigned long long* dst = sc.cand + (size_t)r * XB_TOPK_MAX + s_base;
+        if (threadIdx.x == 0) s_need = 0;
+        __syncthreads();
+        for (int i = lo + (int)threadIdx.x; i < hi; i += blockDim.x) {
+            const unsigned long long key = key_of(cached ? s_vals[i - lo] : row[i], i);
+            if (key >= kth) {
+                const int at = atomicAdd(&s_need, 1);
+                if (at < kc && s_base + at < XB_TOPK_MAX) dst[at] = key;
+            }
         }
     }
+    // ---- the CTA that finishes last among the row's chunks makes the draw ---------------------------------
+    __threadfence();
     __syncthreads();
-    const int n = s_count < k ? s_count : k;
-    for (int i = n + threadIdx.x; i < XB_TOPK_MAX; i += blockDim.x) cand_key[i] = 0ull;
+    if (threadIdx.x == 0) {
+        const int mine = atomicAdd(&sc.ticket[r], 1);
+        s_last = mine == chunks - 1;
+    }
     __syncthreads();
-    // bitonic sort, descending
+    if (!s_last) return;
+    __threadfence();
+    if (!truncated) {
+        Best b{0.f, -1};
+        if ((int)threadIdx.x < chunks) {
+            const Best* src = sc.part + (size_t)r * XB_SAMPLE_CHUNKS_MAX + threadIdx.x;
+            b.v = __ldcg(&src->v);
+            b.i = __ldcg(&src->i);
+        }
+        b = block_best(b, sbest);
+        if (threadIdx.x == 0) {
+            out_tokens[r] = b.i;
+            sc.ticket[r] = 0;
+        }
+        return;
+    }
+    const int total = min(__ldcg(&sc.count[r]), XB_TOPK_MAX);
+    for (int i = threadIdx.x; i < XB_TOPK_MAX; i += blockDim.x)
+        cand_key[i] = i < total ? __ldcg(sc.cand + (size_t)r * XB_TOPK_MAX + i) : 0ull;
+    __syncthreads();
+    if (threadIdx.x == 0) {   // ready for the next launch
+        sc.ticket[r] = 0;
+        sc.count[r] = 0;
+    }
+    const int n = total < k ? total : k;
+    // bitonic sort, descending: the first n keys are the row's n largest
     for (int size = 2; size <= XB_TOPK_MAX; size <<= 1) {
         for (int stride = size >> 1; stride > 0; stride >>= 1) {
             const int i = threadIdx.x;
@@ -215,13 +326,13 @@ sample_kernel(int* __restrict__ out_tokens, const float* __restrict__ logits,
     if (threadIdx.x == 0) {
         int keep = n;
         if (use_p) {
-            float total = 0.f;
-            for (int i = 0; i < n; ++i) total += cand_p[i];
+            float total_p = 0.f;
+            for (int i = 0; i < n; ++i) total_p += cand_p[i];
             float cum = 0.f;
             keep = 0;
             for (int i = 0; i < n; ++i) {
                 if (cum >= p.top_p) break;
-                cum += cand_p[i] / total;
+                cum += cand_p[i] / total_p;
                 ++keep;
             }
         }
@@ -237,11 +348,30 @@ sample_kernel(int* __restrict__ out_tokens, const float* __restrict__ logits,
     if (threadIdx.x == 0) out_tokens[r] = b.i;
 }
 
+// Bytes of scratch for `rows` rows (zero before the first launch; the kernel leaves it zero where it must be).
+XB_EXPORT long long xb_sample_scratch_bytes(int rows) {
+    return (long long)rows * (XB_TOPK_MAX * 8 + XB_SAMPLE_CHUNKS_MAX * (long long)sizeof(Best) + 8);
+}
+
+// `err_word` (nullable): a device int that is copied to out_tokens[rows].  `scratch`: at least
+// xb_sample_scratch_bytes(rows) bytes, 8-byte aligned.
 XB_EXPORT int xb_sample(int* out_tokens, float* logits, const void* params, const int* history,
-                        int rows, int vocab, int apply_penalties, cudaStream_t stream) {
+                        int rows, int vocab, int apply_penalties, void* scratch, const int* err_word, cudaStream_t stream) {
     if (rows <= 0) return 0;
+    if (!scratch || ((uintptr_t)scratch & 7)) return (int)cudaErrorInvalidValue;
     if (apply_penalties) penalties_kernel<<<rows, 128, 0, stream>>>(logits, (const SampleParams*)params, history, vocab);
-    sample_kernel<<<rows, 1024, 0, stream>>>(out_tokens, logits, (const SampleParams*)params, vocab);
+    SampleScratch sc;
+    unsigned char* base = (unsigned char*)scratch;
+    sc.cand = (unsigned long long*)base;
+    base += (size_t)rows * XB_TOPK_MAX * 8;
+    sc.part = (Best*)base;
+    base += (size_t)rows * XB_SAMPLE_CHUNKS_MAX * sizeof(Best);
+    sc.count = (int*)base;
+    sc.ticket = sc.count + rows;
+    int chunks = 296 / rows;   // two CTAs of 1024 threads per SM of a 148-SM part
+    if (chunks < 1) chunks = 1;
+    if (chunks > XB_SAMPLE_CHUNKS_MAX) chunks = XB_SAMPLE_CHUNKS_MAX;
+    sample_kernel<<<dim3(chunks, rows), 1024, 0, stream>>>(out_tokens, logits, (const SampleParams*)params, vocab, chunks, sc, err_word);
     return xb_launch_status();
 }
 

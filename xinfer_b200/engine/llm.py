@@ -84,7 +84,10 @@ class Engine:
             self.runner.cache, max_num_seqs=econfig.max_num_seqs, max_num_batched_tokens=budget,
             prefill_chunk_size=econfig.prefill_chunk_size, max_model_len=self.max_model_len,
             eos_token_ids=self.runner.plan.eos_token_ids)
-        self.samplers = [Sampler(self.runner.device, econfig.max_num_seqs) for _ in range(2)]
+        # two sets of pinned buffers (two batches can be in flight); both leave their ids in the runner's
+        # buffer, where the step after reads them on the device
+        self.samplers = [Sampler(self.runner.device, econfig.max_num_seqs, out_dev=self.runner.sampled_tokens,
+                                 err_word=self.runner.err) for _ in range(2)]
         self.sampler = self.samplers[0]
         self._sampler_i = 0
         self._flight: Optional[_Flight] = None    # a batch queued on the device whose tokens are not recorded yet
@@ -153,13 +156,13 @@ class Engine:
         for e in entries:
             if e.start == 0:
                 self.runner.prepare_slot(e.slot)
-            inputs.append(StepInput(e.slot, e.tokens, [len(e.tokens) - 1] if e.want else []))
+            tokens = e.tokens if after is None else [self.runner.ahead_token(e.src)]
+            inputs.append(StepInput(e.slot, tokens, [len(tokens) - 1] if e.want else []))
             if e.want:
                 wanted.append(e)
             if e.start < self._live[e.req_id].prompt_len:
                 self.stats["prompt_tokens"] += min(len(e.tokens), self._live[e.req_id].prompt_len - e.start)
-        source = (after.tokens_dev, [e.src for e in entries]) if after is not None else None
-        logits = self.runner.step(inputs, allow_graph=self.use_graphs, tokens_from=source)
+        logits = self.runner.step(inputs, allow_graph=self.use_graphs)
         flight = _Flight(wanted=wanted)
         if wanted:
             lives = [self._live[e.req_id] for e in wanted]
@@ -173,7 +176,6 @@ class Engine:
             sampler = self.samplers[self._sampler_i]   # two sets of buffers: two batches can be in flight
             flight.tokens_dev = sampler.sample(logits, [l.params for l in lives], [l.seed for l in lives],
                                                [self.scheduler.num_drawn(e.req_id) + ahead for e in wanted], hist)
-            self.runner.queue_error_check()
             sampler.start_copy(flight.tokens_dev)
             flight.sampler = sampler
         return flight
@@ -182,8 +184,9 @@ class Engine:
         """Wait for a queued batch's tokens and record them; returns the ids that ended."""
         sampled: List[int] = []
         if flight.sampler is not None:
-            sampled = flight.sampler.finish_copy().tolist()
-            self.runner.raise_if_error()
+            ids, word = flight.sampler.finish_copy()
+            sampled = ids.tolist()
+            self.runner.raise_on(word)
             now = time.time()
             for e in flight.wanted:
                 live = self._live.get(e.req_id)

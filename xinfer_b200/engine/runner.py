@@ -106,6 +106,8 @@ class StepAssembler:
         self._meta = _MetaBuffers(self.device)
         self._lib = host_lib()
         self.h2d_bytes = 0   # bytes of the last step's metadata copy
+        # ids a sampler left on the device: a token id -1 - i of a step stands for sampled[i]
+        self.sampled: Optional[torch.Tensor] = None
 
     def prepare(self, entries: Sequence[StepInput], *, pad_entries: int = 0, pad_tokens: int = 0,
                 pad_rows: int = 0, strides: Optional[Sequence[int]] = None,
@@ -148,7 +150,8 @@ class StepAssembler:
             if not cache.extend(slot, start + n):
                 raise StepError(f"entry {b}: the page pool has no room for {n} more tokens "
                                 f"(free pages {[cache.free_pages(g) for g in range(len(cache.groups))]})")
-        if tokens.min() < 0 or tokens.max() >= V:
+        low = -self.sampled.numel() if self.sampled is not None else 0
+        if tokens.min() < low or tokens.max() >= V:
             raise StepError(f"token ids must lie in [0, {V}); got {int(tokens.min())}..{int(tokens.max())}")
         R = len(want_e)
         G = len(cache.groups)
@@ -190,7 +193,7 @@ class StepAssembler:
             err=self.err, workspace=workspace if workspace is not None else self.workspace,
             h_q_start=host[offs[3]: offs[3] + Bp + 1].numpy().copy(), h_start_pos=starts, h_slots=slots,
             real_tokens=T, real_entries=B, max_context=longest, all_single=bool((counts == 1).all()),
-            fixed_shapes=into is not None,
+            fixed_shapes=into is not None, sampled=self.sampled,
         )
 
 
@@ -242,6 +245,10 @@ class ModelRunner:
         self._build_caches(num_blocks, kv_fraction)
         self.assembler = StepAssembler(self.cache, vocab_size=self.plan.vocab_size, max_model_len=self.max_model_len,
                                        dtype=self.dtype, device=self.device, workspace=self.workspace, err=self.err)
+        # Where a sampler leaves its ids for a step that runs before the host has seen them: one id
+        # per request of the batch, and the step's error word behind them.
+        self.sampled_tokens = torch.zeros(self.max_num_seqs + 1, dtype=torch.int32, device=self.device)
+        self.assembler.sampled = self.sampled_tokens[: self.max_num_seqs]
         self.steps_run = 0
         self.last_launches = 0      # kernels of ours launched by the last step
         self.last_used_graph = False
@@ -330,26 +337,26 @@ class ModelRunner:
         self.state.clear_slot(slot)
 
     # ---- the step --------------------------------------------------------------------------------------
-    def step(self, entries: Sequence[StepInput], *, allow_graph: bool = False,
-             tokens_from: Optional[Tuple[torch.Tensor, Sequence[int]]] = None) -> torch.Tensor:
+    def step(self, entries: Sequence[StepInput], *, allow_graph: bool = False) -> torch.Tensor:
         """Run one batch; returns float32 logits ``[wanted, vocab]`` on the device (a view of a
         reused buffer: copy what must outlive the next step).
 
-        ``tokens_from`` = (int32 device tensor, indices): every entry brings one token whose id is
-        not known on the host yet; entry i's id is read on the device from ``tensor[indices[i]]``
-        (the ids given in the entries are placeholders)."""
-        if tokens_from is not None and any(len(e.tokens) != 1 for e in entries):
-            raise StepError("token ids can be taken from the device only for entries of one token")
+        A token id ``-1 - i`` stands for ``sampled_tokens[i]``: the id that a sampler has left on the
+        device and the host has not seen yet (see ``ahead_token``)."""
         if allow_graph and self._graph_eligible(entries):
-            return self._step_graph(entries, tokens_from)
+            return self._step_graph(entries)
         before = kernels.launch_count()
         ctx = self.assembler.prepare(entries)
-        self._patch_tokens(ctx, len(entries), tokens_from)
         logits = self.model.forward(ctx, self.layer_caches, self.layer_states)
         self.finish(entries)
         self.last_launches = kernels.launch_count() - before
         self.last_used_graph = False
         return logits
+
+    @staticmethod
+    def ahead_token(i: int) -> int:
+        """The token id that tells a step to read ``sampled_tokens[i]`` on the device."""
+        return -1 - int(i)
 
     def finish(self, entries: Sequence[StepInput]) -> None:
         for e in entries:
@@ -373,33 +380,7 @@ class ModelRunner:
             s *= 2
         return tuple(s for _ in self.cache.groups)
 
-    def _patch_tokens(self, ctx: StepContext, n: int, tokens_from) -> None:
-        """Overwrite the step's first ``n`` token ids, on the device, with ids a previous step left there."""
-        if tokens_from is None:
-            return
-        src, idx = tokens_from
-        idx = [int(i) for i in idx]
-        if len(idx) != n or src.dtype != torch.int32 or any(i < 0 or i >= src.numel() for i in idx):
-            raise StepError("tokens_from needs an int32 device tensor and one valid index per entry")
-        if idx == list(range(n)):
-            ctx.token_ids[:n].copy_(src[:n])
-            return
-        k = self._patch_i = (getattr(self, "_patch_i", 0) + 1) % 2
-        if not hasattr(self, "_patch_host"):
-            cap = max(self.max_num_seqs, n)
-            self._patch_host = [torch.zeros(cap, dtype=torch.int64, pin_memory=True) for _ in range(2)]
-            self._patch_dev = [torch.zeros(cap, dtype=torch.int64, device=self.device) for _ in range(2)]
-            self._patch_ev = [None, None]
-        if self._patch_ev[k] is not None:
-            self._patch_ev[k].synchronize()   # the copy that last used this pinned buffer has run
-        self._patch_host[k][:n] = torch.tensor(idx, dtype=torch.int64)
-        self._patch_dev[k][:n].copy_(self._patch_host[k][:n], non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record()
-        self._patch_ev[k] = ev
-        torch.index_select(src, 0, self._patch_dev[k][:n], out=ctx.token_ids[:n])
-
-    def _step_graph(self, entries: Sequence[StepInput], tokens_from=None) -> torch.Tensor:
+    def _step_graph(self, entries: Sequence[StepInput]) -> torch.Tensor:
         B = len(entries)
         bucket = _bucket(B, self.max_num_seqs)
         strides = self._graph_strides(entries)
@@ -408,9 +389,8 @@ class ModelRunner:
         if g is None:
             g = self._capture(entries, bucket, strides)
             self._graphs[key] = g
-        ctx = self.assembler.prepare(entries, pad_entries=bucket, pad_tokens=bucket, pad_rows=bucket, strides=strides,
-                                     into=g.meta, workspace=self._graph_workspace)
-        self._patch_tokens(ctx, B, tokens_from)
+        self.assembler.prepare(entries, pad_entries=bucket, pad_tokens=bucket, pad_rows=bucket, strides=strides,
+                               into=g.meta, workspace=self._graph_workspace)
         g.graph.replay()
         self.finish(entries)
         self.last_launches = g.launches
@@ -467,8 +447,12 @@ class ModelRunner:
 
     def raise_if_error(self) -> None:
         word = int(self._err_host[0])
+        self._err_host[0] = 0
+        self.raise_on(word)
+
+    def raise_on(self, word: int) -> None:
+        """Raise for an error word that was read from the device (0: nothing happened)."""
         if word:
-            self._err_host[0] = 0
             self.err.zero_()
             raise StepError("a kernel reported: " + kernels.describe_error(word))
 

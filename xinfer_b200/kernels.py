@@ -85,7 +85,9 @@ def describe_error(word: int) -> str:
 
 
 # ---- wrappers --------------------------------------------------------------------------------------
-def embedding(out, table, ids, err):
+def embedding(out, table, ids, err, sampled=None):
+    """out[t] = table[ids[t]]; an id -1 - i is replaced on the device by ``sampled[i]`` (int32 ids a
+    sampler left there)."""
     T, H = out.shape
     _need(out, "out", table.dtype, (T, H))
     _need(table, "table", None, (None, H))
@@ -93,7 +95,10 @@ def embedding(out, table, ids, err):
     if ids.numel() < T:
         raise KernelError(f"ids holds {ids.numel()} entries for {T} tokens")
     _need(err, "err", torch.int32)
+    if sampled is not None:
+        _need(sampled, "sampled", torch.int32)
     _ok(kernels_lib().xb_embedding(dtype_code(table.dtype), out.data_ptr(), table.data_ptr(), ids.data_ptr(),
+                                   _ptr(sampled), sampled.numel() if sampled is not None else 0,
                                    T, H, table.shape[0], err.data_ptr(), _stream()), "embedding")
 
 
@@ -225,7 +230,14 @@ SAMPLE_PARAMS = np.dtype([
 ])
 
 
-def sample(out_tokens, logits, params_dev, history_dev, apply_penalties: bool):
+def sample_scratch_bytes(rows: int) -> int:
+    return int(kernels_lib().xb_sample_scratch_bytes(int(rows)))
+
+
+def sample(out_tokens, logits, params_dev, history_dev, apply_penalties: bool, scratch, err_word=None):
+    """One token per logits row into ``out_tokens``; with ``err_word`` (a device int32) its value is
+    written to ``out_tokens[R]``, so that one copy brings tokens and error word to the host.
+    ``scratch``: uint8 device buffer of ``sample_scratch_bytes(R)``, zero before its first use."""
     R, V = logits.shape
     _need(logits, "logits", torch.float32, (R, V))
     _need(out_tokens, "out_tokens", torch.int32)
@@ -233,10 +245,13 @@ def sample(out_tokens, logits, params_dev, history_dev, apply_penalties: bool):
     lib = kernels_lib()
     if lib.xb_sample_params_size() != SAMPLE_PARAMS.itemsize:
         raise KernelError("the sampler's parameter record differs between Python and CUDA")
-    if params_dev.numel() < R * SAMPLE_PARAMS.itemsize or out_tokens.numel() < R:
+    _need(scratch, "scratch", torch.uint8)
+    if (params_dev.numel() < R * SAMPLE_PARAMS.itemsize or out_tokens.numel() < R + (err_word is not None)
+            or scratch.numel() < lib.xb_sample_scratch_bytes(R)):
         raise KernelError("sampler buffers are smaller than the number of rows")
     _ok(lib.xb_sample(out_tokens.data_ptr(), logits.data_ptr(), params_dev.data_ptr(), _ptr(history_dev), R, V,
-                      int(bool(apply_penalties)), _stream()), "sample", 2 if apply_penalties else 1)
+                      int(bool(apply_penalties)), scratch.data_ptr(), _ptr(err_word), _stream()), "sample",
+        2 if apply_penalties else 1)
 
 
 # ---- bfloat16 attention on tensor cores ------------------------------------------------------------

@@ -87,7 +87,7 @@ class DecoderModel:
         T, H, V = ctx.num_tokens, self.plan.hidden, self.plan.vocab_size
         ws = ctx.workspace
         x = ws.get("model.x", (T, H), self.dtype)
-        kernels.embedding(x, self.embed, ctx.token_ids, ctx.err)
+        kernels.embedding(x, self.embed, ctx.token_ids, ctx.err, ctx.sampled)
         pending = None
         for pos, run in enumerate(self.plan.runs):
             src = pos if run.cache_from is None else run.cache_from

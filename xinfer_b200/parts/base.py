@@ -75,6 +75,8 @@ class StepContext:
     # the step is (or will be) replayed from a CUDA graph: launch sizes must come from the padded
     # shapes, never from this step's actual lengths
     fixed_shapes: bool = False
+    # int32 ids that a sampler left on the device; a token id -1 - i in token_ids stands for sampled[i]
+    sampled: Optional[torch.Tensor] = None
     # values parts compute once per step and share between layers
     scratch: Dict[str, Any] = field(default_factory=dict)
 

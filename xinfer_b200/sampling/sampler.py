@@ -16,16 +16,24 @@ PENALTY_HISTORY = 128
 
 
 class Sampler:
-    def __init__(self, device, max_rows: int):
+    def __init__(self, device, max_rows: int, out_dev: Optional[torch.Tensor] = None,
+                 err_word: Optional[torch.Tensor] = None):
+        """``out_dev``: int32 device buffer of max_rows + 1 that receives the ids (default: one of
+        its own).  ``err_word``: a device int32 whose value is copied behind the ids, so that the
+        step's tokens and its error word reach the host in one copy (``finish_copy`` returns both)."""
         self.device = device
         self.max_rows = max_rows
+        self.err_word = err_word
         rec = kernels.SAMPLE_PARAMS.itemsize
         self._params_host = torch.zeros(max_rows * rec, dtype=torch.uint8, pin_memory=True)
         self._params_dev = torch.zeros(max_rows * rec, dtype=torch.uint8, device=device)
         self._hist_host = torch.zeros(max_rows * PENALTY_HISTORY, dtype=torch.int32, pin_memory=True)
         self._hist_dev = torch.zeros(max_rows * PENALTY_HISTORY, dtype=torch.int32, device=device)
-        self._out_dev = torch.zeros(max_rows, dtype=torch.int32, device=device)
-        self._out_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=True)
+        self._out_dev = out_dev if out_dev is not None else torch.zeros(max_rows + 1, dtype=torch.int32, device=device)
+        if self._out_dev.numel() < max_rows + 1 or self._out_dev.dtype != torch.int32:
+            raise ValueError("the sampler's output buffer must hold max_rows + 1 int32")
+        self._out_host = torch.zeros(max_rows + 1, dtype=torch.int32, pin_memory=True)
+        self._scratch = torch.zeros(kernels.sample_scratch_bytes(max_rows), dtype=torch.uint8, device=device)
         self._params_np = self._params_host.numpy().view(kernels.SAMPLE_PARAMS)
         self._hist_np = self._hist_host.numpy()
 
@@ -62,23 +70,25 @@ class Sampler:
         self._params_dev[:nb].copy_(self._params_host[:nb], non_blocking=True)
         if any_pen:
             self._hist_dev[:off].copy_(self._hist_host[:off], non_blocking=True)
-        kernels.sample(self._out_dev, logits, self._params_dev, self._hist_dev, any_pen)
+        kernels.sample(self._out_dev, logits, self._params_dev, self._hist_dev, any_pen, self._scratch, self.err_word)
         return self._out_dev[:R]
 
     def to_host(self, tokens_dev: torch.Tensor) -> np.ndarray:
         """Copy sampled ids to the host (synchronises the stream)."""
         self.start_copy(tokens_dev)
-        return self.finish_copy()
+        return self.finish_copy()[0]
 
     def start_copy(self, tokens_dev: torch.Tensor) -> None:
-        """Queue the copy of sampled ids to the host; ``finish_copy`` waits for it alone, so work
-        queued after it keeps running."""
+        """Queue the copy of the sampled ids (and the error word behind them) to the host;
+        ``finish_copy`` waits for it alone, so work queued after it keeps running."""
         n = tokens_dev.shape[0]
-        self._out_host[:n].copy_(tokens_dev, non_blocking=True)
+        self._out_host[:n + 1].copy_(self._out_dev[:n + 1], non_blocking=True)
         self._copied = n
         self._copy_done = torch.cuda.Event()
         self._copy_done.record()
 
-    def finish_copy(self) -> np.ndarray:
+    def finish_copy(self):
+        """(ids, error word); the word is 0 when the sampler was given none."""
         self._copy_done.synchronize()
-        return self._out_host[:self._copied].numpy().copy()
+        n = self._copied
+        return self._out_host[:n].numpy().copy(), (int(self._out_host[n]) if self.err_word is not None else 0)
