@@ -435,15 +435,22 @@ def test_attention_prefill_tile_sizes(warps, monkeypatch):
         assert worst <= tol(torch.bfloat16, 2), worst
 
 
-def test_decode_split_choice_tcgen05():
-    from xinfer_b200.parts.attention_backend import decode_split_tc
-    for bound, pairs, ps in [(1, 1, 16), (4096, 8, 16), (4096, 64, 16), (4096, 512, 8), (40000, 8, 16), (100, 4096, 16), (300000, 1, 8)]:
-        split, n = decode_split_tc(bound, pairs, 128, ps)
-        assert split % 64 == 0 and split >= 64 and (n - 1) * split < bound <= n * split
-        assert split // ps + 2 <= 1024, "a range's block-table entries fit the CTA's staging area"
-    assert decode_split_tc(4096, 8)[1] >= 8                # few pairs: cut finely
-    assert decode_split_tc(4096, 64)[1] * 64 <= 296        # one wave holds every CTA
-    assert decode_split_tc(4096, 512) == (4096, 1)         # many pairs: nothing to merge
+def test_decode_tcgen05_launch_figures():
+    from xinfer_b200 import kernels
+    from xinfer_b200.parts.attention_backend import DECODE_TC_CTAS, decode_tc_launch
+    assert decode_tc_launch(1, 1, 1) == (1, 1)
+    assert decode_tc_launch(4096, 8, 8)[0] == DECODE_TC_CTAS            # enough work for every slot
+    assert decode_tc_launch(300, 1, 2) == (3, 2)                        # 5 tiles x 2 heads, 4 tiles per piece at least
+    assert kernels.attn_decode_plan_size(8, 296, 8) == 4 + 8 * (8 + 37 + 2)
+    for bound, tokens, heads in [(4096, 1, 8), (100000, 3, 2), (64, 500, 8), (5000, 64, 1)]:
+        ctas, splits = decode_tc_launch(bound, tokens, heads)
+        assert 1 <= ctas <= DECODE_TC_CTAS and splits >= 1
+        # what the kernel does with the longest context: pieces = max(1, tiles / share)
+        tiles = (bound + 63) // 64
+        for total in (tiles * heads, tokens * heads * tiles):            # alone, or every token as long
+            share = max(4, -(-total // ctas))
+            assert splits >= max(1, tiles // share)
+        assert splits == kernels.decode_tc_splits_max(ctas, heads, bound, 256)
 
 
 def test_decode_split_choice():

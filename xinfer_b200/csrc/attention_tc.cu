@@ -354,29 +354,135 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 // ------------------------------------------------------------------------------------------------
 constexpr int DEC_ROWS = 16;    // query heads of one key/value head a CTA can hold
 constexpr int DEC_STAGES = 3;   // key/value tiles in flight per CTA
+constexpr int PLAN_HEADER = 4;  // int32 before the first piece of a plan: [0] = number of pieces
+constexpr int PLAN_ENTRY = 8;   // int32 per piece: token row, request, position, first key, first tile, tiles,
+                                // pieces of the token << 16 | index of this one, rank of the token among the small ones
+constexpr int PLAN_THREADS = 512;
+constexpr int PLAN_SORT_MAX = 1024;   // up to this many pieces are put in order of their length, longest first
+constexpr int PLAN_TOKENS_MAX = 16 * PLAN_THREADS;
 
-// One CTA = one token x one key/value head x one of num_splits ranges of the token's keys (`split` is
-// the longest a range can be: it sizes the staging area of block-table entries).  The query heads of
-// the group are rows 0..G-1 of a 128-row MMA tile (rows from G on hold whatever the shared memory
-// behind the 16-row query and probability tiles holds: rows never mix, and only rows below G are
-// read back).  Warp 0: softmax (each row's 64 scores spread over four lanes) and the epilogue.
-// Warps 1 and 3: TMA producers of keys and of values (a ring each), one lane per page box.  Warp 2: MMA
-// issuer.  Shared memory:
+// How the decode step's attention is shared out, decided once per step for all layers: with T the
+// 64-key tiles of all tokens of portions of at most dec_max tokens and t = max(min_tiles,
+// T * kv_heads / target_ctas) the share of one CTA, a token of n tiles is cut into max(1, n / t)
+// equal pieces, whatever lengths the other requests have.  One CTA per piece and key/value head
+// reads its work from the plan; nothing of the step's metadata is looked at again.
+__global__ void __launch_bounds__(PLAN_THREADS)
+attn_decode_plan_kernel(int* __restrict__ plan, int capacity, const int* __restrict__ positions,
+                        const int* __restrict__ req_of_token, const int* __restrict__ q_start, int num_entries, int window,
+                        int dec_max, int direct, int num_small, int min_tiles, int target_ctas, int nkv, int* err) {
+    __shared__ int warp_sums[PLAN_THREADS / 32];
+    __shared__ int piece_tiles[PLAN_SORT_MAX];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    auto block_scan = [&](int mine, int& before_me) -> int {   // exclusive prefix of `mine` over the threads; returns the total
+        int incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += v;
+        }
+        __syncthreads();   // the sums of an earlier scan have been read
+        if (lane == 31) warp_sums[warp] = incl;
+        __syncthreads();
+        before_me = incl - mine;
+        int total = 0;
+        for (int w = 0; w < PLAN_THREADS / 32; ++w) {
+            if (w < warp) before_me += warp_sums[w];
+            total += warp_sums[w];
+        }
+        return total;
+    };
+    constexpr int EACH_MAX = PLAN_TOKENS_MAX / PLAN_THREADS;
+    const int each = (num_small + PLAN_THREADS - 1) / PLAN_THREADS;
+    int tiles[EACH_MAX], tok[EACH_MAX], sum = 0, unused;
+#pragma unroll
+    for (int i = 0; i < EACH_MAX; ++i) {
+        const int z = (int)threadIdx.x * each + i;
+        tiles[i] = 0;
+        tok[i] = -1;
+        if (i < each && z < num_small) {
+            const int t = small_token(z, q_start, num_entries, dec_max, direct);
+            if (t >= 0 && req_of_token[t] >= 0) {
+                const int pos = positions[t];
+                const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+                tiles[i] = pos / KT - lo / KT + 1;
+                tok[i] = t;
+            }
+        }
+        sum += tiles[i];
+    }
+    const long long all_tiles = (long long)block_scan(sum, unused) * nkv;
+    long long share = (all_tiles + target_ctas - 1) / target_ctas;
+    if (share < min_tiles) share = min_tiles;
+    int pieces = 0, at;
+#pragma unroll
+    for (int i = 0; i < EACH_MAX; ++i) pieces += tiles[i] ? max(1, (int)(tiles[i] / share)) : 0;
+    const int total = block_scan(pieces, at);
+    if (threadIdx.x == 0) {
+        plan[0] = total <= capacity ? total : 0;
+        if (total > capacity) atomicOr(err, XB_ERR_BAD_ROW);   // the plan was sized for fewer pieces
+    }
+    if (total > capacity) return;
+    // CTAs start in the order of the plan: the longest pieces first, so that no long one is left for the end
+    const bool sorted = total <= PLAN_SORT_MAX;
+    if (sorted) {
+        int a = at;
+#pragma unroll
+        for (int i = 0; i < EACH_MAX; ++i) {
+            if (!tiles[i]) continue;
+            const int n = tiles[i], cz = max(1, (int)(n / share)), sz = (n + cz - 1) / cz;
+            for (int j = 0; j < cz; ++j, ++a) piece_tiles[a] = j * sz < n ? min(sz, n - j * sz) : 0;
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < EACH_MAX; ++i) {
+        if (!tiles[i]) continue;
+        const int z = (int)threadIdx.x * each + i, t = tok[i], n = tiles[i];
+        const int cz = max(1, (int)(n / share));
+        const int sz = (n + cz - 1) / cz, ns = (n + sz - 1) / sz;   // tiles per piece; pieces that hold any
+        const int pos = positions[t];
+        const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+        for (int j = 0; j < cz; ++j, ++at) {
+            int where = at;
+            if (sorted) {   // as many pieces are longer (or as long and earlier) as this one's place says
+                const int mine = piece_tiles[at];
+                where = 0;
+                for (int o = 0; o < total; ++o) where += (piece_tiles[o] > mine || (piece_tiles[o] == mine && o < at)) ? 1 : 0;
+            }
+            int* e = plan + PLAN_HEADER + (size_t)where * PLAN_ENTRY;
+            const int i0 = j * sz;
+            e[0] = t;
+            e[1] = req_of_token[t];
+            e[2] = pos;
+            e[3] = lo;
+            e[4] = lo / KT + i0;
+            e[5] = i0 < n ? min(sz, n - i0) : 0;   // an empty piece (rounding): its CTA leaves
+            e[6] = (ns << 16) | j;
+            e[7] = z;
+        }
+    }
+}
+
+// One CTA = one piece of the plan x one key/value head.  The query heads of the group are rows
+// 0..G-1 of a 128-row MMA tile (rows from G on hold whatever the shared memory behind the 16-row
+// query and probability tiles holds: rows never mix, and only rows below G are read back).
+// Warp 0: softmax (each row's 64 scores spread over four lanes) and the epilogue.  Warps 1 and 3:
+// TMA producers of keys and of values (a ring each), one lane per page box.  Warp 2: MMA issuer.
+// Shared memory:
 //   Q [DP/64][16 rows][64]   P[2] [16][64]   stage s: K [DP/64][64 keys][64], V likewise   barriers, pages
 // Tensor memory: S[0] at column 0, S[1] at 64, O at 128.  The scores of tile i+1 are computed while
-// tile i's softmax runs; P is double-buffered, so the softmax warp waits for the
-// tensor cores only when a row's reference maximum has to move (then O is rescaled in TMEM).
-// Ranges of one token are merged by the CTA that finishes last (a ticket per token and key/value
-// head), in range order.
+// tile i's softmax runs; P is double-buffered, so the softmax warp waits for the tensor cores only
+// when a row's reference maximum has to move (then O is rescaled in TMEM).  The pieces of one token
+// and head are merged by the CTA that finishes last (a ticket per token and key/value head), in
+// the order of the pieces.
 template <int DP>
 __global__ void __launch_bounds__(128)
 attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
-                      float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ positions,
-                      const int* __restrict__ req_of_token, const int* __restrict__ q_start, int num_entries,
+                      float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ plan,
                       const int* __restrict__ block_table, int table_stride, int nh, int nkv, int d, int ps,
-                      int ps_shift, int num_pages, int window, float scale_log2, int dec_max, int direct, int split,
-                      int num_splits, int page_cap, int* __restrict__ tickets, int* err) {
+                      int ps_shift, int num_pages, float scale_log2, int dec_max, int splits_max, int page_cap,
+                      int* __restrict__ tickets, int* err) {
     constexpr int HALVES = DP / 64;
     constexpr uint32_t Q_HALF = DEC_ROWS * 128, Q_BYTES = HALVES * Q_HALF, P_ONE = DEC_ROWS * 128, P_BYTES = 2 * P_ONE;
     constexpr uint32_t KV_HALF = KT * 128, KV_BYTES = HALVES * KV_HALF, STAGE_BYTES = 2 * KV_BYTES;
@@ -395,20 +501,16 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
 
-    // what this CTA works on: step metadata only (written before the step's first kernel)
-    const int G = nh / nkv, g = blockIdx.y;
-    const int t = small_token(blockIdx.z, q_start, num_entries, dec_max, direct);
-    if (t < 0) return;
-    const int b = req_of_token[t];
-    if (b < 0) return;
-    const int pos = positions[t];
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    // the token's own tiles are shared evenly among the grid's ranges, whatever length the grid was sized for
-    const int tile_lo = lo / KT, tile_hi = pos / KT;
-    const int per = (tile_hi - tile_lo + num_splits) / num_splits;   // tiles per range, rounded up
-    const int ns = (tile_hi - tile_lo + per) / per;                  // ranges that hold any
-    if ((int)blockIdx.x >= ns) return;
-    const int kt_first = tile_lo + (int)blockIdx.x * per, kt_last = min(kt_first + per - 1, tile_hi);
+    // what this CTA works on: the plan was written by the step's first kernel, before any kernel that runs
+    // under programmatic dependent launch could have started
+    const int G = nh / nkv, g = blockIdx.x;   // heads vary fastest: pieces start in the order of the plan
+    if ((int)blockIdx.y >= plan[0]) return;
+    const int4 e0 = __ldg(reinterpret_cast<const int4*>(plan + PLAN_HEADER) + 2 * blockIdx.y);
+    const int4 e1 = __ldg(reinterpret_cast<const int4*>(plan + PLAN_HEADER) + 2 * blockIdx.y + 1);
+    const int t = e0.x, b = e0.y, pos = e0.z, lo = e0.w, kt_first = e1.x, z = e1.w;
+    const int ns = e1.z >> 16, slot = e1.z & 0xFFFF;
+    if (e1.y <= 0) return;
+    const int kt_last = kt_first + e1.y - 1;
     const int k_begin = max(lo, kt_first * KT), k_end = min(pos, kt_last * KT + KT - 1);
     const int fresh = pos - dec_max + 1;   // keys before this were written by earlier steps, not by the kernel before this one
     const int* table = block_table + (size_t)b * table_stride;
@@ -658,15 +760,15 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         if (alive) {
             const float l_row = lane < 8 ? la : lb, m_row = lane < 8 ? ma : mb;
             const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
-            const bool valid = lane < G;
+            const bool valid = lane < G && ns <= splits_max;
             const int h = h0 + lane;
-            const size_t slot = ((size_t)blockIdx.z * nh + h) * num_splits + blockIdx.x;   // by the token's rank among the small ones
+            const size_t pslot = ((size_t)z * nh + h) * splits_max + slot;   // by the token's rank among the small ones
 #pragma unroll
             for (int c0 = 0; c0 < DP; c0 += 32) {
                 float o[32];
                 tmem_ld32(tmem_o + c0, o);   // warp-wide, whatever `valid` is
                 if (!valid) continue;
-                if (num_splits == 1) {
+                if (ns == 1) {
                     __nv_bfloat16* dst = out + ((size_t)t * nh + h) * d;
 #pragma unroll
                     for (int c8 = 0; c8 < 4; ++c8) {
@@ -681,7 +783,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         }
                     }
                 } else {
-                    float* dst = part_o + slot * d;
+                    float* dst = part_o + pslot * d;
 #pragma unroll
                     for (int c4 = 0; c4 < 8; ++c4) {
                         const int c = c0 + c4 * 4;
@@ -690,9 +792,9 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     }
                 }
             }
-            if (valid && num_splits > 1) {
-                part_ml[slot * 2] = m_row;
-                part_ml[slot * 2 + 1] = l_row;
+            if (valid && ns > 1) {
+                part_ml[pslot * 2] = m_row;
+                part_ml[pslot * 2 + 1] = l_row;
             }
         } else {
             words[1] = 1;
@@ -705,11 +807,15 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
-    if (num_splits == 1) return;
-    // The CTA that finishes last among the ranges of this (token, key/value head) merges them:
-    //   out[h] = sum_s w_s O_s / sum_s w_s,  w_s = L_s * 2^(M_s - max M),  in range order.
+    if (ns == 1) return;
+    if (ns > splits_max) {   // the scratch was sized for fewer pieces
+        if (threadIdx.x == 0) atomicOr(err, XB_ERR_BAD_ROW);
+        return;
+    }
+    // The CTA that finishes last among the pieces of this (token, key/value head) merges them:
+    //   out[h] = sum_s w_s O_s / sum_s w_s,  w_s = L_s * 2^(M_s - max M),  in the order of the pieces.
     if (threadIdx.x == 0) {
-        int* ticket = tickets + (size_t)blockIdx.z * gridDim.y + blockIdx.y;
+        int* ticket = tickets + (size_t)z * nkv + g;
         const int mine = atomicAdd(ticket, 1);
         const int last = mine == ns - 1;
         words[2] = (uint32_t)last;
@@ -720,7 +826,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     __threadfence();
     for (int row = warp; row < G; row += 4) {
         const int h = h0 + row;
-        const size_t pbase = ((size_t)blockIdx.z * nh + h) * num_splits;
+        const size_t pbase = ((size_t)z * nh + h) * splits_max;
         float mloc = -INFINITY;
         for (int i = lane; i < ns; i += 32) mloc = fmaxf(mloc, __ldcg(part_ml + (pbase + i) * 2));
         const float M = warp_max(mloc);
@@ -768,22 +874,20 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
                      dec_max, err);
 }
 
+constexpr int DEC_PAGE_CAP = 1024;   // block-table entries of a piece that are staged in shared memory
+
 template <int DP>
 int launch_decode(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, float* part_o,
-                  float* part_ml, const int* positions, const int* req_of_token, const int* q_start, int num_entries,
-                  const int* table, int stride, int nh, int nkv, int d, int ps, int ps_shift, int num_pages, int window,
-                  float sl2, int dec_max, int direct, int split, int num_splits, int tokens, int* tickets, int* err,
+                  float* part_ml, const int* plan, int pieces, const int* table, int stride, int nh, int nkv, int d, int ps,
+                  int ps_shift, int num_pages, float sl2, int dec_max, int splits_max, int* tickets, int overlap, int* err,
                   cudaStream_t stream) {
-    // the range's block-table entries are staged in shared memory, up to what still lets two CTAs share an SM
-    int page_cap = (split + KT) / ps + 2;
-    if (page_cap > 1024) page_cap = 1024;
-    const size_t smem = (size_t)(DP / 64) * DEC_ROWS * 128 + 2 * DEC_ROWS * 128 + DEC_STAGES * 2 * (size_t)(DP / 64) * KT * 128 + 192 +
-                        (size_t)page_cap * 4;
+    constexpr size_t smem = (size_t)(DP / 64) * DEC_ROWS * 128 + 2 * DEC_ROWS * 128 + DEC_STAGES * 2 * (size_t)(DP / 64) * KT * 128 + 192 +
+                            (size_t)DEC_PAGE_CAP * 4;
     cudaFuncSetAttribute(attn_decode_tc_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaFuncSetAttribute(attn_decode_tc_kernel<DP>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    return xb_launch(attn_decode_tc_kernel<DP>, dim3(num_splits, nkv, tokens), dim3(128), smem, stream, mq, mk, mv,
-                     (__nv_bfloat16*)out, part_o, part_ml, positions, req_of_token, q_start, num_entries, table, stride, nh,
-                     nkv, d, ps, ps_shift, num_pages, window, sl2, dec_max, direct, split, num_splits, page_cap, tickets, err);
+    return xb_launch_opt(overlap != 0, attn_decode_tc_kernel<DP>, dim3(nkv, pieces), dim3(128), smem, stream, mq, mk, mv,
+                         (__nv_bfloat16*)out, part_o, part_ml, plan, table, stride, nh, nkv, d, ps, ps_shift, num_pages, sl2,
+                         dec_max, splits_max, DEC_PAGE_CAP, tickets, err);
 }
 
 }  // namespace
@@ -812,35 +916,61 @@ XB_EXPORT int xb_attn_prefill_tc(void* out, const void* q, const void* kc, const
     return launch<128>(mq, mk, mv, out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, shift, num_pages,
                        window, sl2, dec_max, tiles, err, stream);
 }
-// Tokens of portions of at most dec_max tokens on the tensor cores: the same arguments, scratch and
-// results as xb_attn_decode_bf16 (`q_rows` = rows of q), except that each token's own keys are cut
-// evenly into at most num_splits ranges (of at most `split` positions, a multiple of 64, which must
-// cover the longest context: num_splits * split >= its length).  Returns cudaErrorNotSupported (having done
-// nothing) for a head size over 128 or not a multiple of 16, a page size that is no power of two
-// >= 8, or more than 16 query heads per key/value head.
+// int32 a plan for `tokens` small tokens and `ctas` target CTAs must hold.
+XB_EXPORT long long xb_attn_decode_plan_size(int tokens, int ctas, int nkv) {
+    return PLAN_HEADER + (long long)PLAN_ENTRY * ((long long)tokens + ctas / (nkv > 0 ? nkv : 1) + 2);
+}
+
+// Decides how the attention of the step's small tokens (portions of at most dec_max tokens,
+// `tokens` of them; direct != 0: every token of the batch is one) is shared out: pieces of about
+// 1 / ctas of all keys, at least `min_keys` (a multiple of 64) each.  `plan` holds
+// xb_attn_decode_plan_size(tokens, ctas, kv heads) int32.  It must run before the first kernel of
+// the step that is launched with programmatic dependent launch: xb_attn_decode_tc reads the plan
+// before it waits for the kernel before it.
+XB_EXPORT int xb_attn_decode_plan(int* plan, const int* positions, const int* req_of_token, const int* q_start,
+                                  int num_entries, int window, int dec_max, int direct, int tokens, int min_keys, int ctas,
+                                  int nkv, int* err, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (tokens > PLAN_TOKENS_MAX) return (int)cudaErrorNotSupported;
+    if (min_keys <= 0 || min_keys % KT || ctas <= 0 || nkv <= 0) return (int)cudaErrorInvalidValue;
+    const int capacity = tokens + ctas / nkv + 2;
+    attn_decode_plan_kernel<<<1, PLAN_THREADS, 0, stream>>>(plan, capacity, positions, req_of_token, q_start, num_entries, window,
+                                                           dec_max, direct, tokens, min_keys / KT, ctas, nkv, err);
+    return xb_launch_status();
+}
+
+// The step's small tokens on the tensor cores, shared out as `plan` says (made by
+// xb_attn_decode_plan with the same tokens, ctas and kv heads, for the same window).  A token and
+// head in several pieces is merged through scratch: part_o [tokens, nh, splits_max, d] float32,
+// part_ml [tokens, nh, splits_max, 2] float32 and tickets [tokens * kv heads] int32, zero before the
+// first launch (the kernel leaves them zero); splits_max must be at least
+// min(ctas / kv heads + 1, longest context / min_keys + 1).  `q_rows` = rows of q.  `overlap` != 0
+// lets the kernel start while the one before it drains; it then reads the plan before that kernel
+// has finished, so the plan must have been made before the step's first kernel (else pass 0).
+// Returns cudaErrorNotSupported (having done nothing) for a head size over 128 or not a multiple of
+// 16, a page size that is no power of two >= 8, or more than 16 query heads per key/value head.
 XB_EXPORT int xb_attn_decode_tc(void* out, float* part_o, float* part_ml, const void* q, const void* kc, const void* vc,
-                                const int* positions, const int* req_of_token, const int* q_start, int num_entries,
-                                const int* table, int stride, int q_rows, int nh, int nkv, int d, int ps, int num_pages,
-                                int window, float scale, int dec_max, int direct, int split, int num_splits, int tokens,
-                                int* tickets, int* err, cudaStream_t stream) {
+                                const int* plan, const int* table, int stride, int q_rows, int nh, int nkv, int d, int ps,
+                                int num_pages, float scale, int dec_max, int splits_max, int tokens, int ctas, int* tickets,
+                                int overlap, int* err, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     int shift = -1;
     for (int s = 3; s < 20; ++s)
         if ((1 << s) == ps) shift = s;
-    if (d % 16 || d > 128 || d < 16 || nh % nkv || nh / nkv > DEC_ROWS || shift < 0) return (int)cudaErrorNotSupported;
-    if (split <= 0 || split % KT || num_splits <= 0) return (int)cudaErrorInvalidValue;
-    if (num_splits > 1 && (!part_o || !part_ml || !tickets)) return (int)cudaErrorInvalidValue;
+    if (d % 16 || d > 128 || d < 16 || nh % nkv || nh / nkv > DEC_ROWS || shift < 0 || tokens > PLAN_TOKENS_MAX)
+        return (int)cudaErrorNotSupported;
+    if (!plan || splits_max <= 0 || ctas <= 0) return (int)cudaErrorInvalidValue;
+    if (splits_max > 1 && (!part_o || !part_ml || !tickets)) return (int)cudaErrorInvalidValue;
     CUtensorMap mq, mk, mv;
     const long long rows = (long long)num_pages * nkv * ps;
     const int box_rows = ps < KT ? ps : KT;
     if (!map_q3(&mq, q, q_rows, nh, d, nh / nkv, 1) || !map_rows(&mk, kc, rows, d, box_rows) || !map_rows(&mv, vc, rows, d, box_rows))
         return (int)cudaErrorNotSupported;
     const float sl2 = scale * 1.4426950408889634f;
+    const int pieces = tokens + ctas / nkv + 2;   // the most the plan can hold
     if (d <= 64)
-        return launch_decode<64>(mq, mk, mv, out, part_o, part_ml, positions, req_of_token, q_start, num_entries, table, stride,
-                                 nh, nkv, d, ps, shift, num_pages, window, sl2, dec_max, direct, split, num_splits, tokens,
-                                 tickets, err, stream);
-    return launch_decode<128>(mq, mk, mv, out, part_o, part_ml, positions, req_of_token, q_start, num_entries, table, stride,
-                              nh, nkv, d, ps, shift, num_pages, window, sl2, dec_max, direct, split, num_splits, tokens,
-                              tickets, err, stream);
+        return launch_decode<64>(mq, mk, mv, out, part_o, part_ml, plan, pieces, table, stride, nh, nkv, d, ps, shift, num_pages,
+                                 sl2, dec_max, splits_max, tickets, overlap, err, stream);
+    return launch_decode<128>(mq, mk, mv, out, part_o, part_ml, plan, pieces, table, stride, nh, nkv, d, ps, shift, num_pages,
+                              sl2, dec_max, splits_max, tickets, overlap, err, stream);
 }

@@ -79,8 +79,10 @@ static inline bool xb_pdl_enabled() {   // XINFER_B200_PDL=0 switches the overla
     return v != 0;
 }
 
+// `overlap` false: the kernel starts only when the one before it has completed (its pdl_wait() is then a no-op).
 template <typename... KArgs, typename... Args>
-static inline int xb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+static inline int xb_launch_opt(bool overlap, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -90,7 +92,11 @@ static inline int xb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = xb_pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = overlap && xb_pdl_enabled() ? 1 : 0;
     const cudaError_t rc = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
     return rc != cudaSuccess ? (int)rc : xb_launch_status();
+}
+template <typename... KArgs, typename... Args>
+static inline int xb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    return xb_launch_opt(true, kernel, grid, block, smem, stream, args...);
 }

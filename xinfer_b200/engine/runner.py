@@ -434,6 +434,7 @@ class ModelRunner:
         torch.cuda.current_stream().synchronize()
         graph = torch.cuda.CUDAGraph()
         before = kernels.launch_count()
+        ctx.scratch.clear()   # what parts decide once per step (and launch kernels for) is decided again, inside the graph
         with torch.cuda.graph(graph, pool=self._graph_pool):
             logits = self.model.forward(ctx, self.layer_caches, self.layer_states)
         launches = kernels.launch_count() - before

@@ -321,41 +321,75 @@ def attn_decode_bf16(out, part_o, part_ml, q, k_cache, v_cache, positions, req_o
 ERR_NOT_SUPPORTED = 801  # cudaErrorNotSupported
 
 
-def attn_decode_tc(out, part_o, part_ml, q, k_cache, v_cache, positions, req_of_token, q_start, num_entries,
-                   block_table, table_stride, window, scale, dec_max, direct, split, num_splits, tokens, err,
-                   tickets=None) -> bool:
-    """The same work, arguments and scratch as ``attn_decode_bf16`` on tcgen05 tensor cores with
-    TMA-fed pages.  Returns False, having done nothing, for shapes the kernel does not take (a
-    head size over 128, a page size that is no power of two >= 8, more than 16 query heads per
-    key/value head)."""
+def attn_decode_plan_size(tokens: int, ctas: int, kv_heads: int) -> int:
+    return int(kernels_lib().xb_attn_decode_plan_size(int(tokens), int(ctas), int(kv_heads)))
+
+
+def attn_decode_plan(plan, positions, req_of_token, q_start, num_entries, window, dec_max, direct, tokens, min_keys,
+                     ctas, kv_heads, err) -> bool:
+    """Decide how the attention of the step's ``tokens`` small tokens is shared out (pieces of about
+    1 / ``ctas`` of all keys, at least ``min_keys`` each) and write it to ``plan`` (int32,
+    ``attn_decode_plan_size`` elements).  It must run before the step's first kernel when
+    ``attn_decode_tc`` is to overlap with its predecessor.  False: more tokens than a plan takes."""
+    _need(plan, "plan", torch.int32)
+    if plan.numel() < attn_decode_plan_size(tokens, ctas, kv_heads):
+        raise KernelError("the attention plan buffer is too small")
+    rc = kernels_lib().xb_attn_decode_plan(plan.data_ptr(), positions.data_ptr(), req_of_token.data_ptr(), q_start.data_ptr(),
+                                           int(num_entries), int(window or 0), int(dec_max), int(bool(direct)), int(tokens),
+                                           int(min_keys), int(ctas), int(kv_heads), err.data_ptr(), _stream())
+    if rc == ERR_NOT_SUPPORTED:
+        return False
+    _ok(rc, "attn_decode_plan")
+    return True
+
+
+def attn_decode_tc(out, part_o, part_ml, q, k_cache, v_cache, plan, block_table, table_stride, scale, dec_max,
+                   splits_max, tokens, ctas, err, tickets=None, overlap: bool = True) -> bool:
+    """The step's small tokens on tcgen05 tensor cores with TMA-fed pages, shared out as ``plan``
+    says (``attn_decode_plan`` with the same tokens, ctas and kv heads).  A token and head in several
+    pieces is merged through ``part_o`` / ``part_ml`` (float32, tokens*heads*splits_max*head_dim
+    and tokens*heads*splits_max*2 elements) and ``tickets`` (int32, tokens * kv_heads zeros, left
+    zero); ``decode_tc_splits_max`` gives the ``splits_max`` that is always enough.  ``overlap``:
+    start while the kernel before drains - only with a plan made before the step's first kernel.
+    Returns False, having done nothing, for shapes the kernel does not take (a head size over
+    128, a page size that is no power of two >= 8, more than 16 query heads per key/value head)."""
     T, nh, d = q.shape
     _need(q, "q", torch.bfloat16, (T, nh, d))
     _need(out, "out", torch.bfloat16, (T, nh, d))
     _need(k_cache, "k_cache", torch.bfloat16, (None, None, None, d))
     _need(v_cache, "v_cache", torch.bfloat16, tuple(k_cache.shape))
+    _need(plan, "plan", torch.int32)
     num_pages, nkv, ps, _ = k_cache.shape
     if nh % nkv or d % 16:
         raise KernelError(f"tiled attention needs a head size in steps of 16 and heads divisible by key/value heads; "
                           f"got head size {d}, {nh}/{nkv} heads")
-    if tokens > 65535:
-        raise KernelError(f"{tokens} small-portion tokens exceed the decode kernel's grid limit of 65535")
-    if num_splits > 1:
+    if plan.numel() < attn_decode_plan_size(tokens, ctas, nkv):
+        raise KernelError("the attention plan buffer is too small")
+    if splits_max > 1:
         _need(part_o, "part_o", torch.float32)
         _need(part_ml, "part_ml", torch.float32)
-        if part_o.numel() < tokens * nh * num_splits * d or part_ml.numel() < tokens * nh * num_splits * 2:
-            raise KernelError("attention scratch buffers are too small for the number of key ranges")
+        if part_o.numel() < tokens * nh * splits_max * d or part_ml.numel() < tokens * nh * splits_max * 2:
+            raise KernelError("attention scratch buffers are too small for the number of pieces per token")
         _need(tickets, "tickets", torch.int32)
         if tickets.numel() < tokens * nkv:
             raise KernelError("the attention ticket buffer is too small")
     rc = kernels_lib().xb_attn_decode_tc(
-        out.data_ptr(), _ptr(part_o), _ptr(part_ml), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
-        positions.data_ptr(), req_of_token.data_ptr(), q_start.data_ptr(), int(num_entries), block_table.data_ptr(),
-        int(table_stride), T, nh, nkv, d, ps, num_pages, int(window or 0), float(scale), int(dec_max), int(bool(direct)),
-        int(split), int(num_splits), int(tokens), _ptr(tickets), err.data_ptr(), _stream())
+        out.data_ptr(), _ptr(part_o), _ptr(part_ml), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), plan.data_ptr(),
+        block_table.data_ptr(), int(table_stride), T, nh, nkv, d, ps, num_pages, float(scale), int(dec_max),
+        int(splits_max), int(tokens), int(ctas), _ptr(tickets), int(bool(overlap)), err.data_ptr(), _stream())
     if rc == ERR_NOT_SUPPORTED:
         return False
     _ok(rc, "attn_decode_tc")
     return True
+
+
+def decode_tc_splits_max(ctas: int, kv_heads: int, bound: int, min_keys: int) -> int:
+    """Most pieces one token of ``attn_decode_tc`` can be cut into when no context is longer than
+    ``bound``: a (token, head) pair holds at most 1 / kv_heads of all tiles (so it gets at most
+    ctas / kv_heads shares), and a piece at least ``min_keys``."""
+    tiles = (max(int(bound), 1) + 63) // 64
+    per = max(int(min_keys) // 64, 1)
+    return max(1, min(int(ctas) // int(kv_heads) + 1, tiles // per + 1))
 
 
 # ---- matrix product for few tokens on tcgen05 tensor cores ---------------------------------------------

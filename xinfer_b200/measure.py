@@ -74,6 +74,9 @@ def decode_attention(cases: Sequence = ((1, 4096), (8, 4096), (64, 4096), (8, 32
         for name, flag in (("tcgen05_us", True), ("mma_sync_us", False)):
             attention_backend.DECODE_TC = flag
             try:
+                # as in a step: the work is planned once, before the first kernel, for all layers
+                ctx.scratch.clear()
+                attention_backend.prepare_step(ctx, torch.bfloat16, heads, kv_heads, head_dim, page_size, None, stride)
                 rec[name] = round(_graph_time_us(lambda: [attention_backend.attend(o, q, c, ctx, table, stride, None, head_dim ** -0.5)
                                                           for c in caches], layers), 1)
             finally:

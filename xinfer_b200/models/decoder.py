@@ -87,6 +87,10 @@ class DecoderModel:
         T, H, V = ctx.num_tokens, self.plan.hidden, self.plan.vocab_size
         ws = ctx.workspace
         x = ws.get("model.x", (T, H), self.dtype)
+        # what mixers decide once per step from its metadata, before the step's first kernel
+        for pos, run in enumerate(self.plan.runs):
+            src = pos if run.cache_from is None else run.cache_from
+            self.blocks[run.block].mixer.prepare_step(ctx, caches[src])
         kernels.embedding(x, self.embed, ctx.token_ids, ctx.err, ctx.sampled)
         pending = None
         for pos, run in enumerate(self.plan.runs):

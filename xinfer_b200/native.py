@@ -102,5 +102,6 @@ def _declare_kernels(lib):
     _sig(lib, "xb_attn_prefill_bf16", I, [P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, I, I, I, P, P])
     _sig(lib, "xb_attn_decode_bf16", I,
          [P, P, P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, I, I, I, I, P, P, P])
-    _sig(lib, "xb_attn_decode_tc", I,
-         [P, P, P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, F, I, I, I, I, I, P, P, P])
+    _sig(lib, "xb_attn_decode_plan_size", c_longlong, [I, I, I])
+    _sig(lib, "xb_attn_decode_plan", I, [P, P, P, P, I, I, I, I, I, I, I, I, P, P])
+    _sig(lib, "xb_attn_decode_tc", I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, I, P, I, P, P])

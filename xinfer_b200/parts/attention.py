@@ -60,6 +60,12 @@ class Attention(Mixer):
     def cache_need(self) -> PagedCacheNeed:
         return PagedCacheNeed(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
 
+    def prepare_step(self, ctx: StepContext, cache: LayerCache) -> None:
+        from . import attention_backend
+        s = self.spec
+        attention_backend.prepare_step(ctx, self.dtype, s.num_heads, s.num_kv_heads, s.head_dim, cache.page_size, s.window,
+                                       ctx.strides[cache.group])
+
     def forward(self, x, ctx: StepContext, cache: LayerCache, state=None, writes_cache: bool = True):
         s = self.spec
         T = x.shape[0]

@@ -19,13 +19,11 @@ DEC_MAX = 4
 DECODE_RESIDENT_CTAS = 444
 # what starting a CTA of the decode kernel costs, in key positions of work
 DECODE_CTA_OVERHEAD = 96
-# the tcgen05 decode kernel: two CTAs per SM; times in microseconds measured on a B200 at head size 128
-DECODE_TC_SMS = 148
-DECODE_TC_CTA_LATENCY = 7.5      # a CTA's start-up and merge
-DECODE_TC_TILE_ALONE = 0.9       # one 64-key tile of a CTA that has its SM to itself (latency-bound)
-DECODE_TC_TILE_SHARED = 1.16     # the same when two CTAs share the SM's path to memory
-DECODE_TC_MERGE_LATENCY = 0.1    # per range the last CTA merges
-DECODE_TC_TILE_HBM = 0.005       # one tile's keys and values at the memory's full rate
+# the tcgen05 decode kernel: two CTAs per SM; the tiles of all (token, head) pairs are shared out
+# evenly among them, but no CTA gets less than this many keys (a CTA's start-up and the merge of a
+# shared pair cost about as much as reading 256 keys)
+DECODE_TC_CTAS = 296
+DECODE_TC_MIN_KEYS = 256
 PREFILL_WARPS = 8
 # portions of many tokens go to the tcgen05 kernel where it takes the sizes (head size <= 128,
 # page size a power of two >= 8), else to the mma.sync kernel
@@ -48,30 +46,16 @@ def decode_tc_takes(nh: int, nkv: int, d: int, page_size: int) -> bool:
             and page_size & (page_size - 1) == 0)
 
 
-def decode_split_tc(bound: int, pairs: int, head_dim: int = 128, page_size: int = 16) -> tuple:
-    """Longest range (a multiple of 64) and number of ranges for the tcgen05 decode kernel.  The
-    time of a cut is that of the busiest SM - its CTAs run two at a time, each start-up, tiles and
-    merge - or what the memory's rate allows for all tiles, whichever is larger; the cheapest cut
-    wins.  A range stays within the 1,000 block-table entries that a CTA stages in shared memory."""
-    pairs = max(pairs, 1)
-    tiles = max((bound + 63) // 64, 1)
-    width = max(head_dim, 64) / 128.0
-    shared = max(DECODE_TC_TILE_ALONE, DECODE_TC_TILE_SHARED * width)
-    floor = pairs * tiles * DECODE_TC_TILE_HBM * width
-    best = None
-    last_n = None
-    for per in range(1, min(tiles, max(1000 * page_size // 64, 1)) + 1):
-        n = (tiles + per - 1) // per
-        if n > 1024 or n == last_n:
-            continue
-        last_n = n
-        on_sm = (pairs * n + DECODE_TC_SMS - 1) // DECODE_TC_SMS
-        rounds = (on_sm + 1) // 2
-        tile = shared if on_sm >= 2 else DECODE_TC_TILE_ALONE
-        cost = max(rounds * (DECODE_TC_CTA_LATENCY + tile * per + DECODE_TC_MERGE_LATENCY * n), floor)
-        if best is None or cost <= best[0] + 1e-9:   # on a tie the longer ranges: less to merge
-            best = (cost, per * 64, n)
-    return best[1], best[2]
+DECODE_TC_MAX_TOKENS = 8192   # small tokens a plan of the tcgen05 decode kernel takes
+
+
+def decode_tc_launch(bound: int, tokens: int, kv_heads: int) -> tuple:
+    """(ctas, splits_max) of the tcgen05 decode kernel for ``tokens`` tokens whose contexts are at
+    most ``bound`` long: as many CTAs as there is work of DECODE_TC_MIN_KEYS keys, up to two per SM."""
+    tiles = (max(bound, 1) + 63) // 64
+    per = DECODE_TC_MIN_KEYS // 64
+    ctas = max(1, min(DECODE_TC_CTAS, (tokens * kv_heads * tiles + per - 1) // per))
+    return ctas, kernels.decode_tc_splits_max(ctas, kv_heads, bound, DECODE_TC_MIN_KEYS)
 
 
 def decode_split(bound: int, pairs: int, resident: int = DECODE_RESIDENT_CTAS, overhead: int = DECODE_CTA_OVERHEAD) -> tuple:
@@ -115,6 +99,35 @@ def _plan(ctx, head_dim: int):
     return plan
 
 
+def _decode_plan(ctx, nh: int, nkv: int, d: int, page_size: int, window, stride: int, early: bool):
+    """The step's plan of the tcgen05 decode kernel for this head layout and window: made once per
+    step and shared by all layers.  ``early``: the call comes before the step's first kernel.
+    Returns None when the kernel does not take the step, else (plan, ctas, splits_max, overlap)."""
+    key = ("attn_decode_plan", nh, nkv, d, page_size, window)
+    if key in ctx.scratch:
+        return ctx.scratch[key]
+    made = None
+    plan = _plan(ctx, d)
+    small = plan["small"]
+    if small and decode_tc_takes(nh, nkv, d, page_size) and small <= DECODE_TC_MAX_TOKENS:
+        bound = plan["bound"] if plan["bound"] is not None else stride * page_size
+        ctas, splits_max = decode_tc_launch(bound, small, nkv)
+        buf = ctx.workspace.get(f"attn.plan.{nkv}.{window or 0}", (kernels.attn_decode_plan_size(small, ctas, nkv),), torch.int32)
+        if kernels.attn_decode_plan(buf, ctx.positions, ctx.req_of_token, ctx.q_start, ctx.num_entries, window, DEC_MAX,
+                                    plan["direct"], small, DECODE_TC_MIN_KEYS, ctas, nkv, ctx.err):
+            # a plan made in the middle of the step is read only after the kernel before has completed
+            made = (buf, ctas, splits_max, bool(early))
+    ctx.scratch[key] = made
+    return made
+
+
+def prepare_step(ctx, dtype, nh: int, nkv: int, d: int, page_size: int, window, stride: int) -> None:
+    """Called before the step's first kernel for every attention layer (``stride``: the width of
+    its block table): plans the decode kernel."""
+    if _enabled and kernels.attn_tiled_supported(dtype, d):
+        _decode_plan(ctx, nh, nkv, d, page_size, window, stride, early=True)
+
+
 def attend(out, q, cache, ctx, table, stride, window, scale) -> None:
     T, nh, d = q.shape
     if not (_enabled and kernels.attn_tiled_supported(q.dtype, d)):
@@ -132,21 +145,27 @@ def attend(out, q, cache, ctx, table, stride, window, scale) -> None:
     if plan["small"]:
         nkv = cache.k.shape[1]
         bound = plan["bound"] if plan["bound"] is not None else stride * cache.page_size
-        tc = decode_tc_takes(nh, nkv, d, cache.page_size)
-        if tc:
-            pairs = plan["small"] * nkv
-            split, num_splits = decode_split_tc(bound, pairs, d, cache.page_size)
-        else:
-            pairs = plan["small"] * nkv * ((nh // nkv + 15) // 16)
-            split, num_splits = decode_split(bound, pairs)
+        small = plan["small"]
         part_o = part_ml = tickets = None
-        if num_splits > 1:
-            part_o = ctx.workspace.get("attn.part_o", (plan["small"] * nh * num_splits * d,), torch.float32)
-            part_ml = ctx.workspace.get("attn.part_ml", (plan["small"] * nh * num_splits * 2,), torch.float32)
-            # zero-filled when made, left zero by the kernels; sized for either kernel
-            tickets = ctx.workspace.get("attn.tickets", (plan["small"] * nkv * ((nh // nkv + 15) // 16),), torch.int32)
-        args = (out, part_o, part_ml, q, cache.k, cache.v, ctx.positions, ctx.req_of_token, ctx.q_start,
-                ctx.num_entries, table, stride, window, scale, DEC_MAX, plan["direct"], split, num_splits,
-                plan["small"], ctx.err, tickets)
-        if not (tc and kernels.attn_decode_tc(*args)):
-            kernels.attn_decode_bf16(*args)
+
+        def scratch(splits):
+            nonlocal part_o, part_ml, tickets
+            if splits > 1:
+                part_o = ctx.workspace.get("attn.part_o", (small * nh * splits * d,), torch.float32)
+                part_ml = ctx.workspace.get("attn.part_ml", (small * nh * splits * 2,), torch.float32)
+                # zero-filled when made, left zero by the kernels; sized for either kernel
+                tickets = ctx.workspace.get("attn.tickets", (small * nkv * ((nh // nkv + 15) // 16),), torch.int32)
+
+        step = (q, cache.k, cache.v, ctx.positions, ctx.req_of_token, ctx.q_start, ctx.num_entries, table, stride,
+                window, scale, DEC_MAX, plan["direct"])
+        took = False
+        planned = _decode_plan(ctx, nh, nkv, d, cache.page_size, window, stride, early=False)
+        if planned is not None:
+            buf, ctas, splits_max, overlap = planned
+            scratch(splits_max)
+            took = kernels.attn_decode_tc(out, part_o, part_ml, q, cache.k, cache.v, buf, table, stride, scale, DEC_MAX,
+                                          splits_max, small, ctas, ctx.err, tickets, overlap)
+        if not took:
+            split, num_splits = decode_split(bound, small * nkv * ((nh // nkv + 15) // 16))
+            scratch(num_splits)
+            kernels.attn_decode_bf16(out, part_o, part_ml, *step, split, num_splits, small, ctx.err, tickets)

@@ -139,6 +139,10 @@ class Mixer(Part):
     def state_need(self) -> Optional[Dict[str, Tuple[Tuple[int, ...], torch.dtype]]]:
         return None
 
+    def prepare_step(self, ctx: StepContext, cache: Optional[LayerCache]) -> None:
+        """Called for every layer run before the step's first kernel: what a mixer wants decided
+        once per step from the step's metadata (launch figures, work lists) is decided here."""
+
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCache],
                 state: Optional[Dict[str, torch.Tensor]], writes_cache: bool = True) -> torch.Tensor:
         raise NotImplementedError
