@@ -8,8 +8,7 @@ from helpers import TINY
 from xinfer_b200.config import (ConfigError, EngineConfig, Qwen3Config, config_from_dict,
                                 known_architectures, load_config, register_architecture,
                                 unregister_architecture)
-from xinfer_b200.config.plan import (AttentionSpec, BlockSpec, FeedForwardSpec, LayerRun, ModelPlan,
-                                     NormSpec)
+from xinfer_b200.config.plan import LayerRun
 
 
 def test_reads_every_key_from_config_json():

@@ -1,10 +1,9 @@
 """Generation through the Python entry point against the plain implementation."""
-import numpy as np
 import pytest
 import torch
 
 import plain_qwen3 as plain
-from helpers import PAGE_SIZE, TINY, prompts_for
+from helpers import PAGE_SIZE, prompts_for
 
 pytestmark = pytest.mark.gpu
 

@@ -2,7 +2,6 @@
 sizes of their own, and the arrangement of layer runs (a block named twice, a run that reads
 another run's cache)."""
 import dataclasses
-import math
 
 import numpy as np
 import pytest

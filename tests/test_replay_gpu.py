@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import plain_qwen3 as plain
-from helpers import PAGE_SIZE, TINY, build_all_modes, prompts_for, run_trace
+from helpers import PAGE_SIZE, build_all_modes, prompts_for, run_trace
 
 pytestmark = pytest.mark.gpu
 

@@ -1,7 +1,6 @@
 """A toy mixer with state of its own, defined here, is registered, built and stepped without a
 change to the framework's files: a running mean over the request's tokens, kept in the request's
 state slot, in a model that alternates it with attention layers."""
-import math
 
 import numpy as np
 import pytest

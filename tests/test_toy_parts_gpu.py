@@ -3,7 +3,6 @@
 norm with a bias, put together with the framework's attention into a model whose layers differ and
 whose order of layers names one layer twice.  None of them is anyone's model; they show that the
 interfaces of the parts carry more than the one architecture that is built."""
-import math
 from dataclasses import dataclass
 
 import numpy as np

@@ -9,7 +9,7 @@ import torch
 from helpers import TINY
 from xinfer_b200.config import Qwen3Config
 from xinfer_b200.models import model_weight_specs
-from xinfer_b200.weights import (SafetensorsError, SafetensorsFile, WeightError, WeightSpec, WeightStore,
+from xinfer_b200.weights import (SafetensorsError, SafetensorsFile, WeightError, WeightStore, 
                                  write_random_model, write_safetensors)
 
 

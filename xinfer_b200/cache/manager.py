@@ -12,7 +12,6 @@ import ctypes
 from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
-import numpy as np
 
 from ..native import host_lib
 

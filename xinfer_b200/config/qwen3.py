@@ -11,8 +11,8 @@ from __future__ import annotations
 import json
 import math
 import os
-from dataclasses import dataclass, field, asdict
-from typing import Any, Dict, List, Mapping, Optional, Tuple
+from dataclasses import dataclass, asdict
+from typing import Any, Dict, Mapping, Optional, Tuple
 
 from .plan import (AttentionSpec, BlockSpec, FeedForwardSpec, LayerRun, ModelPlan, NormSpec,
                    RopeSpec)

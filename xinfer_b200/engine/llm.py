@@ -9,7 +9,7 @@ prepare_step / run_forward / finish_step (src/core/engine.rs:1034, 1085, 1363).
 from __future__ import annotations
 
 import time
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, Iterator, List, Optional, Sequence, Tuple, Union
 
 import numpy as np

@@ -15,14 +15,14 @@ decode step per batch size (src/utils/graph.rs:400-420, 689-711).
 from __future__ import annotations
 
 import ctypes
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Dict, List, Mapping, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
 
 from .. import kernels
-from ..cache.manager import CacheError, CacheGroup, CacheManager, StateSlots
+from ..cache.manager import CacheGroup, CacheManager, StateSlots
 from ..config import ConfigError, config_from_dict, load_config
 from ..models.decoder import DecoderModel, model_weight_specs
 from ..native import host_lib

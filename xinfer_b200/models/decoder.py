@@ -6,7 +6,7 @@ embedding -> the plan's layer runs in order -> final norm on the wanted rows -> 
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Optional
 
 import torch
 

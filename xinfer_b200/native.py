@@ -6,7 +6,7 @@ from __future__ import annotations
 
 import ctypes
 import threading
-from ctypes import (POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_longlong, c_void_p)
+from ctypes import (POINTER, c_char_p, c_float, c_int, c_int32, c_longlong, c_void_p)
 
 _lock = threading.Lock()
 _host = None

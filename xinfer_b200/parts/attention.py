@@ -9,7 +9,7 @@ then the output projection (:976).  Query head h reads key/value head h // (head
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional
+from typing import List
 
 import torch
 

@@ -6,7 +6,7 @@ the previous block's not-yet-added branch, and hands back the same pair, so each
 once, in float32, inside the norm kernel that needs it."""
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Tuple
+from typing import List, Optional
 
 import torch
 

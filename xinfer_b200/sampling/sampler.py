@@ -2,7 +2,7 @@
 (greedy, temperature, top-k, top-p, top-k then top-p; src/utils/logits_processor.rs:258-344)."""
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import Optional, Sequence
 
 import numpy as np
 import torch

@@ -16,7 +16,7 @@ The reference resolves names through a prefix-pushing handle over the mapped fil
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+from typing import Dict, List, Sequence, Tuple
 
 import torch
 
