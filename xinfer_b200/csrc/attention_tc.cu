@@ -242,7 +242,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 }
             }
 #pragma unroll
-            for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sc[i]);
+            for (int i = 0; i < 64; i += 8) {
+                mx4[0] = max3(mx4[0], sc[i], sc[i + 1]);
+                mx4[1] = max3(mx4[1], sc[i + 2], sc[i + 3]);
+                mx4[2] = max3(mx4[2], sc[i + 4], sc[i + 5]);
+                mx4[3] = max3(mx4[3], sc[i + 6], sc[i + 7]);
+            }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
             // move the reference maximum only when the row's maximum outgrows it by more than 2^8
             float corr = 1.f;
@@ -253,22 +258,33 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 moved = it > 0;
             }
             const float m_neg = m_ref == -INFINITY ? 0.f : -m_ref;
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            // 2^(s * scale - m): the argument by packed FMAs (two per instruction); of every eight
+            // exponentials six go to the special-function unit and two to a polynomial on the FMA pipe, so
+            // that neither unit alone sets the pace; the row sum by packed adds
+            const f32x2 scale2 = pack2(scale_log2, scale_log2), mneg2 = pack2(m_neg, m_neg);
+            f32x2 sum_a = pack2(0.f, 0.f), sum_b = pack2(0.f, 0.f);
             uint4 pk[8];
 #pragma unroll
             for (int c8 = 0; c8 < 8; ++c8) {
-                float e[8];
+                float x[8], e[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    e[i] = ex2(fmaf(sc[c8 * 8 + i], scale_log2, m_neg));   // 2^(s * scale - m), one FMA and one SFU op
-                    sum4[i & 3] += e[i];
-                }
+                for (int i = 0; i < 8; i += 2)
+                    unpack2(fma2(pack2(sc[c8 * 8 + i], sc[c8 * 8 + i + 1]), scale2, mneg2), x[i], x[i + 1]);
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if ((i & 3) != 3) e[i] = ex2(x[i]);
+                ex2_poly2(x[3], x[7], e[3], e[7]);
+                sum_a = add2(sum_a, add2(pack2(e[0], e[1]), pack2(e[2], e[3])));
+                sum_b = add2(sum_b, add2(pack2(e[4], e[5]), pack2(e[6], e[7])));
                 pk[c8].x = pack_bf16(e[0], e[1]);
                 pk[c8].y = pack_bf16(e[2], e[3]);
                 pk[c8].z = pack_bf16(e[4], e[5]);
                 pk[c8].w = pack_bf16(e[6], e[7]);
             }
-            l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            float s0, s1, s2, s3;
+            unpack2(sum_a, s0, s1);
+            unpack2(sum_b, s2, s3);
+            l = l * corr + ((s0 + s1) + (s2 + s3));
             // P and O belong to the previous tile's P V until it has completed
             if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(v_empty0 + 8 * (s ^ 1), ((it - 1) >> 1) & 1, err))) {
                 alive = false;

@@ -171,6 +171,49 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// Two float32 in one 64-bit register, for the packed arithmetic of sm_100 (one instruction, two results).
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+    return v;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("add.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// 2^x for two x <= 0 on the FMA pipe, beside the special-function unit: x = n + f with n the
+// nearest integer and f in [-0.5, 0.5]; 2^f by a cubic (largest relative error 7.5e-5, far below
+// the rounding of the bfloat16 it ends in), n added to the exponent bits.  x below -126 gives 2^-126.
+__device__ __forceinline__ void ex2_poly2(float x0, float x1, float& y0, float& y1) {
+    const float magic = 12582912.f;   // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
+    const f32x2 xc = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+    const f32x2 r = add2(xc, pack2(magic, magic));
+    const f32x2 n = add2(r, pack2(-magic, -magic));
+    const f32x2 f = fma2(n, pack2(-1.f, -1.f), xc);
+    f32x2 p = fma2(f, pack2(0.0551716648f, 0.0551716648f), pack2(0.2426111251f, 0.2426111251f));
+    p = fma2(p, f, pack2(0.6932609677f, 0.6932609677f));
+    p = fma2(p, f, pack2(0.9999280572f, 0.9999280572f));
+    float p0, p1, r0, r1;
+    unpack2(p, p0, p1);
+    unpack2(r, r0, r1);
+    y0 = __int_as_float(__float_as_int(p0) + (__float_as_int(r0) << 23));
+    y1 = __int_as_float(__float_as_int(p1) + (__float_as_int(r1) << 23));
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
