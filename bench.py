@@ -41,6 +41,7 @@ SHAPES = {
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 PAGE = 16
+SETTLE = 24   # untimed decode steps between a prefill burst and any timed decode step, beside --warmup
 
 
 def peaks():
@@ -179,6 +180,7 @@ def main() -> int:
 
     def decode_device(slots, n_steps: int, n_warm: int):
         """K decode steps, kernel time only: token ids come from the host each step, no read-back."""
+        n_warm += SETTLE   # the prefill before leaves the device at its power cap: untimed steps until the clocks are back
         toks = rng.integers(0, V, size=(n_steps + n_warm, len(slots)))
         for i in range(n_warm):
             runner.step([StepInput(s, toks[i, j:j + 1], [0]) for j, s in enumerate(slots)], allow_graph=use_graph)
@@ -229,13 +231,13 @@ def main() -> int:
 
     # ---- decode at the headline batch --------------------------------------------------------------------
     B = args.batch
-    ctx0 = args.context - steps - warmup - 2
+    ctx0 = args.context - steps - warmup - SETTLE - 2
     slots = fill(B, ctx0)
     ms, launches, (t0, t1) = decode_device(slots, steps, warmup)
     ck = clocks.summary(t0, t1)
     value = B / (ms / 1e3)
     weight_bytes = (layer_params * L + V * H) * 2 + (2 * L + 1) * H * 4 + L * 2 * d * 4
-    ctx_mid = ctx0 + warmup + steps / 2
+    ctx_mid = ctx0 + warmup + SETTLE + steps / 2
     kv_bytes = runner.kv_bytes_per_token * ctx_mid * B
     achieved = (weight_bytes + kv_bytes) / (ms / 1e3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
@@ -249,13 +251,16 @@ def main() -> int:
     n_e2e = min(steps, 64)
     # prompts are prefilled two per step, so requests start decoding a few steps apart: leave room
     # for that in the context, and let no request finish inside the timed region
-    prompt_len = args.context - n_e2e - warmup - 16
-    sp = SamplingParams(temperature=0.0, max_tokens=n_e2e + warmup + 64, ignore_eos=True)
+    # the prompts' prefill leaves the device at its power cap for some tens of milliseconds: decode steps
+    # run untimed until the clocks have come back
+    e2e_warmup = warmup + SETTLE
+    prompt_len = args.context - n_e2e - e2e_warmup - 16
+    sp = SamplingParams(temperature=0.0, max_tokens=n_e2e + e2e_warmup + 64, ignore_eos=True)
     for _ in range(B):
         engine.add_request(rng.integers(0, V, size=prompt_len).tolist(), sp)
     while any(engine.scheduler.output(i) == [] for i in list(engine._live)):   # prompts, first tokens
         engine.step()
-    for _ in range(warmup):
+    for _ in range(e2e_warmup):
         engine.step()
     # The clock runs from one step's tokens reaching the host to those of the n-th step after it.  The
     # engine queues the next step before it waits for the current one, so the device is never drained
@@ -283,7 +288,7 @@ def main() -> int:
     if not args.no_points:
         for b in (1, 64):
             k = min(steps, 32)
-            sl = fill(b, args.context - k - warmup - 2)
+            sl = fill(b, args.context - k - warmup - SETTLE - 2)
             m, _, _ = decode_device(sl, k, warmup)
             points[f"decode_b{b}"] = round(b / (m / 1e3), 1)
             close(sl)
@@ -298,7 +303,7 @@ def main() -> int:
                    "hidden": H, "heads": nh, "kv_heads": nkv, "head_dim": d, "intermediate": I, "vocab": V,
                    "global_batch": B, "seq_len": args.context, "page_size": PAGE, "parallelism": "1 GPU",
                    "cuda_graph": use_graph, "l2": "inputs larger than L2 (weights read every step)",
-                   "peaks": pk["source"], "load_s": round(load_s, 1)},
+                   "peaks": pk["source"], "load_s": round(load_s, 1), "settle_steps": SETTLE},
         "clocks": ck, "e2e": e2e, "gpu_launches": int(launches), "prefill": prefill, "roofline": roofline, "points": points,
     }
     print(json.dumps(out))
