@@ -43,15 +43,19 @@ def test_portions_of_six_and_temperature_sampling_equal_plain(model_folders):
     assert eng.stats["steps"] > 10 + 40 // 6
 
 
-@pytest.mark.parametrize("name", ["A", "C"])
-def test_bfloat16_greedy_follows_the_plain_logits(name, model_folders):
+@pytest.mark.parametrize("graphs", [False, True], ids=["launched", "cuda_graph"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_bfloat16_greedy_follows_the_plain_logits(name, graphs, model_folders):
     """bfloat16 may flip a near-tie, so each generated token is checked against the plain logits
-    of the sequence the engine actually produced: it must be the best token up to the drift."""
+    of the sequence the engine actually produced: it must be the best token up to the drift.
+    Decode steps launched kernel by kernel, and replayed from CUDA graphs."""
     from xinfer_b200 import SamplingParams
     folder = model_folders(name, torch.bfloat16)
     cfg, w = plain.load_folder(folder)
     prompts = prompts_for(name, [3, 30, 61])
-    outs = engine(folder, "bf16", name).generate_sync(SamplingParams(max_tokens=40, ignore_eos=True), prompts)
+    eng = engine(folder, "bf16", name, disable_cuda_graph=not graphs)
+    outs = eng.generate_sync(SamplingParams(max_tokens=40, ignore_eos=True), prompts)
+    assert eng.runner.last_used_graph == graphs
     for p, o in zip(prompts, outs):
         seq = p + o.decode_output
         ref = plain.forward(cfg, w, seq)
