@@ -3,7 +3,9 @@ import pytest
 import torch
 
 import plain_qwen3 as plain
-from helpers import PAGE_SIZE, prompts_for
+from helpers import PAGE_SIZE, TINY, prompts_for
+
+TINY_A = TINY["A"][0]
 
 pytestmark = pytest.mark.gpu
 
@@ -204,3 +206,28 @@ def test_cache_sized_from_free_memory_and_the_command_line(model_folders, tmp_pa
                    "--kv-fraction", "0.01", "--max-model-len", "200"])
     out = capsys.readouterr().out
     assert rc == 0 and ",".join(map(str, want)) in out and "Prompt tokens: 9" in out
+
+
+def test_graphs_follow_the_context_past_a_table_width(tmp_path):
+    """Decode graphs are captured per block-table width (64 pages, then 128, ...): a request decodes
+    across the first width while the next step is always queued ahead; every token must still be
+    the plain implementation's best token up to the bfloat16 drift."""
+    from helpers import sharpen
+    from xinfer_b200 import SamplingParams
+    from xinfer_b200.weights import write_random_model
+    cfg = dict(TINY_A, max_position_embeddings=2048)
+    folder = write_random_model(str(tmp_path / "m"), cfg, 4, dtype=torch.bfloat16, override=sharpen)
+    cfg, w = plain.load_folder(folder)
+    prompts = prompts_for("A", [9, 300])
+    eng = engine(folder, "bf16", "A", block_size=8, num_blocks=200, disable_cuda_graph=False, max_model_len=1200)
+    outs = eng.generate_sync(SamplingParams(max_tokens=560, ignore_eos=True), prompts)   # 569 and 860 tokens: past 64 pages of 8
+    assert len(eng.runner._graphs) >= 2 and eng.stats["steps_decided_ahead"] > 500
+    for p, o in zip(prompts, outs):
+        assert o.decoded_length == 560
+        seq = p + o.decode_output
+        ref = plain.forward(cfg, w, seq)
+        drift = 3.0 * (plain.forward(cfg, w, seq, round_to=torch.bfloat16) - ref).abs().max().item()
+        for i, tok in enumerate(o.decode_output):
+            row = ref[len(p) + i - 1]
+            assert row[tok] >= row.max() - 2 * drift, (i, tok)
+    eng.runner.cache.check_consistent()
