@@ -36,11 +36,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* er
     const long long t0 = clock64();
     for (;;) {
         uint32_t ok;
+        // the hint lets the hardware park the thread for up to that many nanoseconds (it is woken when the
+        // phase completes): a waiting role does not take issue slots from the warps that compute
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+            : "=r"(ok) : "r"(bar), "r"(parity), "r"(20000u) : "memory");
         if (ok) return true;
         if (clock64() - t0 > WAIT_CYCLES) break;
     }
