@@ -19,6 +19,7 @@ from .parts import attention_backend
 
 def _graph_time_us(run, per: int, repeats: int = 8) -> float:
     """Median time of one of the ``per`` launches that ``run`` makes, replayed from a CUDA graph."""
+    torch.cuda.synchronize()   # what the caller prepared on the current stream is done
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
         run()
@@ -77,6 +78,7 @@ def decode_attention(cases: Sequence = ((1, 4096), (8, 4096), (64, 4096), (8, 32
                 # as in a step: the work is planned once, before the first kernel, for all layers
                 ctx.scratch.clear()
                 attention_backend.prepare_step(ctx, torch.bfloat16, heads, kv_heads, head_dim, page_size, None, stride)
+                torch.cuda.synchronize()   # the launches below run on a stream of their own
                 rec[name] = round(_graph_time_us(lambda: [attention_backend.attend(o, q, c, ctx, table, stride, None, head_dim ** -0.5)
                                                           for c in caches], layers), 1)
             finally:
