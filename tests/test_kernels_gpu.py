@@ -56,7 +56,8 @@ def test_embedding(dtype, T, H, V):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("rows,dim,eps,offset", [(1, 16, 1e-6, 0.0), (33, 100, 1e-5, 0.0), (7, 5120, 3e-6, 1.0), (5, 8200, 1e-6, 0.0)])
+@pytest.mark.parametrize("rows,dim,eps,offset", [(1, 16, 1e-6, 0.0), (33, 100, 1e-5, 0.0), (7, 5120, 3e-6, 1.0), (5, 8200, 1e-6, 0.0),
+                                                 (3, 20000, 1e-6, 0.0), (700, 4096, 1e-6, 0.0)])
 def test_rmsnorm_plain_fused_and_gathered(dtype, rows, dim, eps, offset, both_families):
     from xinfer_b200 import kernels
     x, br = rnd(rows, dim, dtype=dtype, seed=1), rnd(rows, dim, dtype=dtype, seed=2)
@@ -106,7 +107,7 @@ def test_gemm_plain_is_true_float32_and_row_independent(M, N, K):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T,I", [(1, 8), (13, 48), (37, 11008 // 16 + 3), (5, 12288)])
+@pytest.mark.parametrize("T,I", [(1, 8), (13, 48), (37, 11008 // 16 + 3), (5, 12288), (600, 8200)])
 def test_swiglu(dtype, T, I, both_families):
     from xinfer_b200 import kernels
     gu = rnd(T, 2 * I, dtype=dtype, scale=3.0)

@@ -420,6 +420,56 @@ def gemm_skinny_tc(out, x, w, err, splits: int = 0, next_w: Optional[torch.Tenso
     return True
 
 
+def gemm_skinny_swiglu(out, x, w_gate_up, err, splits: int = 0) -> bool:
+    """out[M, I] = silu(x . Wg^T) * (x . Wu^T) for w_gate_up = [Wg; Wu] of [2 I, K]: the packed gate/up
+    product of few tokens and the SiLU gate in one kernel, with the values that ``gemm_skinny_tc``
+    followed by ``swiglu`` gives.  Returns False, having done nothing, for shapes it does not take."""
+    M, K = x.shape
+    I = w_gate_up.shape[0] // 2
+    _need(x, "x", torch.bfloat16, (M, K))
+    _need(w_gate_up, "w_gate_up", torch.bfloat16, (2 * I, K))
+    _need(out, "out", torch.bfloat16, (M, I))
+    rc = kernels_lib().xb_gemm_skinny_swiglu(out.data_ptr(), x.data_ptr(), w_gate_up.data_ptr(), M, I, K, int(splits),
+                                             err.data_ptr(), _stream())
+    if rc == ERR_NOT_SUPPORTED:
+        return False
+    _ok(rc, "gemm_skinny_swiglu")
+    return True
+
+
+def gemm_skinny_qkv(q_out, k_cache, v_cache, x, w_qkv, q_w, k_w, cos_t, sin_t, positions, req_of_token, block_table,
+                    table_stride, nh, nkv, d, rot, interleaved, eps, write_kv, err, splits: int = 0) -> bool:
+    """The packed q/k/v product of few tokens finished per head in the same kernel: what
+    ``gemm_skinny_tc`` followed by ``qk_norm_rope_write`` gives (q to ``q_out``, k and v into their
+    pages).  Heads must be 128 wide; returns False, having done nothing, for what it does not take."""
+    M, K = x.shape
+    _need(x, "x", torch.bfloat16, (M, K))
+    _need(w_qkv, "w_qkv", torch.bfloat16, ((nh + 2 * nkv) * d, K))
+    _need(q_out, "q_out", torch.bfloat16, (M, nh, d))
+    if write_kv:
+        _need(k_cache, "k_cache", torch.bfloat16, (None, nkv, None, d))
+        _need(v_cache, "v_cache", torch.bfloat16, tuple(k_cache.shape))
+    num_pages = k_cache.shape[0] if k_cache is not None else 0
+    page_size = k_cache.shape[2] if k_cache is not None else 1
+    for name, w_ in (("q_norm", q_w), ("k_norm", k_w)):
+        if w_ is not None:
+            _need(w_, name, torch.float32, (d,))
+    max_pos = 0
+    if cos_t is not None:
+        _need(cos_t, "cos", torch.float32, (None, rot // 2))
+        _need(sin_t, "sin", torch.float32, tuple(cos_t.shape))
+        max_pos = cos_t.shape[0]
+    rc = kernels_lib().xb_gemm_skinny_qkv(
+        q_out.data_ptr(), _ptr(k_cache), _ptr(v_cache), x.data_ptr(), w_qkv.data_ptr(), M, K, int(splits), _ptr(q_w), _ptr(k_w),
+        _ptr(cos_t), _ptr(sin_t), positions.data_ptr(), req_of_token.data_ptr(), block_table.data_ptr(), int(table_stride),
+        nh, nkv, d, rot, int(bool(interleaved)), page_size, num_pages, max_pos, float(eps), int(bool(write_kv)),
+        err.data_ptr(), _stream())
+    if rc == ERR_NOT_SUPPORTED:
+        return False
+    _ok(rc, "gemm_skinny_qkv")
+    return True
+
+
 def attn_prefill_tc(out, q, k_cache, v_cache, q_start, start_pos, num_entries, block_table, table_stride,
                     window, scale, dec_max, tiles, err) -> bool:
     """Prefill attention on tcgen05 (TMA-fed, accumulators in tensor memory): portions of more than

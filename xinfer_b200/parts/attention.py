@@ -17,6 +17,7 @@ from .. import kernels
 from ..config.plan import AttentionSpec
 from ..weights.loader import WeightSpec
 from .base import (LayerCache, Mixer, PagedCacheNeed, StepContext, build_part, register_mixer)
+from . import gemm_backend
 from .linear import linear
 
 
@@ -71,20 +72,22 @@ class Attention(Mixer):
         T = x.shape[0]
         nh, nkv, d = s.num_heads, s.num_kv_heads, s.head_dim
         ws = ctx.workspace
-        qkv = ws.get("attn.qkv", (T, (nh + 2 * nkv) * d), self.dtype)
-        linear(qkv, x, self.w_qkv, ctx.err)
         rot = self.position.rotary() if self.position is not None else None
-        if self.position is not None and rot is None:
-            q_view = qkv[:, : nh * d].view(T, nh, d)
-            k_view = qkv[:, nh * d:(nh + nkv) * d].view(T, nkv, d)
-            self.position.apply(q_view, k_view, ctx)
         q = ws.get("attn.q", (T, nh, d), self.dtype)
         table, stride = ctx.tables[cache.group], ctx.strides[cache.group]
-        kernels.qk_norm_rope_write(
-            q, cache.k, cache.v, qkv, self.q_norm, self.k_norm,
-            rot.cos if rot else None, rot.sin if rot else None, ctx.positions, ctx.req_of_token,
-            table, stride, nh, nkv, d, rot.rotary_dim if rot else 0, rot.interleaved if rot else False,
-            s.qk_norm_eps, writes_cache, ctx.err)
+        head_args = (self.q_norm, self.k_norm, rot.cos if rot else None, rot.sin if rot else None, ctx.positions,
+                     ctx.req_of_token, table, stride, nh, nkv, d, rot.rotary_dim if rot else 0,
+                     rot.interleaved if rot else False, s.qk_norm_eps, writes_cache, ctx.err)
+        fused = (self.position is None or rot is not None) and gemm_backend.try_fused_qkv(
+            q, cache.k, cache.v, x, self.w_qkv, *head_args)
+        if not fused:
+            qkv = ws.get("attn.qkv", (T, (nh + 2 * nkv) * d), self.dtype)
+            linear(qkv, x, self.w_qkv, ctx.err)
+            if self.position is not None and rot is None:
+                q_view = qkv[:, : nh * d].view(T, nh, d)
+                k_view = qkv[:, nh * d:(nh + nkv) * d].view(T, nkv, d)
+                self.position.apply(q_view, k_view, ctx)
+            kernels.qk_norm_rope_write(q, cache.k, cache.v, qkv, *head_args)
         o = ws.get("attn.o", (T, nh, d), self.dtype)
         from . import attention_backend
         attention_backend.attend(o, q, cache, ctx, table, stride, s.window, s.scale)

@@ -10,6 +10,7 @@ from .. import kernels
 from ..config.plan import FeedForwardSpec
 from ..weights.loader import WeightSpec
 from .base import FeedForward, StepContext, register_feed_forward
+from . import gemm_backend
 from .linear import linear
 
 
@@ -45,10 +46,11 @@ class SwiGLU(FeedForward):
         s = self.spec
         T = x.shape[0]
         ws = ctx.workspace
-        gu = ws.get("ffn.gate_up", (T, 2 * s.intermediate), self.dtype)
-        linear(gu, x, self.w_gate_up, ctx.err)
         act = ws.get("ffn.act", (T, s.intermediate), self.dtype)
-        kernels.swiglu(act, gu)
+        if not gemm_backend.try_fused_gate(act, x, self.w_gate_up, ctx.err):
+            gu = ws.get("ffn.gate_up", (T, 2 * s.intermediate), self.dtype)
+            linear(gu, x, self.w_gate_up, ctx.err)
+            kernels.swiglu(act, gu)
         out = ws.get("ffn.out", (T, s.hidden), self.dtype)
         linear(out, act, self.w_down, ctx.err)
         return out
