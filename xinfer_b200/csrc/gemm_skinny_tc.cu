@@ -75,7 +75,7 @@ template <typename TO, int EPI>
 __global__ void __launch_bounds__(128)
 gemm_skinny_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                       TO* __restrict__ out, int M, int N, int K, int mp, int k_per_split, int stages,
-                      const unsigned char* __restrict__ pf_ptr, unsigned long long pf_bytes, const EpiArgs epi, int* err) {
+                      const EpiArgs epi, int* err) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long bars[2 * 16 + 1];
     __shared__ uint32_t s_tmem;
@@ -137,20 +137,6 @@ gemm_skinny_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             mbar_expect_tx(full0 + 8 * s, stage_bytes);
             load_w(dst, k_begin + it * TILE_K, full0 + 8 * s);
             tma_load_2d(dst + w_bytes, &map_x, k_begin + it * TILE_K, 0, full0 + 8 * s);
-        }
-        // Every load of this CTA is on its way: ask the L2 for this CTA's share of what the next
-        // product will stream first, so that the memory keeps working while this kernel drains and
-        // the next one starts up.
-        if (pf_bytes) {
-            const unsigned long long ctas = (unsigned long long)gridDim.x * gridDim.y;
-            const unsigned long long id = (unsigned long long)blockIdx.y * gridDim.x + blockIdx.x;
-            unsigned long long share = ((pf_bytes / ctas) + 15ull) & ~15ull;
-            unsigned long long at = id * share;
-            const unsigned long long end = at + share < pf_bytes ? at + share : (pf_bytes & ~15ull);
-            for (; at < end; at += 16384ull) {
-                const unsigned int n = (unsigned int)(end - at < 16384ull ? end - at : 16384ull);
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pf_ptr + at), "r"(n) : "memory");
-            }
         }
     } else if (threadIdx.x == 32) {
         // ---- MMA issuer -------------------------------------------------------------------------------
@@ -259,8 +245,7 @@ gemm_skinny_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 // ---- host side: the launch ------------------------------------------------------------------------------
 template <typename TO, int EPI>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int M, int N, int K, int mp, int tiles, int splits,
-           int k_per_split, int stages, size_t smem, const void* pf_ptr, unsigned long long pf_bytes, const EpiArgs& epi,
-           int* err, cudaStream_t stream) {
+           int k_per_split, int stages, size_t smem, const EpiArgs& epi, int* err, cudaStream_t stream) {
     cudaFuncSetAttribute(gemm_skinny_tc_kernel<TO, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(tiles, splits, 1);
@@ -277,7 +262,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int M, int N
     cfg.attrs = attr;
     cfg.numAttrs = xb_pdl_enabled() ? 2 : 1;
     const cudaError_t rc = cudaLaunchKernelEx(&cfg, gemm_skinny_tc_kernel<TO, EPI>, mw, mx, (TO*)out, M, N, K, mp, k_per_split, stages,
-                                              (const unsigned char*)pf_ptr, pf_bytes, epi, err);
+                                              epi, err);
     return rc != cudaSuccess ? (int)rc : xb_launch_status();
 }
 
@@ -321,11 +306,9 @@ bool shape_of(Shape* sh, int M, int tiles, int K, int splits, bool finished) {
 
 // out[M, N] (bfloat16 when out_f32 == 0, else float32) = x[M, K] . w[N, K]^T for M <= 256.
 // K must be a multiple of 8 (rows 16-byte aligned); `splits` in 1..8 CTAs share K through a
-// cluster (0: chosen here).  `next_w` / `next_bytes`: the first bytes (16-byte aligned) that the
-// product after this one will read, requested into the L2 while this one drains (0: nothing).
-// Returns cudaErrorNotSupported for shapes it does not take.
+// cluster (0: chosen here).  Returns cudaErrorNotSupported for shapes it does not take.
 XB_EXPORT int xb_gemm_skinny_tc(void* out, int out_f32, const void* x, const void* w, int M, int N, int K, int splits,
-                                const void* next_w, unsigned long long next_bytes, int* err, cudaStream_t stream) {
+                                int* err, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return (int)cudaErrorNotSupported;
     const int tiles = (N + TILE_N - 1) / TILE_N;
@@ -333,13 +316,12 @@ XB_EXPORT int xb_gemm_skinny_tc(void* out, int out_f32, const void* x, const voi
     if (!shape_of(&sh, M, tiles, K, splits, false)) return (int)cudaErrorNotSupported;
     CUtensorMap mw, mx;
     if (!tensor_map_2d(&mw, w, N, K, TILE_N) || !tensor_map_2d(&mx, x, M, K, sh.mp)) return (int)cudaErrorNotSupported;
-    if (!next_w || ((uintptr_t)next_w & 15)) next_bytes = 0;
     const EpiArgs none = {};
     if (out_f32)
         return launch<float, EPI_PLAIN>(mw, mx, out, M, N, K, sh.mp, tiles, sh.splits, sh.tiles_per_split * TILE_K, sh.stages, sh.smem,
-                                        next_w, next_bytes, none, err, stream);
+                                        none, err, stream);
     return launch<__nv_bfloat16, EPI_PLAIN>(mw, mx, out, M, N, K, sh.mp, tiles, sh.splits, sh.tiles_per_split * TILE_K, sh.stages,
-                                            sh.smem, next_w, next_bytes, none, err, stream);
+                                            sh.smem, none, err, stream);
 }
 
 // out[M, I] = silu(x . Wg^T) * (x . Wu^T) for w = [Wg; Wu] of [2 I, K] (gate rows first), bfloat16:
@@ -356,7 +338,7 @@ XB_EXPORT int xb_gemm_skinny_swiglu(void* out, const void* x, const void* w, int
     EpiArgs epi = {};
     epi.up_rows = I;
     return launch<__nv_bfloat16, EPI_SWIGLU>(mw, mx, out, M, I, K, sh.mp, tiles, sh.splits, sh.tiles_per_split * TILE_K, sh.stages,
-                                             sh.smem, nullptr, 0, epi, err, stream);
+                                             sh.smem, epi, err, stream);
 }
 
 // The packed q/k/v projection of M tokens, finished per head: q/k RMSNorm, rotary encoding, q to
@@ -381,5 +363,5 @@ XB_EXPORT int xb_gemm_skinny_qkv(
     epi.qk = {(__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, q_w, k_w, cos_t, sin_t, positions,
               req_of_token, block_table, table_stride, nh, nkv, d, rot, interleaved, page_size, num_pages, max_pos, eps, write_kv};
     return launch<__nv_bfloat16, EPI_QK>(mw, mx, nullptr, M, N, K, sh.mp, tiles, sh.splits, sh.tiles_per_split * TILE_K, sh.stages,
-                                         sh.smem, nullptr, 0, epi, err, stream);
+                                         sh.smem, epi, err, stream);
 }

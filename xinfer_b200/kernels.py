@@ -395,13 +395,10 @@ def decode_tc_splits_max(ctas: int, kv_heads: int, bound: int, min_keys: int) ->
 # ---- matrix product for few tokens on tcgen05 tensor cores ---------------------------------------------
 
 
-def gemm_skinny_tc(out, x, w, err, splits: int = 0, next_w: Optional[torch.Tensor] = None,
-                   next_bytes: int = 0) -> bool:
+def gemm_skinny_tc(out, x, w, err, splits: int = 0) -> bool:
     """out[M, N] = x[M, K] . w[N, K]^T for M <= 256 with TMA-fed tcgen05 MMAs (bfloat16 in, float32
-    accumulation; ``out`` bfloat16 or float32).  ``next_w``: the weights that the product after
-    this one streams; their first ``next_bytes`` bytes are requested into the L2 while this kernel
-    drains.  Returns False, having done nothing, for shapes the kernel does not take (K not a
-    multiple of 8, K < 64, M > 256)."""
+    accumulation; ``out`` bfloat16 or float32).  Returns False, having done nothing, for shapes the
+    kernel does not take (K not a multiple of 8, K < 64, M > 256)."""
     M, K = x.shape
     N = w.shape[0]
     _need(x, "x", torch.bfloat16, (M, K))
@@ -409,11 +406,8 @@ def gemm_skinny_tc(out, x, w, err, splits: int = 0, next_w: Optional[torch.Tenso
     _need(out, "out", None, (M, N))
     if out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError(f"out must be bfloat16 or float32, not {out.dtype}")
-    if next_w is not None:
-        next_bytes = min(int(next_bytes), next_w.numel() * next_w.element_size())
     rc = kernels_lib().xb_gemm_skinny_tc(out.data_ptr(), int(out.dtype == torch.float32), x.data_ptr(), w.data_ptr(),
-                                         M, N, K, int(splits), _ptr(next_w), int(next_bytes) if next_w is not None else 0,
-                                         err.data_ptr(), _stream())
+                                         M, N, K, int(splits), err.data_ptr(), _stream())
     if rc == ERR_NOT_SUPPORTED:
         return False
     _ok(rc, "gemm_skinny_tc")
