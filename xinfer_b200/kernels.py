@@ -31,6 +31,26 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
 
 
 def _need(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
+    """The checks every wrapper makes on its tensors; the message is only put together on failure
+    (these run a few thousand times in a step of a small model)."""
+    try:
+        ok = t.is_cuda and t.is_contiguous() and (dtype is None or t.dtype == dtype)
+    except AttributeError:
+        ok = False
+    if ok and shape is not None:
+        ts = t.shape
+        if len(ts) != len(shape):
+            ok = False
+        else:
+            for want, have in zip(shape, ts):
+                if want is not None and want != have:
+                    ok = False
+                    break
+    if not ok:
+        _need_failed(t, name, dtype, shape)
+
+
+def _need_failed(t, name, dtype, shape) -> None:
     if not isinstance(t, torch.Tensor):
         raise KernelError(f"{name}: expected a tensor, got {type(t).__name__}")
     if not t.is_cuda:
@@ -39,12 +59,18 @@ def _need(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
         raise KernelError(f"{name}: tensor must be contiguous (shape {tuple(t.shape)}, strides {t.stride()})")
     if dtype is not None and t.dtype != dtype:
         raise KernelError(f"{name}: expected {dtype}, got {t.dtype}")
-    if shape is not None:
-        if len(shape) != t.dim() or any(s is not None and s != d for s, d in zip(shape, t.shape)):
-            raise KernelError(f"{name}: expected shape {tuple(shape)}, got {tuple(t.shape)}")
+    raise KernelError(f"{name}: expected shape {tuple(shape)}, got {tuple(t.shape)}")
+
+
+try:    # the raw handle of the current stream without building a Stream object for every launch
+    _raw_stream, _device_index = torch._C._cuda_getCurrentRawStream, torch._C._cuda_getDevice
+except AttributeError:  # pragma: no cover - other torch builds
+    _raw_stream = None
 
 
 def _stream() -> int:
+    if _raw_stream is not None:
+        return _raw_stream(_device_index())
     return torch.cuda.current_stream().cuda_stream
 
 

@@ -22,9 +22,14 @@ class Workspace:
     def __init__(self, device):
         self.device = device
         self._bufs: Dict[str, torch.Tensor] = {}
+        self._views: Dict[tuple, torch.Tensor] = {}   # (name, shape, dtype) -> view of the buffer
         self.frozen = False
 
     def get(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        key = (name, tuple(shape), dtype)
+        view = self._views.get(key)
+        if view is not None:
+            return view
         n = 1
         for s in shape:
             n *= int(s)
@@ -36,7 +41,12 @@ class Workspace:
             # zero-filled: rows that padding tokens never write must stay finite
             buf = torch.zeros(max(cap, 1), dtype=dtype, device=self.device)
             self._bufs[name] = buf
-        return buf[:n].view(*shape)
+            self._views = {k: v for k, v in self._views.items() if k[0] != name}   # they point into the old buffer
+        if len(self._views) > 512:
+            self._views.clear()
+        view = buf[:n].view(*shape)
+        self._views[key] = view
+        return view
 
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._bufs.values())
