@@ -462,3 +462,18 @@ def test_decode_split_choice():
     assert decode_split(4096, 8)[1] >= 16              # few pairs: cut finely
     assert decode_split(4096, 64)[1] * 64 <= 444       # one wave holds every CTA
     assert decode_split(64, 5000) == (64, 1)
+
+
+@pytest.mark.parametrize("shape", [(1, 7), (3, 1000), (64, 1016), (5, 151936), (2, 9)])
+def test_widen_bf16_is_exact(shape):
+    from xinfer_b200 import kernels
+    x = rnd(*shape, dtype=torch.bfloat16, seed=31, scale=30.0)
+    out = torch.full(shape, float("nan"), device=dev())
+    kernels.widen_bf16(out, x)
+    assert torch.equal(out, x.float())
+    # a view that starts off a 16-byte boundary takes the element-wise kernel
+    flat = rnd(4099, dtype=torch.bfloat16, seed=32)
+    part = flat[3:]
+    o2 = torch.empty(4096, device=dev())
+    kernels.widen_bf16(o2, part)
+    assert torch.equal(o2, part.float())
