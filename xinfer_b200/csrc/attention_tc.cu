@@ -366,6 +366,362 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 }
 
 // ------------------------------------------------------------------------------------------------
+// prefill, two heads per CTA
+// ------------------------------------------------------------------------------------------------
+// The kernel above reads every key/value tile once per 128 queries and head; with long contexts that
+// traffic (a tile per 4 MFLOP) is what the L2 can deliver, and its two-stage rings are shorter than
+// a tile's way from memory.  Here a CTA owns the same 128 queries of TWO query heads that share
+// their key/value head, so a tile is loaded once for both and the rings are four stages deep:
+//   warps 0..3: softmax of head A (one row per thread), warps 4..7: softmax of head B,
+//   warp 8: TMA producer of Q (both heads) and of the key pages, warp 10: of the value pages (one lane
+//   per page box; the page ids of the next tile are fetched while this one is issued),
+//   warp 9: MMA issuer: S_A, S_B of the next tile, then O_A += P_A V and O_B += P_B V of this one.
+// Tensor memory (all 512 columns): S_A[0], S_A[1], S_B[0], S_B[1] at 0, 64, 128, 192; O_A at 256, O_B at 384.
+// One CTA per SM.  Needs an even number of query heads per key/value head.
+constexpr int PF2_STAGES = 4;
+constexpr int PF2_THREADS = 352;
+
+template <int DP>
+__global__ void __launch_bounds__(PF2_THREADS)
+attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                        const int* __restrict__ q_start, const int* __restrict__ start_pos, int num_entries,
+                        const int* __restrict__ block_table, int table_stride, int nh, int nkv, int d, int ps,
+                        int ps_shift, int num_pages, int window, float scale_log2, int dec_max, int* err) {
+    constexpr int HALVES = DP / 64, NS = PF2_STAGES;
+    constexpr uint32_t Q_ONE = HALVES * QT * 128, Q_BYTES = 2 * Q_ONE, P_BYTES = 0;
+    constexpr uint32_t KV_HALF = KT * 128, KV_BYTES = HALVES * KV_HALF, STAGE_BYTES = 2 * KV_BYTES;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    const uint32_t base = smem_u32(smem_raw);
+    const uint32_t q_sm = base, kv_sm = base + Q_BYTES;
+    // barriers, 8 bytes each: k_full[4] k_empty[4] v_full[4] v_empty[4] s_ready[head][2] s_free[head][2]
+    // p_ready[head] pv_done[head] q_full bar_o; then four words
+    constexpr uint32_t BAR_OFF = Q_BYTES + P_BYTES + NS * STAGE_BYTES;
+    const uint32_t bars = base + BAR_OFF;
+    const uint32_t k_full0 = bars, k_empty0 = bars + 32, v_full0 = bars + 64, v_empty0 = bars + 96;
+    const uint32_t s_ready0 = bars + 128, p_ready0 = bars + 192, pv_done0 = bars + 208;
+    const uint32_t q_full = bars + 224, bar_o = bars + 232;
+    volatile uint32_t* words = reinterpret_cast<volatile uint32_t*>(smem_raw + BAR_OFF + 240);  // tmem, entry, tile, dead
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = nh / nkv;
+    const int h0 = 2 * (int)blockIdx.x, g = h0 / G;   // heads vary fastest: every pair's longest tiles start first
+    pdl_launch_dependents();
+    pdl_wait();
+
+    if (threadIdx.x == 0) {
+        if (base & 1023u) atomicOr(err, XB_ERR_WAIT);  // the swizzle needs a 1024-byte aligned window
+        int acc = 0, found = -1, tile = 0;
+        for (int b = 0; b < num_entries; ++b) {
+            const int n = q_start[b + 1] - q_start[b];
+            if (n > dec_max) {
+                const int nt = (n + QT - 1) / QT;
+                if ((int)blockIdx.y < acc + nt) {
+                    found = b;
+                    tile = nt - 1 - ((int)blockIdx.y - acc);  // a portion's last (longest) tiles first
+                    break;
+                }
+                acc += nt;
+            }
+        }
+        if (*reinterpret_cast<volatile int*>(err) & XB_ERR_WAIT) found = -1;  // an earlier CTA gave up: do not pile on
+        words[1] = (uint32_t)found;
+        words[2] = (uint32_t)tile;
+        words[3] = 0;
+        for (int i = 0; i < 4 * NS; ++i) mbar_init(bars + 8 * i, 1);        // k_full, k_empty, v_full, v_empty
+        for (int i = 0; i < 4; ++i) mbar_init(s_ready0 + 8 * i, 1);
+        for (int i = 0; i < 2; ++i) mbar_init(p_ready0 + 8 * i, 128);
+        for (int i = 0; i < 2; ++i) mbar_init(pv_done0 + 8 * i, 1);
+        mbar_init(q_full, 1);
+        mbar_init(bar_o, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const int b = (int)words[1];
+    if (b < 0 || (base & 1023u)) return;
+    constexpr uint32_t TMEM_COLS = 512;
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t*>(&words[0]))), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = words[0];
+
+    const int n = q_start[b + 1] - q_start[b];
+    const int row0 = (int)words[2] * QT;
+    const int rows = min(QT, n - row0);
+    const int t0 = q_start[b] + row0;
+    const int p0 = start_pos[b] + row0;
+    const int last_key = p0 + rows - 1;
+    const int first_key = window > 0 ? max(0, p0 - window + 1) : 0;
+    const int* table = block_table + (size_t)b * table_stride;
+    const int kt_first = first_key / KT, kt_last = last_key / KT;
+    const int iters = kt_last - kt_first + 1;
+    const int box_rows = ps < KT ? ps : KT;
+
+    if (warp == 8 || warp == 10) {
+        // ---- producers ------------------------------------------------------------------------------------
+        const bool is_v = warp == 10;
+        const uint32_t full0 = is_v ? v_full0 : k_full0, empty0 = is_v ? v_empty0 : k_empty0;
+        const CUtensorMap* map = is_v ? &map_v : &map_k;
+        if (!is_v && lane == 0) {
+            mbar_expect_tx(q_full, Q_BYTES);
+#pragma unroll
+            for (int hd = 0; hd < 2; ++hd)
+#pragma unroll
+                for (int hf = 0; hf < HALVES; ++hf)
+                    tma_load_3d(q_sm + hd * Q_ONE + hf * QT * 128, &map_q, hf * 64, h0 + hd, t0, q_full);
+        }
+        const int boxes = (KT / box_rows) * HALVES;     // at most 16: one lane each
+        const int bi = lane / HALVES, hf = lane % HALVES;
+        auto page_of = [&](int it) -> int {             // the page of this lane's box in tile `it`, -1: nothing to load
+            const int j = (kt_first + it) * KT + bi * box_rows;
+            if (it >= iters || lane >= boxes || j > last_key || j + box_rows - 1 < first_key) return -1;
+            const int page = table[j >> ps_shift];
+            if (page < 0 || page >= num_pages) {
+                atomicOr(err, XB_ERR_BAD_PAGE);
+                return -1;
+            }
+            return page;
+        };
+        int page_next = page_of(0);
+        for (int it = 0; it < iters; ++it) {
+            const int s = it % NS;
+            const int page = page_next;
+            if (it >= NS && !__all_sync(0xffffffffu, mbar_wait(empty0 + 8 * s, ((it / NS) - 1) & 1, err))) {
+                words[3] = 1;
+                break;
+            }
+            const uint32_t nb = __popc(__ballot_sync(0xffffffffu, page >= 0));
+            if (lane == 0) mbar_expect_tx(full0 + 8 * s, nb * box_rows * 128);
+            __syncwarp();
+            if (page >= 0) {
+                const int j = (kt_first + it) * KT + bi * box_rows;
+                const uint32_t dst = kv_sm + s * STAGE_BYTES + (is_v ? KV_BYTES : 0u) + hf * KV_HALF + bi * box_rows * 128;
+                tma_load_2d(dst, map, hf * 64, (page * nkv + g) * ps + (j & (ps - 1)), full0 + 8 * s);
+            }
+            page_next = page_of(it + 1);
+        }
+    } else if (warp == 9) {
+        // ---- MMA issuer: S of tile 0, then for every tile S(next) of both heads before P V (this) of both ----
+        if (lane == 0) {
+            const uint32_t idesc_s = umma_idesc(KT, 0), idesc_o = umma_idesc(DP, 1);
+            const uint64_t dq0 = umma_desc(q_sm, 16, 1024), dk0 = umma_desc(kv_sm, 16, 1024);
+            const uint64_t dv0 = umma_desc(kv_sm + KV_BYTES, KV_HALF, 1024);
+            auto issue_qk = [&](int it) -> bool {   // S_hd[it & 1] = Q_hd K^T of tile `it`, hd = 0, 1
+                const int sb = it & 1, s = it % NS;
+                if (!mbar_wait(k_full0 + 8 * s, (it / NS) & 1, err)) return false;
+                const uint64_t dk = dk0 + (uint64_t)((s * STAGE_BYTES) >> 4);
+#pragma unroll
+                for (int hd = 0; hd < 2; ++hd) {
+                    // S[sb] of this head held the scores and then P of tile it - 2: its P V was issued before this and
+                    // the tensor pipe runs a thread's MMAs in the order of issue
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t dq = dq0 + (uint64_t)((hd * Q_ONE) >> 4);
+#pragma unroll
+                    for (int kk = 0; kk < DP / 16; ++kk) {
+                        const uint32_t off = (kk >> 2), inner = (kk & 3) * 32;
+                        umma_bf16(tmem + (uint32_t)(hd * 128 + sb * 64), dq + (uint64_t)((off * QT * 128 + inner) >> 4),
+                                  dk + (uint64_t)((off * KV_HALF + inner) >> 4), idesc_s, kk ? 1u : 0u);
+                    }
+                    umma_commit(s_ready0 + 8 * (2 * hd + sb));
+                }
+                umma_commit(k_empty0 + 8 * s);   // the key stage is free once both products have completed
+                return true;
+            };
+            bool ok = mbar_wait(q_full, 0, err) && issue_qk(0);
+            for (int it = 0; it < iters && ok; ++it) {
+                const int s = it % NS;
+                if (it + 1 < iters) ok = issue_qk(it + 1);
+                ok = ok && mbar_wait(v_full0 + 8 * s, (it / NS) & 1, err);
+                const uint64_t dv = dv0 + (uint64_t)((s * STAGE_BYTES) >> 4);
+#pragma unroll
+                for (int hd = 0; hd < 2; ++hd) {
+                    ok = ok && mbar_wait(p_ready0 + 8 * hd, it & 1, err);   // P written, V rows zeroed, O rescaled
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    // O += P V : A = P [128 x 64 keys] in tensor memory (over the scores it came from), B = V [64 keys x DP]
+                    // MN-major (halves 64 columns apart)
+                    const uint32_t tp = tmem + (uint32_t)(hd * 128 + (it & 1) * 64);
+#pragma unroll
+                    for (int kk = 0; kk < KT / 16; ++kk)
+                        umma_bf16_ta(tmem + (uint32_t)(256 + hd * 128), tp + (uint32_t)(kk * 8), dv + (uint64_t)((kk * 2048) >> 4),
+                                     idesc_o, (it | kk) ? 1u : 0u);
+                    umma_commit(pv_done0 + 8 * hd);      // P and O of this head are free again once these have completed
+                }
+                if (!ok) break;
+                umma_commit(v_empty0 + 8 * s);           // and so is the value stage
+                if (it + 1 == iters) umma_commit(bar_o);
+            }
+            if (!ok) words[3] = 1;
+        }
+    } else if (warp < 8) {
+        // ---- softmax: one query row per thread, warps 0..3 for the first head, 4..7 for the second -------------
+        const int hd = warp >> 2, r = (int)threadIdx.x & 127;
+        const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t tmem_s = tmem + (uint32_t)(hd * 128), tmem_o = tmem + (uint32_t)(256 + hd * 128);
+        const uint32_t my_s_ready = s_ready0 + 16 * hd;
+        const uint32_t my_p_ready = p_ready0 + 8 * hd, my_pv_done = pv_done0 + 8 * hd;
+        const int my_pos = p0 + r;
+        float m_ref = -INFINITY, l = 0.f;
+        bool alive = true;
+        for (int it = 0; it < iters; ++it) {
+            const int sb = it & 1, st = it % NS, key0 = (kt_first + it) * KT;
+            // every wait's verdict is made warp-wide: tcgen05.ld / .st below need the whole warp
+            if (!__all_sync(0xffffffffu, mbar_wait(my_s_ready + 8 * sb, (it >> 1) & 1, err))) {
+                alive = false;
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float sc[64];
+            {
+                uint32_t ra[32], rb[32];
+                tmem_ld32_nowait(tmem_s + sb * 64 + lane_addr, ra);
+                tmem_ld32_nowait(tmem_s + sb * 64 + lane_addr + 32, rb);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    sc[i] = __uint_as_float(ra[i]);
+                    sc[32 + i] = __uint_as_float(rb[i]);
+                }
+            }
+            const bool edge = key0 + KT - 1 > p0 || key0 + KT - 1 > last_key || key0 < first_key ||
+                              (window > 0 && key0 < p0 + QT - 1 - window + 1);
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (edge) {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) {
+                    const int j = key0 + i;
+                    const bool ok = j <= my_pos && j <= last_key && (window <= 0 || j > my_pos - window);
+                    sc[i] = ok ? sc[i] : -INFINITY;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 64; i += 8) {
+                mx4[0] = max3(mx4[0], sc[i], sc[i + 1]);
+                mx4[1] = max3(mx4[1], sc[i + 2], sc[i + 3]);
+                mx4[2] = max3(mx4[2], sc[i + 4], sc[i + 5]);
+                mx4[3] = max3(mx4[3], sc[i + 6], sc[i + 7]);
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+            // move the reference maximum only when the row's maximum outgrows it by more than 2^8
+            float corr = 1.f;
+            int moved = 0;
+            if (mx > m_ref + RESCALE_STEP) {
+                corr = m_ref == -INFINITY ? 0.f : ex2(m_ref - mx);
+                m_ref = mx;
+                moved = it > 0;
+            }
+            const float m_neg = m_ref == -INFINITY ? 0.f : -m_ref;
+            const f32x2 scale2 = pack2(scale_log2, scale_log2), mneg2 = pack2(m_neg, m_neg);
+            f32x2 sum_a = pack2(0.f, 0.f), sum_b = pack2(0.f, 0.f);
+            uint32_t pk[32];   // the row of P: two bfloat16 per word, in the order of the keys
+#pragma unroll
+            for (int c8 = 0; c8 < 8; ++c8) {
+                float x[8], e[8];
+#pragma unroll
+                for (int i = 0; i < 8; i += 2)
+                    unpack2(fma2(pack2(sc[c8 * 8 + i], sc[c8 * 8 + i + 1]), scale2, mneg2), x[i], x[i + 1]);
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if ((i & 3) != 3) e[i] = ex2(x[i]);
+                ex2_poly2(x[3], x[7], e[3], e[7]);
+                sum_a = add2(sum_a, add2(pack2(e[0], e[1]), pack2(e[2], e[3])));
+                sum_b = add2(sum_b, add2(pack2(e[4], e[5]), pack2(e[6], e[7])));
+                pk[c8 * 4] = pack_bf16(e[0], e[1]);
+                pk[c8 * 4 + 1] = pack_bf16(e[2], e[3]);
+                pk[c8 * 4 + 2] = pack_bf16(e[4], e[5]);
+                pk[c8 * 4 + 3] = pack_bf16(e[6], e[7]);
+            }
+            float s0, s1, s2, s3;
+            unpack2(sum_a, s0, s1);
+            unpack2(sum_b, s2, s3);
+            l = l * corr + ((s0 + s1) + (s2 + s3));
+            // P goes where the scores were: they are in registers, and the P V that read these columns two tiles
+            // ago ran before the Q K^T that wrote them
+            tmem_st32_u(tmem_s + sb * 64 + lane_addr, pk);
+            // value rows outside the visible keys become zeros (only tiles at the ends of the range): the first
+            // head's threads do it; the second head's P V is issued after the first's, so it sees them too
+            if (hd == 0 && (key0 < first_key || key0 + KT - 1 > last_key)) {
+                if (r < KT) {
+                    mbar_wait(v_full0 + 8 * st, (it / NS) & 1, err);   // orders these writes after the TMA's
+                    const int j = key0 + r;
+                    if (j < first_key || j > last_key) {
+#pragma unroll
+                        for (int hf = 0; hf < HALVES; ++hf) {
+                            uint4* vr = reinterpret_cast<uint4*>(smem_raw + Q_BYTES + P_BYTES + st * STAGE_BYTES + KV_BYTES + hf * KV_HALF + r * 128);
+#pragma unroll
+                            for (int c8 = 0; c8 < 8; ++c8) vr[c8] = make_uint4(0, 0, 0, 0);
+                        }
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the zeroed rows: visible to the MMA
+                }
+            }
+            // rescale O where a row's reference maximum moved (rare after the first tiles); tcgen05.ld / .st
+            // are warp-wide: a warp rescales when any of its rows moved, the other rows by 1.
+            // The previous tile's P V of this head has to be complete before O is touched, and before this tile
+            // is announced at all: the issuer waits for the announcements by their parity, so a head must never
+            // be two of them ahead of it.
+            if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(my_pv_done, (it - 1) & 1, err))) {
+                alive = false;
+                break;
+            }
+            if (__any_sync(0xffffffffu, moved)) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const float f = moved ? corr : 1.f;
+#pragma unroll
+                for (int c0 = 0; c0 < DP; c0 += 32) {
+                    float o[32];
+                    tmem_ld32(tmem_o + lane_addr + c0, o);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] *= f;
+                    tmem_st32(tmem_o + lane_addr + c0, o);
+                }
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");   // P (and O) are in tensor memory
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(my_p_ready);
+        }
+        // ---- O / l -> out -----------------------------------------------------------------------------------
+        if (alive) alive = mbar_wait(bar_o, 0, err);
+        alive = __all_sync(0xffffffffu, alive);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (alive) {
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            const bool valid = r < rows;
+            __nv_bfloat16* dst = out + ((size_t)(t0 + r) * nh + h0 + hd) * d;
+#pragma unroll
+            for (int c0 = 0; c0 < DP; c0 += 32) {
+                float o[32];
+                tmem_ld32(tmem_o + lane_addr + c0, o);   // warp-wide, whatever `valid` is
+                if (valid) {
+#pragma unroll
+                    for (int c8 = 0; c8 < 4; ++c8) {
+                        const int c = c0 + c8 * 8;
+                        if (c < d) {
+                            uint4 pk;
+                            pk.x = pack_bf16(o[c8 * 8] * inv, o[c8 * 8 + 1] * inv);
+                            pk.y = pack_bf16(o[c8 * 8 + 2] * inv, o[c8 * 8 + 3] * inv);
+                            pk.z = pack_bf16(o[c8 * 8 + 4] * inv, o[c8 * 8 + 5] * inv);
+                            pk.w = pack_bf16(o[c8 * 8 + 6] * inv, o[c8 * 8 + 7] * inv);
+                            *reinterpret_cast<uint4*>(dst + c) = pk;
+                        }
+                    }
+                }
+            }
+        } else {
+            words[3] = 1;
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
 // decode: few tokens per request, keys split into ranges
 // ------------------------------------------------------------------------------------------------
 constexpr int DEC_ROWS = 16;    // query heads of one key/value head a CTA can hold
@@ -890,6 +1246,18 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
                      dec_max, err);
 }
 
+template <int DP>
+int launch_pairs(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, const int* q_start,
+                 const int* start_pos, int num_entries, const int* table, int stride, int nh, int nkv, int d, int ps,
+                 int ps_shift, int num_pages, int window, float sl2, int dec_max, int tiles, int* err, cudaStream_t stream) {
+    constexpr size_t smem = 2 * (size_t)(DP / 64) * QT * 128 + PF2_STAGES * 2 * (size_t)(DP / 64) * KT * 128 + 256;
+    cudaFuncSetAttribute(attn_prefill_tc2_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(attn_prefill_tc2_kernel<DP>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    return xb_launch(attn_prefill_tc2_kernel<DP>, dim3(nh / 2, tiles), dim3(PF2_THREADS), smem, stream, mq, mk, mv,
+                     (__nv_bfloat16*)out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, ps_shift, num_pages,
+                     window, sl2, dec_max, err);
+}
+
 constexpr int DEC_PAGE_CAP = 1024;   // block-table entries of a piece that are staged in shared memory
 
 template <int DP>
@@ -911,10 +1279,12 @@ int launch_decode(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
 // Portions of more than dec_max tokens, 128 queries per CTA; `tiles` = sum over those portions of
 // ceil(tokens / 128); `tokens` = rows of q.  Returns cudaErrorNotSupported (having done nothing)
 // for a head size over 128 or not a multiple of 16, or a page size that is no power of two >= 8.
+// `pairs` != 0: two query heads of a key/value head per CTA where their number is even (else, and
+// with 0, one head per CTA).
 XB_EXPORT int xb_attn_prefill_tc(void* out, const void* q, const void* kc, const void* vc, const int* q_start,
                                  const int* start_pos, int num_entries, const int* table, int stride, int tokens,
                                  int nh, int nkv, int d, int ps, int num_pages, int window, float scale, int dec_max,
-                                 int tiles, int* err, cudaStream_t stream) {
+                                 int tiles, int pairs, int* err, cudaStream_t stream) {
     if (tiles <= 0) return 0;
     int shift = -1;
     for (int s = 3; s < 20; ++s)
@@ -926,6 +1296,13 @@ XB_EXPORT int xb_attn_prefill_tc(void* out, const void* q, const void* kc, const
     if (!map_q3(&mq, q, tokens, nh, d, 1, QT) || !map_rows(&mk, kc, rows, d, box_rows) || !map_rows(&mv, vc, rows, d, box_rows))
         return (int)cudaErrorNotSupported;
     const float sl2 = scale * 1.4426950408889634f;
+    if (pairs && (nh / nkv) % 2 == 0) {
+        if (d <= 64)
+            return launch_pairs<64>(mq, mk, mv, out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, shift,
+                                    num_pages, window, sl2, dec_max, tiles, err, stream);
+        return launch_pairs<128>(mq, mk, mv, out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, shift,
+                                 num_pages, window, sl2, dec_max, tiles, err, stream);
+    }
     if (d <= 64)
         return launch<64>(mq, mk, mv, out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, shift, num_pages,
                           window, sl2, dec_max, tiles, err, stream);
