@@ -375,11 +375,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 //   warps 0..3: softmax of head A (one row per thread), warps 4..7: softmax of head B,
 //   warp 8: TMA producer of Q (both heads) and of the key pages, warp 10: of the value pages (one lane
 //   per page box; the page ids of the next tile are fetched while this one is issued),
-//   warp 9: MMA issuer: S_A, S_B of the next tile, then O_A += P_A V and O_B += P_B V of this one.
+//   warp 9: issues S_A, S_B = Q K^T of every tile; warp 11: issues O_A += P_A V and O_B += P_B V (two
+//   issuers, so that the waits of one do not hold up the products of the other; P lies in tensor memory
+//   over the scores it came from, so the first waits for the second before it reuses a score buffer).
 // Tensor memory (all 512 columns): S_A[0], S_A[1], S_B[0], S_B[1] at 0, 64, 128, 192; O_A at 256, O_B at 384.
 // One CTA per SM.  Needs an even number of query heads per key/value head.
 constexpr int PF2_STAGES = 4;
-constexpr int PF2_THREADS = 352;
+constexpr int PF2_THREADS = 384;
 
 template <int DP>
 __global__ void __launch_bounds__(PF2_THREADS)
@@ -394,12 +396,12 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const uint32_t base = smem_u32(smem_raw);
     const uint32_t q_sm = base, kv_sm = base + Q_BYTES;
-    // barriers, 8 bytes each: k_full[4] k_empty[4] v_full[4] v_empty[4] s_ready[head][2] s_free[head][2]
-    // p_ready[head] pv_done[head] q_full bar_o; then four words
+    // barriers, 8 bytes each: k_full[4] k_empty[4] v_full[4] v_empty[4] s_ready[head][2] pv_done[head][2]
+    // p_ready[head] q_full bar_o; then four words
     constexpr uint32_t BAR_OFF = Q_BYTES + P_BYTES + NS * STAGE_BYTES;
     const uint32_t bars = base + BAR_OFF;
     const uint32_t k_full0 = bars, k_empty0 = bars + 32, v_full0 = bars + 64, v_empty0 = bars + 96;
-    const uint32_t s_ready0 = bars + 128, p_ready0 = bars + 192, pv_done0 = bars + 208;
+    const uint32_t s_ready0 = bars + 128, pv_done0 = bars + 160, p_ready0 = bars + 192;
     const uint32_t q_full = bars + 224, bar_o = bars + 232;
     volatile uint32_t* words = reinterpret_cast<volatile uint32_t*>(smem_raw + BAR_OFF + 240);  // tmem, entry, tile, dead
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -430,7 +432,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         for (int i = 0; i < 4 * NS; ++i) mbar_init(bars + 8 * i, 1);        // k_full, k_empty, v_full, v_empty
         for (int i = 0; i < 4; ++i) mbar_init(s_ready0 + 8 * i, 1);
         for (int i = 0; i < 2; ++i) mbar_init(p_ready0 + 8 * i, 128);
-        for (int i = 0; i < 2; ++i) mbar_init(pv_done0 + 8 * i, 1);
+        for (int i = 0; i < 4; ++i) mbar_init(pv_done0 + 8 * i, 1);
         mbar_init(q_full, 1);
         mbar_init(bar_o, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -504,19 +506,20 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             page_next = page_of(it + 1);
         }
     } else if (warp == 9) {
-        // ---- MMA issuer: S of tile 0, then for every tile S(next) of both heads before P V (this) of both ----
+        // ---- issuer of S = Q K^T, both heads, tile after tile ----------------------------------------------
         if (lane == 0) {
-            const uint32_t idesc_s = umma_idesc(KT, 0), idesc_o = umma_idesc(DP, 1);
+            const uint32_t idesc_s = umma_idesc(KT, 0);
             const uint64_t dq0 = umma_desc(q_sm, 16, 1024), dk0 = umma_desc(kv_sm, 16, 1024);
-            const uint64_t dv0 = umma_desc(kv_sm + KV_BYTES, KV_HALF, 1024);
-            auto issue_qk = [&](int it) -> bool {   // S_hd[it & 1] = Q_hd K^T of tile `it`, hd = 0, 1
+            bool ok = mbar_wait(q_full, 0, err);
+            for (int it = 0; it < iters && ok; ++it) {
                 const int sb = it & 1, s = it % NS;
-                if (!mbar_wait(k_full0 + 8 * s, (it / NS) & 1, err)) return false;
+                ok = mbar_wait(k_full0 + 8 * s, (it / NS) & 1, err);
                 const uint64_t dk = dk0 + (uint64_t)((s * STAGE_BYTES) >> 4);
 #pragma unroll
                 for (int hd = 0; hd < 2; ++hd) {
-                    // S[sb] of this head held the scores and then P of tile it - 2: its P V was issued before this and
-                    // the tensor pipe runs a thread's MMAs in the order of issue
+                    // S[sb] of this head held the scores and then P of tile it - 2: its P V must have read it
+                    ok = ok && (it < 2 || mbar_wait(pv_done0 + 8 * (2 * hd + sb), ((it >> 1) - 1) & 1, err));
+                    if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t dq = dq0 + (uint64_t)((hd * Q_ONE) >> 4);
 #pragma unroll
@@ -527,28 +530,34 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                     }
                     umma_commit(s_ready0 + 8 * (2 * hd + sb));
                 }
+                if (!ok) break;
                 umma_commit(k_empty0 + 8 * s);   // the key stage is free once both products have completed
-                return true;
-            };
-            bool ok = mbar_wait(q_full, 0, err) && issue_qk(0);
+            }
+            if (!ok) words[3] = 1;
+        }
+    } else if (warp == 11) {
+        // ---- issuer of O += P V, both heads, tile after tile ------------------------------------------------
+        if (lane == 0) {
+            const uint32_t idesc_o = umma_idesc(DP, 1);
+            const uint64_t dv0 = umma_desc(kv_sm + KV_BYTES, KV_HALF, 1024);
+            bool ok = true;
             for (int it = 0; it < iters && ok; ++it) {
-                const int s = it % NS;
-                if (it + 1 < iters) ok = issue_qk(it + 1);
-                ok = ok && mbar_wait(v_full0 + 8 * s, (it / NS) & 1, err);
+                const int s = it % NS, sb = it & 1;
+                ok = mbar_wait(v_full0 + 8 * s, (it / NS) & 1, err);
                 const uint64_t dv = dv0 + (uint64_t)((s * STAGE_BYTES) >> 4);
 #pragma unroll
                 for (int hd = 0; hd < 2; ++hd) {
                     ok = ok && mbar_wait(p_ready0 + 8 * hd, it & 1, err);   // P written, V rows zeroed, O rescaled
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    // O += P V : A = P [128 x 64 keys] in tensor memory (over the scores it came from), B = V [64 keys x DP]
+                    // A = P [128 x 64 keys] in tensor memory (over the scores it came from), B = V [64 keys x DP]
                     // MN-major (halves 64 columns apart)
-                    const uint32_t tp = tmem + (uint32_t)(hd * 128 + (it & 1) * 64);
+                    const uint32_t tp = tmem + (uint32_t)(hd * 128 + sb * 64);
 #pragma unroll
                     for (int kk = 0; kk < KT / 16; ++kk)
                         umma_bf16_ta(tmem + (uint32_t)(256 + hd * 128), tp + (uint32_t)(kk * 8), dv + (uint64_t)((kk * 2048) >> 4),
                                      idesc_o, (it | kk) ? 1u : 0u);
-                    umma_commit(pv_done0 + 8 * hd);      // P and O of this head are free again once these have completed
+                    umma_commit(pv_done0 + 8 * (2 * hd + sb));   // P, its score buffer and O of this head are free again
                 }
                 if (!ok) break;
                 umma_commit(v_empty0 + 8 * s);           // and so is the value stage
@@ -562,7 +571,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t tmem_s = tmem + (uint32_t)(hd * 128), tmem_o = tmem + (uint32_t)(256 + hd * 128);
         const uint32_t my_s_ready = s_ready0 + 16 * hd;
-        const uint32_t my_p_ready = p_ready0 + 8 * hd, my_pv_done = pv_done0 + 8 * hd;
+        const uint32_t my_p_ready = p_ready0 + 8 * hd, my_pv_done = pv_done0 + 16 * hd;
         const int my_pos = p0 + r;
         float m_ref = -INFINITY, l = 0.f;
         bool alive = true;
@@ -663,7 +672,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             // The previous tile's P V of this head has to be complete before O is touched, and before this tile
             // is announced at all: the issuer waits for the announcements by their parity, so a head must never
             // be two of them ahead of it.
-            if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(my_pv_done, (it - 1) & 1, err))) {
+            if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(my_pv_done + 8 * (sb ^ 1), ((it - 1) >> 1) & 1, err))) {
                 alive = false;
                 break;
             }

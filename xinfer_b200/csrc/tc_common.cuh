@@ -33,6 +33,15 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // it expires.  The bound is taken from the clock, not from a count of polls: a poll may itself
 // sleep for a while.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err) {
+    {   // the phase is often complete already: one poll before the clock is read
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
     const long long t0 = clock64();
     for (;;) {
         uint32_t ok;
