@@ -408,8 +408,8 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const int G = nh / nkv;
     const int h0 = 2 * (int)blockIdx.x, g = h0 / G;   // heads vary fastest: every pair's longest tiles start first
     pdl_launch_dependents();
-    pdl_wait();
 
+    // what follows until the wait reads only what the host sent before the step's first kernel
     if (threadIdx.x == 0) {
         if (base & 1023u) atomicOr(err, XB_ERR_WAIT);  // the swizzle needs a 1024-byte aligned window
         int acc = 0, found = -1, tile = 0;
@@ -439,7 +439,10 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     }
     __syncthreads();
     const int b = (int)words[1];
-    if (b < 0 || (base & 1023u)) return;
+    if (b < 0 || (base & 1023u)) {
+        pdl_wait();   // a kernel that depends on this one may rely on every block having waited
+        return;
+    }
     constexpr uint32_t TMEM_COLS = 512;
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t*>(&words[0]))), "r"(TMEM_COLS) : "memory");
@@ -449,6 +452,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = words[0];
+    pdl_wait();   // q and the new keys and values come from the kernel before
 
     const int n = q_start[b + 1] - q_start[b];
     const int row0 = (int)words[2] * QT;
