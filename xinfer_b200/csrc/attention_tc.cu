@@ -514,15 +514,15 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         if (lane == 0) {
             const uint32_t idesc_s = umma_idesc(KT, 0);
             const uint64_t dq0 = umma_desc(q_sm, 16, 1024), dk0 = umma_desc(kv_sm, 16, 1024);
-            bool ok = mbar_wait(q_full, 0, err);
+            bool ok = mbar_wait(q_full, 0, err, true);
             for (int it = 0; it < iters && ok; ++it) {
                 const int sb = it & 1, s = it % NS;
-                ok = mbar_wait(k_full0 + 8 * s, (it / NS) & 1, err);
+                ok = mbar_wait(k_full0 + 8 * s, (it / NS) & 1, err, true);
                 const uint64_t dk = dk0 + (uint64_t)((s * STAGE_BYTES) >> 4);
 #pragma unroll
                 for (int hd = 0; hd < 2; ++hd) {
                     // S[sb] of this head held the scores and then P of tile it - 2: its P V must have read it
-                    ok = ok && (it < 2 || mbar_wait(pv_done0 + 8 * (2 * hd + sb), ((it >> 1) - 1) & 1, err));
+                    ok = ok && (it < 2 || mbar_wait(pv_done0 + 8 * (2 * hd + sb), ((it >> 1) - 1) & 1, err, true));
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t dq = dq0 + (uint64_t)((hd * Q_ONE) >> 4);
@@ -547,11 +547,11 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             bool ok = true;
             for (int it = 0; it < iters && ok; ++it) {
                 const int s = it % NS, sb = it & 1;
-                ok = mbar_wait(v_full0 + 8 * s, (it / NS) & 1, err);
+                ok = mbar_wait(v_full0 + 8 * s, (it / NS) & 1, err, true);
                 const uint64_t dv = dv0 + (uint64_t)((s * STAGE_BYTES) >> 4);
 #pragma unroll
                 for (int hd = 0; hd < 2; ++hd) {
-                    ok = ok && mbar_wait(p_ready0 + 8 * hd, it & 1, err);   // P written, V rows zeroed, O rescaled
+                    ok = ok && mbar_wait(p_ready0 + 8 * hd, it & 1, err, true);   // P written, V rows zeroed, O rescaled
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     // A = P [128 x 64 keys] in tensor memory (over the scores it came from), B = V [64 keys x DP]

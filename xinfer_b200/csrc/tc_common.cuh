@@ -32,8 +32,10 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // Bounded wait for the phase with the given parity; false (and XB_ERR_WAIT in the error word) when
 // it expires.  The bound is taken from the clock, not from a count of polls: a poll may itself
 // sleep for a while.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err) {
-    {   // the phase is often complete already: one poll before the clock is read
+// `likely_done`: for a thread whose waits are mostly over before it asks (an MMA issuer behind its
+// producers): one poll before the clock is read.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err, bool likely_done = false) {
+    if (likely_done) {
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
