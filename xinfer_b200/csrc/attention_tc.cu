@@ -1212,6 +1212,41 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     for (int row = warp; row < G; row += 4) {
         const int h = h0 + row;
         const size_t pbase = ((size_t)z * nh + h) * splits_max;
+        if (ns <= 32) {
+            // lane i holds the maximum and the sum of piece i; the pieces' rows are requested before those are
+            // reduced, so that the whole merge is one trip to the L2 (the sums are formed in the order of the pieces)
+            const float mi = lane < ns ? __ldcg(part_ml + (pbase + lane) * 2) : -INFINITY;
+            const float li = lane < ns ? __ldcg(part_ml + (pbase + lane) * 2 + 1) : 0.f;
+            const int c4 = lane * 4;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            float M = 0.f, W = 0.f, wi = 0.f;
+            for (int i0 = 0; i0 < ns; i0 += 8) {
+                float4 v[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    v[i] = (i0 + i < ns && c4 < d) ? __ldcg(reinterpret_cast<const float4*>(part_o + (pbase + i0 + i) * d + c4))
+                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+                if (i0 == 0) {
+                    M = warp_max(mi);
+                    wi = lane < ns ? li * exp2f(mi - M) : 0.f;
+                    W = warp_sum(wi);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float w = __shfl_sync(0xffffffffu, wi, (i0 + i) & 31);
+                    if (i0 + i < ns) {
+                        acc.x += v[i].x * w; acc.y += v[i].y * w; acc.z += v[i].z * w; acc.w += v[i].w * w;
+                    }
+                }
+            }
+            const float inv = W > 0.f ? 1.f / W : 0.f;
+            if (c4 < d) {
+                __nv_bfloat16* dst = out + ((size_t)t * nh + h) * d + c4;
+                *reinterpret_cast<uint32_t*>(dst) = pack_bf16(acc.x * inv, acc.y * inv);
+                *reinterpret_cast<uint32_t*>(dst + 2) = pack_bf16(acc.z * inv, acc.w * inv);
+            }
+            continue;
+        }
         float mloc = -INFINITY;
         for (int i = lane; i < ns; i += 32) mloc = fmaxf(mloc, __ldcg(part_ml + (pbase + i) * 2));
         const float M = warp_max(mloc);
