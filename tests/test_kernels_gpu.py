@@ -357,6 +357,16 @@ def test_attention_prefill_tcgen05(nh, nkv, d, ps, entries, window, pairs, monke
     assert worst <= tol(torch.bfloat16, 2), worst
 
 
+@pytest.mark.parametrize("window", [None, 5000])
+def test_attention_prefill_tcgen05_after_a_long_prefix(window, monkeypatch):
+    """A portion of 300 tokens after 20,000 cached ones: some 320 key tiles go through the four-stage
+    rings and the two score buffers of a CTA, with and without a window that starts inside a tile."""
+    from xinfer_b200.parts import attention_backend
+    monkeypatch.setattr(attention_backend, "PREFILL_TC", True)
+    worst = attention_case(tiled_kernel, torch.bfloat16, 4, 2, 128, 16, [(20000, 300)], window)
+    assert worst <= tol(torch.bfloat16, 2), worst
+
+
 def test_attention_tiled_sees_one_far_key_and_the_windows_edge(prefill_family):
     far_key_checks(tiled_kernel, torch.bfloat16)
 
