@@ -40,7 +40,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                        const int* __restrict__ q_start, const int* __restrict__ start_pos, int num_entries,
                        const int* __restrict__ block_table, int table_stride, int nh, int nkv, int d, int ps,
-                       int ps_shift, int num_pages, int window, float scale_log2, int dec_max, int* err) {
+                       int ps_shift, int num_pages, int window, float scale_log2, int dec_max,
+                       const int* __restrict__ tile_map, int* err) {
     constexpr int HALVES = DP / 64;
     constexpr uint32_t Q_BYTES = HALVES * QT * 128, KV_HALF = KT * 128, KV_BYTES = HALVES * KV_HALF;
     constexpr uint32_t STAGE_BYTES = 2 * KV_BYTES, P_BYTES = QT * 128;
@@ -63,16 +64,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (threadIdx.x == 0) {
         if (base & 1023u) atomicOr(err, XB_ERR_WAIT);  // the swizzle needs a 1024-byte aligned window
         int acc = 0, found = -1, tile = 0;
-        for (int b = 0; b < num_entries; ++b) {
-            const int n = q_start[b + 1] - q_start[b];
-            if (n > dec_max) {
-                const int nt = (n + QT - 1) / QT;
-                if ((int)blockIdx.y < acc + nt) {
-                    found = b;
-                    tile = nt - 1 - ((int)blockIdx.y - acc);  // a portion's last (longest) tiles first
-                    break;
+        if (tile_map) {   // (portion, query tile) of every block row, made by the host: longest first over all portions
+            found = tile_map[2 * blockIdx.y];
+            tile = tile_map[2 * blockIdx.y + 1];
+        } else {
+            for (int b = 0; b < num_entries; ++b) {
+                const int n = q_start[b + 1] - q_start[b];
+                if (n > dec_max) {
+                    const int nt = (n + QT - 1) / QT;
+                    if ((int)blockIdx.y < acc + nt) {
+                        found = b;
+                        tile = nt - 1 - ((int)blockIdx.y - acc);  // a portion's last (longest) tiles first
+                        break;
+                    }
+                    acc += nt;
                 }
-                acc += nt;
             }
         }
         if (*reinterpret_cast<volatile int*>(err) & XB_ERR_WAIT) found = -1;  // an earlier CTA gave up: do not pile on
@@ -386,10 +392,12 @@ constexpr int PF2_THREADS = 384;
 template <int DP>
 __global__ void __launch_bounds__(PF2_THREADS)
 attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
+                        __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ q_start, const int* __restrict__ start_pos, int num_entries,
                         const int* __restrict__ block_table, int table_stride, int nh, int nkv, int d, int ps,
-                        int ps_shift, int num_pages, int window, float scale_log2, int dec_max, int* err) {
+                        int ps_shift, int num_pages, int window, float scale_log2, int dec_max,
+                        const int* __restrict__ tile_map, int* err) {
     constexpr int HALVES = DP / 64, NS = PF2_STAGES;
     constexpr uint32_t Q_ONE = HALVES * QT * 128, Q_BYTES = 2 * Q_ONE, P_BYTES = 0;
     constexpr uint32_t KV_HALF = KT * 128, KV_BYTES = HALVES * KV_HALF, STAGE_BYTES = 2 * KV_BYTES;
@@ -413,16 +421,21 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     if (threadIdx.x == 0) {
         if (base & 1023u) atomicOr(err, XB_ERR_WAIT);  // the swizzle needs a 1024-byte aligned window
         int acc = 0, found = -1, tile = 0;
-        for (int b = 0; b < num_entries; ++b) {
-            const int n = q_start[b + 1] - q_start[b];
-            if (n > dec_max) {
-                const int nt = (n + QT - 1) / QT;
-                if ((int)blockIdx.y < acc + nt) {
-                    found = b;
-                    tile = nt - 1 - ((int)blockIdx.y - acc);  // a portion's last (longest) tiles first
-                    break;
+        if (tile_map) {   // (portion, query tile) of every block row, made by the host: longest first over all portions
+            found = tile_map[2 * blockIdx.y];
+            tile = tile_map[2 * blockIdx.y + 1];
+        } else {
+            for (int b = 0; b < num_entries; ++b) {
+                const int n = q_start[b + 1] - q_start[b];
+                if (n > dec_max) {
+                    const int nt = (n + QT - 1) / QT;
+                    if ((int)blockIdx.y < acc + nt) {
+                        found = b;
+                        tile = nt - 1 - ((int)blockIdx.y - acc);  // a portion's last (longest) tiles first
+                        break;
+                    }
+                    acc += nt;
                 }
-                acc += nt;
             }
         }
         if (*reinterpret_cast<volatile int*>(err) & XB_ERR_WAIT) found = -1;  // an earlier CTA gave up: do not pile on
@@ -700,7 +713,38 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         if (alive) alive = mbar_wait(bar_o, 0, err);
         alive = __all_sync(0xffffffffu, alive);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (alive) {
+        if (alive && rows == QT) {
+            // a full tile: the rows go, swizzled as a TMA box wants them, over this head's Q (every MMA has
+            // completed), and a thread of each warp stores the warp's 32 rows, a 64-column half per TMA copy:
+            // whole lines reach the memory instead of 16 bytes per row and instruction
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            unsigned char* stage = smem_raw + hd * Q_ONE;
+#pragma unroll
+            for (int c0 = 0; c0 < DP; c0 += 32) {
+                float o[32];
+                tmem_ld32(tmem_o + lane_addr + c0, o);
+#pragma unroll
+                for (int c8 = 0; c8 < 4; ++c8) {
+                    const int cc = c0 / 8 + c8;   // 16-byte chunk of the row
+                    uint4 w;
+                    w.x = pack_bf16(o[c8 * 8] * inv, o[c8 * 8 + 1] * inv);
+                    w.y = pack_bf16(o[c8 * 8 + 2] * inv, o[c8 * 8 + 3] * inv);
+                    w.z = pack_bf16(o[c8 * 8 + 4] * inv, o[c8 * 8 + 5] * inv);
+                    w.w = pack_bf16(o[c8 * 8 + 6] * inv, o[c8 * 8 + 7] * inv);
+                    *reinterpret_cast<uint4*>(stage + (cc >> 3) * (QT * 128) + r * 128 + (((cc & 7) ^ (r & 7)) << 4)) = w;
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {   // a warp stores its own 32 rows: nobody waits for another warp here
+#pragma unroll
+                for (int hf = 0; hf < HALVES; ++hf)
+                    if (hf * 64 < d)
+                        tma_store_3d(&map_o, q_sm + hd * Q_ONE + hf * QT * 128 + (warp & 3) * 32 * 128, hf * 64, h0 + hd,
+                                     t0 + (warp & 3) * 32);
+                tma_store_commit_and_wait_read();
+            }
+        } else if (alive) {
             const float inv = l > 0.f ? 1.f / l : 0.f;
             const bool valid = r < rows;
             __nv_bfloat16* dst = out + ((size_t)(t0 + r) * nh + h0 + hd) * d;
@@ -1285,25 +1329,28 @@ bool map_q3(CUtensorMap* out, const void* ptr, long long T, int nh, int d, int b
 template <int DP>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, const int* q_start,
            const int* start_pos, int num_entries, const int* table, int stride, int nh, int nkv, int d, int ps,
-           int ps_shift, int num_pages, int window, float sl2, int dec_max, int tiles, int* err, cudaStream_t stream) {
+           int ps_shift, int num_pages, int window, float sl2, int dec_max, int tiles, const int* tile_map, int* err,
+           cudaStream_t stream) {
     constexpr size_t smem = (size_t)(DP / 64) * QT * 128 + 2 * 2 * (size_t)(DP / 64) * KT * 128 + QT * 128 + 144;
     cudaFuncSetAttribute(attn_prefill_tc_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaFuncSetAttribute(attn_prefill_tc_kernel<DP>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     return xb_launch(attn_prefill_tc_kernel<DP>, dim3(nh, tiles), dim3(224), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
                      q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, ps_shift, num_pages, window, sl2,
-                     dec_max, err);
+                     dec_max, tile_map, err);
 }
 
 template <int DP>
-int launch_pairs(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, const int* q_start,
+int launch_pairs(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, void* out,
+                 const int* q_start,
                  const int* start_pos, int num_entries, const int* table, int stride, int nh, int nkv, int d, int ps,
-                 int ps_shift, int num_pages, int window, float sl2, int dec_max, int tiles, int* err, cudaStream_t stream) {
+                 int ps_shift, int num_pages, int window, float sl2, int dec_max, int tiles, const int* tile_map, int* err,
+                 cudaStream_t stream) {
     constexpr size_t smem = 2 * (size_t)(DP / 64) * QT * 128 + PF2_STAGES * 2 * (size_t)(DP / 64) * KT * 128 + 256;
     cudaFuncSetAttribute(attn_prefill_tc2_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaFuncSetAttribute(attn_prefill_tc2_kernel<DP>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    return xb_launch(attn_prefill_tc2_kernel<DP>, dim3(nh / 2, tiles), dim3(PF2_THREADS), smem, stream, mq, mk, mv,
+    return xb_launch(attn_prefill_tc2_kernel<DP>, dim3(nh / 2, tiles), dim3(PF2_THREADS), smem, stream, mq, mk, mv, mo,
                      (__nv_bfloat16*)out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, ps_shift, num_pages,
-                     window, sl2, dec_max, err);
+                     window, sl2, dec_max, tile_map, err);
 }
 
 constexpr int DEC_PAGE_CAP = 1024;   // block-table entries of a piece that are staged in shared memory
@@ -1328,11 +1375,12 @@ int launch_decode(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
 // ceil(tokens / 128); `tokens` = rows of q.  Returns cudaErrorNotSupported (having done nothing)
 // for a head size over 128 or not a multiple of 16, or a page size that is no power of two >= 8.
 // `pairs` != 0: two query heads of a key/value head per CTA where their number is even (else, and
-// with 0, one head per CTA).
+// with 0, one head per CTA).  `tile_map`: null, or 2 * tiles int32 that give every block row its
+// (portion, query tile), so that the longest tiles of all portions start first and no block searches.
 XB_EXPORT int xb_attn_prefill_tc(void* out, const void* q, const void* kc, const void* vc, const int* q_start,
                                  const int* start_pos, int num_entries, const int* table, int stride, int tokens,
                                  int nh, int nkv, int d, int ps, int num_pages, int window, float scale, int dec_max,
-                                 int tiles, int pairs, int* err, cudaStream_t stream) {
+                                 int tiles, int pairs, const int* tile_map, int* err, cudaStream_t stream) {
     if (tiles <= 0) return 0;
     int shift = -1;
     for (int s = 3; s < 20; ++s)
@@ -1345,17 +1393,19 @@ XB_EXPORT int xb_attn_prefill_tc(void* out, const void* q, const void* kc, const
         return (int)cudaErrorNotSupported;
     const float sl2 = scale * 1.4426950408889634f;
     if (pairs && (nh / nkv) % 2 == 0) {
+        CUtensorMap mo;   // out has the layout of q
+        if (!map_q3(&mo, out, tokens, nh, d, 1, 32)) return (int)cudaErrorNotSupported;
         if (d <= 64)
-            return launch_pairs<64>(mq, mk, mv, out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, shift,
-                                    num_pages, window, sl2, dec_max, tiles, err, stream);
-        return launch_pairs<128>(mq, mk, mv, out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, shift,
-                                 num_pages, window, sl2, dec_max, tiles, err, stream);
+            return launch_pairs<64>(mq, mk, mv, mo, out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, shift,
+                                    num_pages, window, sl2, dec_max, tiles, tile_map, err, stream);
+        return launch_pairs<128>(mq, mk, mv, mo, out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, shift,
+                                 num_pages, window, sl2, dec_max, tiles, tile_map, err, stream);
     }
     if (d <= 64)
         return launch<64>(mq, mk, mv, out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, shift, num_pages,
-                          window, sl2, dec_max, tiles, err, stream);
+                          window, sl2, dec_max, tiles, tile_map, err, stream);
     return launch<128>(mq, mk, mv, out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, shift, num_pages,
-                       window, sl2, dec_max, tiles, err, stream);
+                       window, sl2, dec_max, tiles, tile_map, err, stream);
 }
 // int32 a plan for `tokens` small tokens and `ctas` target CTAs must hold.
 XB_EXPORT long long xb_attn_decode_plan_size(int tokens, int ctas, int nkv) {

@@ -98,6 +98,15 @@ def _plan(ctx, head_dim: int):
             plan = dict(tiles=int(((counts[~small] + per - 1) // per).sum()), small=int(counts[small].sum()),
                         direct=bool(small.all()), bound=int(ends[small].max()) if small.any() else 0,
                         prefill_bound=int(ends[~small].max()) if (~small).any() else 0)
+            if plan["tiles"] and per == 128:
+                # (portion, query tile) of every block row of the tcgen05 prefill kernels, the tiles with the
+                # most keys first whatever portion they belong to; sent once per step, before its first kernel
+                rows = [(int(ctx.h_start_pos[b]) + min(int(counts[b]), (ti + 1) * per), b, ti)
+                        for b in np.nonzero(~small)[0] for ti in range((int(counts[b]) + per - 1) // per)]
+                rows.sort(key=lambda r: -r[0])
+                host = torch.tensor([[b, ti] for _, b, ti in rows], dtype=torch.int32).pin_memory()
+                plan["tile_map"] = host.to(ctx.positions.device, non_blocking=True)
+                plan["tile_map_host"] = host   # keeps the pinned source alive until the step is over
         ctx.scratch[key] = plan
     return plan
 
@@ -141,7 +150,8 @@ def attend(out, q, cache, ctx, table, stride, window, scale) -> None:
     took = False
     if plan["tiles"] and PREFILL_TC and kernels.attn_prefill_queries(d, PREFILL_WARPS) == 128:
         took = kernels.attn_prefill_tc(out, q, cache.k, cache.v, ctx.q_start, ctx.start_pos, ctx.num_entries, table, stride,
-                                       window, scale, DEC_MAX, plan["tiles"], ctx.err, pairs=PREFILL_PAIRS)
+                                       window, scale, DEC_MAX, plan["tiles"], ctx.err, pairs=PREFILL_PAIRS,
+                                       tile_map=plan.get("tile_map"))
     if plan["tiles"] and not took:
         kernels.attn_prefill_bf16(out, q, cache.k, cache.v, ctx.q_start, ctx.start_pos, ctx.num_entries, table, stride,
                                   window, scale, DEC_MAX, plan["tiles"], plan["prefill_bound"], ctx.err, warps=PREFILL_WARPS)
