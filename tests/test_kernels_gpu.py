@@ -347,12 +347,12 @@ def test_attention_tiled_bf16(nh, nkv, d, ps, entries, window, prefill_family):
 @pytest.mark.parametrize("nh,nkv,d,ps,entries,window", [
     (2, 1, 128, 16, [(0, 128)], None), (2, 1, 128, 16, [(0, 200)], None), (4, 2, 64, 8, [(37, 300), (0, 129)], None),
     (4, 4, 96, 32, [(1000, 260)], 200), (2, 2, 16, 64, [(5, 150)], None), (8, 2, 128, 128, [(100, 500), (0, 6)], 333),
-    (3, 1, 48, 16, [(600, 700)], None), (6, 1, 80, 16, [(0, 1300), (2000, 131)], None), (4, 1, 128, 8, [(4000, 257)], 1000)])
-@pytest.mark.parametrize("pairs", [True, False], ids=["two_heads_per_cta", "one_head_per_cta"])
-def test_attention_prefill_tcgen05(nh, nkv, d, ps, entries, window, pairs, monkeypatch):
+    (3, 1, 48, 16, [(600, 700)], None), (6, 1, 80, 16, [(0, 1300), (2000, 131)], None), (4, 1, 128, 8, [(4000, 257)], 1000),
+    (5, 5, 128, 16, [(0, 300), (900, 140)], None), (10, 2, 64, 32, [(50, 500)], 300)])
+def test_attention_prefill_tcgen05(nh, nkv, d, ps, entries, window, monkeypatch):
+    """Even and odd numbers of query heads per key/value head (the kernel takes them two at a time)."""
     from xinfer_b200.parts import attention_backend
     monkeypatch.setattr(attention_backend, "PREFILL_TC", True)
-    monkeypatch.setattr(attention_backend, "PREFILL_PAIRS", pairs)
     worst = attention_case(tiled_kernel, torch.bfloat16, nh, nkv, d, ps, entries, window)
     assert worst <= tol(torch.bfloat16, 2), worst
 

@@ -1,18 +1,11 @@
-// Prefill attention over the paged cache on the 5th-generation tensor cores.
-//
-// One CTA (128 row threads, a producer warp, an MMA issuer warp) owns 128 queries of one request's portion for one query head:
-//   * a producer warp streams the request's key/value pages with TMA (cp.async.bulk.tensor,
-//     128-byte swizzle, one box per page and 64-column half) into a two-stage ring guarded by
-//     mbarriers; an issuer warp launches every tcgen05.mma and frees stages with tcgen05.commit;
-//     the roles meet only through mbarriers;
-//   * S = Q K^T (128 x 64 per key tile) accumulates in one of two tensor-memory buffers, so that the
-//     next tile's scores are computed while this tile's softmax runs; each thread owns one query
-//     row (TMEM lane), reads its 64 scores with tcgen05.ld, masks (causal, window, range), and runs
-//     the softmax of its row entirely in registers (float32, base 2), writing P as bfloat16 into a
-//     swizzled shared-memory tile;
-//   * O += P V accumulates in tensor memory (V is the MN-major operand, read where TMA put it).
-//     The running maximum is only moved when it grows by more than 2^8, so O is rescaled
-//     (tcgen05.ld / tcgen05.st) rarely; the final O / l is exact either way.
+// Attention over the paged cache on the 5th-generation tensor cores: a prefill kernel (portions of
+// many tokens) and a decode kernel (few tokens per request, keys split into ranges and planned once
+// per step).  Common to both: key/value pages arrive by TMA (cp.async.bulk.tensor, 128-byte swizzle,
+// one box per page and 64-column half) in rings of shared-memory stages guarded by mbarriers; every
+// tcgen05.mma is issued by one thread of an issuer warp and frees its stages with tcgen05.commit; the
+// roles meet only through mbarriers; S = Q K^T, P and O live in tensor memory; the softmax of a row
+// runs in registers (float32, base 2), and the running maximum is only moved when it grows by more
+// than 2^8, so O is rescaled (tcgen05.ld / tcgen05.st) rarely; the final O / l is exact either way.
 // Value rows outside the request's visible keys are zeroed in shared memory before they are
 // multiplied, so stale or poisoned pages cannot reach a result.  Every mbarrier wait is bounded
 // (XB_ERR_WAIT in the error word on expiry, then the CTA frees its TMEM and leaves).
@@ -28,370 +21,30 @@ constexpr int QT = 128;  // queries per CTA
 constexpr int KT = 64;   // keys per tile
 constexpr float RESCALE_STEP = 8.f;  // the row maximum moves only when it grows by more than 2^8
 
-// DP: head size padded to 64 or 128.  Shared memory (1024-byte aligned):
-//   Q  [DP/64][128 rows][64]   K stage s [DP/64][64 keys][64]   V stage s likewise   P [128][64]
-// every [rows][64] piece is a tile of 128-byte rows whose 16-byte chunks are XOR-ed with row & 7.
-// Warps 0..3: one query row per thread (softmax).  Warps 4 and 6: TMA producers of keys and of values.
-// Warp 5: MMA issuer.
-// Tensor memory: S[0] at column 0, S[1] at 64, O at 128.
-template <int DP>
-__global__ void __launch_bounds__(224)
-attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                       const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
-                       const int* __restrict__ q_start, const int* __restrict__ start_pos, int num_entries,
-                       const int* __restrict__ block_table, int table_stride, int nh, int nkv, int d, int ps,
-                       int ps_shift, int num_pages, int window, float scale_log2, int dec_max,
-                       const int* __restrict__ tile_map, int* err) {
-    constexpr int HALVES = DP / 64;
-    constexpr uint32_t Q_BYTES = HALVES * QT * 128, KV_HALF = KT * 128, KV_BYTES = HALVES * KV_HALF;
-    constexpr uint32_t STAGE_BYTES = 2 * KV_BYTES, P_BYTES = QT * 128;
-    extern __shared__ __align__(1024) unsigned char smem_raw[];
-    const uint32_t base = smem_u32(smem_raw);
-    const uint32_t q_sm = base, kv_sm = base + Q_BYTES, p_sm = kv_sm + 2 * STAGE_BYTES;
-    unsigned char* p_ptr = smem_raw + Q_BYTES + 2 * STAGE_BYTES;
-    // barriers, 8 bytes each: k_full[2] k_empty[2] v_full[2] v_empty[2] s_ready[2] s_free[2] q_full p_ready bar_o;
-    // then four words
-    const uint32_t bars = p_sm + P_BYTES;
-    const uint32_t k_full0 = bars, k_empty0 = bars + 16, v_full0 = bars + 32, v_empty0 = bars + 48;
-    const uint32_t s_ready0 = bars + 64, s_free0 = bars + 80;
-    const uint32_t q_full = bars + 96, p_ready = bars + 104, bar_o = bars + 112;
-    volatile uint32_t* words = reinterpret_cast<volatile uint32_t*>(p_ptr + P_BYTES + 120);  // tmem, entry, tile, dead
-    const int warp = threadIdx.x >> 5;
-    const int h = blockIdx.x, g = h / (nh / nkv);   // heads vary fastest: every head's longest tiles start first
-    pdl_launch_dependents();
-    pdl_wait();
-
-    if (threadIdx.x == 0) {
-        if (base & 1023u) atomicOr(err, XB_ERR_WAIT);  // the swizzle needs a 1024-byte aligned window
-        int acc = 0, found = -1, tile = 0;
-        if (tile_map) {   // (portion, query tile) of every block row, made by the host: longest first over all portions
-            found = tile_map[2 * blockIdx.y];
-            tile = tile_map[2 * blockIdx.y + 1];
-        } else {
-            for (int b = 0; b < num_entries; ++b) {
-                const int n = q_start[b + 1] - q_start[b];
-                if (n > dec_max) {
-                    const int nt = (n + QT - 1) / QT;
-                    if ((int)blockIdx.y < acc + nt) {
-                        found = b;
-                        tile = nt - 1 - ((int)blockIdx.y - acc);  // a portion's last (longest) tiles first
-                        break;
-                    }
-                    acc += nt;
-                }
-            }
-        }
-        if (*reinterpret_cast<volatile int*>(err) & XB_ERR_WAIT) found = -1;  // an earlier CTA gave up: do not pile on
-        words[1] = (uint32_t)found;
-        words[2] = (uint32_t)tile;
-        words[3] = 0;
-        for (int i = 0; i < 10; ++i) mbar_init(bars + 8 * i, 1);   // k_full, k_empty, v_full, v_empty, s_ready
-        mbar_init(s_free0, 128);
-        mbar_init(s_free0 + 8, 128);
-        mbar_init(q_full, 1);
-        mbar_init(p_ready, 128);
-        mbar_init(bar_o, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-    const int b = (int)words[1];
-    if (b < 0 || (base & 1023u)) return;
-    constexpr uint32_t TMEM_COLS = 256;
-    if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t*>(&words[0]))), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem = words[0];
-    const uint32_t tmem_s = tmem, tmem_o = tmem + 128;
-
-    const int n = q_start[b + 1] - q_start[b];
-    const int row0 = (int)words[2] * QT;
-    const int rows = min(QT, n - row0);
-    const int t0 = q_start[b] + row0;
-    const int p0 = start_pos[b] + row0;
-    const int last_key = p0 + rows - 1;
-    const int first_key = window > 0 ? max(0, p0 - window + 1) : 0;
-    const int* table = block_table + (size_t)b * table_stride;
-    const int kt_first = first_key / KT, kt_last = last_key / KT;
-    const int iters = kt_last - kt_first + 1;
-    const int box_rows = ps < KT ? ps : KT;
-
-    if (warp == 4 || warp == 6) {
-        // ---- producers: warp 4 streams Q once and then the key pages, warp 6 the value pages, each through
-        // its own two-stage ring: a key stage is free again after its Q K^T, a value stage only after its
-        // P V, two steps later, so keys can be requested that much earlier
-        const bool is_v = warp == 6;
-        const uint32_t full0 = is_v ? v_full0 : k_full0, empty0 = is_v ? v_empty0 : k_empty0;
-        const CUtensorMap* map = is_v ? &map_v : &map_k;
-        if ((threadIdx.x & 31) == 0) {
-            if (!is_v) {
-                mbar_expect_tx(q_full, Q_BYTES);
-#pragma unroll
-                for (int hf = 0; hf < HALVES; ++hf) tma_load_3d(q_sm + hf * QT * 128, &map_q, hf * 64, h, t0, q_full);
-            }
-            for (int it = 0; it < iters; ++it) {
-                const int s = it & 1, kt = kt_first + it;
-                if (it >= 2 && !mbar_wait(empty0 + 8 * s, ((it >> 1) - 1) & 1, err)) {
-                    words[3] = 1;
-                    break;
-                }
-                const uint32_t dst0 = kv_sm + s * STAGE_BYTES + (is_v ? KV_BYTES : 0u);
-                uint32_t bytes = 0;
-                int pages[KT / 8];
-                for (int i = 0; i < KT / box_rows; ++i) {
-                    const int j = kt * KT + i * box_rows;
-                    pages[i] = -1;
-                    if (j > last_key || j + box_rows - 1 < first_key) continue;
-                    const int page = table[j >> ps_shift];
-                    if (page < 0 || page >= num_pages) {
-                        atomicOr(err, XB_ERR_BAD_PAGE);
-                        continue;
-                    }
-                    pages[i] = page;
-                    bytes += HALVES * box_rows * 128;
-                }
-                mbar_expect_tx(full0 + 8 * s, bytes);
-                for (int i = 0; i < KT / box_rows; ++i) {
-                    if (pages[i] < 0) continue;
-                    const int j = kt * KT + i * box_rows;
-                    const int grow = (pages[i] * nkv + g) * ps + (j & (ps - 1));
-#pragma unroll
-                    for (int hf = 0; hf < HALVES; ++hf)
-                        tma_load_2d(dst0 + hf * KV_HALF + i * box_rows * 128, map, hf * 64, grow, full0 + 8 * s);
-                }
-            }
-        }
-    } else if (warp == 5) {
-        // ---- MMA issuer: QK(0), then for every tile QK(next) before PV(this) ----------------------------
-        if (threadIdx.x == 160) {
-            const uint32_t idesc_s = umma_idesc(KT, 0), idesc_o = umma_idesc(DP, 1);
-            // operand descriptors differ only in their start address (bits 0..13, in 16-byte units)
-            const uint64_t dq0 = umma_desc(q_sm, 16, 1024), dk0 = umma_desc(kv_sm, 16, 1024);
-            const uint64_t dp0 = umma_desc(p_sm, 16, 1024), dv0 = umma_desc(kv_sm + KV_BYTES, KV_HALF, 1024);
-            auto issue_qk = [&](int it) -> bool {   // S[it & 1] = Q K^T of tile `it`
-                const int sb = it & 1;
-                if (!mbar_wait(k_full0 + 8 * sb, (it >> 1) & 1, err)) return false;
-                if (it >= 2 && !mbar_wait(s_free0 + 8 * sb, ((it >> 1) - 1) & 1, err)) return false;  // every row of S[sb] was read
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t dk = dk0 + (uint64_t)((sb * STAGE_BYTES) >> 4);
-#pragma unroll
-                for (int kk = 0; kk < DP / 16; ++kk) {
-                    const uint32_t off = (kk >> 2), inner = (kk & 3) * 32;
-                    umma_bf16(tmem_s + (uint32_t)sb * 64, dq0 + (uint64_t)((off * QT * 128 + inner) >> 4),
-                              dk + (uint64_t)((off * KV_HALF + inner) >> 4), idesc_s, kk ? 1u : 0u);
-                }
-                umma_commit(k_empty0 + 8 * sb);   // the key stage is free once these have completed
-                umma_commit(s_ready0 + 8 * sb);
-                return true;
-            };
-            bool ok = mbar_wait(q_full, 0, err) && issue_qk(0);
-            for (int it = 0; it < iters && ok; ++it) {
-                const int s = it & 1;
-                if (it + 1 < iters) ok = issue_qk(it + 1);
-                ok = ok && mbar_wait(v_full0 + 8 * s, (it >> 1) & 1, err);
-                ok = ok && mbar_wait(p_ready, it & 1, err);   // P written, V rows zeroed, O rescaled
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                // O += P V : A = P [128 x 64 keys] K-major, B = V [64 keys x DP] MN-major (halves 64 columns apart)
-                const uint64_t dv = dv0 + (uint64_t)((s * STAGE_BYTES) >> 4);
-#pragma unroll
-                for (int kk = 0; kk < KT / 16; ++kk)
-                    umma_bf16(tmem_o, dp0 + (uint64_t)((kk * 32) >> 4), dv + (uint64_t)((kk * 2048) >> 4), idesc_o, (it | kk) ? 1u : 0u);
-                umma_commit(v_empty0 + 8 * s);        // the value stage, P and O are free again once these have completed
-                if (it + 1 == iters) umma_commit(bar_o);
-            }
-            if (!ok) words[3] = 1;
-        }
-    } else {
-        // ---- softmax: one query row per thread ------------------------------------------------------------------
-        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-        const int my_pos = p0 + (int)threadIdx.x;
-        float m_ref = -INFINITY, l = 0.f;
-        bool alive = true;
-        for (int it = 0; it < iters; ++it) {
-            const int s = it & 1, key0 = (kt_first + it) * KT;
-            const uint32_t v_sm = kv_sm + s * STAGE_BYTES + KV_BYTES;
-            // every wait's verdict is made warp-wide: tcgen05.ld / .st below need the whole warp
-            if (!__all_sync(0xffffffffu, mbar_wait(s_ready0 + 8 * s, (it >> 1) & 1, err))) {
-                alive = false;
-                break;
-            }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            float sc[64];
-            {
-                uint32_t ra[32], rb[32];
-                tmem_ld32_nowait(tmem_s + s * 64 + lane_addr, ra);
-                tmem_ld32_nowait(tmem_s + s * 64 + lane_addr + 32, rb);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    sc[i] = __uint_as_float(ra[i]);
-                    sc[32 + i] = __uint_as_float(rb[i]);
-                }
-            }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(s_free0 + 8 * s);   // this row of S[s] is in registers
-            const bool edge = key0 + KT - 1 > p0 || key0 + KT - 1 > last_key || key0 < first_key ||
-                              (window > 0 && key0 < p0 + QT - 1 - window + 1);
-            // the maximum is taken over the raw scores (the scale is positive); four chains, as a thread
-            // has no one to wait for
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-            if (edge) {
-#pragma unroll
-                for (int i = 0; i < 64; ++i) {
-                    const int j = key0 + i;
-                    const bool ok = j <= my_pos && j <= last_key && (window <= 0 || j > my_pos - window);
-                    sc[i] = ok ? sc[i] : -INFINITY;
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < 64; i += 8) {
-                mx4[0] = max3(mx4[0], sc[i], sc[i + 1]);
-                mx4[1] = max3(mx4[1], sc[i + 2], sc[i + 3]);
-                mx4[2] = max3(mx4[2], sc[i + 4], sc[i + 5]);
-                mx4[3] = max3(mx4[3], sc[i + 6], sc[i + 7]);
-            }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
-            // move the reference maximum only when the row's maximum outgrows it by more than 2^8
-            float corr = 1.f;
-            int moved = 0;
-            if (mx > m_ref + RESCALE_STEP) {
-                corr = m_ref == -INFINITY ? 0.f : ex2(m_ref - mx);
-                m_ref = mx;
-                moved = it > 0;
-            }
-            const float m_neg = m_ref == -INFINITY ? 0.f : -m_ref;
-            // 2^(s * scale - m): the argument by packed FMAs (two per instruction); of every eight
-            // exponentials six go to the special-function unit and two to a polynomial on the FMA pipe, so
-            // that neither unit alone sets the pace; the row sum by packed adds
-            const f32x2 scale2 = pack2(scale_log2, scale_log2), mneg2 = pack2(m_neg, m_neg);
-            f32x2 sum_a = pack2(0.f, 0.f), sum_b = pack2(0.f, 0.f);
-            uint4 pk[8];
-#pragma unroll
-            for (int c8 = 0; c8 < 8; ++c8) {
-                float x[8], e[8];
-#pragma unroll
-                for (int i = 0; i < 8; i += 2)
-                    unpack2(fma2(pack2(sc[c8 * 8 + i], sc[c8 * 8 + i + 1]), scale2, mneg2), x[i], x[i + 1]);
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    if ((i & 3) != 3) e[i] = ex2(x[i]);
-                ex2_poly2(x[3], x[7], e[3], e[7]);
-                sum_a = add2(sum_a, add2(pack2(e[0], e[1]), pack2(e[2], e[3])));
-                sum_b = add2(sum_b, add2(pack2(e[4], e[5]), pack2(e[6], e[7])));
-                pk[c8].x = pack_bf16(e[0], e[1]);
-                pk[c8].y = pack_bf16(e[2], e[3]);
-                pk[c8].z = pack_bf16(e[4], e[5]);
-                pk[c8].w = pack_bf16(e[6], e[7]);
-            }
-            float s0, s1, s2, s3;
-            unpack2(sum_a, s0, s1);
-            unpack2(sum_b, s2, s3);
-            l = l * corr + ((s0 + s1) + (s2 + s3));
-            // P and O belong to the previous tile's P V until it has completed
-            if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(v_empty0 + 8 * (s ^ 1), ((it - 1) >> 1) & 1, err))) {
-                alive = false;
-                break;
-            }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            unsigned char* prow = p_ptr + threadIdx.x * 128;
-#pragma unroll
-            for (int c8 = 0; c8 < 8; ++c8) *reinterpret_cast<uint4*>(prow + ((c8 ^ (threadIdx.x & 7)) << 4)) = pk[c8];
-            // value rows outside the visible keys become zeros (only tiles at the ends of the range)
-            if (key0 < first_key || key0 + KT - 1 > last_key) {
-                if (threadIdx.x < KT) {
-                    mbar_wait(v_full0 + 8 * s, (it >> 1) & 1, err);   // orders these writes after the TMA's
-                    const int j = key0 + (int)threadIdx.x;
-                    if (j < first_key || j > last_key) {
-#pragma unroll
-                        for (int hf = 0; hf < HALVES; ++hf) {
-                            uint4* vr = reinterpret_cast<uint4*>(smem_raw + (v_sm - base) + hf * KV_HALF + threadIdx.x * 128);
-#pragma unroll
-                            for (int c8 = 0; c8 < 8; ++c8) vr[c8] = make_uint4(0, 0, 0, 0);
-                        }
-                    }
-                }
-            }
-            // rescale O where a row's reference maximum moved (rare after the first tiles); tcgen05.ld / .st
-            // are warp-wide: a warp rescales when any of its rows moved, the other rows by 1
-            if (__any_sync(0xffffffffu, moved)) {
-                const float f = moved ? corr : 1.f;
-#pragma unroll
-                for (int c0 = 0; c0 < DP; c0 += 32) {
-                    float o[32];
-                    tmem_ld32(tmem_o + lane_addr + c0, o);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] *= f;
-                    tmem_st32(tmem_o + lane_addr + c0, o);
-                }
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P and zeroed V rows: visible to the MMA
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(p_ready);
-        }
-        // ---- O / l -> out -----------------------------------------------------------------------------------
-        if (alive) alive = mbar_wait(bar_o, 0, err);
-        alive = __all_sync(0xffffffffu, alive);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (alive) {
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            const bool valid = (int)threadIdx.x < rows;
-            __nv_bfloat16* dst = out + ((size_t)(t0 + (int)threadIdx.x) * nh + h) * d;
-#pragma unroll
-            for (int c0 = 0; c0 < DP; c0 += 32) {
-                float o[32];
-                tmem_ld32(tmem_o + lane_addr + c0, o);   // warp-wide, whatever `valid` is
-                if (valid) {
-#pragma unroll
-                    for (int c8 = 0; c8 < 4; ++c8) {
-                        const int c = c0 + c8 * 8;
-                        if (c < d) {
-                            uint4 pk;
-                            pk.x = pack_bf16(o[c8 * 8] * inv, o[c8 * 8 + 1] * inv);
-                            pk.y = pack_bf16(o[c8 * 8 + 2] * inv, o[c8 * 8 + 3] * inv);
-                            pk.z = pack_bf16(o[c8 * 8 + 4] * inv, o[c8 * 8 + 5] * inv);
-                            pk.w = pack_bf16(o[c8 * 8 + 6] * inv, o[c8 * 8 + 7] * inv);
-                            *reinterpret_cast<uint4*>(dst + c) = pk;
-                        }
-                    }
-                }
-            }
-        } else {
-            words[3] = 1;
-        }
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (warp == 0) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
-    }
-}
-
 // ------------------------------------------------------------------------------------------------
-// prefill, two heads per CTA
+// prefill: 128 queries of two query heads per CTA
 // ------------------------------------------------------------------------------------------------
-// The kernel above reads every key/value tile once per 128 queries and head; with long contexts that
-// traffic (a tile per 4 MFLOP) is what the L2 can deliver, and its two-stage rings are shorter than
-// a tile's way from memory.  Here a CTA owns the same 128 queries of TWO query heads that share
-// their key/value head, so a tile is loaded once for both and the rings are four stages deep:
+// A CTA owns 128 queries of one request's portion for TWO query heads that share their key/value head,
+// so a key/value tile is loaded once for both (a tile per 8 MFLOP instead of 4) and the rings are four
+// stages deep (a tile's way from memory is longer than two):
 //   warps 0..3: softmax of head A (one row per thread), warps 4..7: softmax of head B,
 //   warp 8: TMA producer of Q (both heads) and of the key pages, warp 10: of the value pages (one lane
 //   per page box; the page ids of the next tile are fetched while this one is issued),
 //   warp 9: issues S_A, S_B = Q K^T of every tile; warp 11: issues O_A += P_A V and O_B += P_B V (two
 //   issuers, so that the waits of one do not hold up the products of the other; P lies in tensor memory
 //   over the scores it came from, so the first waits for the second before it reuses a score buffer).
+// Shared memory (1024-byte aligned): Q [2 heads][DP/64][128 rows][64], then four stages of K and V
+// [DP/64][64 keys][64]; every [rows][64] piece is a tile of 128-byte rows whose 16-byte chunks are
+// XOR-ed with row & 7.  Full output tiles leave through the space of Q and TMA stores.
 // Tensor memory (all 512 columns): S_A[0], S_A[1], S_B[0], S_B[1] at 0, 64, 128, 192; O_A at 256, O_B at 384.
-// One CTA per SM.  Needs an even number of query heads per key/value head.
+// One CTA per SM.  With an odd number of query heads per key/value head the last CTA of the group has
+// one head and its second softmax warpgroup idles.
 constexpr int PF2_STAGES = 4;
 constexpr int PF2_THREADS = 384;
 
 template <int DP>
 __global__ void __launch_bounds__(PF2_THREADS)
-attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
                         __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ q_start, const int* __restrict__ start_pos, int num_entries,
@@ -414,7 +67,10 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     volatile uint32_t* words = reinterpret_cast<volatile uint32_t*>(smem_raw + BAR_OFF + 240);  // tmem, entry, tile, dead
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = nh / nkv;
-    const int h0 = 2 * (int)blockIdx.x, g = h0 / G;   // heads vary fastest: every pair's longest tiles start first
+    // a key/value head's query heads are taken two at a time; the last CTA of an odd number has one (nhd = 1)
+    const int per_group = (G + 1) / 2;
+    const int g = (int)blockIdx.x / per_group, pair = (int)blockIdx.x % per_group;
+    const int h0 = g * G + 2 * pair, nhd = 2 * pair + 1 < G ? 2 : 1;   // heads vary fastest: the longest tiles start first
     pdl_launch_dependents();
 
     // what follows until the wait reads only what the host sent before the step's first kernel
@@ -485,9 +141,8 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const uint32_t full0 = is_v ? v_full0 : k_full0, empty0 = is_v ? v_empty0 : k_empty0;
         const CUtensorMap* map = is_v ? &map_v : &map_k;
         if (!is_v && lane == 0) {
-            mbar_expect_tx(q_full, Q_BYTES);
-#pragma unroll
-            for (int hd = 0; hd < 2; ++hd)
+            mbar_expect_tx(q_full, (uint32_t)nhd * Q_ONE);
+            for (int hd = 0; hd < nhd; ++hd)
 #pragma unroll
                 for (int hf = 0; hf < HALVES; ++hf)
                     tma_load_3d(q_sm + hd * Q_ONE + hf * QT * 128, &map_q, hf * 64, h0 + hd, t0, q_full);
@@ -534,6 +189,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 const uint64_t dk = dk0 + (uint64_t)((s * STAGE_BYTES) >> 4);
 #pragma unroll
                 for (int hd = 0; hd < 2; ++hd) {
+                    if (hd >= nhd) break;
                     // S[sb] of this head held the scores and then P of tile it - 2: its P V must have read it
                     ok = ok && (it < 2 || mbar_wait(pv_done0 + 8 * (2 * hd + sb), ((it >> 1) - 1) & 1, err, true));
                     if (!ok) break;
@@ -564,6 +220,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 const uint64_t dv = dv0 + (uint64_t)((s * STAGE_BYTES) >> 4);
 #pragma unroll
                 for (int hd = 0; hd < 2; ++hd) {
+                    if (hd >= nhd) break;
                     ok = ok && mbar_wait(p_ready0 + 8 * hd, it & 1, err, true);   // P written, V rows zeroed, O rescaled
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -582,7 +239,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             }
             if (!ok) words[3] = 1;
         }
-    } else if (warp < 8) {
+    } else if (warp < 4 * nhd) {
         // ---- softmax: one query row per thread, warps 0..3 for the first head, 4..7 for the second -------------
         const int hd = warp >> 2, r = (int)threadIdx.x & 127;
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
@@ -1327,28 +984,15 @@ bool map_q3(CUtensorMap* out, const void* ptr, long long T, int nh, int d, int b
 }
 
 template <int DP>
-int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, const int* q_start,
-           const int* start_pos, int num_entries, const int* table, int stride, int nh, int nkv, int d, int ps,
-           int ps_shift, int num_pages, int window, float sl2, int dec_max, int tiles, const int* tile_map, int* err,
-           cudaStream_t stream) {
-    constexpr size_t smem = (size_t)(DP / 64) * QT * 128 + 2 * 2 * (size_t)(DP / 64) * KT * 128 + QT * 128 + 144;
-    cudaFuncSetAttribute(attn_prefill_tc_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    cudaFuncSetAttribute(attn_prefill_tc_kernel<DP>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    return xb_launch(attn_prefill_tc_kernel<DP>, dim3(nh, tiles), dim3(224), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
-                     q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, ps_shift, num_pages, window, sl2,
-                     dec_max, tile_map, err);
-}
-
-template <int DP>
-int launch_pairs(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, void* out,
+int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, void* out,
                  const int* q_start,
                  const int* start_pos, int num_entries, const int* table, int stride, int nh, int nkv, int d, int ps,
                  int ps_shift, int num_pages, int window, float sl2, int dec_max, int tiles, const int* tile_map, int* err,
                  cudaStream_t stream) {
     constexpr size_t smem = 2 * (size_t)(DP / 64) * QT * 128 + PF2_STAGES * 2 * (size_t)(DP / 64) * KT * 128 + 256;
-    cudaFuncSetAttribute(attn_prefill_tc2_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    cudaFuncSetAttribute(attn_prefill_tc2_kernel<DP>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    return xb_launch(attn_prefill_tc2_kernel<DP>, dim3(nh / 2, tiles), dim3(PF2_THREADS), smem, stream, mq, mk, mv, mo,
+    cudaFuncSetAttribute(attn_prefill_tc_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(attn_prefill_tc_kernel<DP>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    return xb_launch(attn_prefill_tc_kernel<DP>, dim3(nkv * ((nh / nkv + 1) / 2), tiles), dim3(PF2_THREADS), smem, stream, mq, mk, mv, mo,
                      (__nv_bfloat16*)out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, ps_shift, num_pages,
                      window, sl2, dec_max, tile_map, err);
 }
@@ -1371,41 +1015,32 @@ int launch_decode(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
 
 }  // namespace
 
-// Portions of more than dec_max tokens, 128 queries per CTA; `tiles` = sum over those portions of
-// ceil(tokens / 128); `tokens` = rows of q.  Returns cudaErrorNotSupported (having done nothing)
-// for a head size over 128 or not a multiple of 16, or a page size that is no power of two >= 8.
-// `pairs` != 0: two query heads of a key/value head per CTA where their number is even (else, and
-// with 0, one head per CTA).  `tile_map`: null, or 2 * tiles int32 that give every block row its
-// (portion, query tile), so that the longest tiles of all portions start first and no block searches.
+// Portions of more than dec_max tokens, 128 queries of two query heads per CTA; `tiles` = sum over
+// those portions of ceil(tokens / 128); `tokens` = rows of q.  `tile_map`: null, or 2 * tiles int32 that
+// give every block row its (portion, query tile), so that the longest tiles of all portions start
+// first and no block searches.  Returns cudaErrorNotSupported (having done nothing) for a head size
+// over 128 or not a multiple of 16, or a page size that is no power of two >= 8.
 XB_EXPORT int xb_attn_prefill_tc(void* out, const void* q, const void* kc, const void* vc, const int* q_start,
                                  const int* start_pos, int num_entries, const int* table, int stride, int tokens,
                                  int nh, int nkv, int d, int ps, int num_pages, int window, float scale, int dec_max,
-                                 int tiles, int pairs, const int* tile_map, int* err, cudaStream_t stream) {
+                                 int tiles, const int* tile_map, int* err, cudaStream_t stream) {
     if (tiles <= 0) return 0;
     int shift = -1;
     for (int s = 3; s < 20; ++s)
         if ((1 << s) == ps) shift = s;
     if (d % 16 || d > 128 || d < 16 || nh % nkv || shift < 0) return (int)cudaErrorNotSupported;
-    CUtensorMap mq, mk, mv;
+    CUtensorMap mq, mk, mv, mo;   // out has the layout of q; a warp stores its 32 rows
     const long long rows = (long long)num_pages * nkv * ps;
     const int box_rows = ps < KT ? ps : KT;
-    if (!map_q3(&mq, q, tokens, nh, d, 1, QT) || !map_rows(&mk, kc, rows, d, box_rows) || !map_rows(&mv, vc, rows, d, box_rows))
+    if (!map_q3(&mq, q, tokens, nh, d, 1, QT) || !map_q3(&mo, out, tokens, nh, d, 1, 32) || !map_rows(&mk, kc, rows, d, box_rows) ||
+        !map_rows(&mv, vc, rows, d, box_rows))
         return (int)cudaErrorNotSupported;
     const float sl2 = scale * 1.4426950408889634f;
-    if (pairs && (nh / nkv) % 2 == 0) {
-        CUtensorMap mo;   // out has the layout of q
-        if (!map_q3(&mo, out, tokens, nh, d, 1, 32)) return (int)cudaErrorNotSupported;
-        if (d <= 64)
-            return launch_pairs<64>(mq, mk, mv, mo, out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, shift,
-                                    num_pages, window, sl2, dec_max, tiles, tile_map, err, stream);
-        return launch_pairs<128>(mq, mk, mv, mo, out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, shift,
-                                 num_pages, window, sl2, dec_max, tiles, tile_map, err, stream);
-    }
     if (d <= 64)
-        return launch<64>(mq, mk, mv, out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, shift, num_pages,
-                          window, sl2, dec_max, tiles, tile_map, err, stream);
-    return launch<128>(mq, mk, mv, out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, shift, num_pages,
-                       window, sl2, dec_max, tiles, tile_map, err, stream);
+        return launch_prefill<64>(mq, mk, mv, mo, out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, shift,
+                                  num_pages, window, sl2, dec_max, tiles, tile_map, err, stream);
+    return launch_prefill<128>(mq, mk, mv, mo, out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, shift,
+                               num_pages, window, sl2, dec_max, tiles, tile_map, err, stream);
 }
 // int32 a plan for `tokens` small tokens and `ctas` target CTAs must hold.
 XB_EXPORT long long xb_attn_decode_plan_size(int tokens, int ctas, int nkv) {

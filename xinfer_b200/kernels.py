@@ -491,13 +491,13 @@ def gemm_skinny_qkv(q_out, k_cache, v_cache, x, w_qkv, q_w, k_w, cos_t, sin_t, p
 
 
 def attn_prefill_tc(out, q, k_cache, v_cache, q_start, start_pos, num_entries, block_table, table_stride,
-                    window, scale, dec_max, tiles, err, pairs: bool = True, tile_map: Optional[torch.Tensor] = None) -> bool:
-    """Prefill attention on tcgen05 (TMA-fed, accumulators in tensor memory): portions of more than
-    ``dec_max`` tokens, 128 queries per CTA; ``tiles`` = sum over them of ceil(tokens / 128).
-    ``pairs``: a CTA takes two query heads of a key/value head (when their number is even), so a
-    key/value tile is loaded once for both.  ``tile_map``: int32 [tiles, 2], the (portion, query
-    tile) of every block row (longest first); without it every block searches ``q_start``.  Returns False, having done nothing, for sizes it does not take (head size over 128, page size
-    not a power of two from 8)."""
+                    window, scale, dec_max, tiles, err, tile_map: Optional[torch.Tensor] = None) -> bool:
+    """Prefill attention on tcgen05 (TMA-fed; scores, probabilities and accumulators in tensor memory):
+    portions of more than ``dec_max`` tokens, 128 queries of two query heads of a key/value head per
+    CTA; ``tiles`` = sum over the portions of ceil(tokens / 128).  ``tile_map``: int32 [tiles, 2], the
+    (portion, query tile) of every block row (longest first); without it every block searches
+    ``q_start``.  Returns False, having done nothing, for sizes it does not take (head size over 128,
+    page size not a power of two from 8)."""
     T, nh, d = q.shape
     _need(q, "q", torch.bfloat16, (T, nh, d))
     _need(out, "out", torch.bfloat16, (T, nh, d))
@@ -509,7 +509,7 @@ def attn_prefill_tc(out, q, k_cache, v_cache, q_start, start_pos, num_entries, b
     rc = kernels_lib().xb_attn_prefill_tc(
         out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), q_start.data_ptr(), start_pos.data_ptr(),
         int(num_entries), block_table.data_ptr(), int(table_stride), T, nh, nkv, d, ps, num_pages, int(window or 0),
-        float(scale), int(dec_max), int(tiles), int(bool(pairs)), _ptr(tile_map), err.data_ptr(), _stream())
+        float(scale), int(dec_max), int(tiles), _ptr(tile_map), err.data_ptr(), _stream())
     if rc == ERR_NOT_SUPPORTED:
         return False
     _ok(rc, "attn_prefill_tc")

@@ -28,9 +28,6 @@ PREFILL_WARPS = 8
 # portions of many tokens go to the tcgen05 kernel where it takes the sizes (head size <= 128,
 # page size a power of two >= 8), else to the mma.sync kernel
 PREFILL_TC = True
-# ... with two query heads of a key/value head per CTA where their number is even: a key/value tile
-# is then loaded once for both (half the traffic from the L2 per score)
-PREFILL_PAIRS = True
 # the tokens of small portions go to the tcgen05 decode kernel where it takes the sizes (as above,
 # and at most 16 query heads per key/value head), else to the mma.sync kernel
 DECODE_TC = True
@@ -150,8 +147,7 @@ def attend(out, q, cache, ctx, table, stride, window, scale) -> None:
     took = False
     if plan["tiles"] and PREFILL_TC and kernels.attn_prefill_queries(d, PREFILL_WARPS) == 128:
         took = kernels.attn_prefill_tc(out, q, cache.k, cache.v, ctx.q_start, ctx.start_pos, ctx.num_entries, table, stride,
-                                       window, scale, DEC_MAX, plan["tiles"], ctx.err, pairs=PREFILL_PAIRS,
-                                       tile_map=plan.get("tile_map"))
+                                       window, scale, DEC_MAX, plan["tiles"], ctx.err, tile_map=plan.get("tile_map"))
     if plan["tiles"] and not took:
         kernels.attn_prefill_bf16(out, q, cache.k, cache.v, ctx.q_start, ctx.start_pos, ctx.num_entries, table, stride,
                                   window, scale, DEC_MAX, plan["tiles"], plan["prefill_bound"], ctx.err, warps=PREFILL_WARPS)
