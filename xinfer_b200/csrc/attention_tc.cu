@@ -39,27 +39,26 @@ constexpr float RESCALE_STEP = 8.f;  // the row maximum moves only when it grows
 // Tensor memory (all 512 columns): S_A[0], S_A[1], S_B[0], S_B[1] at 0, 64, 128, 192; O_A at 256, O_B at 384.
 // One CTA per SM.  With an odd number of query heads per key/value head the last CTA of the group has
 // one head and its second softmax warpgroup idles.
-constexpr int PF2_STAGES = 4;
-constexpr int PF2_THREADS = 384;
+constexpr int PREFILL_STAGES = 4;
+constexpr int PREFILL_THREADS = 384;
 
 template <int DP>
-__global__ void __launch_bounds__(PF2_THREADS)
+__global__ void __launch_bounds__(PREFILL_THREADS)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
-                        __nv_bfloat16* __restrict__ out,
-                        const int* __restrict__ q_start, const int* __restrict__ start_pos, int num_entries,
-                        const int* __restrict__ block_table, int table_stride, int nh, int nkv, int d, int ps,
-                        int ps_shift, int num_pages, int window, float scale_log2, int dec_max,
-                        const int* __restrict__ tile_map, int* err) {
-    constexpr int HALVES = DP / 64, NS = PF2_STAGES;
-    constexpr uint32_t Q_ONE = HALVES * QT * 128, Q_BYTES = 2 * Q_ONE, P_BYTES = 0;
+                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
+                       __nv_bfloat16* __restrict__ out, const int* __restrict__ q_start, const int* __restrict__ start_pos,
+                       int num_entries, const int* __restrict__ block_table, int table_stride, int nh, int nkv, int d,
+                       int ps, int ps_shift, int num_pages, int window, float scale_log2, int dec_max,
+                       const int* __restrict__ tile_map, int* err) {
+    constexpr int HALVES = DP / 64, NS = PREFILL_STAGES;
+    constexpr uint32_t Q_ONE = HALVES * QT * 128, Q_BYTES = 2 * Q_ONE;
     constexpr uint32_t KV_HALF = KT * 128, KV_BYTES = HALVES * KV_HALF, STAGE_BYTES = 2 * KV_BYTES;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const uint32_t base = smem_u32(smem_raw);
     const uint32_t q_sm = base, kv_sm = base + Q_BYTES;
     // barriers, 8 bytes each: k_full[4] k_empty[4] v_full[4] v_empty[4] s_ready[head][2] pv_done[head][2]
     // p_ready[head] q_full bar_o; then four words
-    constexpr uint32_t BAR_OFF = Q_BYTES + P_BYTES + NS * STAGE_BYTES;
+    constexpr uint32_t BAR_OFF = Q_BYTES + NS * STAGE_BYTES;
     const uint32_t bars = base + BAR_OFF;
     const uint32_t k_full0 = bars, k_empty0 = bars + 32, v_full0 = bars + 64, v_empty0 = bars + 96;
     const uint32_t s_ready0 = bars + 128, pv_done0 = bars + 160, p_ready0 = bars + 192;
@@ -333,7 +332,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     if (j < first_key || j > last_key) {
 #pragma unroll
                         for (int hf = 0; hf < HALVES; ++hf) {
-                            uint4* vr = reinterpret_cast<uint4*>(smem_raw + Q_BYTES + P_BYTES + st * STAGE_BYTES + KV_BYTES + hf * KV_HALF + r * 128);
+                            uint4* vr = reinterpret_cast<uint4*>(smem_raw + Q_BYTES + st * STAGE_BYTES + KV_BYTES + hf * KV_HALF + r * 128);
 #pragma unroll
                             for (int c8 = 0; c8 < 8; ++c8) vr[c8] = make_uint4(0, 0, 0, 0);
                         }
@@ -989,10 +988,10 @@ int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
                  const int* start_pos, int num_entries, const int* table, int stride, int nh, int nkv, int d, int ps,
                  int ps_shift, int num_pages, int window, float sl2, int dec_max, int tiles, const int* tile_map, int* err,
                  cudaStream_t stream) {
-    constexpr size_t smem = 2 * (size_t)(DP / 64) * QT * 128 + PF2_STAGES * 2 * (size_t)(DP / 64) * KT * 128 + 256;
+    constexpr size_t smem = 2 * (size_t)(DP / 64) * QT * 128 + PREFILL_STAGES * 2 * (size_t)(DP / 64) * KT * 128 + 256;
     cudaFuncSetAttribute(attn_prefill_tc_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaFuncSetAttribute(attn_prefill_tc_kernel<DP>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    return xb_launch(attn_prefill_tc_kernel<DP>, dim3(nkv * ((nh / nkv + 1) / 2), tiles), dim3(PF2_THREADS), smem, stream, mq, mk, mv, mo,
+    return xb_launch(attn_prefill_tc_kernel<DP>, dim3(nkv * ((nh / nkv + 1) / 2), tiles), dim3(PREFILL_THREADS), smem, stream, mq, mk, mv, mo,
                      (__nv_bfloat16*)out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, ps_shift, num_pages,
                      window, sl2, dec_max, tile_map, err);
 }
