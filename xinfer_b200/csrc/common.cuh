@@ -59,6 +59,12 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
     return scratch[32];
 }
 
+// silu(g) * u for bfloat16 activations: the exponential and the quotient by the fast intrinsics, whose
+// error (a few units in the last place of float32) is far below half a unit of the bfloat16 result.
+// Every bfloat16 kernel that forms this product uses this function, so that they agree bit for bit;
+// the float32 path divides and exponentiates exactly.
+__device__ __forceinline__ float silu_mul_bf16(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
+
 // Last CUDA error of a launch as an int for the caller (0 = ok).
 static inline int xb_launch_status() { return (int)cudaGetLastError(); }
 

@@ -125,7 +125,7 @@ swiglu_bf16_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restr
                 unpack8(pg[k], g);
                 unpack8(pu[k], u);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) y[e] = g[e] / (1.f + expf(-g[e])) * u[e];
+                for (int e = 0; e < 8; ++e) y[e] = silu_mul_bf16(g[e], u[e]);
                 reinterpret_cast<Pack8*>(out + (size_t)t * inter)[c] = pack8(y);
             }
         }

@@ -217,7 +217,7 @@ gemm_skinny_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 const float g = bf16_round(cluster_sum(part_addr, m * TILE_N + j, csize));
                 const float u = bf16_round(cluster_sum(part_addr, m * TILE_N + TILE_N / 2 + j, csize));
                 const int col = n0 + j;
-                if (col < N) out[(size_t)m * N + col] = from_f32<TO>(g / (1.f + expf(-g)) * u);
+                if (col < N) out[(size_t)m * N + col] = from_f32<TO>(silu_mul_bf16(g, u));
             }
         } else {
             // the first pass uses what was prepared above; more than 16 tokens per rank take further passes

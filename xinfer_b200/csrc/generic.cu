@@ -446,7 +446,7 @@ __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int
     const size_t t = i / inter, c = i % inter;
     const float g = to_f32<T>(gu[t * 2 * inter + c]);
     const float u = to_f32<T>(gu[t * 2 * inter + inter + c]);
-    out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
+    out[i] = from_f32<T>(sizeof(T) == 2 ? silu_mul_bf16(g, u) : g / (1.f + expf(-g)) * u);
 }
 
 XB_EXPORT int xb_swiglu(int dtype, void* out, const void* gu, int tokens, int inter, cudaStream_t stream) {
