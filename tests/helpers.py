@@ -86,11 +86,12 @@ class TraceBuilder:
         self.peak = 0
 
     def step(self, entries, end=()):
-        """entries: list of (id, key, start, tokens, want_all)."""
+        """entries: list of (id, key, start, tokens, want): want is True (every token), False (none) or a
+        list of places among these tokens."""
         n = len(self.steps)
         rows, out = [], []
         for rid, key, start, tokens, want in entries:
-            w = list(range(len(tokens))) if want else []
+            w = list(want) if isinstance(want, (list, tuple)) else (list(range(len(tokens))) if want else [])
             out.append({"id": rid, "tokens": list(tokens), "want": w})
             rows += [(key, start + i) for i in w]
             self.live[rid] = self.live.get(rid, 0) + len(tokens)

@@ -75,3 +75,37 @@ def test_real_layer_sizes_match_the_plain_implementation(name, dtype, sized_fold
             covered[i].add(pos)
     assert covered[0] == set(range(len(whole))) and covered[1] == set(range(len(cut)))
     print(name, dtype, f"worst {worst:.3g} tolerance", [f"{t:.3g}" for t in tol])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_prompt_at_real_layer_sizes(dtype, sized_folder, tmp_path):
+    """900 tokens at the 0.6B layer sizes, whole and in portions that end inside a 128-query tile and
+    inside a 64-key tile: eight query tiles, key/value rings that wrap, cached prefixes of odd lengths."""
+    folder = sized_folder("0.6b")
+    vocab = SHAPES["0.6b"][-1]
+    rng = np.random.default_rng(8)
+    whole = rng.integers(0, vocab, size=900).tolist()
+    cut = rng.integers(0, vocab, size=900).tolist()
+    want_whole = [0, 1, 127, 128, 129, 500, 898, 899]
+    tb = TraceBuilder()
+    tb.step([("w", ("whole", 0), 0, whole, want_whole)])
+    at = 0
+    for n in (300, 77, 523):
+        last = at + n == len(cut)
+        tb.step([("c", ("cut", 1), at, cut[at:at + n], [0, n // 2, n - 1])], end=["c"] if last else [])
+        at += n
+    out = run_trace(folder, dtype, tb.steps, str(tmp_path / "out"), max_tokens=tb.peak, page_size=16)
+    cfg, w = plain.load_folder(folder)
+    prompts = [whole, cut]
+    ref = [plain.forward(cfg, w, p).numpy() for p in prompts]
+    if dtype == "float32":
+        tol = [2e-5 * max(1.0, float(np.abs(r).max())) for r in ref]
+    else:
+        tol = [3.0 * np.abs(plain.forward(cfg, w, p, round_to=torch.bfloat16).numpy() - r).max() for p, r in zip(prompts, ref)]
+    checked = 0
+    for step, rows in tb.rows.items():
+        for r, ((mode, i), pos) in enumerate(rows):
+            d = float(np.abs(out[step][r] - ref[i][pos]).max())
+            assert d <= tol[i], f"{dtype} {mode}: position {pos} (step {step}) differs by {d:.3g} > {tol[i]:.3g}"
+            checked += 1
+    assert checked == len(want_whole) + 9
