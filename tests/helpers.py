@@ -164,3 +164,26 @@ def build_all_modes(prompts: List[List[int]], seed: int = 0):
         for rid in ended:
             del live[rid]
     return tb
+
+
+def replay_in_process(runner, steps: List[dict]) -> Dict[int, np.ndarray]:
+    """What bin/trace_run does, inside this process: for models whose parts a test has registered
+    (a child process would not know them).  Returns {step: logits [wanted, vocab]}."""
+    from xinfer_b200.engine.runner import StepInput
+    slots, out = {}, {}
+    for s in steps:
+        entries = []
+        for e in s["entries"]:
+            if e["id"] not in slots:
+                slots[e["id"]] = runner.open_request()
+            entries.append(StepInput(slots[e["id"]], e["tokens"], e.get("want", [])))
+        if entries:
+            logits = runner.step(entries)
+            runner.check_errors()
+            if logits.shape[0]:
+                out[s["step"]] = logits.float().cpu().numpy().copy()
+        for rid in s.get("end", []):
+            if rid in slots:
+                runner.close_request(slots.pop(rid))
+    assert not slots, "every request of a trace must end"
+    return out

@@ -99,7 +99,8 @@ def test_plan_carries_every_constant():
         assert b.mixer.scale == pytest.approx(raw["head_dim"] ** -0.5)
         assert b.mixer.rope.theta == raw["rope_theta"] and b.mixer.rope.max_positions == raw["max_position_embeddings"]
         assert b.mixer.qk_norm and b.mixer.qk_norm_eps == raw["rms_norm_eps"]
-        assert b.norm_in.eps == raw["rms_norm_eps"] == plan.final_norm.eps
+        assert [n.eps for n in b.norms()] == [raw["rms_norm_eps"]] * 2 and plan.final_norm.eps == raw["rms_norm_eps"]
+        assert [o.op for o in b.program] == ["norm", "mixer", "add", "norm", "feed_forward", "add"]
         assert b.feed_forward.intermediate == raw["intermediate_size"]
         assert (plan.head_name is None) == bool(raw["tie_word_embeddings"])
 
@@ -134,3 +135,61 @@ def test_engine_config_validation():
     for bad in (dict(block_size=0), dict(max_num_seqs=-1), dict(kv_fraction=0.0), dict(num_blocks=0)):
         with pytest.raises(ValueError):
             EngineConfig(weight_path="x", **bad).validate()
+
+
+def test_the_longest_sequence_may_not_exceed_the_position_tables():
+    from xinfer_b200.engine.runner import resolve_max_model_len
+    assert resolve_max_model_len(None, 512) == 512
+    assert resolve_max_model_len(200, 512) == 200
+    assert resolve_max_model_len(512, 512) == 512
+    with pytest.raises(ConfigError, match="max_position_embeddings 512"):
+        resolve_max_model_len(513, 512)
+    with pytest.raises(ConfigError, match="positive"):
+        resolve_max_model_len(0, 512)
+
+
+def test_a_block_is_a_program_and_bad_programs_are_refused():
+    from xinfer_b200.config import BlockOp, BlockSpec, FeedForwardSpec, NormSpec, pre_norm_block
+    from xinfer_b200.config.plan import PartSpec
+    n = NormSpec(kind="rmsnorm", dim=8)
+    m, f = PartSpec(kind="some_mixer"), FeedForwardSpec(kind="swiglu", hidden=8, intermediate=16)
+    b = pre_norm_block("l.", n, m, n, f)
+    b.validate()
+    assert b.mixer is m and b.feed_forward is f and len(b.norms()) == 2
+    assert [o.name for o in b.program if o.spec is not None] == ["input_layernorm.", "self_attn.", "post_attention_layernorm.", "mlp."]
+    # no feed-forward, no mixer: both are fine
+    BlockSpec("l.", (BlockOp("norm", "x", "h", n, "n."), BlockOp("mixer", "h", "a", m, "m."), BlockOp("add", "a", "x"))).validate()
+    only_ffn = BlockSpec("l.", (BlockOp("feed_forward", "x", "f", f, "f."), BlockOp("add", "f", "x")))
+    only_ffn.validate()
+    assert only_ffn.mixer is None
+    bad = [
+        (BlockOp("norm", "y", "h", n, "n."),),                                        # reads what nothing produced
+        (BlockOp("add", "x", "y"),),                                                  # adds into what nothing produced
+        (BlockOp("add", "x", "x"),),                                                  # a value to itself
+        (BlockOp("mixer", "x", "x", m, "m."),),                                       # a part over its own input
+        (BlockOp("norm", "x", "h", None, "n."),),                                     # no spec
+        (BlockOp("gate", "x", "h", n, "n."),),                                        # unknown operation
+        (BlockOp("mixer", "x", "a", m, "m1."), BlockOp("mixer", "x", "b", m, "m2.")),   # two mixers
+    ]
+    for prog in bad:
+        with pytest.raises(ValueError):
+            BlockSpec("l.", prog).validate()
+
+
+def test_nvtx_ranges_follow_the_flag():
+    from xinfer_b200 import tracing
+    calls = []
+    was = tracing.ENABLED
+    try:
+        tracing.enable(True, push=lambda name: calls.append(("push", name)), pop=lambda: calls.append(("pop",)))
+        tracing.push("decode step")
+        tracing.pop()
+        assert calls == [("push", "decode step"), ("pop",)]
+        tracing.enable(False)
+        tracing.push("nothing")
+        tracing.pop()
+        assert len(calls) == 2 and not tracing.ENABLED
+    finally:
+        tracing.enable(was)
+    assert tracing.step_kind([1, 1, 1]) == "decode" and tracing.step_kind([5, 9]) == "prefill"
+    assert tracing.step_kind([1, 7]) == "mixed"

@@ -313,7 +313,7 @@ def tiled_kernel(out, q, kc, vc, pos, req, table, stride, window, scale, e, entr
                           h_start_pos=np.asarray([s for s, _ in entries], dtype=np.int32),
                           max_context=max(s + c for s, c in entries), fixed_shapes=False, scratch={},
                           workspace=Workspace(dev()), err=e)
-    cache = LayerCache(kc, vc, 0, kc.shape[2])
+    cache = LayerCache.of_keys_and_values(kc, vc, 0, kc.shape[2])
     attention_backend.attend(out, q, cache, ctx, table, stride, window, scale)
 
 

@@ -19,9 +19,9 @@ class FakeStore:
     def __init__(self, tensors):
         self.tensors = tensors
 
-    def get(self, name, device, compute_dtype):
+    def get(self, name, device, compute_dtype, operand=False):
         t = self.tensors[name]
-        if compute_dtype == torch.float32 or t.dtype == torch.float32:
+        if compute_dtype == torch.float32 or (t.dtype == torch.float32 and not operand):
             return t.to(device).float().contiguous()
         return t.to(device).to(torch.bfloat16).contiguous()
 
@@ -102,7 +102,7 @@ def test_attention_part_in_portions(dtype, nh, nkv, d, window, page):
     need = part.cache_need()
     assert (need.kv_heads, need.head_dim, need.window) == (nkv, d, window)
     cm, asm = context(None, dtype, page=page, pages=40, window=window)
-    cache = LayerCache(torch.zeros(40, nkv, page, d, dtype=dtype, device=DEV), torch.zeros(40, nkv, page, d, dtype=dtype, device=DEV), 0, page)
+    cache = LayerCache.of_keys_and_values(torch.zeros(40, nkv, page, d, dtype=dtype, device=DEV), torch.zeros(40, nkv, page, d, dtype=dtype, device=DEV), 0, page)
     x = (torch.randn(T, H)).to(dtype)
     slot = cm.open_request()
     outs, at = [], 0

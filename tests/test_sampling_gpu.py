@@ -73,3 +73,28 @@ def test_distribution_follows_softmax():
     freq = np.bincount(toks, minlength=5) / n
     expect = np.exp(small[0]) / np.exp(small[0]).sum()
     assert np.abs(freq - expect).max() < 0.03
+
+
+@pytest.mark.parametrize("mode", ["topk_topp", "greedy", "top_p_alone"])
+def test_one_sampler_over_shrinking_and_growing_batches(mode):
+    """One sampler (one scratch buffer, laid out for its capacity) serves batches of changing
+    size, as the engine's does while requests end: the counters of a smaller batch must not fall
+    where a larger batch left candidates or partial results."""
+    from xinfer_b200.sampling import Sampler, SamplingParams
+    dev = torch.device("cuda:0")
+    vocab = 5003
+    s = Sampler(dev, max_rows=17)
+    rng = np.random.default_rng(11)
+    if mode == "topk_topp":
+        p = SamplingParams(temperature=0.9, top_k=32, top_p=0.95)
+    elif mode == "top_p_alone":
+        p = SamplingParams(temperature=0.9, top_p=0.9)
+    else:
+        p = SamplingParams()
+    for draw, R in enumerate([8, 7, 3, 1, 17, 16, 9, 17, 2]):
+        logits = np.round(rng.normal(size=(R, vocab)) * 3 * 8).astype(np.float32) / 8
+        seeds = list(range(50, 50 + R))
+        got = s.to_host(s.sample(torch.tensor(logits, device=dev), [p] * R, seeds, [draw] * R)).tolist()
+        want = [plain.sample(logits[r], p.temperature or 0.0, top_k=p.top_k or 0,
+                             top_p=p.top_p if p.top_p is not None else 1.0, seed=seeds[r], draw=draw) for r in range(R)]
+        assert got == want, (R, got, want)

@@ -14,7 +14,7 @@ DEV = "cuda:0"
 
 def register_toy():
     from xinfer_b200.config import register_architecture
-    from xinfer_b200.config.plan import (AttentionSpec, BlockSpec, FeedForwardSpec, LayerRun, ModelPlan, NormSpec,
+    from xinfer_b200.config.plan import (AttentionSpec, pre_norm_block, FeedForwardSpec, LayerRun, ModelPlan, NormSpec,
                                          PartSpec, RopeSpec)
     from xinfer_b200.parts import Mixer, register_mixer
     from xinfer_b200.parts.linear import linear
@@ -66,7 +66,7 @@ def register_toy():
                                       rope=RopeSpec(kind="rope", head_dim=16, rotary_dim=16, theta=1e4, max_positions=256))
             else:
                 mixer = RunningMeanSpec(kind="running_mean", hidden=H)
-            blocks.append(BlockSpec(prefix=f"model.layers.{i}.", norm_in=NormSpec(kind="rmsnorm", dim=H, eps=1e-6), mixer=mixer,
+            blocks.append(pre_norm_block(prefix=f"model.layers.{i}.", norm_in=NormSpec(kind="rmsnorm", dim=H, eps=1e-6), mixer=mixer,
                                     norm_post=NormSpec(kind="rmsnorm", dim=H, eps=1e-6),
                                     feed_forward=FeedForwardSpec(kind="swiglu", hidden=H, intermediate=2 * H)))
         return ModelPlan(architecture="ToyHybridForTest", vocab_size=V, hidden=H, embed_name="model.embed_tokens.weight",
@@ -129,3 +129,133 @@ def test_toy_state_mixer_is_registered_built_and_stepped(tmp_path):
     finally:
         unregister_architecture("ToyHybridForTest")
         unregister("mixer", "running_mean")
+
+
+def register_decay():
+    """A second toy mixer with state: s <- decay * s + x[t] per request, out[t] = W . s.  For steps of
+    single tokens it takes the requests' slots from the device (``ctx.slots``), so such steps can
+    be captured in a CUDA graph and replayed; it says so with ``graph_safe``."""
+    from xinfer_b200.config import register_architecture
+    from xinfer_b200.config.plan import FeedForwardSpec, LayerRun, ModelPlan, NormSpec, PartSpec, pre_norm_block
+    from xinfer_b200.parts import Mixer, register_mixer
+    from xinfer_b200.parts.linear import linear
+    from xinfer_b200.weights import WeightSpec
+    from dataclasses import dataclass
+
+    @dataclass(frozen=True)
+    class DecaySpec(PartSpec):
+        hidden: int = 0
+        decay: float = 0.5
+
+    class Decay(Mixer):
+        kind = "toy_decay"
+        graph_safe = True
+
+        @classmethod
+        def weight_specs(cls, spec, prefix):
+            return [WeightSpec(prefix + "mix.weight", (spec.hidden, spec.hidden))]
+
+        def load(self, store):
+            self.w = store.get(self.prefix + "mix.weight", self.device, self.dtype, operand=True)
+
+        def state_need(self):
+            return {"s": ((self.spec.hidden,), torch.float32)}
+
+        def forward(self, x, ctx, cache, state, writes_cache=True):
+            T, H = x.shape
+            table = state["s"]                                         # [request slots, H]
+            d = self.spec.decay
+            acc = ctx.workspace.get("toy.decay_s", (T, H), self.dtype)
+            if ctx.fixed_shapes or ctx.all_single:
+                # one token per entry: everything from device tensors (padding entries have slot -1)
+                slots = ctx.slots[:T].long()
+                onehot = (slots[:, None] == torch.arange(table.shape[0], device=x.device)[None, :]).float()   # [T, slots]
+                new = (onehot @ table) * d + x.float()                  # each row: its request's state, or zeros for padding
+                touched = onehot.sum(0) > 0
+                table.copy_(torch.where(touched[:, None], onehot.t() @ new, table))
+                acc.copy_(new.to(self.dtype))
+            else:
+                for b in range(ctx.real_entries):
+                    lo, hi = int(ctx.h_q_start[b]), int(ctx.h_q_start[b + 1])
+                    s = table[int(ctx.h_slots[b])].clone()
+                    for t in range(lo, hi):
+                        s = s * d + x[t].float()
+                        acc[t] = s.to(self.dtype)
+                    table[int(ctx.h_slots[b])] = s
+            out = ctx.workspace.get("toy.decay_out", (T, H), self.dtype)
+            return linear(out, acc, self.w, ctx.err)
+
+    register_mixer("toy_decay", Decay, replace=True)
+
+    def plan_of(raw):
+        H, V = raw["hidden_size"], raw["vocab_size"]
+        norm = lambda: NormSpec(kind="rmsnorm", dim=H, eps=1e-6)
+        blocks = [pre_norm_block(prefix=f"model.layers.{i}.", norm_in=norm(), mixer=DecaySpec(kind="toy_decay", hidden=H, decay=raw["decay"]),
+                                 norm_post=norm(), feed_forward=FeedForwardSpec(kind="swiglu", hidden=H, intermediate=2 * H))
+                  for i in range(raw["layers"])]
+        return ModelPlan(architecture="ToyDecayForTest", vocab_size=V, hidden=H, embed_name="model.embed_tokens.weight",
+                         blocks=tuple(blocks), runs=tuple(LayerRun(i) for i in range(len(blocks))),
+                         final_norm=norm(), final_norm_name="model.norm.", head_name="lm_head.weight", max_positions=256)
+    register_architecture("ToyDecayForTest", lambda raw: dict(raw), plan_of, replace=True)
+
+
+def plain_decay(raw, w, ids, round_to=None):
+    rnd = lambda t: plain._round(t, round_to)
+    T = len(ids)
+    x = plain.embed(ids, w["model.embed_tokens.weight"])
+    for i in range(raw["layers"]):
+        p = f"model.layers.{i}."
+        h = rnd(plain.rms_norm(x, w[p + "input_layernorm.weight"], 1e-6))
+        s, rows = torch.zeros(raw["hidden_size"]), []
+        for t in range(T):
+            s = s * raw["decay"] + h[t].float()
+            rows.append(s)
+        a = rnd(plain.linear(rnd(torch.stack(rows).to(h.dtype)), w[p + "self_attn.mix.weight"]))
+        r1 = rnd(x + a)
+        x = rnd(r1 + plain.mlp_block(rnd(plain.rms_norm(r1, w[p + "post_attention_layernorm.weight"], 1e-6)), w, p + "mlp.", round_to))
+    return plain.linear(rnd(plain.rms_norm(x, w["model.norm.weight"], 1e-6)), w["lm_head.weight"])
+
+
+def test_a_stateful_mixer_that_reads_slots_on_the_device_decodes_from_cuda_graphs(tmp_path):
+    """Decode steps of a model whose mixers keep per-request state are replayed from CUDA graphs:
+    the state rows are addressed through the step's device metadata, the capture's trial runs leave
+    the state as it was, batches shrink and grow across graph buckets."""
+    from xinfer_b200.config import unregister_architecture
+    from xinfer_b200.engine.runner import ModelRunner, StepInput
+    from xinfer_b200.parts import unregister
+    from xinfer_b200.weights import write_random_model
+    register_decay()
+    try:
+        raw = dict(architectures=["ToyDecayForTest"], vocab_size=101, hidden_size=64, layers=2, decay=0.6)
+        folder = write_random_model(str(tmp_path / "toy"), raw, seed=8, dtype=torch.bfloat16, std=0.08)
+        _, w = plain.load_folder(folder)
+        r = ModelRunner(folder, "bfloat16", block_size=8, num_blocks=8, max_num_seqs=3)
+        assert r.has_state and r._graph_safe
+        rng = np.random.default_rng(1)
+        seqs = [rng.integers(0, 101, n).tolist() for n in (40, 31, 22)]
+        ref = [plain_decay(raw, w, s) for s in seqs]
+        tol = [3.0 * float((plain_decay(raw, w, s, round_to=torch.bfloat16) - f).abs().max()) for s, f in zip(seqs, ref)]
+        slots = [r.open_request() for _ in seqs]
+        heads = (9, 5, 2)
+        got = [[] for _ in seqs]
+        out = r.step([StepInput(slots[i], seqs[i][:heads[i]], range(heads[i])) for i in range(3)]).float().cpu()   # prompts, launched
+        assert not r.last_used_graph
+        at = 0
+        for i in range(3):
+            got[i].append(out[at:at + heads[i]].clone()); at += heads[i]
+        done = list(heads)
+        graphs = 0
+        while any(done[i] < len(seqs[i]) for i in range(3)):
+            live = [i for i in range(3) if done[i] < len(seqs[i])]
+            out = r.step([StepInput(slots[i], seqs[i][done[i]:done[i] + 1], [0]) for i in live], allow_graph=True).float().cpu()
+            graphs += r.last_used_graph
+            for k, i in enumerate(live):
+                got[i].append(out[k:k + 1].clone()); done[i] += 1
+        r.check_errors()
+        assert graphs == len(seqs[0]) - heads[0] and len(r._graphs) >= 2      # buckets of 3, 2 and 1 requests
+        for i in range(3):
+            d = float((torch.cat(got[i]) - ref[i]).abs().max())
+            assert d <= tol[i], (i, d, tol[i])
+    finally:
+        unregister_architecture("ToyDecayForTest")
+        unregister("mixer", "toy_decay")

@@ -19,7 +19,7 @@ EXPERTS = 5
 
 def register_toys():
     from xinfer_b200.config import register_architecture
-    from xinfer_b200.config.plan import (AttentionSpec, BlockSpec, FeedForwardSpec, LayerRun, ModelPlan, NormSpec,
+    from xinfer_b200.config.plan import (AttentionSpec, pre_norm_block, FeedForwardSpec, LayerRun, ModelPlan, NormSpec,
                                          PartSpec)
     from xinfer_b200.parts import (FeedForward, Norm, PositionEncoding, register_feed_forward, register_norm,
                                    register_position_encoding)
@@ -134,7 +134,7 @@ def register_toys():
             else:
                 ff = FeedForwardSpec(kind="swiglu", hidden=H, intermediate=raw["inner"])
             norm = (CenteredSpec(kind="toy_centered", dim=H, eps=1e-5) if i % 2 else NormSpec(kind="rmsnorm", dim=H, eps=1e-6))
-            blocks.append(BlockSpec(prefix=f"model.layers.{i}.", norm_in=norm, mixer=mixer,
+            blocks.append(pre_norm_block(prefix=f"model.layers.{i}.", norm_in=norm, mixer=mixer,
                                     norm_post=NormSpec(kind="rmsnorm", dim=H, eps=1e-6), feed_forward=ff))
         return ModelPlan(architecture="ToyPartsForTest", vocab_size=V, hidden=H, embed_name="model.embed_tokens.weight",
                          blocks=tuple(blocks), runs=tuple(LayerRun(i) for i in raw["order"]),

@@ -67,7 +67,11 @@ def test_dtype_policy(tmp_path):
     s = WeightStore(str(tmp_path))
     assert s.get("w16", "cpu", torch.bfloat16).dtype == torch.bfloat16
     assert s.get("wb", "cpu", torch.bfloat16).dtype == torch.bfloat16
-    assert s.get("w32", "cpu", torch.bfloat16).dtype == torch.float32   # stored in 32-bit stays so
+    assert s.get("w32", "cpu", torch.bfloat16).dtype == torch.float32   # stored in 32-bit stays so ...
+    # ... unless a part asks for it as an operand of the engine's matrix products
+    assert s.get("w32", "cpu", torch.bfloat16, operand=True).dtype == torch.bfloat16
+    assert s.get("w32", "cpu", torch.float32, operand=True).dtype == torch.float32
+    assert s.get("tab", "cpu", torch.bfloat16, operand=True).dtype == torch.int32
     assert s.get("tab", "cpu", torch.bfloat16).dtype == torch.int32      # integer tables as int32
     assert s.get("wb", "cpu", torch.float32).dtype == torch.float32
 
@@ -95,13 +99,24 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
         assert frag in msg
 
 
-def test_untied_head_is_required_and_tied_head_is_unexpected(tmp_path):
+def test_a_spare_head_beside_a_tied_one_is_a_warning_and_an_untied_head_is_required(tmp_path):
+    from xinfer_b200.weights import UnexpectedWeightsWarning
     raw, seed = TINY["B"]
-    write_random_model(str(tmp_path), raw, seed, dtype=torch.bfloat16)
+    write_random_model(str(tmp_path / "untied"), raw, seed, dtype=torch.bfloat16)
     tied = dict(raw, tie_word_embeddings=True)
-    with pytest.raises(WeightError) as e:
-        WeightStore(str(tmp_path)).check(model_weight_specs(Qwen3Config.from_dict(tied).plan()))
+    tied_specs = model_weight_specs(Qwen3Config.from_dict(tied).plan())
+    store = WeightStore(str(tmp_path / "untied"))
+    with pytest.warns(UnexpectedWeightsWarning, match="lm_head.weight"):
+        assert store.check(tied_specs) == ["lm_head.weight"]
+    assert store.unexpected == ["lm_head.weight"]
+    with pytest.raises(WeightError) as e:                      # on request the same is fatal
+        store.check(tied_specs, strict=True)
     assert e.value.unexpected == ["lm_head.weight"] and not e.value.missing
+    # the other way round: a folder written for a tied head lacks the head an untied model needs
+    write_random_model(str(tmp_path / "tied"), tied, seed, dtype=torch.bfloat16)
+    with pytest.raises(WeightError) as e:
+        WeightStore(str(tmp_path / "tied")).check(model_weight_specs(Qwen3Config.from_dict(raw).plan()))
+    assert e.value.missing == ["lm_head.weight"]
 
 
 def test_random_model_is_seeded_and_order_free(tmp_path):

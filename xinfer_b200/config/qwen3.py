@@ -14,12 +14,9 @@ import os
 from dataclasses import dataclass, asdict
 from typing import Any, Dict, Mapping, Optional, Tuple
 
-from .plan import (AttentionSpec, BlockSpec, FeedForwardSpec, LayerRun, ModelPlan, NormSpec,
-                   RopeSpec)
-
-
-class ConfigError(ValueError):
-    """config.json is missing a key, has a wrong type or asks for something this engine lacks."""
+from .errors import ConfigError
+from .plan import (AttentionSpec, FeedForwardSpec, LayerRun, ModelPlan, NormSpec, RopeSpec,
+                   pre_norm_block)
 
 
 _REQUIRED = (
@@ -146,7 +143,7 @@ class Qwen3Config:
         blocks = []
         for i in range(self.num_hidden_layers):
             p = f"model.layers.{i}."
-            blocks.append(BlockSpec(
+            blocks.append(pre_norm_block(
                 prefix=p,
                 norm_in=NormSpec(kind="rmsnorm", dim=self.hidden_size, eps=self.rms_norm_eps),
                 mixer=AttentionSpec(

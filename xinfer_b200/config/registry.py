@@ -12,8 +12,8 @@ import os
 from dataclasses import dataclass
 from typing import Any, Callable, Dict, Mapping
 
+from .errors import ConfigError
 from .plan import ModelPlan
-from .qwen3 import ConfigError, Qwen3Config
 
 
 @dataclass(frozen=True)
@@ -77,4 +77,10 @@ def load_config(model_dir: str):
     return config_from_dict(read_config_json(model_dir))
 
 
-register_architecture(Qwen3Config.ARCHITECTURE, Qwen3Config.from_dict, lambda c: c.plan())
+def _register_builtin() -> None:
+    # the one architecture this engine ships; others are added by their own modules the same way
+    from .qwen3 import Qwen3Config
+    register_architecture(Qwen3Config.ARCHITECTURE, Qwen3Config.from_dict, lambda c: c.plan())
+
+
+_register_builtin()

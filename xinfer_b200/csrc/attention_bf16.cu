@@ -602,6 +602,8 @@ XB_EXPORT int xb_attn_decode_bf16(void* out, float* part_o, float* part_ml, cons
 // The same decode attention for callers that cannot allocate (see no_alloc.h): the scratch that
 // xb_attn_decode_bf16 takes from its caller lives in a fixed device array of this module.
 // ------------------------------------------------------------------------------------------------
+#include <atomic>
+
 #include "no_alloc.h"
 
 namespace {
@@ -610,7 +612,9 @@ namespace {
 static __device__ __align__(256) unsigned char xb_noalloc_scratch[XB_NOALLOC_SCRATCH_BYTES];
 
 constexpr int NOALLOC_MAX_DEVICES = 64;
-unsigned char* g_noalloc_base[NOALLOC_MAX_DEVICES] = {};
+// the array's address per device; two host threads that make a device's first call together both
+// look it up and store the same value
+std::atomic<unsigned char*> g_noalloc_base[NOALLOC_MAX_DEVICES];
 
 size_t noalloc_align(size_t n) { return (n + 255) & ~(size_t)255; }
 }  // namespace
@@ -635,12 +639,13 @@ XB_EXPORT int xb_attn_decode_bf16_noalloc(void* out, const void* q, const void* 
     // the array's address on the current device, looked up once per device
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return XB_NOALLOC_NO_SYMBOL;
-    if (!g_noalloc_base[dev]) {
+    unsigned char* base = g_noalloc_base[dev].load(std::memory_order_acquire);
+    if (!base) {
         void* p = nullptr;
         if (cudaGetSymbolAddress(&p, xb_noalloc_scratch) != cudaSuccess || !p) return XB_NOALLOC_NO_SYMBOL;
-        g_noalloc_base[dev] = static_cast<unsigned char*>(p);
+        base = static_cast<unsigned char*>(p);
+        g_noalloc_base[dev].store(base, std::memory_order_release);
     }
-    unsigned char* base = g_noalloc_base[dev];
     int* tickets = nullptr;
     float *part_ml = nullptr, *part_o = nullptr;
     if (num_splits > 1) {

@@ -9,6 +9,8 @@
 #define XB_ERR_BAD_PAGE 2    // a block-table entry outside [0, num_pages)
 #define XB_ERR_WAIT 4        // a bounded wait on an mbarrier gave up
 #define XB_ERR_BAD_ROW 8     // a requested row outside [0, tokens)
+#define XB_ERR_SCRATCH 16    // scratch memory that a kernel must find zeroed was not
+#define XB_ERR_BAD_POSITION 32  // a token position outside the position table
 
 // Element type codes shared with the Python side.
 #define XB_F32 0

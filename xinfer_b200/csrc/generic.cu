@@ -13,7 +13,8 @@
 // ------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embedding_kernel(T* __restrict__ out, const T* __restrict__ table, const int* __restrict__ ids,
-                                 const int* __restrict__ sampled, int num_sampled, int hidden, int vocab, int* err) {
+                                 const int* __restrict__ sampled, int num_sampled, int hidden, int vocab, float scale,
+                                 int* err) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -26,7 +27,9 @@ __global__ void embedding_kernel(T* __restrict__ out, const T* __restrict__ tabl
         return;
     }
     const T* r = table + (size_t)id * hidden;
-    if ((hidden * sizeof(T)) % 16 == 0) {
+    if (scale != 1.f) {   // row times a constant, the product rounded to the activation type
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_f32<T>(to_f32<T>(r[i]) * scale);
+    } else if ((hidden * sizeof(T)) % 16 == 0) {
         const int n16 = hidden * sizeof(T) / 16;
         const uint4* r4 = reinterpret_cast<const uint4*>(r);
         uint4* o4 = reinterpret_cast<uint4*>(o);
@@ -37,13 +40,33 @@ __global__ void embedding_kernel(T* __restrict__ out, const T* __restrict__ tabl
 }
 
 XB_EXPORT int xb_embedding(int dtype, void* out, const void* table, const int* ids, const int* sampled, int num_sampled,
-                           int tokens, int hidden, int vocab, int* err, cudaStream_t stream) {
+                           int tokens, int hidden, int vocab, float scale, int* err, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (dtype == XB_F32)
         return xb_launch(embedding_kernel<float>, dim3(tokens), dim3(256), 0, stream, (float*)out, (const float*)table, ids,
-                         sampled, num_sampled, hidden, vocab, err);
+                         sampled, num_sampled, hidden, vocab, scale, err);
     return xb_launch(embedding_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, (__nv_bfloat16*)out,
-                     (const __nv_bfloat16*)table, ids, sampled, num_sampled, hidden, vocab, err);
+                     (const __nv_bfloat16*)table, ids, sampled, num_sampled, hidden, vocab, scale, err);
+}
+
+// ------------------------------------------------------------------------------------------
+// What a model may do to its float32 logits after the head: v *= scale, then v = cap * tanh(v / cap)
+// (cap <= 0: no cap).  In place.
+// ------------------------------------------------------------------------------------------
+__global__ void logits_post_kernel(float* __restrict__ logits, size_t n, float scale, float cap) {
+    const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float v = logits[i] * scale;
+        if (cap > 0.f) v = cap * tanhf(v * inv_cap);
+        logits[i] = v;
+    }
+}
+
+XB_EXPORT int xb_logits_post(float* logits, long long n, float scale, float cap, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const long long blocks = (n + 255) / 256;
+    logits_post_kernel<<<(unsigned)(blocks < 4096 ? blocks : 4096), 256, 0, stream>>>(logits, (size_t)n, scale, cap);
+    return xb_launch_status();
 }
 
 // ------------------------------------------------------------------------------------------
@@ -257,6 +280,8 @@ __global__ void qk_norm_rope_write_kernel(
             kv_row = (long long)page * nkv * page_size + (pos % page_size);  // + g * page_size
         }
     }
+    // a position the table does not hold is reported; the row read instead keeps the access in bounds
+    if (cos_t && (pos < 0 || pos >= max_pos) && req_of_token[t] >= 0 && threadIdx.x == 0) atomicOr(err, XB_ERR_BAD_POSITION);
     const int tp = pos < max_pos ? (pos < 0 ? 0 : pos) : max_pos - 1;
     for (int h = warp; h < total_heads; h += nwarps) {
         const T* x = row + (size_t)h * d;

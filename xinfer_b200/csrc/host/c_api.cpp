@@ -215,6 +215,19 @@ XB_API int xb_sched_schedule_ahead(void* h, int cap_entries, long long* req_ids,
     s->ahead = e;
     return (int)e.size();
 }
+// A scheduled step failed on the device or on the way there: every request of the steps that are
+// scheduled and not committed (the running one and the one decided ahead) ends as aborted, its pages
+// go back, and nothing stays scheduled.  Returns how many requests that ended.
+XB_API int xb_sched_fail_steps(void* h) {
+    SchedHandle* s = static_cast<SchedHandle*>(h);
+    int n = 0;
+    for (std::vector<StepEntry>* v : {&s->last, &s->ahead}) {
+        for (const StepEntry& e : *v)
+            if (s->sched.abort(e.req_id)) ++n;
+        v->clear();
+    }
+    return n;
+}
 XB_API int xb_sched_drain_finished(void* h, long long* out, int cap) {
     auto v = static_cast<SchedHandle*>(h)->sched.drain_finished();
     const int n = std::min((int)v.size(), cap);

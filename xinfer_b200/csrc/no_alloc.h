@@ -21,7 +21,8 @@
 //     tickets; xb_attn_decode_bf16_noalloc_need() computes it.
 //   * The first call on each device looks up the array's device address (cudaGetSymbolAddress,
 //     with that device current).  That first call per device should be made before any stream
-//     capture is begun.  Later calls only read the cached address.
+//     capture is begun.  Later calls only read the cached address (an atomic: host threads that
+//     make a device's first call at the same moment both look the address up and agree).
 //   * There is ONE array per device and every call uses it.  It still holds whatever the last call
 //     left there.  The part that must start as zeros (the tickets) is cleared on the stream at
 //     the start of every call; the rest is fully overwritten before it is read.  Two calls whose

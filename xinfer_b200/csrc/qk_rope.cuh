@@ -87,6 +87,8 @@ __device__ __forceinline__ QkItem qk_prepare(const QkArgs& A, int t, int h, int 
         it.wb[0] = b0.x, it.wb[1] = b0.y, it.wb[2] = b0.z, it.wb[3] = b0.w, it.wb[4] = b1.x, it.wb[5] = b1.y, it.wb[6] = b1.z, it.wb[7] = b1.w;
     }
     it.rotated = A.cos_t && active && (is_q || is_k);
+    // a position the table does not hold is reported; the row read instead keeps the access in bounds
+    if (it.rotated && (pos < 0 || pos >= A.max_pos) && A.req_of_token[t] >= 0) atomicOr(err, XB_ERR_BAD_POSITION);
     const int tp = pos < A.max_pos ? (pos < 0 ? 0 : pos) : A.max_pos - 1;
     const int half = A.rot / 2;
     it.cr = A.cos_t + (size_t)tp * half;

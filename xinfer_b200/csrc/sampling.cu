@@ -128,13 +128,15 @@ __device__ __forceinline__ unsigned long long key_of(float v, int i) {
 #define XB_SAMPLE_CHUNK_SMEM 8192   // values of a chunk that are kept in shared memory
 #define XB_SAMPLE_CHUNKS_MAX 64
 
-// Scratch of the sampler, per row: candidate keys, partial results of the chunks, a candidate
-// counter and a ticket (both zero between launches).
+// Scratch of the sampler, per row: a candidate counter and a ticket (both zero between launches),
+// candidate keys, partial results of the chunks.  The arrays are laid out for the buffer's capacity
+// (the most rows it will ever see), not for a launch's rows: the counters of a smaller batch must
+// not fall where a larger batch left keys.
 struct SampleScratch {
-    unsigned long long* cand;   // [rows][XB_TOPK_MAX]
-    Best* part;                 // [rows][XB_SAMPLE_CHUNKS_MAX]
-    int* count;                 // [rows]
-    int* ticket;                // [rows]
+    int* count;                 // [capacity]
+    int* ticket;                // [capacity]
+    unsigned long long* cand;   // [capacity][XB_TOPK_MAX]
+    Best* part;                 // [capacity][XB_SAMPLE_CHUNKS_MAX]
 };
 
 // Grid (chunks, rows): a row's vocabulary is cut into chunks of whole Philox blocks (4 tokens); every
@@ -143,8 +145,9 @@ struct SampleScratch {
 // at most 1024 / k chunks, so that the candidates of all chunks fit the final sort.
 __global__ void __launch_bounds__(1024)
 sample_kernel(int* __restrict__ out_tokens, const float* __restrict__ logits, const SampleParams* __restrict__ params,
-              int vocab, int grid_chunks, SampleScratch sc, const int* __restrict__ err_word) {
-    // the step's error word travels to the host behind the tokens, in the same copy
+              int vocab, int grid_chunks, SampleScratch sc, int* __restrict__ err_word) {
+    // the step's error word travels to the host behind the tokens, in the same copy (what this launch
+    // itself reports reaches the host with the next one)
     if (err_word != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) out_tokens[gridDim.y] = *err_word;
     __shared__ Best sbest[32];
     __shared__ unsigned int hist[256];
@@ -253,14 +256,18 @@ sample_kernel(int* __restrict__ out_tokens, const float* __restrict__ logits, co
         const unsigned long long kth = s_prefix;  // the chunk's kc-th largest key; keys are unique
         if (threadIdx.x == 0) s_base = atomicAdd(&sc.count[r], kc);   // room for this chunk's candidates
         __syncthreads();
-        unsigned long long* dst = sc.cand + (size_t)r * XB_TOPK_MAX + s_base;
+        // a counter that was not zero at launch (scratch shared with something else) must not turn
+        // into a write outside the row's candidates: report it and write nothing
+        const bool room = s_base >= 0 && s_base + kc <= XB_TOPK_MAX;
+        if (!room && threadIdx.x == 0 && err_word != nullptr) atomicOr(err_word, XB_ERR_SCRATCH);
+        unsigned long long* dst = sc.cand + (size_t)r * XB_TOPK_MAX + (room ? s_base : 0);
         if (threadIdx.x == 0) s_need = 0;
         __syncthreads();
         for (int i = lo + (int)threadIdx.x; i < hi; i += blockDim.x) {
             const unsigned long long key = key_of(cached ? s_vals[i - lo] : row[i], i);
             if (key >= kth) {
                 const int at = atomicAdd(&s_need, 1);
-                if (at < kc && s_base + at < XB_TOPK_MAX) dst[at] = key;
+                if (room && at < kc) dst[at] = key;
             }
         }
     }
@@ -288,7 +295,7 @@ sample_kernel(int* __restrict__ out_tokens, const float* __restrict__ logits, co
         }
         return;
     }
-    const int total = min(__ldcg(&sc.count[r]), XB_TOPK_MAX);
+    const int total = max(0, min(__ldcg(&sc.count[r]), XB_TOPK_MAX));
     for (int i = threadIdx.x; i < XB_TOPK_MAX; i += blockDim.x)
         cand_key[i] = i < total ? __ldcg(sc.cand + (size_t)r * XB_TOPK_MAX + i) : 0ull;
     __syncthreads();
@@ -348,26 +355,29 @@ sample_kernel(int* __restrict__ out_tokens, const float* __restrict__ logits, co
     if (threadIdx.x == 0) out_tokens[r] = b.i;
 }
 
-// Bytes of scratch for `rows` rows (zero before the first launch; the kernel leaves it zero where it must be).
-XB_EXPORT long long xb_sample_scratch_bytes(int rows) {
-    return (long long)rows * (XB_TOPK_MAX * 8 + XB_SAMPLE_CHUNKS_MAX * (long long)sizeof(Best) + 8);
+// Bytes of scratch for a sampler that sees at most `capacity` rows in a launch (zero before the first
+// launch; the kernel leaves it zero where it must be).
+XB_EXPORT long long xb_sample_scratch_bytes(int capacity) {
+    return (long long)capacity * (8 + XB_TOPK_MAX * 8 + XB_SAMPLE_CHUNKS_MAX * (long long)sizeof(Best));
 }
 
 // `err_word` (nullable): a device int that is copied to out_tokens[rows].  `scratch`: at least
-// xb_sample_scratch_bytes(rows) bytes, 8-byte aligned.
+// xb_sample_scratch_bytes(capacity) bytes, 8-byte aligned, laid out by `capacity` (the same value in
+// every call that shares the buffer), rows <= capacity.
 XB_EXPORT int xb_sample(int* out_tokens, float* logits, const void* params, const int* history,
-                        int rows, int vocab, int apply_penalties, void* scratch, const int* err_word, cudaStream_t stream) {
+                        int rows, int capacity, int vocab, int apply_penalties, void* scratch, int* err_word,
+                        cudaStream_t stream) {
     if (rows <= 0) return 0;
-    if (!scratch || ((uintptr_t)scratch & 7)) return (int)cudaErrorInvalidValue;
+    if (!scratch || ((uintptr_t)scratch & 7) || rows > capacity) return (int)cudaErrorInvalidValue;
     if (apply_penalties) penalties_kernel<<<rows, 128, 0, stream>>>(logits, (const SampleParams*)params, history, vocab);
     SampleScratch sc;
     unsigned char* base = (unsigned char*)scratch;
-    sc.cand = (unsigned long long*)base;
-    base += (size_t)rows * XB_TOPK_MAX * 8;
-    sc.part = (Best*)base;
-    base += (size_t)rows * XB_SAMPLE_CHUNKS_MAX * sizeof(Best);
     sc.count = (int*)base;
-    sc.ticket = sc.count + rows;
+    sc.ticket = sc.count + capacity;
+    base += (size_t)capacity * 8;
+    sc.cand = (unsigned long long*)base;
+    base += (size_t)capacity * XB_TOPK_MAX * 8;
+    sc.part = (Best*)base;
     int chunks = 296 / rows;   // two CTAs of 1024 threads per SM of a 148-SM part
     if (chunks < 1) chunks = 1;
     if (chunks > XB_SAMPLE_CHUNKS_MAX) chunks = XB_SAMPLE_CHUNKS_MAX;

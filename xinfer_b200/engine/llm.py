@@ -5,6 +5,12 @@ and tokenisers are outside this engine).
 
 One loop iteration = schedule -> step -> sample -> commit, as the reference's
 prepare_step / run_forward / finish_step (src/core/engine.rs:1034, 1085, 1363).
+
+A step that fails (no pages at the last moment, an error word from a kernel, a bounded wait that
+gave up, a launch error) ends the requests of the batches that were scheduled and not yet recorded
+with ``finish_reason == "abort"`` and the reason in ``error``; their pages go back, nothing stays
+scheduled, and the loop goes on with the other requests.  The reference cancels every request with
+the reason and keeps its loop alive (src/core/engine.rs:2392-2408).
 """
 from __future__ import annotations
 
@@ -34,6 +40,8 @@ class GenerationOutput:
     decoded_length: int
     decode_output: List[int]
     finish_reason: Optional[str] = None
+    # why the request was aborted, when a step it was part of failed
+    error: Optional[str] = None
 
 
 @dataclass
@@ -98,7 +106,9 @@ class Engine:
         self._done: Dict[int, GenerationOutput] = {}
         self.use_graphs = not econfig.disable_cuda_graph
         # counters (the reference logs the same two throughputs, src/core/engine.rs:1584-1716)
-        self.stats = {"steps": 0, "prompt_tokens": 0, "decoded_tokens": 0, "preemptions": 0, "steps_decided_ahead": 0}
+        self.stats = {"steps": 0, "prompt_tokens": 0, "decoded_tokens": 0, "preemptions": 0, "steps_decided_ahead": 0,
+                      "failed_steps": 0}
+        self._errors: Dict[int, str] = {}   # request id -> why it was aborted
 
     # ---- admission ------------------------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
@@ -127,25 +137,48 @@ class Engine:
         is dropped."""
         flight, self._flight = self._flight, None
         ended: List[int] = []
-        if flight is None:
-            entries = self.scheduler.schedule()
-            ended = self.scheduler.drain_finished()  # requests the scheduler had to abort
-            if entries:
-                flight = self._launch(entries, None)
-        if flight is not None:
-            if self.run_ahead and flight.sampler is not None and not flight.penalties:
-                ahead = self.scheduler.schedule_ahead()
-                if ahead:
-                    self._flight = self._launch(ahead, flight)
-                    self.stats["steps_decided_ahead"] += 1
-            ended += self._retire(flight)
-            self.stats["steps"] += 1
+        try:
+            if flight is None:
+                entries = self.scheduler.schedule()
+                ended = self.scheduler.drain_finished()  # requests the scheduler had to abort
+                if entries:
+                    flight = self._launch(entries, None)
+            if flight is not None:
+                if self.run_ahead and flight.sampler is not None and not flight.penalties:
+                    ahead = self.scheduler.schedule_ahead()
+                    if ahead:
+                        self._flight = self._launch(ahead, flight)
+                        self.stats["steps_decided_ahead"] += 1
+                ended += self._retire(flight)
+                self.stats["steps"] += 1
+        except RuntimeError as e:     # StepError, SchedulerError, KernelError, a CUDA error raised by torch
+            ended += self._fail_scheduled(e)
         self.stats["preemptions"] = self.scheduler.preemptions
         for seq_id in ended:
             self._finish(seq_id)
         if self._flight is not None and not any(e.req_id in self._live for e in self._flight.wanted):
-            self._retire(self._flight)   # queued for requests that have all ended meanwhile: nothing to keep
+            try:
+                self._retire(self._flight)   # queued for requests that have all ended meanwhile: nothing to keep
+            except RuntimeError as e:
+                for seq_id in self._fail_scheduled(e):
+                    self._finish(seq_id)
             self._flight = None
+        return ended
+
+    def _fail_scheduled(self, error: Exception) -> List[int]:
+        """A step failed.  The requests of every batch that is scheduled and not recorded (the one
+        that failed and one queued behind it) end as aborted with the reason; their pages go back;
+        the device is drained and its error word, scratch and samplers are made ready for the next
+        step.  Returns the ids that ended.  Requests that were only waiting are untouched."""
+        reason = f"{type(error).__name__}: {error}"
+        self.stats["failed_steps"] += 1
+        self._flight = None
+        ended = self.scheduler.fail_steps()
+        for seq_id in ended:
+            self._errors[seq_id] = reason
+        self.runner.recover()
+        for s in self.samplers:
+            s.reset()
         return ended
 
     def _launch(self, entries, after: Optional["_Flight"]) -> "_Flight":
@@ -204,7 +237,8 @@ class Engine:
         self._done[seq_id] = GenerationOutput(
             seq_id=seq_id, prompt_length=live.prompt_len, prompt_start_time=_ms(live.t_start),
             decode_start_time=_ms(live.t_first or now), decode_finish_time=_ms(now),
-            decoded_length=len(out), decode_output=out, finish_reason=self.scheduler.finish_reason(seq_id))
+            decoded_length=len(out), decode_output=out, finish_reason=self.scheduler.finish_reason(seq_id),
+            error=self._errors.pop(seq_id, None))
         self.scheduler.release(seq_id)
 
     def has_work(self) -> bool:
@@ -232,19 +266,18 @@ class Engine:
         live = self._live[seq_id]
 
         def stream() -> Iterator[StreamItem]:
-            try:
-                while seq_id in self._live:
-                    self.step()
-                    src = self._done[seq_id].decode_output if seq_id in self._done else self.scheduler.output(seq_id)
-                    for tok in src[live.streamed:]:
-                        yield StreamItem("TOKEN_ID", int(tok))
-                    live.streamed = len(src)
-                out = self._done.pop(seq_id)
-                yield StreamItem("DONE", (seq_id, out.prompt_length, out.decoded_length,
-                                          out.decode_finish_time - out.decode_start_time))
-            except (StepError, SchedulerError) as e:
-                self.scheduler.abort(seq_id)
-                yield StreamItem("ERROR", str(e))
+            while seq_id in self._live:
+                self.step()
+                src = self._done[seq_id].decode_output if seq_id in self._done else self.scheduler.output(seq_id)
+                for tok in src[live.streamed:]:
+                    yield StreamItem("TOKEN_ID", int(tok))
+                live.streamed = len(src)
+            out = self._done.pop(seq_id)
+            if out.error is not None:
+                yield StreamItem("ERROR", out.error)
+                return
+            yield StreamItem("DONE", (seq_id, out.prompt_length, out.decoded_length,
+                                      out.decode_finish_time - out.decode_start_time))
 
         return seq_id, len(prompt), stream()
 

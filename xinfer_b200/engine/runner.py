@@ -21,7 +21,7 @@ from typing import Any, Dict, List, Mapping, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from .. import kernels
+from .. import kernels, tracing
 from ..cache.manager import CacheGroup, CacheManager, StateSlots
 from ..config import ConfigError, config_from_dict, load_config
 from ..models.decoder import DecoderModel, model_weight_specs
@@ -52,6 +52,21 @@ def _dtype_of(name) -> torch.dtype:
     if key in ("f32", "fp32", "float32"):
         return torch.float32
     raise ConfigError(f"dtype '{name}' is not supported (bf16/bfloat16 or f32/float32)")
+
+
+def resolve_max_model_len(asked: Optional[int], max_positions: int) -> int:
+    """The longest sequence the engine will hold: what was asked for, or all positions the model's
+    position tables have.  More than the tables hold is refused here, before any token could run
+    at a position without an angle."""
+    if asked is None:
+        return int(max_positions)
+    asked = int(asked)
+    if asked <= 0:
+        raise ConfigError(f"max_model_len must be positive, got {asked}")
+    if asked > max_positions:
+        raise ConfigError(f"max_model_len {asked} exceeds the model's max_position_embeddings {max_positions}: "
+                          f"its position tables end there")
+    return asked
 
 
 class _MetaBuffers:
@@ -100,7 +115,7 @@ class StepAssembler:
         self.max_model_len = int(max_model_len)
         self.dtype = dtype
         self.device = torch.device(device)
-        self.block_size = cache.groups[0].page_size
+        self.page_sizes = [g.page_size for g in cache.groups]
         self.workspace = workspace if workspace is not None else Workspace(self.device)
         self.err = err if err is not None else torch.zeros(1, dtype=torch.int32, device=self.device)
         self._meta = _MetaBuffers(self.device)
@@ -157,7 +172,7 @@ class StepAssembler:
         G = len(cache.groups)
         Bp, Tp, Rp = max(B, pad_entries), max(T, pad_tokens), max(R, pad_rows, 1)
         longest = int((starts + counts).max())
-        max_stride = max((longest + self.block_size - 1) // self.block_size + 8, max(strides) if strides else 0)
+        max_stride = max(max((longest + ps - 1) // ps for ps in self.page_sizes) + 8, max(strides) if strides else 0)
         need = 3 * (Tp + 4) + 3 * (Bp + 5) + Rp + 8 + G * (Bp * max_stride + 4) + 64
         self._meta.reserve(need)
         host, dev, which = self._meta.next()
@@ -238,7 +253,7 @@ class ModelRunner:
         self.plan = model.plan
         self.block_size = int(block_size)
         self.max_num_seqs = int(max_num_seqs)
-        self.max_model_len = int(max_model_len or self.plan.max_positions)
+        self.max_model_len = resolve_max_model_len(max_model_len, self.plan.max_positions)
         self.workspace = Workspace(self.device)
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._err_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
@@ -270,39 +285,50 @@ class ModelRunner:
 
     # ---- caches --------------------------------------------------------------------------------------
     def _build_caches(self, num_blocks: Optional[int], kv_fraction: float) -> None:
+        """Page pools and page tensors from what the mixers ask for.  Runs that own pages are
+        grouped by (window, page size): a group has one pool and one block table per request;
+        every run of a group holds its own page tensors, addressed by the group's page ids.
+        ``num_blocks`` counts pages of the engine's ``block_size``; a group with another page size
+        gets as many pages as hold the same number of tokens."""
         needs = self.model.cache_needs()
         runs = self.plan.runs
-        # runs that own pages, grouped by how long keys are kept
-        keys: List[Optional[int]] = []
+        keys: List[Tuple[Optional[int], int]] = []
         run_group: Dict[int, int] = {}
         for pos, (run, need) in enumerate(zip(runs, needs)):
             if need is None or run.cache_from is not None:
                 continue
-            if need.window not in keys:
-                keys.append(need.window)
-            run_group[pos] = keys.index(need.window)
-        esize = 4 if self.dtype == torch.float32 else 2
-        page_bytes = [0] * max(len(keys), 1)
+            key = (need.window, int(need.page_size or self.block_size))
+            if key[1] <= 0:
+                raise StepError(f"layer run {pos} asks for a page size of {key[1]}")
+            if key not in keys:
+                keys.append(key)
+            run_group[pos] = keys.index(key)
+        token_bytes = [0] * max(len(keys), 1)     # bytes one cached token takes in each group
         for pos, g in run_group.items():
-            page_bytes[g] += 2 * needs[pos].kv_heads * needs[pos].head_dim * self.block_size * esize
+            token_bytes[g] += needs[pos].bytes_per_token(self.dtype)
         if num_blocks is None:
             free, _ = torch.cuda.mem_get_info(self.device)
             budget = int(free * kv_fraction)
-            total = sum(page_bytes) or 1
+            total = sum(token_bytes) * self.block_size or 1
             num_blocks = max(budget // total, 1)
             # no group needs more pages than every request at full length
             num_blocks = min(num_blocks, self.max_num_seqs * ((self.max_model_len + self.block_size - 1) // self.block_size))
         self.num_blocks = int(num_blocks)
-        self.kv_bytes_per_token = sum(page_bytes) // self.block_size
-        groups = [CacheGroup(self.block_size, self.num_blocks, w) for w in keys] or [CacheGroup(self.block_size, 1, None)]
+        self.kv_bytes_per_token = sum(token_bytes)
+        tokens = self.num_blocks * self.block_size
+        groups = [CacheGroup(ps, max(tokens // ps, 1), w) for w, ps in keys]
+        if not groups:
+            # no mixer caches anything: one group of bookkeeping alone (no device memory) that never runs
+            # out, so that requests still have lengths and slots
+            groups = [CacheGroup(self.block_size, self.max_num_seqs * ((self.max_model_len + self.block_size - 1) // self.block_size), None)]
         self.cache = CacheManager(groups, self.max_num_seqs)
         self.layer_caches: List[Optional[LayerCache]] = [None] * len(runs)
         for pos, g in run_group.items():
-            n = needs[pos]
-            shape = (self.num_blocks, n.kv_heads, self.block_size, n.head_dim)
-            self.layer_caches[pos] = LayerCache(torch.zeros(shape, dtype=self.dtype, device=self.device),
-                                                torch.zeros(shape, dtype=self.dtype, device=self.device),
-                                                g, self.block_size)
+            grp = groups[g]
+            pages = {name: torch.zeros(t.page_shape(grp.num_pages, grp.page_size), dtype=t.dtype or self.dtype,
+                                       device=self.device)
+                     for name, t in needs[pos].tensors}
+            self.layer_caches[pos] = LayerCache(pages, g, grp.page_size)
         for pos, run in enumerate(runs):
             if run.cache_from is not None and needs[pos] is not None and self.layer_caches[run.cache_from] is None:
                 raise StepError(f"layer run {pos} reads the cache of run {run.cache_from}, which has none")
@@ -316,12 +342,14 @@ class ModelRunner:
             self.layer_states.append({name: self.state.add(f"run{pos}.{name}", shape, dt)
                                       for name, (shape, dt) in need.items()})
         self.has_state = any(s is not None for s in self.layer_states)
+        # decode steps may be replayed from CUDA graphs when every part takes the step from device tensors
+        self._graph_safe = self.model.graph_safe()
 
     def kv_cache_tokens(self) -> int:
         return self.num_blocks * self.block_size
 
     def available_kv_tokens(self) -> int:
-        return min(self.cache.free_pages(g) for g in range(len(self.cache.groups))) * self.block_size
+        return min(self.cache.free_pages(g) * grp.page_size for g, grp in enumerate(self.cache.groups))
 
     # ---- requests ----------------------------------------------------------------------------------
     def open_request(self) -> int:
@@ -343,6 +371,16 @@ class ModelRunner:
 
         A token id ``-1 - i`` stands for ``sampled_tokens[i]``: the id that a sampler has left on the
         device and the host has not seen yet (see ``ahead_token``)."""
+        if tracing.ENABLED:
+            counts = [len(e.tokens) for e in entries]
+            tracing.push(f"{tracing.step_kind(counts)} step: {sum(counts)} tokens of {len(counts)} requests")
+            try:
+                return self._step(entries, allow_graph)
+            finally:
+                tracing.pop()
+        return self._step(entries, allow_graph)
+
+    def _step(self, entries: Sequence[StepInput], allow_graph: bool) -> torch.Tensor:
         if allow_graph and self._graph_eligible(entries):
             return self._step_graph(entries)
         before = kernels.launch_count()
@@ -365,7 +403,7 @@ class ModelRunner:
 
     # ---- decode steps from a CUDA graph ---------------------------------------------------------------
     def _graph_eligible(self, entries: Sequence[StepInput]) -> bool:
-        if self.has_state or self.dtype != torch.bfloat16:
+        if self.dtype != torch.bfloat16 or not self._graph_safe:
             return False
         for e in entries:
             if len(e.tokens) != 1 or len(e.want) != 1:
@@ -374,11 +412,14 @@ class ModelRunner:
 
     def _graph_strides(self, entries: Sequence[StepInput]) -> Tuple[int, ...]:
         longest = max(self.cache.length(e.slot) for e in entries) + 1
-        pages = (longest + self.block_size - 1) // self.block_size
-        s = 64
-        while s < pages:
-            s *= 2
-        return tuple(s for _ in self.cache.groups)
+        out = []
+        for grp in self.cache.groups:
+            pages = (longest + grp.page_size - 1) // grp.page_size
+            s = 64
+            while s < pages:
+                s *= 2
+            out.append(s)
+        return tuple(out)
 
     def _step_graph(self, entries: Sequence[StepInput]) -> torch.Tensor:
         B = len(entries)
@@ -405,23 +446,28 @@ class ModelRunner:
         cap = 3 * (bucket + 4) + 3 * (bucket + 5) + bucket + 8 + sum(bucket * s + 4 for s in strides) + 64
         meta = torch.zeros(cap, dtype=torch.int32, device=self.device)
         kw = dict(pad_entries=bucket, pad_tokens=bucket, pad_rows=bucket, strides=strides, workspace=ws)
+        saved_state = {name: t.clone() for name, t in self.state.tables.items()} if self.has_state else None
         # size every buffer for the largest bucket first, so that no later capture moves them
         if not getattr(ws, "sized", False):
             ws.frozen = False
             top = _bucket(self.max_num_seqs, self.max_num_seqs)
-            widest = 64
-            while widest * self.block_size < self.max_model_len:
-                widest *= 2
-            wide = tuple(widest for _ in strides)
+            wide = []
+            for grp in self.cache.groups:
+                widest = 64
+                while widest * grp.page_size < self.max_model_len:
+                    widest *= 2
+                wide.append(widest)
+            wide = tuple(wide)
             tmp = torch.zeros(3 * (top + 4) + 3 * (top + 5) + top + 8 + sum(top * s + 4 for s in wide) + 64,
                               dtype=torch.int32, device=self.device)
-            # every bucket once (scratch sizes are not monotonic in the batch size), largest first
-            sizes = []
-            b = top
-            while b >= 1:
+            # every bucket that _bucket can give, once (scratch sizes are not monotonic in the batch
+            # size), largest first: the powers of two below the most requests, and that number itself
+            sizes = [top]
+            b = 1
+            while b < top:
                 sizes.append(b)
-                b //= 2
-            for b in sizes:
+                b *= 2
+            for b in sorted(set(sizes), reverse=True):
                 big = self.assembler.prepare(entries[:b], pad_entries=b, pad_tokens=b, pad_rows=b, strides=wide,
                                              into=tmp, workspace=ws)
                 self.model.forward(big, self.layer_caches, self.layer_states)
@@ -432,6 +478,11 @@ class ModelRunner:
         ctx = self.assembler.prepare(entries, into=meta, **kw)
         self.model.forward(ctx, self.layer_caches, self.layer_states)   # warm-up on this stream
         torch.cuda.current_stream().synchronize()
+        if saved_state is not None:
+            # the passes above ran this step's tokens for real: pages take the same values again when the
+            # step is replayed, per-request state would not - it goes back to what it was
+            for name, t in saved_state.items():
+                self.state.tables[name].copy_(t)
         graph = torch.cuda.CUDAGraph()
         before = kernels.launch_count()
         ctx.scratch.clear()   # what parts decide once per step (and launch kernels for) is decided again, inside the graph
@@ -456,6 +507,19 @@ class ModelRunner:
         if word:
             self.err.zero_()
             raise StepError("a kernel reported: " + kernels.describe_error(word))
+
+    def recover(self) -> None:
+        """After a failed step: wait for what is queued on the device, clear the error word and
+        every scratch buffer (kernels keep counters there that must be zero between launches).
+        Pages, weights and captured graphs stay as they are."""
+        torch.cuda.synchronize(self.device)
+        self.err.zero_()
+        self._err_host[0] = 0
+        self.workspace.clear()
+        if self._graph_workspace is not None:
+            self._graph_workspace.clear()
+        self.sampled_tokens.zero_()
+        torch.cuda.synchronize(self.device)
 
     def check_errors(self) -> None:
         """Synchronises and raises if any kernel has set the device error word since the last check."""

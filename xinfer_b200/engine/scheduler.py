@@ -108,6 +108,13 @@ class Scheduler:
         self._lib.xb_sched_commit(self._h, s.ctypes.data if len(s) else None, len(s))
         return self.drain_finished()
 
+    def fail_steps(self) -> List[int]:
+        """A scheduled step failed: abort every request of the steps that are scheduled and not
+        recorded (the running one and the one decided ahead), give their pages back and leave nothing
+        scheduled.  Returns the ids that ended."""
+        self._lib.xb_sched_fail_steps(self._h)
+        return self.drain_finished()
+
     def drain_finished(self) -> List[int]:
         buf = np.zeros(max(self._cap_e, 64), dtype=np.int64)
         out: List[int] = []

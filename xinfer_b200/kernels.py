@@ -94,7 +94,7 @@ def _ok(status: int, what: str, n: int = 1) -> None:
 
 
 # device-side error word -------------------------------------------------------------------------
-ERR_BAD_TOKEN, ERR_BAD_PAGE, ERR_WAIT, ERR_BAD_ROW = 1, 2, 4, 8
+ERR_BAD_TOKEN, ERR_BAD_PAGE, ERR_WAIT, ERR_BAD_ROW, ERR_SCRATCH, ERR_BAD_POSITION = 1, 2, 4, 8, 16, 32
 
 
 def describe_error(word: int) -> str:
@@ -107,13 +107,17 @@ def describe_error(word: int) -> str:
         parts.append("a bounded wait inside a kernel gave up")
     if word & ERR_BAD_ROW:
         parts.append("a requested row outside the step's tokens")
+    if word & ERR_BAD_POSITION:
+        parts.append("a token position outside the position table")
+    if word & ERR_SCRATCH:
+        parts.append("scratch memory that a kernel must find zeroed was not")
     return "; ".join(parts) or "no error"
 
 
 # ---- wrappers --------------------------------------------------------------------------------------
-def embedding(out, table, ids, err, sampled=None):
-    """out[t] = table[ids[t]]; an id -1 - i is replaced on the device by ``sampled[i]`` (int32 ids a
-    sampler left there)."""
+def embedding(out, table, ids, err, sampled=None, scale=None):
+    """out[t] = table[ids[t]] (times ``scale``, if given, rounded to the table's dtype); an id -1 - i
+    is replaced on the device by ``sampled[i]`` (int32 ids a sampler left there)."""
     T, H = out.shape
     _need(out, "out", table.dtype, (T, H))
     _need(table, "table", None, (None, H))
@@ -125,7 +129,15 @@ def embedding(out, table, ids, err, sampled=None):
         _need(sampled, "sampled", torch.int32)
     _ok(kernels_lib().xb_embedding(dtype_code(table.dtype), out.data_ptr(), table.data_ptr(), ids.data_ptr(),
                                    _ptr(sampled), sampled.numel() if sampled is not None else 0,
-                                   T, H, table.shape[0], err.data_ptr(), _stream()), "embedding")
+                                   T, H, table.shape[0], 1.0 if scale is None else float(scale), err.data_ptr(),
+                                   _stream()), "embedding")
+
+
+def logits_post(logits, scale=None, softcap=None):
+    """In place on float32 logits: ``logits *= scale``, then ``logits = softcap * tanh(logits / softcap)``."""
+    _need(logits, "logits", torch.float32)
+    _ok(kernels_lib().xb_logits_post(logits.data_ptr(), logits.numel(), 1.0 if scale is None else float(scale),
+                                     0.0 if softcap is None else float(softcap), _stream()), "logits_post")
 
 
 def rmsnorm(out, x, weight, eps, err, *, branch=None, sum_out=None, rows=None, weight_offset=0.0):
@@ -256,15 +268,22 @@ SAMPLE_PARAMS = np.dtype([
 ])
 
 
-def sample_scratch_bytes(rows: int) -> int:
-    return int(kernels_lib().xb_sample_scratch_bytes(int(rows)))
+def sample_scratch_bytes(capacity: int) -> int:
+    """Bytes of scratch for a sampler that sees at most ``capacity`` rows in one call."""
+    return int(kernels_lib().xb_sample_scratch_bytes(int(capacity)))
 
 
-def sample(out_tokens, logits, params_dev, history_dev, apply_penalties: bool, scratch, err_word=None):
+def sample(out_tokens, logits, params_dev, history_dev, apply_penalties: bool, scratch, err_word=None, *,
+           capacity: Optional[int] = None):
     """One token per logits row into ``out_tokens``; with ``err_word`` (a device int32) its value is
     written to ``out_tokens[R]``, so that one copy brings tokens and error word to the host.
-    ``scratch``: uint8 device buffer of ``sample_scratch_bytes(R)``, zero before its first use."""
+    ``scratch``: uint8 device buffer of ``sample_scratch_bytes(capacity)``, zero before its first use
+    and laid out by ``capacity`` (default: the rows of this call): calls that share a buffer must
+    give the same capacity, whatever their rows."""
     R, V = logits.shape
+    capacity = R if capacity is None else int(capacity)
+    if R > capacity:
+        raise KernelError(f"{R} rows exceed the sampler scratch's capacity {capacity}")
     _need(logits, "logits", torch.float32, (R, V))
     _need(out_tokens, "out_tokens", torch.int32)
     _need(params_dev, "params", torch.uint8)
@@ -273,9 +292,9 @@ def sample(out_tokens, logits, params_dev, history_dev, apply_penalties: bool, s
         raise KernelError("the sampler's parameter record differs between Python and CUDA")
     _need(scratch, "scratch", torch.uint8)
     if (params_dev.numel() < R * SAMPLE_PARAMS.itemsize or out_tokens.numel() < R + (err_word is not None)
-            or scratch.numel() < lib.xb_sample_scratch_bytes(R)):
+            or scratch.numel() < lib.xb_sample_scratch_bytes(capacity)):
         raise KernelError("sampler buffers are smaller than the number of rows")
-    _ok(lib.xb_sample(out_tokens.data_ptr(), logits.data_ptr(), params_dev.data_ptr(), _ptr(history_dev), R, V,
+    _ok(lib.xb_sample(out_tokens.data_ptr(), logits.data_ptr(), params_dev.data_ptr(), _ptr(history_dev), R, capacity, V,
                       int(bool(apply_penalties)), scratch.data_ptr(), _ptr(err_word), _stream()), "sample",
         2 if apply_penalties else 1)
 

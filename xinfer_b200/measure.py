@@ -65,7 +65,7 @@ def decode_attention(cases: Sequence = ((1, 4096), (8, 4096), (64, 4096), (8, 32
     for batch, context in cases:
         ctx, table, stride, num_pages = _attention_context([(context - 1, 1)] * batch, page_size, device)
         layers = 8 if batch * context <= 8 * 32768 else 2
-        caches = [LayerCache(torch.randn(num_pages, kv_heads, page_size, head_dim, device=device).bfloat16(),
+        caches = [LayerCache.of_keys_and_values(torch.randn(num_pages, kv_heads, page_size, head_dim, device=device).bfloat16(),
                              torch.randn(num_pages, kv_heads, page_size, head_dim, device=device).bfloat16(), 0, page_size)
                   for _ in range(layers)]
         q = torch.randn(batch, heads, head_dim, device=device).bfloat16()
@@ -98,7 +98,7 @@ def prefill_attention(cases: Sequence = ((0, 2048), (0, 8192), (24576, 8192)), *
     out = []
     for cached, new in cases:
         ctx, table, stride, num_pages = _attention_context([(cached, new)], page_size, device)
-        cache = LayerCache(torch.randn(num_pages, kv_heads, page_size, head_dim, device=device).bfloat16(),
+        cache = LayerCache.of_keys_and_values(torch.randn(num_pages, kv_heads, page_size, head_dim, device=device).bfloat16(),
                            torch.randn(num_pages, kv_heads, page_size, head_dim, device=device).bfloat16(), 0, page_size)
         q = torch.randn(new, heads, head_dim, device=device).bfloat16()
         o = torch.empty_like(q)

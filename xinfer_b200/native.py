@@ -68,6 +68,7 @@ def _declare_host(lib):
          [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p])
     _sig(lib, "xb_sched_commit", None, [c_void_p, c_void_p, c_int])
     _sig(lib, "xb_sched_schedule_ahead", c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _sig(lib, "xb_sched_fail_steps", c_int, [c_void_p])
     _sig(lib, "xb_sched_drain_finished", c_int, [c_void_p, c_void_p, c_int])
     for name in ("xb_sched_num_waiting", "xb_sched_num_running", "xb_sched_preemptions"):
         _sig(lib, name, c_int, [c_void_p])
@@ -80,7 +81,8 @@ def _declare_host(lib):
 
 def _declare_kernels(lib):
     P, I, F, L = c_void_p, c_int, c_float, c_longlong
-    _sig(lib, "xb_embedding", I, [I, P, P, P, P, I, I, I, I, P, P])
+    _sig(lib, "xb_embedding", I, [I, P, P, P, P, I, I, I, I, F, P, P])
+    _sig(lib, "xb_logits_post", I, [P, L, F, F, P])
     _sig(lib, "xb_rmsnorm", I, [I, P, P, P, P, P, P, I, I, I, F, F, P, P])
     _sig(lib, "xb_add", I, [I, P, P, P, L, P])
     _sig(lib, "xb_gemm_plain", I, [I, I, I, P, P, P, I, I, I, P])
@@ -90,7 +92,7 @@ def _declare_kernels(lib):
     _sig(lib, "xb_attention_plain", I, [I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, P])
     _sig(lib, "xb_swiglu", I, [I, P, P, I, I, P])
     _sig(lib, "xb_widen_bf16", I, [P, P, L, P])
-    _sig(lib, "xb_sample", I, [P, P, P, P, I, I, I, P, P, P])
+    _sig(lib, "xb_sample", I, [P, P, P, P, I, I, I, I, P, P, P])
     _sig(lib, "xb_sample_scratch_bytes", c_longlong, [I])
     _sig(lib, "xb_sample_params_size", I, [])
     _sig(lib, "xb_rmsnorm_bf16", I, [P, P, P, P, P, P, I, I, I, F, F, P, P])

@@ -23,6 +23,7 @@ from .linear import linear
 
 class Attention(Mixer):
     kind = "attention"
+    graph_safe = True
 
     def __init__(self, spec: AttentionSpec, prefix: str, dtype, device):
         super().__init__(spec, prefix, dtype, device)
@@ -48,18 +49,17 @@ class Attention(Mixer):
 
     def load(self, store) -> None:
         p = self.prefix
-        parts = [store.get(p + n + ".weight", self.device, self.dtype) for n in ("q_proj", "k_proj", "v_proj")]
-        if len({t.dtype for t in parts}) != 1:
-            parts = [t.float() for t in parts]
+        # projection matrices take the engine's dtype whatever the file holds (src/models/layers/linear.rs:133-138)
+        parts = [store.get(p + n + ".weight", self.device, self.dtype, operand=True) for n in ("q_proj", "k_proj", "v_proj")]
         self.w_qkv = torch.cat(parts, dim=0).contiguous()
         del parts
-        self.w_o = store.get(p + "o_proj.weight", self.device, self.dtype)
+        self.w_o = store.get(p + "o_proj.weight", self.device, self.dtype, operand=True)
         if self.spec.qk_norm:
             self.q_norm = store.get(p + "q_norm.weight", self.device, torch.float32).float().contiguous()
             self.k_norm = store.get(p + "k_norm.weight", self.device, torch.float32).float().contiguous()
 
     def cache_need(self) -> PagedCacheNeed:
-        return PagedCacheNeed(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
+        return PagedCacheNeed.keys_and_values(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
 
     def prepare_step(self, ctx: StepContext, cache: LayerCache) -> None:
         from . import attention_backend
@@ -78,8 +78,9 @@ class Attention(Mixer):
         head_args = (self.q_norm, self.k_norm, rot.cos if rot else None, rot.sin if rot else None, ctx.positions,
                      ctx.req_of_token, table, stride, nh, nkv, d, rot.rotary_dim if rot else 0,
                      rot.interleaved if rot else False, s.qk_norm_eps, writes_cache, ctx.err)
+        k_pages, v_pages = cache["k"], cache["v"]
         fused = (self.position is None or rot is not None) and gemm_backend.try_fused_qkv(
-            q, cache.k, cache.v, x, self.w_qkv, *head_args)
+            q, k_pages, v_pages, x, self.w_qkv, *head_args)
         if not fused:
             qkv = ws.get("attn.qkv", (T, (nh + 2 * nkv) * d), self.dtype)
             linear(qkv, x, self.w_qkv, ctx.err)
@@ -87,7 +88,7 @@ class Attention(Mixer):
                 q_view = qkv[:, : nh * d].view(T, nh, d)
                 k_view = qkv[:, nh * d:(nh + nkv) * d].view(T, nkv, d)
                 self.position.apply(q_view, k_view, ctx)
-            kernels.qk_norm_rope_write(q, cache.k, cache.v, qkv, *head_args)
+            kernels.qk_norm_rope_write(q, k_pages, v_pages, qkv, *head_args)
         o = ws.get("attn.o", (T, nh, d), self.dtype)
         from . import attention_backend
         attention_backend.attend(o, q, cache, ctx, table, stride, s.window, s.scale)

@@ -139,20 +139,21 @@ def prepare_step(ctx, dtype, nh: int, nkv: int, d: int, page_size: int, window, 
 
 def attend(out, q, cache, ctx, table, stride, window, scale) -> None:
     T, nh, d = q.shape
+    k_pages, v_pages = cache["k"], cache["v"]
     if not (_enabled and kernels.attn_tiled_supported(q.dtype, d)):
-        kernels.attention_plain(out, q, cache.k, cache.v, ctx.positions, ctx.req_of_token, table, stride,
+        kernels.attention_plain(out, q, k_pages, v_pages, ctx.positions, ctx.req_of_token, table, stride,
                                 window, scale, ctx.err)
         return
     plan = _plan(ctx, d)
     took = False
     if plan["tiles"] and PREFILL_TC and kernels.attn_prefill_queries(d, PREFILL_WARPS) == 128:
-        took = kernels.attn_prefill_tc(out, q, cache.k, cache.v, ctx.q_start, ctx.start_pos, ctx.num_entries, table, stride,
+        took = kernels.attn_prefill_tc(out, q, k_pages, v_pages, ctx.q_start, ctx.start_pos, ctx.num_entries, table, stride,
                                        window, scale, DEC_MAX, plan["tiles"], ctx.err, tile_map=plan.get("tile_map"))
     if plan["tiles"] and not took:
-        kernels.attn_prefill_bf16(out, q, cache.k, cache.v, ctx.q_start, ctx.start_pos, ctx.num_entries, table, stride,
+        kernels.attn_prefill_bf16(out, q, k_pages, v_pages, ctx.q_start, ctx.start_pos, ctx.num_entries, table, stride,
                                   window, scale, DEC_MAX, plan["tiles"], plan["prefill_bound"], ctx.err, warps=PREFILL_WARPS)
     if plan["small"]:
-        nkv = cache.k.shape[1]
+        nkv = k_pages.shape[1]
         bound = plan["bound"] if plan["bound"] is not None else stride * cache.page_size
         small = plan["small"]
         part_o = part_ml = tickets = None
@@ -165,14 +166,14 @@ def attend(out, q, cache, ctx, table, stride, window, scale) -> None:
                 # zero-filled when made, left zero by the kernels; sized for either kernel
                 tickets = ctx.workspace.get("attn.tickets", (small * nkv * ((nh // nkv + 15) // 16),), torch.int32)
 
-        step = (q, cache.k, cache.v, ctx.positions, ctx.req_of_token, ctx.q_start, ctx.num_entries, table, stride,
+        step = (q, k_pages, v_pages, ctx.positions, ctx.req_of_token, ctx.q_start, ctx.num_entries, table, stride,
                 window, scale, DEC_MAX, plan["direct"])
         took = False
         planned = _decode_plan(ctx, nh, nkv, d, cache.page_size, window, stride, early=False)
         if planned is not None:
             buf, ctas, splits_max, overlap = planned
             scratch(splits_max)
-            took = kernels.attn_decode_tc(out, part_o, part_ml, q, cache.k, cache.v, buf, table, stride, scale, DEC_MAX,
+            took = kernels.attn_decode_tc(out, part_o, part_ml, q, k_pages, v_pages, buf, table, stride, scale, DEC_MAX,
                                           splits_max, small, ctas, ctx.err, tickets, overlap)
         if not took:
             split, num_splits = decode_split(bound, small * nkv * ((nh // nkv + 15) // 16))

@@ -51,6 +51,12 @@ class Workspace:
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._bufs.values())
 
+    def clear(self) -> None:
+        """Zero every buffer (their addresses stay): counters and tickets that kernels keep at zero
+        between launches are zero again after a step that did not run to its end."""
+        for b in self._bufs.values():
+            b.zero_()
+
 
 @dataclass
 class StepContext:
@@ -92,24 +98,65 @@ class StepContext:
 
 
 @dataclass(frozen=True)
-class PagedCacheNeed:
-    """What a mixer wants from the paged cache: per token, ``kv_heads x head_dim`` keys and the
-    same of values; ``window`` None keeps all tokens."""
+class CacheTensor:
+    """One tensor a mixer keeps per cached token: ``shape`` per token, ``dtype`` (None: the
+    engine's dtype) and where the in-page token axis sits in the page tensor, which has the shape
+    ``(num_pages,) + shape[:token_axis] + (page_size,) + shape[token_axis:]``."""
 
-    kv_heads: int
-    head_dim: int
+    shape: Tuple[int, ...]
+    dtype: Optional[torch.dtype] = None
+    token_axis: int = 0
+
+    def page_shape(self, num_pages: int, page_size: int) -> Tuple[int, ...]:
+        a = self.token_axis
+        if not (0 <= a <= len(self.shape)):
+            raise ValueError(f"token_axis {a} does not fit a per-token shape {self.shape}")
+        return (int(num_pages),) + tuple(self.shape[:a]) + (int(page_size),) + tuple(self.shape[a:])
+
+    def bytes_per_token(self, engine_dtype: torch.dtype) -> int:
+        n = 1
+        for s in self.shape:
+            n *= int(s)
+        return n * torch.empty((), dtype=self.dtype or engine_dtype).element_size()
+
+
+@dataclass(frozen=True)
+class PagedCacheNeed:
+    """What a mixer wants from the paged cache: named tensors per token (keys and values for
+    attention, one latent vector for a mixer that caches that, ...), how long tokens are kept
+    (``window`` None keeps all) and, if it matters to its kernels, the page size (None: the
+    engine's).  Mixers with the same window and page size share a page pool and block tables."""
+
+    tensors: Tuple[Tuple[str, CacheTensor], ...]
     window: Optional[int] = None
+    page_size: Optional[int] = None
+
+    @staticmethod
+    def keys_and_values(kv_heads: int, head_dim: int, window: Optional[int] = None,
+                        page_size: Optional[int] = None) -> "PagedCacheNeed":
+        """Keys and values ``[page, kv_head, slot, head_dim]``: a head's page is one contiguous block."""
+        t = CacheTensor((int(kv_heads), int(head_dim)), None, 1)
+        return PagedCacheNeed((("k", t), ("v", t)), window, page_size)
+
+    def bytes_per_token(self, engine_dtype: torch.dtype) -> int:
+        return sum(t.bytes_per_token(engine_dtype) for _, t in self.tensors)
 
 
 @dataclass
 class LayerCache:
-    """The pages of one layer run: K and V ``[num_pages, kv_heads, page_size, head_dim]`` and
-    the index of the cache group whose block tables address them."""
+    """The pages of one layer run: the mixer's named page tensors (see ``CacheTensor.page_shape``),
+    the index of the cache group whose block tables address them, and that group's page size."""
 
-    k: torch.Tensor
-    v: torch.Tensor
+    tensors: Dict[str, torch.Tensor]
     group: int
     page_size: int
+
+    @staticmethod
+    def of_keys_and_values(k: torch.Tensor, v: torch.Tensor, group: int, page_size: int) -> "LayerCache":
+        return LayerCache({"k": k, "v": v}, group, page_size)
+
+    def __getitem__(self, name: str) -> torch.Tensor:
+        return self.tensors[name]
 
 
 class Part:
@@ -117,6 +164,10 @@ class Part:
     ``weight_specs(spec, prefix)`` and the methods ``load`` and ``forward``."""
 
     kind: str = ""
+    # True: ``forward`` takes everything about the step from device tensors of the context (never
+    # from its host copies or actual lengths), so a decode step through this part can be captured
+    # in a CUDA graph and replayed.  Parts that loop over entries on the host leave it False.
+    graph_safe: bool = False
 
     def __init__(self, spec: PartSpec, prefix: str, dtype: torch.dtype, device):
         self.spec = spec

@@ -15,6 +15,7 @@ from .base import Norm, register_norm
 
 class RMSNorm(Norm):
     kind = "rmsnorm"
+    graph_safe = True
 
     def __init__(self, spec: NormSpec, prefix: str, dtype, device):
         super().__init__(spec, prefix, dtype, device)

@@ -33,6 +33,7 @@ def inv_frequencies(theta: float, rotary_dim: int) -> np.ndarray:
 
 class Rope(PositionEncoding):
     kind = "rope"
+    graph_safe = True
 
     def __init__(self, spec: RopeSpec, prefix: str, dtype, device):
         super().__init__(spec, prefix, dtype, device)

@@ -16,6 +16,7 @@ from .linear import linear
 
 class SwiGLU(FeedForward):
     kind = "swiglu"
+    graph_safe = True
 
     def __init__(self, spec: FeedForwardSpec, prefix: str, dtype, device):
         super().__init__(spec, prefix, dtype, device)
@@ -34,13 +35,11 @@ class SwiGLU(FeedForward):
 
     def load(self, store) -> None:
         p = self.prefix
-        g = store.get(p + "gate_proj.weight", self.device, self.dtype)
-        u = store.get(p + "up_proj.weight", self.device, self.dtype)
-        if g.dtype != u.dtype:
-            g, u = g.float(), u.float()
+        g = store.get(p + "gate_proj.weight", self.device, self.dtype, operand=True)
+        u = store.get(p + "up_proj.weight", self.device, self.dtype, operand=True)
         self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
         del g, u
-        self.w_down = store.get(p + "down_proj.weight", self.device, self.dtype)
+        self.w_down = store.get(p + "down_proj.weight", self.device, self.dtype, operand=True)
 
     def forward(self, x, ctx: StepContext):
         s = self.spec

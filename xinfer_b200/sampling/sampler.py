@@ -7,7 +7,7 @@ from typing import Optional, Sequence
 import numpy as np
 import torch
 
-from .. import kernels
+from .. import kernels, tracing
 from .params import SamplingParams
 
 # tokens that the penalties count: the most recent ones of the request, as many as the reference
@@ -70,8 +70,20 @@ class Sampler:
         self._params_dev[:nb].copy_(self._params_host[:nb], non_blocking=True)
         if any_pen:
             self._hist_dev[:off].copy_(self._hist_host[:off], non_blocking=True)
-        kernels.sample(self._out_dev, logits, self._params_dev, self._hist_dev, any_pen, self._scratch, self.err_word)
+        if tracing.ENABLED:
+            tracing.push("sample")
+        kernels.sample(self._out_dev, logits, self._params_dev, self._hist_dev, any_pen, self._scratch, self.err_word,
+                       capacity=self.max_rows)
+        if tracing.ENABLED:
+            tracing.pop()
         return self._out_dev[:R]
+
+    def reset(self) -> None:
+        """After a failed step: the scratch is zeroed again (a kernel that did not finish may have
+        left counters behind) and a queued copy is forgotten."""
+        self._scratch.zero_()
+        self._copied = 0
+        self._copy_done = None
 
     def to_host(self, tokens_dev: torch.Tensor) -> np.ndarray:
         """Copy sampled ids to the host (synchronises the stream)."""

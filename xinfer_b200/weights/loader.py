@@ -3,10 +3,15 @@
 Every part declares the tensors it needs as ``WeightSpec`` (full name, shape, how the
 random-weights mode draws it).  ``WeightStore.check`` compares the declared set with what the
 files hold and raises ONE error that lists missing tensors, unexpected tensors and wrong shapes.
+Tensors the model does not declare are no error by themselves (a checkpoint may carry a spare
+head beside a tied one, or position buffers): they are listed in a warning and in
+``WeightStore.unexpected``; ``strict=True`` makes them fatal.
 ``WeightStore.get`` hands a tensor to a part on the target device:
 
 * 16-bit floats arrive as bfloat16 (float32 when the engine runs in float32);
-* a tensor stored in 32-bit floats stays float32;
+* a tensor stored in 32-bit floats stays float32 - unless the part asks for it as an operand of
+  the engine's matrix products (``operand=True``: projection, embedding and head matrices), which
+  take the engine's dtype whatever the file holds, as the reference casts them at load;
 * integer tables arrive as int32.
 
 The reference resolves names through a prefix-pushing handle over the mapped files
@@ -15,6 +20,7 @@ The reference resolves names through a prefix-pushing handle over the mapped fil
 """
 from __future__ import annotations
 
+import warnings
 from dataclasses import dataclass
 from typing import Dict, List, Sequence, Tuple
 
@@ -45,6 +51,10 @@ class WeightError(ValueError):
         super().__init__("\n".join(lines))
 
 
+class UnexpectedWeightsWarning(UserWarning):
+    """The files hold tensors that the model does not declare; they are not loaded."""
+
+
 @dataclass(frozen=True)
 class WeightSpec:
     name: str
@@ -66,11 +76,15 @@ class WeightStore:
         for f in self.files:
             for name in f.entries:
                 self.index[name] = f
+        self.unexpected: List[str] = []   # filled by check(): tensors of the files that no part declared
 
     def names(self) -> List[str]:
         return sorted(self.index)
 
-    def check(self, specs: Sequence[WeightSpec]) -> None:
+    def check(self, specs: Sequence[WeightSpec], *, strict: bool = False) -> List[str]:
+        """Raise one ``WeightError`` for missing tensors, wrong shapes and unsupported dtypes (it
+        lists the unexpected tensors too).  Unexpected tensors alone are returned and warned about,
+        or raised for with ``strict``."""
         want = {}
         for s in specs:
             want[s.name] = tuple(s.shape)
@@ -86,18 +100,26 @@ class WeightStore:
                 wrong_shape.append((n, e.shape, shape))
             if e.dtype not in _FLOATS and e.dtype not in _INTS:
                 wrong_dtype.append((n, str(e.dtype)))
-        if missing or unexpected or wrong_shape or wrong_dtype:
+        if missing or wrong_shape or wrong_dtype or (strict and unexpected):
             raise WeightError(missing, unexpected, wrong_shape, wrong_dtype)
+        self.unexpected = unexpected
+        if unexpected:
+            shown = ", ".join(unexpected[:8]) + (f", ... ({len(unexpected) - 8} more)" if len(unexpected) > 8 else "")
+            warnings.warn(f"{len(unexpected)} tensor(s) of '{self.model_dir}' are not part of the model and are not "
+                          f"loaded: {shown}", UnexpectedWeightsWarning, stacklevel=2)
+        return unexpected
 
     def raw(self, name: str) -> torch.Tensor:
         """The stored tensor on the CPU, in its stored dtype."""
         return self.index[name].tensor(name)
 
-    def get(self, name: str, device, compute_dtype: torch.dtype) -> torch.Tensor:
+    def get(self, name: str, device, compute_dtype: torch.dtype, *, operand: bool = False) -> torch.Tensor:
+        """``operand``: the tensor is an operand of the engine's matrix products and takes
+        ``compute_dtype`` whatever it was stored in (src/models/layers/linear.rs:133-138)."""
         t = self.raw(name)
         if t.dtype in _INTS:
             return t.to(device=device, dtype=torch.int32)
-        if compute_dtype == torch.float32 or t.dtype in (torch.float32, torch.float64):
+        if compute_dtype == torch.float32 or (not operand and t.dtype in (torch.float32, torch.float64)):
             target = torch.float32
         else:
             target = torch.bfloat16

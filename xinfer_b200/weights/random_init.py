@@ -91,16 +91,17 @@ class RandomWeightStore:
     def names(self) -> List[str]:
         return sorted(self.specs)
 
-    def check(self, specs: Sequence[WeightSpec]) -> None:
+    def check(self, specs: Sequence[WeightSpec], *, strict: bool = False) -> List[str]:
         from .loader import WeightError
         want = {s.name: tuple(s.shape) for s in specs}
         missing = sorted(n for n in want if n not in self.specs)
         unexpected = sorted(n for n in self.specs if n not in want)
         wrong = [(n, self.specs[n].shape, want[n]) for n in sorted(want) if n in self.specs and tuple(self.specs[n].shape) != want[n]]
-        if missing or unexpected or wrong:
+        if missing or wrong or (strict and unexpected):
             raise WeightError(missing, unexpected, wrong)
+        return unexpected
 
-    def get(self, name: str, device, compute_dtype: torch.dtype) -> torch.Tensor:
+    def get(self, name: str, device, compute_dtype: torch.dtype, *, operand: bool = False) -> torch.Tensor:
         spec = self.specs[name]
         target = torch.float32 if compute_dtype == torch.float32 else torch.bfloat16
         dev = torch.device(device)
