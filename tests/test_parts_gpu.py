@@ -100,7 +100,8 @@ def test_attention_part_in_portions(dtype, nh, nkv, d, window, page):
     part = build_part("mixer", spec, "a.", dtype, DEV)
     part.load(FakeStore(w))
     need = part.cache_need()
-    assert (need.kv_heads, need.head_dim, need.window) == (nkv, d, window)
+    assert [n for n, _ in need.tensors] == ["k", "v"] and need.window == window and need.page_size is None
+    assert all(t.shape == (nkv, d) and t.page_shape(40, page) == (40, nkv, page, d) for _, t in need.tensors)
     cm, asm = context(None, dtype, page=page, pages=40, window=window)
     cache = LayerCache.of_keys_and_values(torch.zeros(40, nkv, page, d, dtype=dtype, device=DEV), torch.zeros(40, nkv, page, d, dtype=dtype, device=DEV), 0, page)
     x = (torch.randn(T, H)).to(dtype)
