@@ -1,7 +1,9 @@
 #!/usr/bin/env python3
 """Decode and prefill throughput at Qwen3-8B layer sizes with random weights, on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--shape 8b|0.6b|32b] [--impl ours|reference]
+    python bench.py --workload mixed [--shape 0.6b|8b]     # 64 requests, continuous batching
+    python bench.py --kernels                               # single kernels at serving sizes
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 and the context length
 of the configuration (a "step" is one decode step of the whole batch), timed on the device with
@@ -9,7 +11,16 @@ CUDA events around exactly K steps; ``e2e`` is the same through the Python entry
 (``Engine.step``: host token ids in through pinned memory every step, sampled ids read back every
 step).  ``prefill`` times one step of 2,048 prompt tokens; ``roofline`` divides the bytes a decode
 step must read (every weight once, the cache of the live requests) by its time; ``points`` holds
-decode at batch 1 and 64.  Peaks come from MEASURED_PEAKS.json beside this file when present.
+decode at batch 1 and 64 at the same context, and ``baseline_b1/8/64``: decode tokens per second
+over 256 steps after a 2,048-token prompt (context 2,048 -> 2,304).  Fractions are given against the
+measured peaks (MEASURED_PEAKS.json beside this file, when present) and, as ``frac_nominal``, against
+the nominal 8 TB/s and 2.25 PFLOP/s.  The logits of the first prefill and of the last decode step
+are checked to be finite (their largest magnitudes stand in ``config``).
+
+``--workload mixed``: 64 requests with prompt lengths uniform in 16..2,048 (seeded), 256 new tokens
+each, through ``Engine.generate_sync``: decoded and total tokens per second, steps, the distribution
+of step times and the number of preemptions, as one JSON line (the reference's batch test,
+src/main.rs:103-115, 502-555, is the counterpart).
 """
 from __future__ import annotations
 
@@ -40,6 +51,8 @@ SHAPES = {
 }
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
+NOMINAL_HBM_GBS = 8000.0
+NOMINAL_BF16_TFLOPS = 2250.0
 PAGE = 16
 SETTLE = 24   # untimed decode steps between a prefill burst and any timed decode step, beside --warmup
 
@@ -66,7 +79,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "25"],
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "10"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -112,6 +125,84 @@ def reference_arm():
     return 0
 
 
+def check_finite(logits, what: str) -> float:
+    """A benchmark line must not come from a model that computes nonsense: every logit finite, and
+    not all of them alike.  Returns the largest magnitude."""
+    import torch
+    v = logits.float()
+    if not bool(torch.isfinite(v).all()):
+        raise SystemExit(f"bench.py: the logits of {what} are not finite")
+    if float(v.max() - v.min()) == 0.0:
+        raise SystemExit(f"bench.py: the logits of {what} are all equal")
+    return round(float(v.abs().max()), 3)
+
+
+def mixed_workload(args, cfg, full, pk) -> int:
+    """Continuous batching: ``--requests`` requests, prompt lengths uniform in [16, 2048] (seeded), 256 new
+    tokens each, greedy, through the Python entry point.  One untimed pass (graphs are captured, buffers
+    sized), then the timed one with fresh prompts of the same lengths."""
+    import numpy as np
+    import torch
+    from xinfer_b200.config import EngineConfig
+    from xinfer_b200.engine.llm import Engine
+    from xinfer_b200.engine.runner import ModelRunner
+    from xinfer_b200.sampling import SamplingParams
+
+    N, new_tokens = args.requests, 256
+    max_len = 2048 + new_tokens + 64
+    runner = ModelRunner.random(cfg, seed=0, dtype="bfloat16", block_size=PAGE, num_blocks=N * (max_len // PAGE + 1),
+                                max_num_seqs=N, max_model_len=max_len)
+    engine = Engine(EngineConfig(weight_path="(random)", block_size=PAGE, max_num_seqs=N, max_num_batched_tokens=8192,
+                                 prefill_chunk_size=2048, max_model_len=max_len, disable_cuda_graph=args.no_graph),
+                    "bf16", runner=runner)
+    rng = np.random.default_rng(0)
+    V = cfg["vocab_size"]
+    lens = rng.integers(16, 2049, size=N)
+    sp = SamplingParams(temperature=0.0, max_tokens=new_tokens, ignore_eos=True)
+    clocks = ClockSampler()
+    clocks.start()
+    result = None
+    for timed in (False, True):
+        prompts = [rng.integers(0, V, size=int(n)).tolist() for n in lens]
+        before = dict(engine.stats)
+        torch.cuda.synchronize()
+        t0 = time.time()
+        ids = [engine.add_request(p, sp) for p in prompts]
+        step_ms = []
+        last = t0
+        while any(i in engine._live for i in ids):
+            engine.step()
+            now = time.time()
+            step_ms.append((now - last) * 1e3)
+            last = now
+        torch.cuda.synchronize()
+        t1 = time.time()
+        outs = [engine._done.pop(i) for i in ids]
+        if any(o.error for o in outs) or any(o.decoded_length != new_tokens for o in outs):
+            raise SystemExit("bench.py: the mixed workload did not finish every request")
+        if timed:
+            st = {k: engine.stats[k] - before[k] for k in before}
+            decoded, prompt = sum(o.decoded_length for o in outs), int(lens.sum())
+            step_ms.sort()
+            pick = lambda q: round(step_ms[min(len(step_ms) - 1, int(q * len(step_ms)))], 3)
+            result = {
+                "metric": f"decoded tok/s, continuous batching of {N} requests (Qwen3-{args.shape.upper()} shape)",
+                "value": round(decoded / (t1 - t0), 1), "unit": "tokens/s", "total_tok_s": round((decoded + prompt) / (t1 - t0), 1),
+                "n_gpus": 1, "seconds": round(t1 - t0, 3), "steps": st["steps"], "steps_decided_ahead": st["steps_decided_ahead"],
+                "preemptions": st["preemptions"], "step_ms": {"p50": pick(0.5), "p90": pick(0.9), "p99": pick(0.99), "max": round(step_ms[-1], 3)},
+                "prompt_tokens": prompt, "decoded_tokens": decoded, "dtype": "bf16", "impl": "ours",
+                "data": "synthetic (random weights, seeded uniform token ids)", "higher_is_better": True,
+                "config": {"model": f"Qwen3-{args.shape.upper()} shape", "layers": cfg["num_hidden_layers"],
+                           "layers_of_config": full["num_hidden_layers"], "requests": N, "prompt_len": "uniform 16..2048",
+                           "new_tokens": new_tokens, "page_size": PAGE, "max_num_batched_tokens": 8192,
+                           "prefill_chunk_size": 2048, "cuda_graph": not args.no_graph},
+                "clocks": clocks.summary(t0, t1),
+            }
+    clocks.stop()
+    print(json.dumps(result))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -126,6 +217,9 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--workload", default="steps", choices=["steps", "mixed"],
+                    help="'mixed': 64 requests of 16..2,048 prompt tokens under continuous batching, instead of the step benchmark")
+    ap.add_argument("--requests", type=int, default=64, help="requests of the mixed workload")
     ap.add_argument("--kernels", action="store_true",
                     help="instead of the step benchmark, time single kernels at serving sizes: one JSON line each")
     args = ap.parse_args()
@@ -154,6 +248,8 @@ def main() -> int:
     pk = peaks()
     full = dict(CONFIG, **SHAPES[args.shape])
     cfg = dict(full, num_hidden_layers=args.layers or full["num_hidden_layers"])
+    if args.workload == "mixed":
+        return mixed_workload(args, cfg, full, pk)
     max_b = args.batch if args.no_points else max(args.batch, 64)
     pages_per_req = (args.context + PAGE - 1) // PAGE + 1
     t_load = time.time()
@@ -213,9 +309,11 @@ def main() -> int:
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        runner.step([StepInput(s, ids, [PREFILL_TOKENS - 1])])
+        logits = runner.step([StepInput(s, ids, [PREFILL_TOKENS - 1])])
         e1.record()
         torch.cuda.synchronize()
+        if i == 0:
+            absmax_prefill = check_finite(logits, "the first prefill")
         if i >= 3:
             pre_ms.append(e0.elapsed_time(e1))
         runner.close_request(s)
@@ -227,7 +325,8 @@ def main() -> int:
     T = PREFILL_TOKENS
     flops = 2.0 * T * layer_params * L + 2.0 * V * H + L * 4.0 * nh * d * (T * (T + 1) / 2)
     prefill = {"value": round(T / (pre / 1e3), 1), "tokens": T, "ms": round(pre, 3),
-               "frac": round(flops / (pre / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+               "frac": round(flops / (pre / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+               "frac_nominal": round(flops / (pre / 1e3) / (NOMINAL_BF16_TFLOPS * 1e12), 4)}
 
     # ---- decode at the headline batch --------------------------------------------------------------------
     B = args.batch
@@ -241,7 +340,9 @@ def main() -> int:
     kv_bytes = runner.kv_bytes_per_token * ctx_mid * B
     achieved = (weight_bytes + kv_bytes) / (ms / 1e3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": round(achieved / pk["hbm_gbs"], 4)}
+                "frac": round(achieved / pk["hbm_gbs"], 4), "frac_nominal": round(achieved / NOMINAL_HBM_GBS, 4)}
+    absmax_decode = check_finite(runner.step([StepInput(s, rng.integers(0, V, size=1), [0]) for s in slots],
+                                             allow_graph=use_graph), "the last decode step")
     close(slots)
 
     # ---- the same through the Python entry point ----------------------------------------------------------
@@ -292,6 +393,12 @@ def main() -> int:
             m, _, _ = decode_device(sl, k, warmup)
             points[f"decode_b{b}"] = round(b / (m / 1e3), 1)
             close(sl)
+        # the reference configuration's own decode setting: a 2,048-token prompt, then 256 decoded tokens
+        for b in (1, 8, 64):
+            sl = fill(b, PREFILL_TOKENS - warmup - SETTLE)
+            m, _, _ = decode_device(sl, 256, warmup)
+            points[f"baseline_b{b}"] = round(b / (m / 1e3), 1)
+            close(sl)
     clocks.stop()
 
     out = {
@@ -303,7 +410,8 @@ def main() -> int:
                    "hidden": H, "heads": nh, "kv_heads": nkv, "head_dim": d, "intermediate": I, "vocab": V,
                    "global_batch": B, "seq_len": args.context, "page_size": PAGE, "parallelism": "1 GPU",
                    "cuda_graph": use_graph, "l2": "inputs larger than L2 (weights read every step)",
-                   "peaks": pk["source"], "load_s": round(load_s, 1), "settle_steps": SETTLE},
+                   "peaks": pk["source"], "settle_steps": SETTLE,
+                   "logit_absmax_prefill": absmax_prefill, "logit_absmax_decode": absmax_decode},
         "clocks": ck, "e2e": e2e, "gpu_launches": int(launches), "prefill": prefill, "roofline": roofline, "points": points,
     }
     print(json.dumps(out))

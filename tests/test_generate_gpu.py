@@ -231,3 +231,77 @@ def test_graphs_follow_the_context_past_a_table_width(tmp_path):
             row = ref[len(p) + i - 1]
             assert row[tok] >= row.max() - 2 * drift, (i, tok)
     eng.runner.cache.check_consistent()
+
+
+def test_a_checkpoint_stored_in_float32_runs_a_bfloat16_engine_on_bfloat16_weights(model_folders):
+    """Projection, embedding and head matrices take the engine's dtype at load whatever the file
+    holds (norm weights stay float32): a decode step then runs on the tcgen05 product, not on the
+    float32 FMA product, and the logits are the plain implementation's up to the bfloat16 drift."""
+    from xinfer_b200 import kernels
+    from xinfer_b200.engine.runner import ModelRunner, StepInput
+    folder = model_folders("A", torch.float32)
+    cfg, w = plain.load_folder(folder)
+    r = ModelRunner(folder, "bfloat16", block_size=16, num_blocks=16, max_num_seqs=2)
+    block = r.model.blocks[0]
+    assert block.mixer.w_qkv.dtype == torch.bfloat16 and block.mixer.w_o.dtype == torch.bfloat16
+    assert block.mixer.q_norm.dtype == torch.float32
+    assert r.model.embed.dtype == torch.bfloat16 and r.model.final_norm.weight.dtype == torch.float32
+    ffn = [p for p in block.all_parts() if p.kind == "swiglu"][0]
+    assert ffn.w_gate_up.dtype == torch.bfloat16 and ffn.w_down.dtype == torch.bfloat16
+    p = prompts_for("A", [40])[0]
+    slot = r.open_request()
+    got = [r.step([StepInput(slot, p[:30], range(30))]).float().cpu().clone()]
+    before = kernels.launch_counts()
+    for j in range(30, 40):
+        got.append(r.step([StepInput(slot, p[j:j + 1], [0])]).float().cpu().clone())
+    r.check_errors()
+    after = kernels.launch_counts()
+    assert after.get("gemm_skinny_tc", 0) - before.get("gemm_skinny_tc", 0) >= 10 * (4 * 2 + 1)
+    assert after.get("gemm_plain", 0) == before.get("gemm_plain", 0)
+    # the engine's weights are the file's rounded to bfloat16: the oracle gets the same
+    wb = {k: (v.to(torch.bfloat16).float() if not k.endswith("norm.weight") and "layernorm" not in k else v) for k, v in w.items()}
+    ref = plain.forward(cfg, wb, p)
+    tol = 3.0 * (plain.forward(cfg, wb, p, round_to=torch.bfloat16) - ref).abs().max().item()
+    assert (torch.cat(got) - ref).abs().max().item() <= tol
+
+
+def test_scarce_pages_under_bfloat16_graphs_and_steps_decided_ahead(model_folders):
+    """Preemption while the next decode step is already queued on the device, with decode steps
+    replayed from CUDA graphs: the tight pool must give the tokens of the roomy one, and be whole after."""
+    from xinfer_b200 import SamplingParams
+    folder = model_folders("B", torch.bfloat16)
+    prompts = prompts_for("B", [30, 26, 22, 18], seed=3)
+    sp = [SamplingParams(temperature=0.7, max_tokens=40, ignore_eos=True, seed=i) for i in range(4)]
+    opts = dict(disable_cuda_graph=False, disable_run_ahead=False)
+    roomy_engine = engine(folder, "bf16", "B", num_blocks=64, **opts)
+    roomy = roomy_engine.generate_sync(sp, prompts)
+    assert roomy_engine.stats["preemptions"] == 0 and roomy_engine.stats["steps_decided_ahead"] > 20
+    tight_engine = engine(folder, "bf16", "B", num_blocks=20, **opts)     # 160 tokens for 4 requests that grow to ~260
+    tight = tight_engine.generate_sync(sp, prompts)
+    assert tight_engine.stats["preemptions"] > 0 and tight_engine.stats["steps_decided_ahead"] > 5
+    assert tight_engine.runner.last_used_graph
+    for a, b in zip(roomy, tight):
+        assert a.decode_output == b.decode_output and b.finish_reason == "length"
+    tight_engine.runner.cache.check_consistent()
+    assert tight_engine.runner.cache.free_pages() == 20 and tight_engine.runner.cache.live_requests() == 0
+
+
+def test_logits_do_not_change_precision_with_the_number_of_rows(model_folders):
+    """Up to 32 wanted rows the head runs on the engine's tcgen05 product, above on the library's; both
+    write float32 accumulators.  The same token's logits at 32 and at 33 rows must agree to float32
+    accumulation order, far below the spacing of bfloat16 (which would make ties and move a greedy token)."""
+    from xinfer_b200.engine.runner import ModelRunner, StepInput
+    folder = model_folders("B", torch.bfloat16)
+    r = ModelRunner(folder, "bfloat16", block_size=8, num_blocks=64, max_num_seqs=2)
+    p = prompts_for("B", [33])[0]
+    rows = {}
+    for n in (32, 33):
+        slot = r.open_request()
+        rows[n] = r.step([StepInput(slot, p[:n], range(n))]).float().cpu().clone()
+        r.close_request(slot)
+    r.check_errors()
+    a, b = rows[32], rows[33][:32]
+    assert (a - b).abs().max().item() < 1e-4 * max(1.0, a.abs().max().item())
+    # not values of bfloat16: the low 16 bits of the float32 words are in use in both
+    for t in (a, rows[33]):
+        assert (t.view(torch.int32) & 0xFFFF).ne(0).float().mean().item() > 0.9

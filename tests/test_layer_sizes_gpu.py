@@ -109,3 +109,41 @@ def test_a_long_prompt_at_real_layer_sizes(dtype, sized_folder, tmp_path):
             assert d <= tol[i], f"{dtype} {mode}: position {pos} (step {step}) differs by {d:.3g} > {tol[i]:.3g}"
             checked += 1
     assert checked == len(want_whole) + 9
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_full_depth_at_the_smallest_published_shape(dtype, tmp_path):
+    """All 28 layers of the 0.6B shape (a small vocabulary keeps the plain implementation quick):
+    200 tokens whole, then 60 token by token.  What only depth shows - error growth over the
+    layers in bfloat16, a scratch buffer reused one layer too early - shows here."""
+    from xinfer_b200.weights import write_random_model
+    H, nh, nkv, d, inter, _, tied, _ = SHAPES["0.6b"]
+    vocab, layers = 2003, 28
+    cfg = dict(architectures=["Qwen3ForCausalLM"], vocab_size=vocab, hidden_size=H, intermediate_size=inter,
+               num_hidden_layers=layers, num_attention_heads=nh, num_key_value_heads=nkv, head_dim=d,
+               rms_norm_eps=1e-6, rope_theta=1000000.0, max_position_embeddings=4096,
+               tie_word_embeddings=tied, sliding_window=None, eos_token_id=1)
+    folder = write_random_model(str(tmp_path / "deep"), cfg, seed=13, dtype=torch.bfloat16, override=sharpen)
+    rng = np.random.default_rng(6)
+    seq = rng.integers(0, vocab, size=260).tolist()
+    tb = TraceBuilder()
+    tb.step([("d", ("deep", 0), 0, seq[:200], True)])
+    for j in range(200, 260):
+        tb.step([("d", ("deep", 0), j, seq[j:j + 1], True)], end=["d"] if j == 259 else [])
+    out = run_trace(folder, dtype, tb.steps, str(tmp_path / "out"), max_tokens=tb.peak, page_size=16)
+    cfg_p, w = plain.load_folder(folder)
+    ref = plain.forward(cfg_p, w, seq).numpy()
+    if dtype == "float32":
+        _, w64 = plain.load_folder(folder, dtype=torch.float64)
+        own = float(np.abs(plain.forward(cfg_p, w64, seq).float().numpy() - ref).max())
+        tol = max(2e-5, 4.0 * own)
+    else:
+        tol = 3.0 * float(np.abs(plain.forward(cfg_p, w, seq, round_to=torch.bfloat16).numpy() - ref).max())
+    worst = 0.0
+    for step, rows in tb.rows.items():
+        for r, (_, pos) in enumerate(rows):
+            dlt = float(np.abs(out[step][r] - ref[pos]).max())
+            worst = max(worst, dlt)
+            assert dlt <= tol, f"{dtype}: position {pos} (step {step}) differs by {dlt:.3g} > {tol:.3g}"
+    assert np.isfinite(ref).all()
+    print(f"full depth {dtype}: worst difference {worst:.3g}, tolerance {tol:.3g}")

@@ -75,6 +75,7 @@ def _stream() -> int:
 
 
 _launches = 0
+_by_name: dict = {}
 
 # Use the 16-byte-access bfloat16 kernels for norm / gate / q-k preparation where sizes allow;
 # tests switch this off to compare them with the plain kernels.
@@ -86,11 +87,17 @@ def launch_count() -> int:
     return _launches
 
 
+def launch_counts() -> dict:
+    """Launches so far by wrapper name (a copy): which kernels a step really ran."""
+    return dict(_by_name)
+
+
 def _ok(status: int, what: str, n: int = 1) -> None:
     global _launches
     if status != 0:
         raise KernelError(f"{what}: CUDA error {status} at launch")
     _launches += n
+    _by_name[what] = _by_name.get(what, 0) + n
 
 
 # device-side error word -------------------------------------------------------------------------

@@ -2,7 +2,8 @@
 
 float32: the engine's own FMA kernel (true 32-bit, no tensor-core mode).  bfloat16: the engine's
 tcgen05 kernel for steps of few tokens, else the library matrix product, as in the reference
-(cuBLAS through its tensor library); see ``gemm_backend``.
+(cuBLAS through its tensor library); see ``gemm_backend``.  Both write float32 accumulators
+straight into a float32 ``out`` (the logits).
 """
 from __future__ import annotations
 
@@ -23,8 +24,9 @@ def linear(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, err: Option
         if out.dtype == torch.bfloat16:
             torch.mm(x, weight.t(), out=out)
         else:
-            tmp = torch.mm(x, weight.t())
-            kernels.widen_bf16(out, tmp)
+            # float32 out of the library product too: its accumulators are never rounded to bfloat16, so a
+            # row's logits are the same numbers whichever kernel the size of the batch selects
+            torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
         return out
     kernels.gemm_plain(out, x, weight)
     return out
