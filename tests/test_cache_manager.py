@@ -131,3 +131,25 @@ def test_random_orders_keep_every_page_accounted_for(seed):
     for s in list(live):
         cm.close_request(s)
     assert [cm.free_pages(g) for g in range(2)] == [g.num_pages for g in groups]
+
+
+def test_the_log_of_freed_pages():
+    """With the log on, every page that goes back (a closed request, a window that has passed) is
+    reported exactly once; with it off nothing is kept."""
+    from xinfer_b200.cache.manager import CacheGroup, CacheManager
+    cm = CacheManager([CacheGroup(4, 16, None), CacheGroup(4, 16, 6)], 2)
+    a = cm.open_request()
+    assert cm.extend(a, 10) and cm.drain_freed() == []
+    cm.advance(a, 10)
+    assert cm.drain_freed() == []          # the log is off
+    cm.log_freed(True)
+    assert cm.extend(a, 21)
+    cm.advance(a, 21)                      # the windowed group lets go of what lies wholly before position 16
+    freed = cm.drain_freed()
+    assert freed and all(g == 1 for g, _ in freed) and cm.drain_freed() == []
+    held = [p for p in cm.table(a, 0)] + [p for p in cm.table(a, 1) if p >= 0]
+    cm.close_request(a)
+    rest = cm.drain_freed()
+    assert sorted(p for g, p in rest if g == 0) == sorted(cm_pages for cm_pages in held[:6])
+    assert len(rest) == len(held) and len(set(rest)) == len(rest)
+    cm.check_consistent()

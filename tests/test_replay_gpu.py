@@ -56,3 +56,29 @@ def test_every_way_of_cutting_gives_the_plain_logits(name, dtype, model_folders,
                 for r in rows:
                     assert np.array_equal(r, base), f"{mode} request {i} position {pos} is not bit-identical to the whole run"
     print(name, dtype, "worst difference per mode:", {k: f"{v:.3g}" for k, v in worst.items()}, "tolerance", [f"{t:.3g}" for t in tol])
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("C", "bfloat16")])
+def test_freed_pages_are_poisoned_and_nothing_reads_them(name, dtype, model_folders):
+    """The debug mode that fills every freed page with NaN in every layer before the next step: the
+    four ways of cutting over a pool so small that pages cycle (configuration C also gives pages back
+    behind its window) must still give the plain logits - no kernel reads a page it does not own."""
+    from helpers import replay_in_process
+    from xinfer_b200.engine.runner import ModelRunner
+    store = torch.float32 if dtype == "float32" else torch.bfloat16
+    folder = model_folders(name, store)
+    prompts = prompts_for(name, LENGTHS[name])
+    tb = build_all_modes(prompts, seed=len(name))
+    page = PAGE_SIZE[name]
+    runner = ModelRunner(folder, dtype, block_size=page, num_blocks=(tb.peak + page - 1) // page, max_num_seqs=8,
+                         poison_freed_pages=True)
+    out = replay_in_process(runner, tb.steps)
+    assert runner.pages_poisoned > runner.num_blocks, "pages must have been freed, poisoned and used again"
+    cfg, w = plain.load_folder(folder)
+    ref = [plain.forward(cfg, w, p).numpy() for p in prompts]
+    tol = [2e-5 if dtype == "float32" else 3.0 * np.abs(plain.forward(cfg, w, p, round_to=torch.bfloat16).numpy() - r).max()
+           for p, r in zip(prompts, ref)]
+    for step, rows in tb.rows.items():
+        assert np.isfinite(out[step]).all(), f"step {step} read a poisoned page"
+        for r, ((mode, i), pos) in enumerate(rows):
+            assert float(np.abs(out[step][r] - ref[i][pos]).max()) <= tol[i], (mode, i, pos)

@@ -100,6 +100,22 @@ class CacheManager:
         self._lib.xb_cm_copy_table(self._h, slot, group, buf, n)
         return list(buf[:n])
 
+    def log_freed(self, on: bool = True) -> None:
+        """Debug aid: record every page that goes back to a pool, for ``drain_freed``."""
+        self._lib.xb_cm_log_freed(self._h, int(bool(on)))
+
+    def drain_freed(self) -> List[tuple]:
+        """(group, page) of the pages that went back since the last call (with ``log_freed`` on)."""
+        import numpy as np
+        out: List[tuple] = []
+        g = np.zeros(256, dtype=np.int32)
+        p = np.zeros(256, dtype=np.int32)
+        while True:
+            n = self._lib.xb_cm_drain_freed(self._h, g.ctypes.data, p.ctypes.data, 256)
+            out += list(zip(g[:n].tolist(), p[:n].tolist()))
+            if n < 256:
+                return out
+
     def check_consistent(self) -> None:
         why = ctypes.create_string_buffer(256)
         if not self._lib.xb_cm_consistent(self._h, why, 256):

@@ -43,6 +43,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
     ap.add_argument("--num-blocks", type=int, help="cache pages (default: from --kv-fraction)")
     ap.add_argument("--disable-cuda-graph", action="store_true")
+    ap.add_argument("--poison-freed-pages", action="store_true",
+                    help="debug: fill every cache page that is given back with NaN before the next step")
     ap.add_argument("--disable-run-ahead", action="store_true",
                     help="wait for every step's tokens before the next step is decided")
     ap.add_argument("--random", metavar="CONFIG_JSON", help="write a random-weight model folder to --m from this config and --seed, then exit")
@@ -94,7 +96,8 @@ def main(argv: Optional[List[str]] = None) -> int:
         kv_fraction=args.kv_fraction, max_num_seqs=args.max_num_seqs or max(len(prompts), 1),
         max_num_batched_tokens=args.max_num_batched_tokens, prefill_chunk_size=args.prefill_chunk_size,
         max_model_len=args.max_model_len, max_tokens=args.max_tokens, seed=args.seed,
-        disable_cuda_graph=args.disable_cuda_graph, disable_run_ahead=args.disable_run_ahead)
+        disable_cuda_graph=args.disable_cuda_graph, disable_run_ahead=args.disable_run_ahead,
+        poison_freed_pages=args.poison_freed_pages)
     t0 = time.time()
     engine = Engine(econfig, args.dtype)
     print(f"model loaded in {time.time() - t0:.1f} s; cache holds {engine.runner.kv_cache_tokens()} tokens", file=sys.stderr)

@@ -32,6 +32,8 @@ class EngineConfig:
     # wait for the host between steps); off: every step waits for its tokens before the next is decided
     disable_run_ahead: bool = False
     device: str = "cuda:0"
+    # debug: fill every page that goes back to its pool with NaN before the next step runs
+    poison_freed_pages: bool = False
 
     def model_dir(self) -> str:
         path = self.weight_path or self.model_id

@@ -38,6 +38,10 @@ XB_API int xb_cm_free_pages(void* h, int g) { return static_cast<CacheManager*>(
 XB_API int xb_cm_table_size(void* h, int slot, int g) { return static_cast<CacheManager*>(h)->table_size(slot, g); }
 XB_API int xb_cm_copy_table(void* h, int slot, int g, int32_t* out, int cap) { return static_cast<CacheManager*>(h)->copy_table(slot, g, out, cap); }
 XB_API int xb_cm_live_requests(void* h) { return static_cast<CacheManager*>(h)->live_requests(); }
+XB_API void xb_cm_log_freed(void* h, int on) { static_cast<CacheManager*>(h)->log_freed(on != 0); }
+XB_API int xb_cm_drain_freed(void* h, int32_t* groups, int32_t* pages, int cap) {
+    return static_cast<CacheManager*>(h)->drain_freed(groups, pages, cap);
+}
 XB_API int xb_cm_consistent(void* h, char* why, int cap) {
     std::string s;
     const bool ok = static_cast<CacheManager*>(h)->consistent(&s);

@@ -55,7 +55,11 @@ bool CacheManager::close_request(int slot) {
     for (int g = 0; g < (int)groups_.size(); ++g) {
         // newest first, so the oldest pages of a finished request are reused last
         for (auto it = r.tables[g].rbegin(); it != r.tables[g].rend(); ++it)
-            if (*it >= 0) ok = pools_[g].give(*it) && ok;
+            if (*it >= 0) {
+                const bool gave = pools_[g].give(*it);
+                if (gave && log_freed_) freed_.emplace_back(g, *it);
+                ok = gave && ok;
+            }
         r.tables[g].clear();
     }
     r.live = false;
@@ -110,12 +114,22 @@ bool CacheManager::advance(int slot, int new_len) {
         const int keep_from = std::min(first_needed_page(g, new_len), (int)r.tables[g].size());
         for (int i = 0; i < keep_from; ++i) {
             if (r.tables[g][i] >= 0) {
-                pools_[g].give(r.tables[g][i]);
+                if (pools_[g].give(r.tables[g][i]) && log_freed_) freed_.emplace_back(g, r.tables[g][i]);
                 r.tables[g][i] = -1;
             }
         }
     }
     return true;
+}
+
+int CacheManager::drain_freed(int32_t* groups, int32_t* pages, int capacity) {
+    const int n = std::min((int)freed_.size(), capacity);
+    for (int i = 0; i < n; ++i) {
+        groups[i] = freed_[i].first;
+        pages[i] = freed_[i].second;
+    }
+    freed_.erase(freed_.begin(), freed_.begin() + n);
+    return n;
 }
 
 int CacheManager::table_size(int slot, int g) const {

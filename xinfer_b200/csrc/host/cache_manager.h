@@ -10,6 +10,7 @@
 #include <cstdint>
 #include <deque>
 #include <string>
+#include <utility>
 #include <vector>
 
 namespace xb {
@@ -65,6 +66,12 @@ public:
     int copy_table(int slot, int g, int32_t* out, int capacity) const;
     int live_requests() const;
 
+    // Debug aid: while on, every page that goes back to a pool is also written to a log, which the
+    // owner of the device pages drains to overwrite them (stale contents must never be read).
+    void log_freed(bool on) { log_freed_ = on; if (!on) freed_.clear(); }
+    // Moves up to `capacity` (group, page) pairs of the log to `groups` / `pages`; returns how many.
+    int drain_freed(int32_t* groups, int32_t* pages, int capacity);
+
     // Self-check for tests: every page is either free or held by exactly one table entry.
     bool consistent(std::string* why) const;
 
@@ -75,6 +82,8 @@ private:
         std::vector<std::vector<int32_t>> tables;  // per group, indexed by position / page_size
     };
     int first_needed_page(int g, int len) const;
+    bool log_freed_ = false;
+    std::vector<std::pair<int32_t, int32_t>> freed_;
 
     std::vector<GroupSpec> groups_;
     std::vector<PagePool> pools_;

@@ -85,7 +85,7 @@ class Engine:
         self.runner = runner if runner is not None else ModelRunner(
             econfig.model_dir(), dtype, block_size=econfig.block_size, num_blocks=econfig.num_blocks,
             max_num_seqs=econfig.max_num_seqs, kv_fraction=econfig.kv_fraction, device=econfig.device,
-            max_model_len=econfig.max_model_len)
+            max_model_len=econfig.max_model_len, poison_freed_pages=econfig.poison_freed_pages)
         self.max_model_len = self.runner.max_model_len
         budget = min(econfig.max_num_batched_tokens, max(self.runner.kv_cache_tokens(), 1))
         self.scheduler = Scheduler(

@@ -231,7 +231,9 @@ class ModelRunner:
     def __init__(self, model_dir: Optional[str], dtype="bfloat16", *, block_size: int = 16,
                  num_blocks: Optional[int] = None, max_num_seqs: int = 32,
                  kv_fraction: float = 0.7, device="cuda:0", max_model_len: Optional[int] = None,
-                 model: Optional[DecoderModel] = None):
+                 model: Optional[DecoderModel] = None, poison_freed_pages: bool = False):
+        """``poison_freed_pages`` (debug): every page that goes back to its pool is filled with NaN in
+        every layer before the next step runs, so a kernel that read a stale page would show at once."""
         if not torch.cuda.is_available():
             raise StepError("no CUDA device: this engine runs on a B200 (sm_100a) only and has no CPU path")
         self.device = torch.device(device)
@@ -264,6 +266,10 @@ class ModelRunner:
         # per request of the batch, and the step's error word behind them.
         self.sampled_tokens = torch.zeros(self.max_num_seqs + 1, dtype=torch.int32, device=self.device)
         self.assembler.sampled = self.sampled_tokens[: self.max_num_seqs]
+        self.poison_freed_pages = bool(poison_freed_pages)
+        if self.poison_freed_pages:
+            self.cache.log_freed(True)
+        self.pages_poisoned = 0
         self.steps_run = 0
         self.last_launches = 0      # kernels of ours launched by the last step
         self.last_used_graph = False
@@ -380,7 +386,25 @@ class ModelRunner:
                 tracing.pop()
         return self._step(entries, allow_graph)
 
+    def _poison_freed(self) -> None:
+        """Fill the pages that went back to their pools since the last step with NaN (integer tensors:
+        their lowest value).  It is queued before this step's kernels, so a page that was taken again
+        at once is poisoned first and written afterwards."""
+        by_group: Dict[int, List[int]] = {}
+        for g, page in self.cache.drain_freed():
+            by_group.setdefault(g, []).append(page)
+        for g, pages in by_group.items():
+            idx = torch.tensor(sorted(set(pages)), dtype=torch.long, device=self.device)
+            for lc in self.layer_caches:
+                if lc is None or lc.group != g:
+                    continue
+                for t in lc.tensors.values():
+                    t.index_fill_(0, idx, float("nan") if t.is_floating_point() else torch.iinfo(t.dtype).min)
+            self.pages_poisoned += int(idx.numel())
+
     def _step(self, entries: Sequence[StepInput], allow_graph: bool) -> torch.Tensor:
+        if self.poison_freed_pages:
+            self._poison_freed()
         if allow_graph and self._graph_eligible(entries):
             return self._step_graph(entries)
         before = kernels.launch_count()
