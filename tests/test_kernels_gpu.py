@@ -489,3 +489,43 @@ def test_widen_bf16_is_exact(shape):
     o2 = torch.empty(4096, device=dev())
     kernels.widen_bf16(o2, part)
     assert torch.equal(o2, part.float())
+
+
+# ---------------------------------------------------------------------------------------------
+# the many-row form of the SiLU gate against its few-row form: the same bits
+# ---------------------------------------------------------------------------------------------
+DEV = "cuda:0"
+
+
+def _both_forms(fn):
+    """Run ``fn`` with the few-row kernels, then with the many-row ones."""
+    from xinfer_b200 import kernels
+    was = kernels.many_rows
+    try:
+        kernels.many_rows = 1 << 30
+        before = dict(kernels.launch_counts())
+        few = fn()
+        kernels.many_rows = 1
+        many = fn()
+        after = kernels.launch_counts()
+    finally:
+        kernels.many_rows = was
+    return few, many, {k: after[k] - before.get(k, 0) for k in after if after[k] != before.get(k, 0)}
+
+
+@pytest.mark.parametrize("tokens,inter", [(300, 12288), (1111, 176), (600, 3072), (2, 25600)])
+def test_swiglu_many_rows_equals_few_rows(tokens, inter):
+    from xinfer_b200 import kernels
+    g = torch.Generator().manual_seed(tokens)
+    gu = (torch.randn(tokens, 2 * inter, generator=g) * 3).to(torch.bfloat16).to(DEV)
+
+    def run():
+        out = torch.zeros(tokens, inter, dtype=torch.bfloat16, device=DEV)
+        kernels.swiglu(out, gu)
+        return out
+
+    o1, o2, ran = _both_forms(run)
+    assert ran.get("swiglu_rows_bf16") == 1 and ran.get("swiglu_bf16") == 1
+    assert torch.equal(o1, o2)
+    gate, up = gu[:, :inter].float(), gu[:, inter:].float()
+    assert (o2.float() - torch.nn.functional.silu(gate) * up).abs().max().item() <= 0.02 * (gate.abs() * up.abs()).max().item()

@@ -132,6 +132,51 @@ swiglu_bf16_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restr
     }
 }
 
+// ---- SiLU gate over many rows -----------------------------------------------------------------------
+// grid (blocks along a row, row walkers): a block takes U vectors per thread of rows blockIdx.y,
+// blockIdx.y + gridDim.y, ...; the next row's vectors are requested before this row's are computed.
+constexpr int SG_THREADS = 128, SG_U = 4;
+__global__ void __launch_bounds__(SG_THREADS)
+swiglu_rows_bf16_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu, int inter, int tokens) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int vpr = inter / 8;
+    const int c0 = blockIdx.x * (SG_THREADS * SG_U) + threadIdx.x;
+    Pack8 pg[SG_U], pu[SG_U];
+    auto fetch = [&](int t) {
+        const Pack8* row = reinterpret_cast<const Pack8*>(gu + (size_t)t * 2 * inter);
+#pragma unroll
+        for (int k = 0; k < SG_U; ++k) {
+            const int c = c0 + k * SG_THREADS;
+            if (c < vpr) {
+                pg[k] = row[c];
+                pu[k] = row[vpr + c];
+            }
+        }
+    };
+    int t = blockIdx.y;
+    if (t < tokens) fetch(t);
+    while (t < tokens) {
+        float y[SG_U][8];
+#pragma unroll
+        for (int k = 0; k < SG_U; ++k) {
+            float g[8], u[8];
+            unpack8(pg[k], g);
+            unpack8(pu[k], u);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) y[k][e] = silu_mul_bf16(g[e], u[e]);
+        }
+        const int next = t + gridDim.y;
+        if (next < tokens) fetch(next);
+#pragma unroll
+        for (int k = 0; k < SG_U; ++k) {
+            const int c = c0 + k * SG_THREADS;
+            if (c < vpr) reinterpret_cast<Pack8*>(out + (size_t)t * inter)[c] = pack8(y[k]);
+        }
+        t = next;
+    }
+}
+
 // ---- q/k norm + rotary + cache write -----------------------------------------------------------------
 // A group of LPH lanes owns one (token, head); the arithmetic is that of qk_rope.cuh.  What does not
 // depend on the projection (positions, pages, weights, angles) is fetched before the wait for its producer.
@@ -195,6 +240,21 @@ XB_EXPORT int xb_swiglu_bf16(void* out, const void* gu, int tokens, int inter, c
     }
     return xb_launch(swiglu_bf16_kernel<1>, dim3((unsigned)((vpr + SWIGLU_THREADS - 1) / SWIGLU_THREADS), rows), dim3(SWIGLU_THREADS), 0,
                      stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, inter, tokens);
+}
+
+// The SiLU gate for many rows (a prompt portion): about eight blocks per SM stay resident and walk over
+// the rows with the next row requested early; the same values as xb_swiglu_bf16.
+XB_EXPORT int xb_swiglu_rows_bf16(void* out, const void* gu, int tokens, int inter, cudaStream_t stream) {
+    if (tokens <= 0 || inter <= 0) return 0;
+    if (inter % 8) return (int)cudaErrorNotSupported;
+    const int vpr = inter / 8;
+    const int per_block = SG_THREADS * SG_U;
+    const unsigned bx = (unsigned)((vpr + per_block - 1) / per_block);
+    // about eight blocks per SM stay resident and walk over the rows
+    unsigned by = (148u * 8u + bx - 1) / bx;
+    if (by > (unsigned)tokens) by = (unsigned)tokens;
+    return xb_launch(swiglu_rows_bf16_kernel, dim3(bx, by), dim3(SG_THREADS), 0, stream, (__nv_bfloat16*)out,
+                     (const __nv_bfloat16*)gu, inter, tokens);
 }
 
 // Needs d a multiple of 16 (at most 512) and, for the NeoX layout, rot == d.

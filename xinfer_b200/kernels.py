@@ -4,6 +4,7 @@ CPU or through a library: a missing extension or a CPU tensor is an error.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import numpy as np
@@ -80,6 +81,10 @@ _by_name: dict = {}
 # Use the 16-byte-access bfloat16 kernels for norm / gate / q-k preparation where sizes allow;
 # tests switch this off to compare them with the plain kernels.
 vectorized = True
+# From this many rows (tokens) on, the SiLU gate runs in its many-row form (blocks that stay on
+# their SM and walk over rows with the next row's loads in flight); below, in the form shaped for a
+# decode step's few rows.  The two forms give the same bits; tests move this bound to compare them.
+many_rows = int(os.environ.get("XINFER_B200_MANY_ROWS", "256"))
 
 
 def launch_count() -> int:
@@ -256,6 +261,9 @@ def swiglu(out, gate_up):
     _need(gate_up, "gate_up", None, (T, two_i))
     _need(out, "out", gate_up.dtype, (T, two_i // 2))
     if vectorized and gate_up.dtype == torch.bfloat16 and two_i % 16 == 0:
+        if T >= many_rows:
+            _ok(kernels_lib().xb_swiglu_rows_bf16(out.data_ptr(), gate_up.data_ptr(), T, two_i // 2, _stream()), "swiglu_rows_bf16")
+            return
         _ok(kernels_lib().xb_swiglu_bf16(out.data_ptr(), gate_up.data_ptr(), T, two_i // 2, _stream()), "swiglu_bf16")
         return
     _ok(kernels_lib().xb_swiglu(dtype_code(gate_up.dtype), out.data_ptr(), gate_up.data_ptr(), T, two_i // 2, _stream()), "swiglu")

@@ -166,3 +166,66 @@ def decode_gemms(tokens: Sequence[int] = (1, 8, 32), *, hidden: int = 4096, head
     if int(err):
         raise RuntimeError("a kernel reported an error: " + kernels.describe_error(int(err)))
     return out
+
+
+def _loop_time_us(run, repeats: int = 9) -> float:
+    """Median time of one call of ``run`` (CUDA events, a synchronisation on both sides)."""
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(repeats):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        run()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1000.0)
+    return float(sorted(times)[len(times) // 2])
+
+
+def prefill_elementwise(tokens: int = 2048, *, hidden: int = 4096, heads: int = 32, kv_heads: int = 8, head_dim: int = 128,
+                        intermediate: int = 12288, page_size: int = 16, hbm_gbs: float = 0.0, device="cuda:0") -> List[Dict]:
+    """The memory-bound kernels between the matrix products at a prompt portion's size: residual sum +
+    RMSNorm, q/k norm + rotation + cache write, SiLU gate.  Each call works on one of several sets of
+    buffers in turn, together larger than the L2, and the time is per call."""
+    sets = 4
+    err = torch.zeros(1, dtype=torch.int32, device=device)
+    bf = lambda *shape: torch.randn(*shape, device=device).bfloat16()
+    out = []
+
+    def record(name, nbytes, run):
+        us = _loop_time_us(lambda: [run(i) for i in range(sets)]) / sets
+        rec = {"kernel": name, "tokens": tokens, "bytes": nbytes, "us": round(us, 1), "gbs": round(nbytes / us / 1e3, 1)}
+        if hbm_gbs:
+            rec["frac_of_hbm"] = round(rec["gbs"] / hbm_gbs, 3)
+        out.append(rec)
+
+    # residual sum + RMSNorm: reads x and the branch, writes the sum and the normed rows
+    xs, bs, os_ = [bf(tokens, hidden) for _ in range(sets)], [bf(tokens, hidden) for _ in range(sets)], [bf(tokens, hidden) for _ in range(sets)]
+    w = torch.randn(hidden, device=device).float()
+    record("residual sum + RMSNorm", 4 * tokens * hidden * 2,
+           lambda i: kernels.rmsnorm(os_[i], xs[i], w, 1e-6, err, branch=bs[i], sum_out=xs[i]))
+    # q/k norm + rotation + cache write: reads the packed projection, writes q and the pages
+    width = (heads + 2 * kv_heads) * head_dim
+    qkvs = [bf(tokens, width) for _ in range(sets)]
+    qs = [torch.empty(tokens, heads, head_dim, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+    pages = (tokens + page_size - 1) // page_size
+    kc = [torch.zeros(pages, kv_heads, page_size, head_dim, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+    vc = [torch.zeros_like(k) for k in kc]
+    qw, kw = torch.randn(head_dim, device=device).float(), torch.randn(head_dim, device=device).float()
+    half = head_dim // 2
+    cos, sin = torch.randn(tokens, half, device=device).float(), torch.randn(tokens, half, device=device).float()
+    pos = torch.arange(tokens, dtype=torch.int32, device=device)
+    req = torch.zeros(tokens, dtype=torch.int32, device=device)
+    table = torch.randperm(pages, device=device).to(torch.int32)
+    record("q/k norm + rotation + cache write", 2 * tokens * width * 2,
+           lambda i: kernels.qk_norm_rope_write(qs[i], kc[i], vc[i], qkvs[i], qw, kw, cos, sin, pos, req, table, pages, heads, kv_heads,
+                                                head_dim, head_dim, False, 1e-6, True, err))
+    # SiLU gate: reads gate and up, writes their product
+    gus = [bf(tokens, 2 * intermediate) for _ in range(sets)]
+    acts = [torch.empty(tokens, intermediate, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+    record("SiLU gate", 3 * tokens * intermediate * 2, lambda i: kernels.swiglu(acts[i], gus[i]))
+    if int(err):
+        raise RuntimeError("a kernel reported an error: " + kernels.describe_error(int(err)))
+    return out

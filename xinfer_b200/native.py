@@ -101,6 +101,7 @@ def _declare_kernels(lib):
     _sig(lib, "xb_swiglu_bf16", I, [P, P, I, I, P])
     _sig(lib, "xb_qk_norm_rope_write_bf16", I,
          [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P])
+    _sig(lib, "xb_swiglu_rows_bf16", I, [P, P, I, I, P])
     _sig(lib, "xb_attn_prefill_tc", I, [P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, F, I, I, P, P, P])
     _sig(lib, "xb_gemm_skinny_tc", I, [P, I, P, P, I, I, I, I, P, P])
     _sig(lib, "xb_gemm_skinny_swiglu", I, [P, P, P, I, I, I, I, P, P])
