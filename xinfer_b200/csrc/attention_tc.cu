@@ -22,92 +22,116 @@ constexpr int KT = 64;   // keys per tile
 constexpr float RESCALE_STEP = 8.f;  // the row maximum moves only when it grows by more than 2^8
 
 // ------------------------------------------------------------------------------------------------
-// prefill: 128 queries of two query heads per CTA
+// prefill: 128 queries of two query heads per work item; a CTA per SM works through a list of items
 // ------------------------------------------------------------------------------------------------
-// A CTA owns 128 queries of one request's portion for TWO query heads that share their key/value head,
-// so a key/value tile is loaded once for both (a tile per 8 MFLOP instead of 4) and the rings are four
-// stages deep (a tile's way from memory is longer than two):
+// A work item is 128 queries of one request's portion for TWO query heads that share their key/value
+// head, so a key/value tile is loaded once for both (a tile per 8 MFLOP instead of 4) and the rings are
+// three stages deep (a tile's way from memory is longer than two; a fourth stage gave its room to
+// the output staging).  The host shares the step's items out
+// among at most one CTA per SM, longest first onto the least loaded CTA (xb_attn_prefill_work), so that
+// SMs finish together whatever the lengths are, and a CTA that stays on its SM overlaps the end of an
+// item with the start of the next: the key pages of the next item are requested as soon as ring stages
+// are free, its Q as soon as the last Q K^T of this item has read the old one, and its first scores are
+// computed while this item's output leaves.
 //   warps 0..3: softmax of head A (one row per thread), warps 4..7: softmax of head B,
-//   warp 8: TMA producer of Q (both heads) and of the key pages, warp 10: of the value pages (one lane
-//   per page box; the page ids of the next tile are fetched while this one is issued),
-//   warp 9: issues S_A, S_B = Q K^T of every tile; warp 11: issues O_A += P_A V and O_B += P_B V (two
-//   issuers, so that the waits of one do not hold up the products of the other; P lies in tensor memory
-//   over the scores it came from, so the first waits for the second before it reuses a score buffer).
-// Shared memory (1024-byte aligned): Q [2 heads][DP/64][128 rows][64], then four stages of K and V
+//   warp 8: TMA producer of the key pages, warp 10: of the value pages (one lane per page box; the page
+//   ids of the next tile are fetched while this one is issued),
+//   warp 9: loads Q (both heads) and issues S_A, S_B = Q K^T of every tile; warp 11: issues O_A += P_A V
+//   and O_B += P_B V (two issuers, so that the waits of one do not hold up the products of the other; P
+//   lies in tensor memory over the scores it came from, so the first waits for the second before it
+//   reuses a score buffer).
+// Shared memory (1024-byte aligned): Q [2 heads][DP/64][128 rows][64], then three stages of K and V
 // [DP/64][64 keys][64]; every [rows][64] piece is a tile of 128-byte rows whose 16-byte chunks are
-// XOR-ed with row & 7.  Full output tiles leave through the space of Q and TMA stores.
+// XOR-ed with row & 7; then the barriers; then 4 KB per softmax warp and 64-column half through which
+// full output tiles leave by TMA stores (a warp's 32 rows; nobody waits for the stores until the warp
+// needs the space for its next item).
 // Tensor memory (all 512 columns): S_A[0], S_A[1], S_B[0], S_B[1] at 0, 64, 128, 192; O_A at 256, O_B at 384.
-// One CTA per SM.  With an odd number of query heads per key/value head the last CTA of the group has
-// one head and its second softmax warpgroup idles.
-constexpr int PREFILL_STAGES = 4;
+// Barriers carry on from item to item: their parities come from running counts of tiles (of all tiles
+// for the rings, of a head's tiles for what belongs to a head) and of items.
+// With an odd number of query heads per key/value head the last item of the group has one head and the
+// second softmax warpgroup sits it out.
+constexpr int PREFILL_STAGES = 3;
 constexpr int PREFILL_THREADS = 384;
+constexpr int PREFILL_ITEM_INTS = 3;   // portion, query tile, head pair
 
+// What the roles of a CTA derive, each for itself, from an item of the work list.
+struct PrefillItem {
+    int g, h0, nhd;               // key/value head, first query head, heads (2, or 1)
+    int rows, t0, p0;             // queries, their first row in q / out, the first one's position
+    int first_key, last_key, kt_first, iters;
+    const int* table;
+};
+
+__device__ __forceinline__ PrefillItem prefill_item(const int* __restrict__ item, const int* __restrict__ q_start,
+                                                    const int* __restrict__ start_pos, const int* __restrict__ block_table,
+                                                    int table_stride, int nh, int nkv, int window) {
+    PrefillItem w;
+    const int b = item[0], tile = item[1], hp = item[2];
+    const int G = nh / nkv, per_group = (G + 1) / 2;
+    w.g = hp / per_group;
+    const int pair = hp % per_group;
+    w.h0 = w.g * G + 2 * pair;
+    w.nhd = 2 * pair + 1 < G ? 2 : 1;
+    const int n = q_start[b + 1] - q_start[b];
+    const int row0 = tile * QT;
+    w.rows = min(QT, n - row0);
+    w.t0 = q_start[b] + row0;
+    w.p0 = start_pos[b] + row0;
+    w.last_key = w.p0 + w.rows - 1;
+    w.first_key = window > 0 ? max(0, w.p0 - window + 1) : 0;
+    w.table = block_table + (size_t)b * table_stride;
+    w.kt_first = w.first_key / KT;
+    w.iters = w.last_key / KT - w.kt_first + 1;
+    return w;
+}
+
+// `work`: [ctas + 1] offsets into the items that follow them, PREFILL_ITEM_INTS int32 each; CTA c takes
+// items work[c] .. work[c + 1] - 1 in that order.
 template <int DP>
 __global__ void __launch_bounds__(PREFILL_THREADS)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
                        __nv_bfloat16* __restrict__ out, const int* __restrict__ q_start, const int* __restrict__ start_pos,
-                       int num_entries, const int* __restrict__ block_table, int table_stride, int nh, int nkv, int d,
-                       int ps, int ps_shift, int num_pages, int window, float scale_log2, int dec_max,
-                       const int* __restrict__ tile_map, int* err) {
+                       const int* __restrict__ block_table, int table_stride, int nh, int nkv, int d,
+                       int ps, int ps_shift, int num_pages, int window, float scale_log2,
+                       const int* __restrict__ work, int* err) {
     constexpr int HALVES = DP / 64, NS = PREFILL_STAGES;
     constexpr uint32_t Q_ONE = HALVES * QT * 128, Q_BYTES = 2 * Q_ONE;
     constexpr uint32_t KV_HALF = KT * 128, KV_BYTES = HALVES * KV_HALF, STAGE_BYTES = 2 * KV_BYTES;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const uint32_t base = smem_u32(smem_raw);
     const uint32_t q_sm = base, kv_sm = base + Q_BYTES;
-    // barriers, 8 bytes each: k_full[4] k_empty[4] v_full[4] v_empty[4] s_ready[head][2] pv_done[head][2]
-    // p_ready[head] q_full bar_o; then four words
-    constexpr uint32_t BAR_OFF = Q_BYTES + NS * STAGE_BYTES;
+    // barriers, 8 bytes each: k_full[4] k_empty[4] v_full[4] v_empty[4] (NS of each in use) s_ready[head][2]
+    // pv_done[head][2] p_ready[head] q_full bar_o q_empty; then four words; the output staging 1024 bytes after BAR_OFF
+    constexpr uint32_t BAR_OFF = Q_BYTES + NS * STAGE_BYTES, OUT_OFF = BAR_OFF + 1024;
     const uint32_t bars = base + BAR_OFF;
     const uint32_t k_full0 = bars, k_empty0 = bars + 32, v_full0 = bars + 64, v_empty0 = bars + 96;
     const uint32_t s_ready0 = bars + 128, pv_done0 = bars + 160, p_ready0 = bars + 192;
-    const uint32_t q_full = bars + 224, bar_o = bars + 232;
-    volatile uint32_t* words = reinterpret_cast<volatile uint32_t*>(smem_raw + BAR_OFF + 240);  // tmem, entry, tile, dead
+    const uint32_t q_full = bars + 208, bar_o = bars + 216, q_empty = bars + 224;
+    volatile uint32_t* words = reinterpret_cast<volatile uint32_t*>(smem_raw + BAR_OFF + 240);  // tmem, -, -, dead
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int G = nh / nkv;
-    // a key/value head's query heads are taken two at a time; the last CTA of an odd number has one (nhd = 1)
-    const int per_group = (G + 1) / 2;
-    const int g = (int)blockIdx.x / per_group, pair = (int)blockIdx.x % per_group;
-    const int h0 = g * G + 2 * pair, nhd = 2 * pair + 1 < G ? 2 : 1;   // heads vary fastest: the longest tiles start first
     pdl_launch_dependents();
 
     // what follows until the wait reads only what the host sent before the step's first kernel
+    const int ctas = (int)gridDim.x;
+    int item_begin = work[blockIdx.x], item_end = work[blockIdx.x + 1];
+    const int* const items = work + ctas + 1;
     if (threadIdx.x == 0) {
         if (base & 1023u) atomicOr(err, XB_ERR_WAIT);  // the swizzle needs a 1024-byte aligned window
-        int acc = 0, found = -1, tile = 0;
-        if (tile_map) {   // (portion, query tile) of every block row, made by the host: longest first over all portions
-            found = tile_map[2 * blockIdx.y];
-            tile = tile_map[2 * blockIdx.y + 1];
-        } else {
-            for (int b = 0; b < num_entries; ++b) {
-                const int n = q_start[b + 1] - q_start[b];
-                if (n > dec_max) {
-                    const int nt = (n + QT - 1) / QT;
-                    if ((int)blockIdx.y < acc + nt) {
-                        found = b;
-                        tile = nt - 1 - ((int)blockIdx.y - acc);  // a portion's last (longest) tiles first
-                        break;
-                    }
-                    acc += nt;
-                }
-            }
-        }
-        if (*reinterpret_cast<volatile int*>(err) & XB_ERR_WAIT) found = -1;  // an earlier CTA gave up: do not pile on
-        words[1] = (uint32_t)found;
-        words[2] = (uint32_t)tile;
         words[3] = 0;
-        for (int i = 0; i < 4 * NS; ++i) mbar_init(bars + 8 * i, 1);        // k_full, k_empty, v_full, v_empty
+        for (int i = 0; i < 4 * 4; ++i) mbar_init(bars + 8 * i, 1);         // k_full, k_empty, v_full, v_empty
         for (int i = 0; i < 4; ++i) mbar_init(s_ready0 + 8 * i, 1);
         for (int i = 0; i < 2; ++i) mbar_init(p_ready0 + 8 * i, 128);
         for (int i = 0; i < 4; ++i) mbar_init(pv_done0 + 8 * i, 1);
         mbar_init(q_full, 1);
         mbar_init(bar_o, 1);
+        mbar_init(q_empty, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // an earlier CTA gave up: do not pile on
+    if (*reinterpret_cast<volatile int*>(err) & XB_ERR_WAIT) item_end = item_begin;
     __syncthreads();
-    const int b = (int)words[1];
-    if (b < 0 || (base & 1023u)) {
+    if (item_end <= item_begin || (base & 1023u)) {
         pdl_wait();   // a kernel that depends on this one may rely on every block having waited
         return;
     }
@@ -122,310 +146,356 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t tmem = words[0];
     pdl_wait();   // q and the new keys and values come from the kernel before
 
-    const int n = q_start[b + 1] - q_start[b];
-    const int row0 = (int)words[2] * QT;
-    const int rows = min(QT, n - row0);
-    const int t0 = q_start[b] + row0;
-    const int p0 = start_pos[b] + row0;
-    const int last_key = p0 + rows - 1;
-    const int first_key = window > 0 ? max(0, p0 - window + 1) : 0;
-    const int* table = block_table + (size_t)b * table_stride;
-    const int kt_first = first_key / KT, kt_last = last_key / KT;
-    const int iters = kt_last - kt_first + 1;
     const int box_rows = ps < KT ? ps : KT;
-
+    auto item_at = [&](int k) {
+        return prefill_item(items + (size_t)k * PREFILL_ITEM_INTS, q_start, start_pos, block_table, table_stride, nh, nkv, window);
+    };
     if (warp == 8 || warp == 10) {
-        // ---- producers ------------------------------------------------------------------------------------
+        // ---- producers of key pages (warp 8) and value pages (warp 10), item after item ----------------------
         const bool is_v = warp == 10;
         const uint32_t full0 = is_v ? v_full0 : k_full0, empty0 = is_v ? v_empty0 : k_empty0;
         const CUtensorMap* map = is_v ? &map_v : &map_k;
-        if (!is_v && lane == 0) {
-            mbar_expect_tx(q_full, (uint32_t)nhd * Q_ONE);
-            for (int hd = 0; hd < nhd; ++hd)
-#pragma unroll
-                for (int hf = 0; hf < HALVES; ++hf)
-                    tma_load_3d(q_sm + hd * Q_ONE + hf * QT * 128, &map_q, hf * 64, h0 + hd, t0, q_full);
-        }
-        const int boxes = (KT / box_rows) * HALVES;     // at most 16: one lane each
-        const int bi = lane / HALVES, hf = lane % HALVES;
-        auto page_of = [&](int it) -> int {             // the page of this lane's box in tile `it`, -1: nothing to load
-            const int j = (kt_first + it) * KT + bi * box_rows;
-            if (it >= iters || lane >= boxes || j > last_key || j + box_rows - 1 < first_key) return -1;
-            const int page = table[j >> ps_shift];
-            if (page < 0 || page >= num_pages) {
-                atomicOr(err, XB_ERR_BAD_PAGE);
-                return -1;
+        int T = 0;   // tiles of the items before this one
+        bool ok = true;
+        for (int k = item_begin; k < item_end && ok; ++k) {
+            const PrefillItem w = item_at(k);
+            const int boxes = (KT / box_rows) * HALVES;     // at most 16: one lane each
+            const int bi = lane / HALVES, hf = lane % HALVES;
+            auto page_of = [&](int it) -> int {             // the page of this lane's box in tile `it`, -1: nothing to load
+                const int j = (w.kt_first + it) * KT + bi * box_rows;
+                if (it >= w.iters || lane >= boxes || j > w.last_key || j + box_rows - 1 < w.first_key) return -1;
+                const int page = w.table[j >> ps_shift];
+                if (page < 0 || page >= num_pages) {
+                    atomicOr(err, XB_ERR_BAD_PAGE);
+                    return -1;
+                }
+                return page;
+            };
+            int page_next = page_of(0);
+            for (int it = 0; it < w.iters; ++it) {
+                const int gt = T + it, s = gt % NS;
+                const int page = page_next;
+                if (gt >= NS && !__all_sync(0xffffffffu, mbar_wait(empty0 + 8 * s, ((gt / NS) - 1) & 1, err))) {
+                    words[3] = 1;
+                    ok = false;
+                    break;
+                }
+                const uint32_t nb = __popc(__ballot_sync(0xffffffffu, page >= 0));
+                if (lane == 0) mbar_expect_tx(full0 + 8 * s, nb * box_rows * 128);
+                __syncwarp();
+                if (page >= 0) {
+                    const int j = (w.kt_first + it) * KT + bi * box_rows;
+                    const uint32_t dst = kv_sm + s * STAGE_BYTES + (is_v ? KV_BYTES : 0u) + hf * KV_HALF + bi * box_rows * 128;
+                    tma_load_2d(dst, map, hf * 64, (page * nkv + w.g) * ps + (j & (ps - 1)), full0 + 8 * s);
+                }
+                page_next = page_of(it + 1);
             }
-            return page;
-        };
-        int page_next = page_of(0);
-        for (int it = 0; it < iters; ++it) {
-            const int s = it % NS;
-            const int page = page_next;
-            if (it >= NS && !__all_sync(0xffffffffu, mbar_wait(empty0 + 8 * s, ((it / NS) - 1) & 1, err))) {
-                words[3] = 1;
-                break;
-            }
-            const uint32_t nb = __popc(__ballot_sync(0xffffffffu, page >= 0));
-            if (lane == 0) mbar_expect_tx(full0 + 8 * s, nb * box_rows * 128);
-            __syncwarp();
-            if (page >= 0) {
-                const int j = (kt_first + it) * KT + bi * box_rows;
-                const uint32_t dst = kv_sm + s * STAGE_BYTES + (is_v ? KV_BYTES : 0u) + hf * KV_HALF + bi * box_rows * 128;
-                tma_load_2d(dst, map, hf * 64, (page * nkv + g) * ps + (j & (ps - 1)), full0 + 8 * s);
-            }
-            page_next = page_of(it + 1);
+            T += w.iters;
         }
     } else if (warp == 9) {
-        // ---- issuer of S = Q K^T, both heads, tile after tile ----------------------------------------------
+        // ---- Q loads and S = Q K^T, both heads, tile after tile, item after item -----------------------------
         if (lane == 0) {
             const uint32_t idesc_s = umma_idesc(KT, 0);
             const uint64_t dq0 = umma_desc(q_sm, 16, 1024), dk0 = umma_desc(kv_sm, 16, 1024);
-            bool ok = mbar_wait(q_full, 0, err, true);
-            for (int it = 0; it < iters && ok; ++it) {
-                const int sb = it & 1, s = it % NS;
-                ok = mbar_wait(k_full0 + 8 * s, (it / NS) & 1, err, true);
-                const uint64_t dk = dk0 + (uint64_t)((s * STAGE_BYTES) >> 4);
+            auto load_q = [&](const PrefillItem& w) {
+                mbar_expect_tx(q_full, (uint32_t)w.nhd * Q_ONE);
+                for (int hd = 0; hd < w.nhd; ++hd)
 #pragma unroll
-                for (int hd = 0; hd < 2; ++hd) {
-                    if (hd >= nhd) break;
-                    // S[sb] of this head held the scores and then P of tile it - 2: its P V must have read it
-                    ok = ok && (it < 2 || mbar_wait(pv_done0 + 8 * (2 * hd + sb), ((it >> 1) - 1) & 1, err, true));
-                    if (!ok) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t dq = dq0 + (uint64_t)((hd * Q_ONE) >> 4);
+                    for (int hf = 0; hf < HALVES; ++hf)
+                        tma_load_3d(q_sm + hd * Q_ONE + hf * QT * 128, &map_q, hf * 64, w.h0 + hd, w.t0, q_full);
+            };
+            int T = 0, Th[2] = {0, 0};
+            bool ok = true;
+            PrefillItem w = item_at(item_begin);
+            load_q(w);
+            for (int k = item_begin; k < item_end && ok; ++k) {
+                const int I = k - item_begin;
+                ok = mbar_wait(q_full, (uint32_t)I & 1u, err, true);
+                for (int it = 0; it < w.iters && ok; ++it) {
+                    const int gt = T + it, s = gt % NS;
+                    ok = mbar_wait(k_full0 + 8 * s, (gt / NS) & 1, err, true);
+                    const uint64_t dk = dk0 + (uint64_t)((s * STAGE_BYTES) >> 4);
 #pragma unroll
-                    for (int kk = 0; kk < DP / 16; ++kk) {
-                        const uint32_t off = (kk >> 2), inner = (kk & 3) * 32;
-                        umma_bf16(tmem + (uint32_t)(hd * 128 + sb * 64), dq + (uint64_t)((off * QT * 128 + inner) >> 4),
-                                  dk + (uint64_t)((off * KV_HALF + inner) >> 4), idesc_s, kk ? 1u : 0u);
+                    for (int hd = 0; hd < 2; ++hd) {
+                        if (hd >= w.nhd) break;
+                        const int th = Th[hd] + it, sb = th & 1;
+                        // S[sb] of this head held the scores and then P of its tile th - 2: that P V must have read it
+                        ok = ok && (th < 2 || mbar_wait(pv_done0 + 8 * (2 * hd + sb), ((th >> 1) - 1) & 1, err, true));
+                        if (!ok) break;
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint64_t dq = dq0 + (uint64_t)((hd * Q_ONE) >> 4);
+#pragma unroll
+                        for (int kk = 0; kk < DP / 16; ++kk) {
+                            const uint32_t off = (kk >> 2), inner = (kk & 3) * 32;
+                            umma_bf16(tmem + (uint32_t)(hd * 128 + sb * 64), dq + (uint64_t)((off * QT * 128 + inner) >> 4),
+                                      dk + (uint64_t)((off * KV_HALF + inner) >> 4), idesc_s, kk ? 1u : 0u);
+                        }
+                        umma_commit(s_ready0 + 8 * (2 * hd + sb));
                     }
-                    umma_commit(s_ready0 + 8 * (2 * hd + sb));
+                    if (!ok) break;
+                    umma_commit(k_empty0 + 8 * s);   // the key stage is free once both products have completed
                 }
                 if (!ok) break;
-                umma_commit(k_empty0 + 8 * s);   // the key stage is free once both products have completed
+                T += w.iters;
+                Th[0] += w.iters;
+                if (w.nhd == 2) Th[1] += w.iters;
+                if (k + 1 < item_end) {
+                    // the next item's Q goes where this one's lies: once every product that reads it has completed
+                    umma_commit(q_empty);
+                    ok = mbar_wait(q_empty, (uint32_t)I & 1u, err, true);
+                    if (ok) {
+                        w = item_at(k + 1);
+                        load_q(w);
+                    }
+                }
             }
             if (!ok) words[3] = 1;
         }
     } else if (warp == 11) {
-        // ---- issuer of O += P V, both heads, tile after tile ------------------------------------------------
+        // ---- issuer of O += P V, both heads, tile after tile, item after item ---------------------------------
         if (lane == 0) {
             const uint32_t idesc_o = umma_idesc(DP, 1);
             const uint64_t dv0 = umma_desc(kv_sm + KV_BYTES, KV_HALF, 1024);
+            int T = 0, Th[2] = {0, 0};
             bool ok = true;
-            for (int it = 0; it < iters && ok; ++it) {
-                const int s = it % NS, sb = it & 1;
-                ok = mbar_wait(v_full0 + 8 * s, (it / NS) & 1, err, true);
-                const uint64_t dv = dv0 + (uint64_t)((s * STAGE_BYTES) >> 4);
+            for (int k = item_begin; k < item_end && ok; ++k) {
+                const PrefillItem w = item_at(k);
+                for (int it = 0; it < w.iters && ok; ++it) {
+                    const int gt = T + it, s = gt % NS;
+                    ok = mbar_wait(v_full0 + 8 * s, (gt / NS) & 1, err, true);
+                    const uint64_t dv = dv0 + (uint64_t)((s * STAGE_BYTES) >> 4);
 #pragma unroll
-                for (int hd = 0; hd < 2; ++hd) {
-                    if (hd >= nhd) break;
-                    ok = ok && mbar_wait(p_ready0 + 8 * hd, it & 1, err, true);   // P written, V rows zeroed, O rescaled
+                    for (int hd = 0; hd < 2; ++hd) {
+                        if (hd >= w.nhd) break;
+                        const int th = Th[hd] + it, sb = th & 1;
+                        ok = ok && mbar_wait(p_ready0 + 8 * hd, th & 1, err, true);   // P written, V rows zeroed, O rescaled
+                        if (!ok) break;
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        // A = P [128 x 64 keys] in tensor memory (over the scores it came from), B = V [64 keys x DP]
+                        // MN-major (halves 64 columns apart); the item's first tile overwrites O
+                        const uint32_t tp = tmem + (uint32_t)(hd * 128 + sb * 64);
+#pragma unroll
+                        for (int kk = 0; kk < KT / 16; ++kk)
+                            umma_bf16_ta(tmem + (uint32_t)(256 + hd * 128), tp + (uint32_t)(kk * 8), dv + (uint64_t)((kk * 2048) >> 4),
+                                         idesc_o, (it | kk) ? 1u : 0u);
+                        umma_commit(pv_done0 + 8 * (2 * hd + sb));   // P, its score buffer and O of this head are free again
+                    }
                     if (!ok) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    // A = P [128 x 64 keys] in tensor memory (over the scores it came from), B = V [64 keys x DP]
-                    // MN-major (halves 64 columns apart)
-                    const uint32_t tp = tmem + (uint32_t)(hd * 128 + sb * 64);
-#pragma unroll
-                    for (int kk = 0; kk < KT / 16; ++kk)
-                        umma_bf16_ta(tmem + (uint32_t)(256 + hd * 128), tp + (uint32_t)(kk * 8), dv + (uint64_t)((kk * 2048) >> 4),
-                                     idesc_o, (it | kk) ? 1u : 0u);
-                    umma_commit(pv_done0 + 8 * (2 * hd + sb));   // P, its score buffer and O of this head are free again
+                    umma_commit(v_empty0 + 8 * s);           // and so is the value stage
+                    if (it + 1 == w.iters) umma_commit(bar_o);
                 }
-                if (!ok) break;
-                umma_commit(v_empty0 + 8 * s);           // and so is the value stage
-                if (it + 1 == iters) umma_commit(bar_o);
+                T += w.iters;
+                Th[0] += w.iters;
+                if (w.nhd == 2) Th[1] += w.iters;
             }
             if (!ok) words[3] = 1;
         }
-    } else if (warp < 4 * nhd) {
+    } else if (warp < 8) {
         // ---- softmax: one query row per thread, warps 0..3 for the first head, 4..7 for the second -------------
         const int hd = warp >> 2, r = (int)threadIdx.x & 127;
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t tmem_s = tmem + (uint32_t)(hd * 128), tmem_o = tmem + (uint32_t)(256 + hd * 128);
         const uint32_t my_s_ready = s_ready0 + 16 * hd;
         const uint32_t my_p_ready = p_ready0 + 8 * hd, my_pv_done = pv_done0 + 16 * hd;
-        const int my_pos = p0 + r;
-        float m_ref = -INFINITY, l = 0.f;
+        // this warp's output staging: 32 rows of each 64-column half, swizzled as a TMA box wants them
+        unsigned char* const stage = smem_raw + OUT_OFF + warp * (HALVES * 4096);
+        const uint32_t stage_sm = base + OUT_OFF + warp * (HALVES * 4096);
+        int T = 0, Th = 0;   // tiles of the items before this one: all of them, and those this head took part in
         bool alive = true;
-        for (int it = 0; it < iters; ++it) {
-            const int sb = it & 1, st = it % NS, key0 = (kt_first + it) * KT;
-            // every wait's verdict is made warp-wide: tcgen05.ld / .st below need the whole warp
-            if (!__all_sync(0xffffffffu, mbar_wait(my_s_ready + 8 * sb, (it >> 1) & 1, err))) {
-                alive = false;
-                break;
+        for (int k = item_begin; k < item_end && alive; ++k) {
+            const PrefillItem w = item_at(k);
+            const int I = k - item_begin;
+            if (hd >= w.nhd) {   // an item of one head: the second warpgroup sits it out
+                T += w.iters;
+                continue;
             }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            float sc[64];
-            {
-                uint32_t ra[32], rb[32];
-                tmem_ld32_nowait(tmem_s + sb * 64 + lane_addr, ra);
-                tmem_ld32_nowait(tmem_s + sb * 64 + lane_addr + 32, rb);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    sc[i] = __uint_as_float(ra[i]);
-                    sc[32 + i] = __uint_as_float(rb[i]);
+            const int iters = w.iters, kt_first = w.kt_first, first_key = w.first_key, last_key = w.last_key, p0 = w.p0;
+            const int rows = w.rows, t0 = w.t0, h0 = w.h0;
+            const int my_pos = p0 + r;
+            float m_ref = -INFINITY, l = 0.f;
+            for (int it = 0; it < iters; ++it) {
+                const int th = Th + it, sb = th & 1, gt = T + it, st = gt % NS, key0 = (kt_first + it) * KT;
+                // every wait's verdict is made warp-wide: tcgen05.ld / .st below need the whole warp
+                if (!__all_sync(0xffffffffu, mbar_wait(my_s_ready + 8 * sb, (th >> 1) & 1, err))) {
+                    alive = false;
+                    break;
                 }
-            }
-            const bool edge = key0 + KT - 1 > p0 || key0 + KT - 1 > last_key || key0 < first_key ||
-                              (window > 0 && key0 < p0 + QT - 1 - window + 1);
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-            if (edge) {
-#pragma unroll
-                for (int i = 0; i < 64; ++i) {
-                    const int j = key0 + i;
-                    const bool ok = j <= my_pos && j <= last_key && (window <= 0 || j > my_pos - window);
-                    sc[i] = ok ? sc[i] : -INFINITY;
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < 64; i += 8) {
-                mx4[0] = max3(mx4[0], sc[i], sc[i + 1]);
-                mx4[1] = max3(mx4[1], sc[i + 2], sc[i + 3]);
-                mx4[2] = max3(mx4[2], sc[i + 4], sc[i + 5]);
-                mx4[3] = max3(mx4[3], sc[i + 6], sc[i + 7]);
-            }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
-            // move the reference maximum only when the row's maximum outgrows it by more than 2^8
-            float corr = 1.f;
-            int moved = 0;
-            if (mx > m_ref + RESCALE_STEP) {
-                corr = m_ref == -INFINITY ? 0.f : ex2(m_ref - mx);
-                m_ref = mx;
-                moved = it > 0;
-            }
-            const float m_neg = m_ref == -INFINITY ? 0.f : -m_ref;
-            const f32x2 scale2 = pack2(scale_log2, scale_log2), mneg2 = pack2(m_neg, m_neg);
-            f32x2 sum_a = pack2(0.f, 0.f), sum_b = pack2(0.f, 0.f);
-            uint32_t pk[32];   // the row of P: two bfloat16 per word, in the order of the keys
-#pragma unroll
-            for (int c8 = 0; c8 < 8; ++c8) {
-                float x[8], e[8];
-#pragma unroll
-                for (int i = 0; i < 8; i += 2)
-                    unpack2(fma2(pack2(sc[c8 * 8 + i], sc[c8 * 8 + i + 1]), scale2, mneg2), x[i], x[i + 1]);
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    if ((i & 3) != 3) e[i] = ex2(x[i]);
-                ex2_poly2(x[3], x[7], e[3], e[7]);
-                sum_a = add2(sum_a, add2(pack2(e[0], e[1]), pack2(e[2], e[3])));
-                sum_b = add2(sum_b, add2(pack2(e[4], e[5]), pack2(e[6], e[7])));
-                pk[c8 * 4] = pack_bf16(e[0], e[1]);
-                pk[c8 * 4 + 1] = pack_bf16(e[2], e[3]);
-                pk[c8 * 4 + 2] = pack_bf16(e[4], e[5]);
-                pk[c8 * 4 + 3] = pack_bf16(e[6], e[7]);
-            }
-            float s0, s1, s2, s3;
-            unpack2(sum_a, s0, s1);
-            unpack2(sum_b, s2, s3);
-            l = l * corr + ((s0 + s1) + (s2 + s3));
-            // P goes where the scores were: they are in registers, and the P V that read these columns two tiles
-            // ago ran before the Q K^T that wrote them
-            tmem_st32_u(tmem_s + sb * 64 + lane_addr, pk);
-            // value rows outside the visible keys become zeros (only tiles at the ends of the range): the first
-            // head's threads do it; the second head's P V is issued after the first's, so it sees them too
-            if (hd == 0 && (key0 < first_key || key0 + KT - 1 > last_key)) {
-                if (r < KT) {
-                    mbar_wait(v_full0 + 8 * st, (it / NS) & 1, err);   // orders these writes after the TMA's
-                    const int j = key0 + r;
-                    if (j < first_key || j > last_key) {
-#pragma unroll
-                        for (int hf = 0; hf < HALVES; ++hf) {
-                            uint4* vr = reinterpret_cast<uint4*>(smem_raw + Q_BYTES + st * STAGE_BYTES + KV_BYTES + hf * KV_HALF + r * 128);
-#pragma unroll
-                            for (int c8 = 0; c8 < 8; ++c8) vr[c8] = make_uint4(0, 0, 0, 0);
-                        }
-                    }
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the zeroed rows: visible to the MMA
-                }
-            }
-            // rescale O where a row's reference maximum moved (rare after the first tiles); tcgen05.ld / .st
-            // are warp-wide: a warp rescales when any of its rows moved, the other rows by 1.
-            // The previous tile's P V of this head has to be complete before O is touched, and before this tile
-            // is announced at all: the issuer waits for the announcements by their parity, so a head must never
-            // be two of them ahead of it.
-            if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(my_pv_done + 8 * (sb ^ 1), ((it - 1) >> 1) & 1, err))) {
-                alive = false;
-                break;
-            }
-            if (__any_sync(0xffffffffu, moved)) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const float f = moved ? corr : 1.f;
+                float sc[64];
+                {
+                    uint32_t ra[32], rb[32];
+                    tmem_ld32_nowait(tmem_s + sb * 64 + lane_addr, ra);
+                    tmem_ld32_nowait(tmem_s + sb * 64 + lane_addr + 32, rb);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    #pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        sc[i] = __uint_as_float(ra[i]);
+                        sc[32 + i] = __uint_as_float(rb[i]);
+                    }
+                }
+                const bool edge = key0 + KT - 1 > p0 || key0 + KT - 1 > last_key || key0 < first_key ||
+                                  (window > 0 && key0 < p0 + QT - 1 - window + 1);
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                if (edge) {
+    #pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        const int j = key0 + i;
+                        const bool ok = j <= my_pos && j <= last_key && (window <= 0 || j > my_pos - window);
+                        sc[i] = ok ? sc[i] : -INFINITY;
+                    }
+                }
+    #pragma unroll
+                for (int i = 0; i < 64; i += 8) {
+                    mx4[0] = max3(mx4[0], sc[i], sc[i + 1]);
+                    mx4[1] = max3(mx4[1], sc[i + 2], sc[i + 3]);
+                    mx4[2] = max3(mx4[2], sc[i + 4], sc[i + 5]);
+                    mx4[3] = max3(mx4[3], sc[i + 6], sc[i + 7]);
+                }
+                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+                // move the reference maximum only when the row's maximum outgrows it by more than 2^8
+                float corr = 1.f;
+                int moved = 0;
+                if (mx > m_ref + RESCALE_STEP) {
+                    corr = m_ref == -INFINITY ? 0.f : ex2(m_ref - mx);
+                    m_ref = mx;
+                    moved = it > 0;
+                }
+                const float m_neg = m_ref == -INFINITY ? 0.f : -m_ref;
+                const f32x2 scale2 = pack2(scale_log2, scale_log2), mneg2 = pack2(m_neg, m_neg);
+                f32x2 sum_a = pack2(0.f, 0.f), sum_b = pack2(0.f, 0.f);
+                uint32_t pk[32];   // the row of P: two bfloat16 per word, in the order of the keys
+    #pragma unroll
+                for (int c8 = 0; c8 < 8; ++c8) {
+                    float x[8], e[8];
+    #pragma unroll
+                    for (int i = 0; i < 8; i += 2)
+                        unpack2(fma2(pack2(sc[c8 * 8 + i], sc[c8 * 8 + i + 1]), scale2, mneg2), x[i], x[i + 1]);
+    #pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        if ((i & 3) != 3) e[i] = ex2(x[i]);
+                    ex2_poly2(x[3], x[7], e[3], e[7]);
+                    sum_a = add2(sum_a, add2(pack2(e[0], e[1]), pack2(e[2], e[3])));
+                    sum_b = add2(sum_b, add2(pack2(e[4], e[5]), pack2(e[6], e[7])));
+                    pk[c8 * 4] = pack_bf16(e[0], e[1]);
+                    pk[c8 * 4 + 1] = pack_bf16(e[2], e[3]);
+                    pk[c8 * 4 + 2] = pack_bf16(e[4], e[5]);
+                    pk[c8 * 4 + 3] = pack_bf16(e[6], e[7]);
+                }
+                float s0, s1, s2, s3;
+                unpack2(sum_a, s0, s1);
+                unpack2(sum_b, s2, s3);
+                l = l * corr + ((s0 + s1) + (s2 + s3));
+                // P goes where the scores were: they are in registers, and the P V that read these columns two tiles
+                // ago ran before the Q K^T that wrote them
+                tmem_st32_u(tmem_s + sb * 64 + lane_addr, pk);
+                // value rows outside the visible keys become zeros (only tiles at the ends of the range): the first
+                // head's threads do it; the second head's P V is issued after the first's, so it sees them too
+                if (hd == 0 && (key0 < first_key || key0 + KT - 1 > last_key)) {
+                    if (r < KT) {
+                        mbar_wait(v_full0 + 8 * st, (gt / NS) & 1, err);   // orders these writes after the TMA's
+                        const int j = key0 + r;
+                        if (j < first_key || j > last_key) {
+    #pragma unroll
+                            for (int hf = 0; hf < HALVES; ++hf) {
+                                uint4* vr = reinterpret_cast<uint4*>(smem_raw + Q_BYTES + st * STAGE_BYTES + KV_BYTES + hf * KV_HALF + r * 128);
+    #pragma unroll
+                                for (int c8 = 0; c8 < 8; ++c8) vr[c8] = make_uint4(0, 0, 0, 0);
+                            }
+                        }
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the zeroed rows: visible to the MMA
+                    }
+                }
+                // rescale O where a row's reference maximum moved (rare after the first tiles); tcgen05.ld / .st
+                // are warp-wide: a warp rescales when any of its rows moved, the other rows by 1.
+                // The previous tile's P V of this head has to be complete before O is touched, and before this tile
+                // is announced at all: the issuer waits for the announcements by their parity, so a head must never
+                // be two of them ahead of it.
+                if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(my_pv_done + 8 * (sb ^ 1), ((th - 1) >> 1) & 1, err))) {
+                    alive = false;
+                    break;
+                }
+                if (__any_sync(0xffffffffu, moved)) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const float f = moved ? corr : 1.f;
+    #pragma unroll
+                    for (int c0 = 0; c0 < DP; c0 += 32) {
+                        float o[32];
+                        tmem_ld32(tmem_o + lane_addr + c0, o);
+    #pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] *= f;
+                        tmem_st32(tmem_o + lane_addr + c0, o);
+                    }
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");   // P (and O) are in tensor memory
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(my_p_ready);
+            }
+            // ---- O / l -> out -----------------------------------------------------------------------------------
+            if (alive) alive = mbar_wait(bar_o, (uint32_t)I & 1u, err);
+            alive = __all_sync(0xffffffffu, alive);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (alive && rows == QT) {
+                // a full tile: a warp writes its 32 rows of a 64-column half, swizzled, into its staging space and
+                // one thread stores them with a TMA copy: whole lines reach the memory instead of 16 bytes per row
+                // and instruction.  Meanwhile the issuers are at work on the next item.
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+                const int rr = lane;   // row within the warp's 32
+                if (lane == 0) tma_store_wait_read();   // the stores of this warp's item before have read the staging space
+                __syncwarp();
 #pragma unroll
                 for (int c0 = 0; c0 < DP; c0 += 32) {
                     float o[32];
                     tmem_ld32(tmem_o + lane_addr + c0, o);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] *= f;
-                    tmem_st32(tmem_o + lane_addr + c0, o);
-                }
-            }
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");   // P (and O) are in tensor memory
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(my_p_ready);
-        }
-        // ---- O / l -> out -----------------------------------------------------------------------------------
-        if (alive) alive = mbar_wait(bar_o, 0, err);
-        alive = __all_sync(0xffffffffu, alive);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (alive && rows == QT) {
-            // a full tile: the rows go, swizzled as a TMA box wants them, over this head's Q (every MMA has
-            // completed), and a thread of each warp stores the warp's 32 rows, a 64-column half per TMA copy:
-            // whole lines reach the memory instead of 16 bytes per row and instruction
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            unsigned char* stage = smem_raw + hd * Q_ONE;
-#pragma unroll
-            for (int c0 = 0; c0 < DP; c0 += 32) {
-                float o[32];
-                tmem_ld32(tmem_o + lane_addr + c0, o);
-#pragma unroll
-                for (int c8 = 0; c8 < 4; ++c8) {
-                    const int cc = c0 / 8 + c8;   // 16-byte chunk of the row
-                    uint4 w;
-                    w.x = pack_bf16(o[c8 * 8] * inv, o[c8 * 8 + 1] * inv);
-                    w.y = pack_bf16(o[c8 * 8 + 2] * inv, o[c8 * 8 + 3] * inv);
-                    w.z = pack_bf16(o[c8 * 8 + 4] * inv, o[c8 * 8 + 5] * inv);
-                    w.w = pack_bf16(o[c8 * 8 + 6] * inv, o[c8 * 8 + 7] * inv);
-                    *reinterpret_cast<uint4*>(stage + (cc >> 3) * (QT * 128) + r * 128 + (((cc & 7) ^ (r & 7)) << 4)) = w;
-                }
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) {   // a warp stores its own 32 rows: nobody waits for another warp here
-#pragma unroll
-                for (int hf = 0; hf < HALVES; ++hf)
-                    if (hf * 64 < d)
-                        tma_store_3d(&map_o, q_sm + hd * Q_ONE + hf * QT * 128 + (warp & 3) * 32 * 128, hf * 64, h0 + hd,
-                                     t0 + (warp & 3) * 32);
-                tma_store_commit_and_wait_read();
-            }
-        } else if (alive) {
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            const bool valid = r < rows;
-            __nv_bfloat16* dst = out + ((size_t)(t0 + r) * nh + h0 + hd) * d;
-#pragma unroll
-            for (int c0 = 0; c0 < DP; c0 += 32) {
-                float o[32];
-                tmem_ld32(tmem_o + lane_addr + c0, o);   // warp-wide, whatever `valid` is
-                if (valid) {
-#pragma unroll
                     for (int c8 = 0; c8 < 4; ++c8) {
-                        const int c = c0 + c8 * 8;
-                        if (c < d) {
-                            uint4 pk;
-                            pk.x = pack_bf16(o[c8 * 8] * inv, o[c8 * 8 + 1] * inv);
-                            pk.y = pack_bf16(o[c8 * 8 + 2] * inv, o[c8 * 8 + 3] * inv);
-                            pk.z = pack_bf16(o[c8 * 8 + 4] * inv, o[c8 * 8 + 5] * inv);
-                            pk.w = pack_bf16(o[c8 * 8 + 6] * inv, o[c8 * 8 + 7] * inv);
-                            *reinterpret_cast<uint4*>(dst + c) = pk;
+                        const int cc = (c0 & 63) / 8 + c8;   // 16-byte chunk of the half's row
+                        uint4 v;
+                        v.x = pack_bf16(o[c8 * 8] * inv, o[c8 * 8 + 1] * inv);
+                        v.y = pack_bf16(o[c8 * 8 + 2] * inv, o[c8 * 8 + 3] * inv);
+                        v.z = pack_bf16(o[c8 * 8 + 4] * inv, o[c8 * 8 + 5] * inv);
+                        v.w = pack_bf16(o[c8 * 8 + 6] * inv, o[c8 * 8 + 7] * inv);
+                        *reinterpret_cast<uint4*>(stage + (c0 >> 6) * 4096 + rr * 128 + ((cc ^ (rr & 7)) << 4)) = v;
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+#pragma unroll
+                    for (int hf = 0; hf < HALVES; ++hf)
+                        if (hf * 64 < d) tma_store_3d(&map_o, stage_sm + hf * 4096, hf * 64, h0 + hd, t0 + (warp & 3) * 32);
+                    tma_store_commit();
+                }
+            } else if (alive) {
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+                const bool valid = r < rows;
+                __nv_bfloat16* dst = out + ((size_t)(t0 + r) * nh + h0 + hd) * d;
+#pragma unroll
+                for (int c0 = 0; c0 < DP; c0 += 32) {
+                    float o[32];
+                    tmem_ld32(tmem_o + lane_addr + c0, o);   // warp-wide, whatever `valid` is
+                    if (valid) {
+#pragma unroll
+                        for (int c8 = 0; c8 < 4; ++c8) {
+                            const int c = c0 + c8 * 8;
+                            if (c < d) {
+                                uint4 pk;
+                                pk.x = pack_bf16(o[c8 * 8] * inv, o[c8 * 8 + 1] * inv);
+                                pk.y = pack_bf16(o[c8 * 8 + 2] * inv, o[c8 * 8 + 3] * inv);
+                                pk.z = pack_bf16(o[c8 * 8 + 4] * inv, o[c8 * 8 + 5] * inv);
+                                pk.w = pack_bf16(o[c8 * 8 + 6] * inv, o[c8 * 8 + 7] * inv);
+                                *reinterpret_cast<uint4*>(dst + c) = pk;
+                            }
                         }
                     }
                 }
             }
-        } else {
-            words[3] = 1;
+            // the reads of O above come before this head's next announcement (and so before the product that
+            // overwrites O): the fence stands in front of that arrive, in the tile loop
+            T += iters;
+            Th += iters;
         }
+        if (lane == 0) tma_store_wait_all();   // the last stores have left before the block does
+        if (!alive) words[3] = 1;
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -984,16 +1054,16 @@ bool map_q3(CUtensorMap* out, const void* ptr, long long T, int nh, int d, int b
 
 template <int DP>
 int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, void* out,
-                 const int* q_start,
-                 const int* start_pos, int num_entries, const int* table, int stride, int nh, int nkv, int d, int ps,
-                 int ps_shift, int num_pages, int window, float sl2, int dec_max, int tiles, const int* tile_map, int* err,
-                 cudaStream_t stream) {
-    constexpr size_t smem = 2 * (size_t)(DP / 64) * QT * 128 + PREFILL_STAGES * 2 * (size_t)(DP / 64) * KT * 128 + 256;
+                   const int* q_start, const int* start_pos, const int* table, int stride, int nh, int nkv, int d, int ps,
+                   int ps_shift, int num_pages, int window, float sl2, const int* work, int ctas, int* err, cudaStream_t stream) {
+    // Q of two heads, the key/value stages, the barriers' kilobyte, 4 KB of output staging per softmax warp and half
+    constexpr size_t smem = 2 * (size_t)(DP / 64) * QT * 128 + PREFILL_STAGES * 2 * (size_t)(DP / 64) * KT * 128 + 1024 +
+                            8 * (size_t)(DP / 64) * 4096;
     cudaFuncSetAttribute(attn_prefill_tc_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaFuncSetAttribute(attn_prefill_tc_kernel<DP>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    return xb_launch(attn_prefill_tc_kernel<DP>, dim3(nkv * ((nh / nkv + 1) / 2), tiles), dim3(PREFILL_THREADS), smem, stream, mq, mk, mv, mo,
-                     (__nv_bfloat16*)out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, ps_shift, num_pages,
-                     window, sl2, dec_max, tile_map, err);
+    return xb_launch(attn_prefill_tc_kernel<DP>, dim3(ctas), dim3(PREFILL_THREADS), smem, stream, mq, mk, mv, mo,
+                     (__nv_bfloat16*)out, q_start, start_pos, table, stride, nh, nkv, d, ps, ps_shift, num_pages,
+                     window, sl2, work, err);
 }
 
 constexpr int DEC_PAGE_CAP = 1024;   // block-table entries of a piece that are staged in shared memory
@@ -1014,20 +1084,20 @@ int launch_decode(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
 
 }  // namespace
 
-// Portions of more than dec_max tokens, 128 queries of two query heads per CTA; `tiles` = sum over
-// those portions of ceil(tokens / 128); `tokens` = rows of q.  `tile_map`: null, or 2 * tiles int32 that
-// give every block row its (portion, query tile), so that the longest tiles of all portions start
-// first and no block searches.  Returns cudaErrorNotSupported (having done nothing) for a head size
-// over 128 or not a multiple of 16, or a page size that is no power of two >= 8.
+// Portions of many tokens on the tensor cores: 128 queries of two query heads per work item, the items
+// shared out among `ctas` CTAs (at most one per SM) by `work`, which xb_attn_prefill_work (host
+// library) makes from the step's portions: [ctas + 1] offsets, then (portion, query tile, head pair)
+// per item, on the device.  `tokens` = rows of q.  Returns cudaErrorNotSupported (having done nothing)
+// for a head size over 128 or not a multiple of 16, or a page size that is no power of two >= 8.
 XB_EXPORT int xb_attn_prefill_tc(void* out, const void* q, const void* kc, const void* vc, const int* q_start,
-                                 const int* start_pos, int num_entries, const int* table, int stride, int tokens,
-                                 int nh, int nkv, int d, int ps, int num_pages, int window, float scale, int dec_max,
-                                 int tiles, const int* tile_map, int* err, cudaStream_t stream) {
-    if (tiles <= 0) return 0;
+                                 const int* start_pos, const int* table, int stride, int tokens,
+                                 int nh, int nkv, int d, int ps, int num_pages, int window, float scale,
+                                 const int* work, int ctas, int* err, cudaStream_t stream) {
+    if (ctas <= 0) return 0;
     int shift = -1;
     for (int s = 3; s < 20; ++s)
         if ((1 << s) == ps) shift = s;
-    if (d % 16 || d > 128 || d < 16 || nh % nkv || shift < 0) return (int)cudaErrorNotSupported;
+    if (d % 16 || d > 128 || d < 16 || nh % nkv || shift < 0 || !work) return (int)cudaErrorNotSupported;
     CUtensorMap mq, mk, mv, mo;   // out has the layout of q; a warp stores its 32 rows
     const long long rows = (long long)num_pages * nkv * ps;
     const int box_rows = ps < KT ? ps : KT;
@@ -1036,10 +1106,10 @@ XB_EXPORT int xb_attn_prefill_tc(void* out, const void* q, const void* kc, const
         return (int)cudaErrorNotSupported;
     const float sl2 = scale * 1.4426950408889634f;
     if (d <= 64)
-        return launch_prefill<64>(mq, mk, mv, mo, out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, shift,
-                                  num_pages, window, sl2, dec_max, tiles, tile_map, err, stream);
-    return launch_prefill<128>(mq, mk, mv, mo, out, q_start, start_pos, num_entries, table, stride, nh, nkv, d, ps, shift,
-                               num_pages, window, sl2, dec_max, tiles, tile_map, err, stream);
+        return launch_prefill<64>(mq, mk, mv, mo, out, q_start, start_pos, table, stride, nh, nkv, d, ps, shift, num_pages, window,
+                                  sl2, work, ctas, err, stream);
+    return launch_prefill<128>(mq, mk, mv, mo, out, q_start, start_pos, table, stride, nh, nkv, d, ps, shift, num_pages, window,
+                               sl2, work, ctas, err, stream);
 }
 // int32 a plan for `tokens` small tokens and `ctas` target CTAs must hold.
 XB_EXPORT long long xb_attn_decode_plan_size(int tokens, int ctas, int nkv) {

@@ -4,6 +4,7 @@
 #include <algorithm>
 #include <cstring>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "cache_manager.h"
@@ -148,6 +149,60 @@ XB_API long long xb_assemble(void* h, int B, const int* slots, const int* counts
         offsets_out[7 + G + g] = stride[g];
     }
     return off;
+}
+
+// ---- work lists of the prefill attention kernel ---------------------------------------------------
+// The step's portions of more than dec_max tokens are cut into items of 128 queries (a query tile) of
+// one pair of query heads; an item's cost is its number of 64-key tiles plus a fixed start-up.  The
+// items go, longest first, each onto the CTA with the least work so far (at most max_ctas CTAs), so
+// that all CTAs end together whatever the portions' lengths are; items of equal cost - the head pairs
+// of one query tile, which read the same keys - land on different CTAs and run at the same time.
+// out: [ctas + 1] offsets (in items) then 3 int32 per item: portion, query tile, head pair.
+// Returns the number of int32 written (-1: capacity too small) and the number of CTAs in *ctas_out.
+XB_API long long xb_attn_prefill_work(int B, const int* counts, const int* starts, int dec_max, int window,
+                                      int head_pairs, int max_ctas, int32_t* out, long long capacity, int* ctas_out) {
+    constexpr int QT = 128, KT = 64, START_UP = 3;
+    struct Item { int cost, b, tile; };
+    std::vector<Item> tiles;
+    for (int b = 0; b < B; ++b) {
+        const int n = counts[b];
+        if (n <= dec_max) continue;
+        for (int ti = 0; ti * QT < n; ++ti) {
+            const int p0 = starts[b] + ti * QT, rows = std::min(QT, n - ti * QT);
+            const int last_key = p0 + rows - 1, first_key = window > 0 ? std::max(0, p0 - window + 1) : 0;
+            tiles.push_back({last_key / KT - first_key / KT + 1 + START_UP, b, ti});
+        }
+    }
+    std::stable_sort(tiles.begin(), tiles.end(), [](const Item& x, const Item& y) { return x.cost > y.cost; });
+    const long long n_items = (long long)tiles.size() * head_pairs;
+    const int ctas = (int)std::min<long long>(max_ctas, n_items);
+    *ctas_out = ctas;
+    if (ctas <= 0) return 0;
+    if ((long long)ctas + 1 + 3 * n_items > capacity) return -1;
+    // least loaded CTA first; ties go to the lower index
+    std::vector<std::pair<long long, int>> heap;
+    for (int c = 0; c < ctas; ++c) heap.emplace_back(0, c);
+    auto later = [](const std::pair<long long, int>& x, const std::pair<long long, int>& y) { return x > y; };
+    std::make_heap(heap.begin(), heap.end(), later);
+    std::vector<std::vector<int32_t>> lists(ctas);
+    for (const Item& it : tiles) {
+        for (int hp = 0; hp < head_pairs; ++hp) {
+            std::pop_heap(heap.begin(), heap.end(), later);
+            auto& top = heap.back();
+            lists[top.second].insert(lists[top.second].end(), {it.b, it.tile, hp});
+            top.first += it.cost;
+            std::push_heap(heap.begin(), heap.end(), later);
+        }
+    }
+    int32_t* items = out + ctas + 1;
+    int at = 0;
+    for (int c = 0; c < ctas; ++c) {
+        out[c] = at;
+        std::copy(lists[c].begin(), lists[c].end(), items + 3 * (long long)at);
+        at += (int)lists[c].size() / 3;
+    }
+    out[ctas] = at;
+    return (long long)ctas + 1 + 3 * n_items;
 }
 
 // ---- scheduler ---------------------------------------------------------------------------------

@@ -4,6 +4,7 @@ CPU or through a library: a missing extension or a CPU tensor is an error.
 """
 from __future__ import annotations
 
+import ctypes
 import os
 from typing import Optional
 
@@ -524,26 +525,50 @@ def gemm_skinny_qkv(q_out, k_cache, v_cache, x, w_qkv, q_w, k_w, cos_t, sin_t, p
     return True
 
 
-def attn_prefill_tc(out, q, k_cache, v_cache, q_start, start_pos, num_entries, block_table, table_stride,
-                    window, scale, dec_max, tiles, err, tile_map: Optional[torch.Tensor] = None) -> bool:
+PREFILL_TC_MAX_CTAS = 148   # one CTA of the tcgen05 prefill kernel per SM
+
+
+def attn_prefill_work(counts, starts, dec_max: int, window, heads: int, kv_heads: int, max_ctas: int = PREFILL_TC_MAX_CTAS):
+    """The work list of ``attn_prefill_tc`` for a step whose entries bring ``counts`` tokens after
+    ``starts`` cached ones (host arrays): the portions of more than ``dec_max`` tokens cut into items of
+    128 queries of a pair of query heads and shared out among at most ``max_ctas`` CTAs, longest first
+    onto the least loaded.  Returns (pinned int32 host tensor, number of CTAs); no CTAs: nothing to do."""
+    from .native import host_lib
+    counts = np.ascontiguousarray(counts, dtype=np.int32)
+    starts = np.ascontiguousarray(starts, dtype=np.int32)
+    per_group = (heads // kv_heads + 1) // 2
+    tiles = int(((counts[counts > dec_max] + 127) // 128).sum())
+    cap = max_ctas + 1 + 3 * tiles * kv_heads * per_group + 4
+    host = torch.empty(cap, dtype=torch.int32).pin_memory()
+    ctas = ctypes.c_int(0)
+    used = host_lib().xb_attn_prefill_work(len(counts), counts.ctypes.data, starts.ctypes.data, int(dec_max), int(window or 0),
+                                           kv_heads * per_group, int(max_ctas), host.data_ptr(), cap, ctypes.byref(ctas))
+    if used < 0:
+        raise KernelError("the prefill work list does not fit its buffer")
+    return host[:max(int(used), 1)], int(ctas.value)
+
+
+def attn_prefill_tc(out, q, k_cache, v_cache, q_start, start_pos, block_table, table_stride, window, scale, work, ctas, err) -> bool:
     """Prefill attention on tcgen05 (TMA-fed; scores, probabilities and accumulators in tensor memory):
-    portions of more than ``dec_max`` tokens, 128 queries of two query heads of a key/value head per
-    CTA; ``tiles`` = sum over the portions of ceil(tokens / 128).  ``tile_map``: int32 [tiles, 2], the
-    (portion, query tile) of every block row (longest first); without it every block searches
-    ``q_start``.  Returns False, having done nothing, for sizes it does not take (head size over 128,
-    page size not a power of two from 8)."""
+    128 queries of two query heads of a key/value head per work item; ``work`` (int32, on the device)
+    and ``ctas`` come from ``attn_prefill_work`` for the same step, heads and window.  Returns False,
+    having done nothing, for sizes it does not take (head size over 128, page size not a power of two
+    from 8)."""
     T, nh, d = q.shape
     _need(q, "q", torch.bfloat16, (T, nh, d))
     _need(out, "out", torch.bfloat16, (T, nh, d))
     _need(k_cache, "k_cache", torch.bfloat16, (None, None, None, d))
     _need(v_cache, "v_cache", torch.bfloat16, tuple(k_cache.shape))
+    _need(work, "work", torch.int32)
     num_pages, nkv, ps, _ = k_cache.shape
-    if tile_map is not None:
-        _need(tile_map, "tile_map", torch.int32, (int(tiles), 2))
+    if ctas <= 0:
+        return True
+    if work.numel() < ctas + 1:
+        raise KernelError("the prefill work list is shorter than its table of CTAs")
     rc = kernels_lib().xb_attn_prefill_tc(
         out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), q_start.data_ptr(), start_pos.data_ptr(),
-        int(num_entries), block_table.data_ptr(), int(table_stride), T, nh, nkv, d, ps, num_pages, int(window or 0),
-        float(scale), int(dec_max), int(tiles), _ptr(tile_map), err.data_ptr(), _stream())
+        block_table.data_ptr(), int(table_stride), T, nh, nkv, d, ps, num_pages, int(window or 0), float(scale),
+        work.data_ptr(), int(ctas), err.data_ptr(), _stream())
     if rc == ERR_NOT_SUPPORTED:
         return False
     _ok(rc, "attn_prefill_tc")

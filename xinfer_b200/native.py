@@ -57,6 +57,8 @@ def _declare_host(lib):
         _sig(lib, name, c_int, [c_void_p, c_int, c_int])
     _sig(lib, "xb_cm_copy_table", c_int, [c_void_p, c_int, c_int, _I32P, c_int])
     _sig(lib, "xb_cm_consistent", c_int, [c_void_p, c_char_p, c_int])
+    _sig(lib, "xb_attn_prefill_work", c_longlong,
+         [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p])
     _sig(lib, "xb_cm_log_freed", None, [c_void_p, c_int])
     _sig(lib, "xb_cm_drain_freed", c_int, [c_void_p, c_void_p, c_void_p, c_int])
     _sig(lib, "xb_assemble", c_longlong,
@@ -102,7 +104,7 @@ def _declare_kernels(lib):
     _sig(lib, "xb_qk_norm_rope_write_bf16", I,
          [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P])
     _sig(lib, "xb_swiglu_rows_bf16", I, [P, P, I, I, P])
-    _sig(lib, "xb_attn_prefill_tc", I, [P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, F, I, I, P, P, P])
+    _sig(lib, "xb_attn_prefill_tc", I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, I, P, P])
     _sig(lib, "xb_gemm_skinny_tc", I, [P, I, P, P, I, I, I, I, P, P])
     _sig(lib, "xb_gemm_skinny_swiglu", I, [P, P, P, I, I, I, I, P, P])
     _sig(lib, "xb_gemm_skinny_qkv", I,

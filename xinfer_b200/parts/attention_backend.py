@@ -46,6 +46,11 @@ def decode_tc_takes(nh: int, nkv: int, d: int, page_size: int) -> bool:
             and page_size & (page_size - 1) == 0)
 
 
+def prefill_tc_takes(d: int, page_size: int) -> bool:
+    return (d % 16 == 0 and 16 <= d <= 128 and page_size >= 8 and page_size & (page_size - 1) == 0
+            and kernels.attn_prefill_queries(d, PREFILL_WARPS) == 128)
+
+
 DECODE_TC_MAX_TOKENS = 8192   # small tokens a plan of the tcgen05 decode kernel takes
 
 
@@ -95,17 +100,22 @@ def _plan(ctx, head_dim: int):
             plan = dict(tiles=int(((counts[~small] + per - 1) // per).sum()), small=int(counts[small].sum()),
                         direct=bool(small.all()), bound=int(ends[small].max()) if small.any() else 0,
                         prefill_bound=int(ends[~small].max()) if (~small).any() else 0)
-            if plan["tiles"] and per == 128:
-                # (portion, query tile) of every block row of the tcgen05 prefill kernels, the tiles with the
-                # most keys first whatever portion they belong to; sent once per step, before its first kernel
-                rows = [(int(ctx.h_start_pos[b]) + min(int(counts[b]), (ti + 1) * per), b, ti)
-                        for b in np.nonzero(~small)[0] for ti in range((int(counts[b]) + per - 1) // per)]
-                rows.sort(key=lambda r: -r[0])
-                host = torch.tensor([[b, ti] for _, b, ti in rows], dtype=torch.int32).pin_memory()
-                plan["tile_map"] = host.to(ctx.positions.device, non_blocking=True)
-                plan["tile_map_host"] = host   # keeps the pinned source alive until the step is over
         ctx.scratch[key] = plan
     return plan
+
+
+def _prefill_work(ctx, nh: int, nkv: int, window):
+    """The step's work list of the tcgen05 prefill kernel for this head layout and window, made once
+    per step (natively, on the host) and sent before the step's first kernel; shared by all layers."""
+    key = ("attn_prefill_work", nh, nkv, window)
+    made = ctx.scratch.get(key)
+    if made is None:
+        counts = np.diff(ctx.h_q_start[: ctx.real_entries + 1])
+        host, ctas = kernels.attn_prefill_work(counts, ctx.h_start_pos[: ctx.real_entries], DEC_MAX, window, nh, nkv)
+        # the pinned source stays alive until the step is over
+        made = (host.to(ctx.positions.device, non_blocking=True), ctas, host)
+        ctx.scratch[key] = made
+    return made
 
 
 def _decode_plan(ctx, nh: int, nkv: int, d: int, page_size: int, window, stride: int, early: bool):
@@ -135,6 +145,8 @@ def prepare_step(ctx, dtype, nh: int, nkv: int, d: int, page_size: int, window, 
     its block table): plans the decode kernel."""
     if _enabled and kernels.attn_tiled_supported(dtype, d):
         _decode_plan(ctx, nh, nkv, d, page_size, window, stride, early=True)
+        if _plan(ctx, d)["tiles"] and PREFILL_TC and prefill_tc_takes(d, page_size):
+            _prefill_work(ctx, nh, nkv, window)
 
 
 def attend(out, q, cache, ctx, table, stride, window, scale) -> None:
@@ -146,9 +158,10 @@ def attend(out, q, cache, ctx, table, stride, window, scale) -> None:
         return
     plan = _plan(ctx, d)
     took = False
-    if plan["tiles"] and PREFILL_TC and kernels.attn_prefill_queries(d, PREFILL_WARPS) == 128:
-        took = kernels.attn_prefill_tc(out, q, k_pages, v_pages, ctx.q_start, ctx.start_pos, ctx.num_entries, table, stride,
-                                       window, scale, DEC_MAX, plan["tiles"], ctx.err, tile_map=plan.get("tile_map"))
+    if plan["tiles"] and PREFILL_TC and prefill_tc_takes(d, cache.page_size):
+        work, ctas, _ = _prefill_work(ctx, nh, k_pages.shape[1], window)
+        took = kernels.attn_prefill_tc(out, q, k_pages, v_pages, ctx.q_start, ctx.start_pos, table, stride, window, scale,
+                                       work, ctas, ctx.err)
     if plan["tiles"] and not took:
         kernels.attn_prefill_bf16(out, q, k_pages, v_pages, ctx.q_start, ctx.start_pos, ctx.num_entries, table, stride,
                                   window, scale, DEC_MAX, plan["tiles"], plan["prefill_bound"], ctx.err, warps=PREFILL_WARPS)
