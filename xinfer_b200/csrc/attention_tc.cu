@@ -49,10 +49,11 @@ constexpr float RESCALE_STEP = 8.f;  // the row maximum moves only when it grows
 // Barriers carry on from item to item: their parities come from running counts of tiles (of all tiles
 // for the rings, of a head's tiles for what belongs to a head) and of items.
 // With an odd number of query heads per key/value head the last item of the group has one head and the
-// second softmax warpgroup sits it out.
+// second softmax warpgroup sits it out; the host also makes items of one head when two-head items would be
+// too few to fill the SMs (short portions, few heads).
 constexpr int PREFILL_STAGES = 3;
 constexpr int PREFILL_THREADS = 384;
-constexpr int PREFILL_ITEM_INTS = 3;   // portion, query tile, head pair
+constexpr int PREFILL_ITEM_INTS = 4;   // portion, query tile, first query head, heads (2 of one key/value head, or 1)
 
 // What the roles of a CTA derive, each for itself, from an item of the work list.
 struct PrefillItem {
@@ -66,12 +67,10 @@ __device__ __forceinline__ PrefillItem prefill_item(const int* __restrict__ item
                                                     const int* __restrict__ start_pos, const int* __restrict__ block_table,
                                                     int table_stride, int nh, int nkv, int window) {
     PrefillItem w;
-    const int b = item[0], tile = item[1], hp = item[2];
-    const int G = nh / nkv, per_group = (G + 1) / 2;
-    w.g = hp / per_group;
-    const int pair = hp % per_group;
-    w.h0 = w.g * G + 2 * pair;
-    w.nhd = 2 * pair + 1 < G ? 2 : 1;
+    const int b = item[0], tile = item[1];
+    w.h0 = item[2];
+    w.nhd = item[3];
+    w.g = w.h0 / (nh / nkv);
     const int n = q_start[b + 1] - q_start[b];
     const int row0 = tile * QT;
     w.rows = min(QT, n - row0);
@@ -1086,8 +1085,8 @@ int launch_decode(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
 
 // Portions of many tokens on the tensor cores: 128 queries of two query heads per work item, the items
 // shared out among `ctas` CTAs (at most one per SM) by `work`, which xb_attn_prefill_work (host
-// library) makes from the step's portions: [ctas + 1] offsets, then (portion, query tile, head pair)
-// per item, on the device.  `tokens` = rows of q.  Returns cudaErrorNotSupported (having done nothing)
+// library) makes from the step's portions: [ctas + 1] offsets, then (portion, query tile, first query
+// head, heads) per item, on the device.  `tokens` = rows of q.  Returns cudaErrorNotSupported (having done nothing)
 // for a head size over 128 or not a multiple of 16, or a page size that is no power of two >= 8.
 XB_EXPORT int xb_attn_prefill_tc(void* out, const void* q, const void* kc, const void* vc, const int* q_start,
                                  const int* start_pos, const int* table, int stride, int tokens,

@@ -153,44 +153,62 @@ XB_API long long xb_assemble(void* h, int B, const int* slots, const int* counts
 
 // ---- work lists of the prefill attention kernel ---------------------------------------------------
 // The step's portions of more than dec_max tokens are cut into items of 128 queries (a query tile) of
-// one pair of query heads; an item's cost is its number of 64-key tiles plus a fixed start-up.  The
-// items go, longest first, each onto the CTA with the least work so far (at most max_ctas CTAs), so
-// that all CTAs end together whatever the portions' lengths are; items of equal cost - the head pairs
-// of one query tile, which read the same keys - land on different CTAs and run at the same time.
-// out: [ctas + 1] offsets (in items) then 3 int32 per item: portion, query tile, head pair.
+// two query heads that share a key/value head (one head where a group has an odd head left); an item's
+// cost is its number of 64-key tiles (half of it for an item of one head) plus a fixed start-up.  Where
+// two-head items would not give every one of max_ctas CTAs an item (short portions, few heads), every
+// item takes one head instead: twice the items of half the length.  The items go, longest first, each onto
+// the CTA with the least work so far, so that all CTAs end together whatever the portions' lengths
+// are; items of equal cost - the heads of one query tile, which read the same keys - land on different
+// CTAs and run at the same time.
+// out: [ctas + 1] offsets (in items) then 4 int32 per item: portion, query tile, first query head, heads.
 // Returns the number of int32 written (-1: capacity too small) and the number of CTAs in *ctas_out.
 XB_API long long xb_attn_prefill_work(int B, const int* counts, const int* starts, int dec_max, int window,
-                                      int head_pairs, int max_ctas, int32_t* out, long long capacity, int* ctas_out) {
-    constexpr int QT = 128, KT = 64, START_UP = 3;
-    struct Item { int cost, b, tile; };
-    std::vector<Item> tiles;
+                                      int heads, int kv_heads, int max_ctas, int32_t* out, long long capacity,
+                                      int* ctas_out) {
+    constexpr int QT = 128, KT = 64, START_UP = 6, INTS = 4;   // costs in half tiles of two heads
+    struct Tile { int tiles, b, tile; };
+    std::vector<Tile> tiles;
     for (int b = 0; b < B; ++b) {
         const int n = counts[b];
         if (n <= dec_max) continue;
         for (int ti = 0; ti * QT < n; ++ti) {
             const int p0 = starts[b] + ti * QT, rows = std::min(QT, n - ti * QT);
             const int last_key = p0 + rows - 1, first_key = window > 0 ? std::max(0, p0 - window + 1) : 0;
-            tiles.push_back({last_key / KT - first_key / KT + 1 + START_UP, b, ti});
+            tiles.push_back({last_key / KT - first_key / KT + 1, b, ti});
         }
     }
-    std::stable_sort(tiles.begin(), tiles.end(), [](const Item& x, const Item& y) { return x.cost > y.cost; });
-    const long long n_items = (long long)tiles.size() * head_pairs;
+    *ctas_out = 0;
+    if (tiles.empty() || heads <= 0 || kv_heads <= 0 || heads % kv_heads) return 0;
+    std::stable_sort(tiles.begin(), tiles.end(), [](const Tile& x, const Tile& y) { return x.tiles > y.tiles; });
+    const int G = heads / kv_heads, per_group = (G + 1) / 2;
+    // pairs that would not even give every CTA an item leave SMs idle while the longest item runs alone; a
+    // tile of one head takes more than half the time of a tile of two, so pairs stay wherever they fill the CTAs
+    const bool singles = G >= 2 && (long long)tiles.size() * kv_heads * per_group <= max_ctas;
+    struct Head { int h0, nhd; };
+    std::vector<Head> head_items;
+    for (int g = 0; g < kv_heads; ++g) {
+        if (singles) {
+            for (int h = 0; h < G; ++h) head_items.push_back({g * G + h, 1});
+        } else {
+            for (int pr = 0; pr < per_group; ++pr) head_items.push_back({g * G + 2 * pr, 2 * pr + 1 < G ? 2 : 1});
+        }
+    }
+    const long long n_items = (long long)tiles.size() * (long long)head_items.size();
     const int ctas = (int)std::min<long long>(max_ctas, n_items);
     *ctas_out = ctas;
-    if (ctas <= 0) return 0;
-    if ((long long)ctas + 1 + 3 * n_items > capacity) return -1;
+    if ((long long)ctas + 1 + INTS * n_items > capacity) return -1;
     // least loaded CTA first; ties go to the lower index
     std::vector<std::pair<long long, int>> heap;
     for (int c = 0; c < ctas; ++c) heap.emplace_back(0, c);
     auto later = [](const std::pair<long long, int>& x, const std::pair<long long, int>& y) { return x > y; };
     std::make_heap(heap.begin(), heap.end(), later);
     std::vector<std::vector<int32_t>> lists(ctas);
-    for (const Item& it : tiles) {
-        for (int hp = 0; hp < head_pairs; ++hp) {
+    for (const Tile& t : tiles) {
+        for (const Head& h : head_items) {
             std::pop_heap(heap.begin(), heap.end(), later);
             auto& top = heap.back();
-            lists[top.second].insert(lists[top.second].end(), {it.b, it.tile, hp});
-            top.first += it.cost;
+            lists[top.second].insert(lists[top.second].end(), {t.b, t.tile, h.h0, h.nhd});
+            top.first += t.tiles * h.nhd + START_UP;
             std::push_heap(heap.begin(), heap.end(), later);
         }
     }
@@ -198,11 +216,11 @@ XB_API long long xb_attn_prefill_work(int B, const int* counts, const int* start
     int at = 0;
     for (int c = 0; c < ctas; ++c) {
         out[c] = at;
-        std::copy(lists[c].begin(), lists[c].end(), items + 3 * (long long)at);
-        at += (int)lists[c].size() / 3;
+        std::copy(lists[c].begin(), lists[c].end(), items + INTS * (long long)at);
+        at += (int)lists[c].size() / INTS;
     }
     out[ctas] = at;
-    return (long long)ctas + 1 + 3 * n_items;
+    return (long long)ctas + 1 + INTS * n_items;
 }
 
 // ---- scheduler ---------------------------------------------------------------------------------

@@ -531,18 +531,17 @@ PREFILL_TC_MAX_CTAS = 148   # one CTA of the tcgen05 prefill kernel per SM
 def attn_prefill_work(counts, starts, dec_max: int, window, heads: int, kv_heads: int, max_ctas: int = PREFILL_TC_MAX_CTAS):
     """The work list of ``attn_prefill_tc`` for a step whose entries bring ``counts`` tokens after
     ``starts`` cached ones (host arrays): the portions of more than ``dec_max`` tokens cut into items of
-    128 queries of a pair of query heads and shared out among at most ``max_ctas`` CTAs, longest first
+    128 queries of a pair of query heads (of single heads where pairs would be too few) and shared out among at most ``max_ctas`` CTAs, longest first
     onto the least loaded.  Returns (pinned int32 host tensor, number of CTAs); no CTAs: nothing to do."""
     from .native import host_lib
     counts = np.ascontiguousarray(counts, dtype=np.int32)
     starts = np.ascontiguousarray(starts, dtype=np.int32)
-    per_group = (heads // kv_heads + 1) // 2
     tiles = int(((counts[counts > dec_max] + 127) // 128).sum())
-    cap = max_ctas + 1 + 3 * tiles * kv_heads * per_group + 4
+    cap = max_ctas + 1 + 4 * tiles * heads + 4
     host = torch.empty(cap, dtype=torch.int32).pin_memory()
     ctas = ctypes.c_int(0)
     used = host_lib().xb_attn_prefill_work(len(counts), counts.ctypes.data, starts.ctypes.data, int(dec_max), int(window or 0),
-                                           kv_heads * per_group, int(max_ctas), host.data_ptr(), cap, ctypes.byref(ctas))
+                                           int(heads), int(kv_heads), int(max_ctas), host.data_ptr(), cap, ctypes.byref(ctas))
     if used < 0:
         raise KernelError("the prefill work list does not fit its buffer")
     return host[:max(int(used), 1)], int(ctas.value)

@@ -58,7 +58,7 @@ def _declare_host(lib):
     _sig(lib, "xb_cm_copy_table", c_int, [c_void_p, c_int, c_int, _I32P, c_int])
     _sig(lib, "xb_cm_consistent", c_int, [c_void_p, c_char_p, c_int])
     _sig(lib, "xb_attn_prefill_work", c_longlong,
-         [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p])
+         [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p])
     _sig(lib, "xb_cm_log_freed", None, [c_void_p, c_int])
     _sig(lib, "xb_cm_drain_freed", c_int, [c_void_p, c_void_p, c_void_p, c_int])
     _sig(lib, "xb_assemble", c_longlong,
