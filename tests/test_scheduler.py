@@ -326,3 +326,40 @@ def test_deciding_ahead_gives_the_same_outputs(seed):
         cm.check_consistent()
         outs.append(outputs)
     assert outs[0] == outs[1]
+
+
+def test_a_failed_step_aborts_what_was_scheduled_and_nothing_else():
+    """A step fails with one batch running and one decided ahead: the requests of both end as aborted,
+    their pages go back, nothing stays scheduled; a request that only waited is served afterwards."""
+    cm, s = make(pages=16, page=4, seqs=2)
+    s.add(0, [1] * 5, max_tokens=9)
+    s.add(1, [2] * 6, max_tokens=9)
+    s.add(2, [3] * 4, max_tokens=2)                          # waits: both slots are taken
+    s.schedule(); s.commit([5, 5])                           # prompts done, first tokens known
+    running = s.schedule()
+    assert [e.req_id for e in running] == [0, 1] and s.schedule_ahead() == []     # request 2 waits: nothing ahead
+    assert sorted(s.fail_steps()) == [0, 1]
+    assert s.finish_reason(0) == s.finish_reason(1) == "abort"
+    assert s.output(0) == [5] and s.output(1) == [5]         # what was recorded before stays readable
+    assert cm.live_requests() == 0 and cm.free_pages() == 16
+    cm.check_consistent()
+    assert s.fail_steps() == []                              # nothing is scheduled any more
+    s.release(0); s.release(1)
+    batches, ended = run(s)
+    assert list(ended) == [2] and s.finish_reason(2) == "length" and len(s.output(2)) == 2
+    assert cm.free_pages() == 16
+
+    # with a step decided ahead: both steps' requests go
+    cm, s = make(pages=16, page=4, seqs=2)
+    s.add(0, [1] * 5, max_tokens=9)
+    s.add(1, [2] * 6, max_tokens=9)
+    s.schedule(); s.commit([5, 5])
+    s.schedule()
+    ahead = s.schedule_ahead()
+    assert [e.req_id for e in ahead] == [0, 1]
+    assert sorted(s.fail_steps()) == [0, 1] and not s.has_work()
+    assert cm.live_requests() == 0 and cm.free_pages() == 16
+    cm.check_consistent()
+    s.add(7, [4] * 3, max_tokens=2)                          # the scheduler goes on
+    _, ended = run(s)
+    assert list(ended) == [7]
