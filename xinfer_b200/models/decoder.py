@@ -114,8 +114,7 @@ class DecoderModel:
         R = ctx.num_logit_rows
         logits = ws.get("model.logits", (max(R, 1), V), torch.float32)[:R]
         if R == 0:
-            stream.settle()
-            return logits
+            return logits      # nothing reads the stream again: its waiting additions are void
         if trace:
             tracing.push("head")
         y = ws.get("model.final", (R, H), self.dtype)
