@@ -528,17 +528,19 @@ def gemm_skinny_qkv(q_out, k_cache, v_cache, x, w_qkv, q_w, k_w, cos_t, sin_t, p
 PREFILL_TC_MAX_CTAS = 148   # one CTA of the tcgen05 prefill kernel per SM
 
 
-def attn_prefill_work(counts, starts, dec_max: int, window, heads: int, kv_heads: int, max_ctas: int = PREFILL_TC_MAX_CTAS):
+def attn_prefill_work(counts, starts, dec_max: int, window, heads: int, kv_heads: int, max_ctas: int = PREFILL_TC_MAX_CTAS,
+                      host_buffer=None):
     """The work list of ``attn_prefill_tc`` for a step whose entries bring ``counts`` tokens after
     ``starts`` cached ones (host arrays): the portions of more than ``dec_max`` tokens cut into items of
     128 queries of a pair of query heads (of single heads where pairs would be too few) and shared out among at most ``max_ctas`` CTAs, longest first
-    onto the least loaded.  Returns (pinned int32 host tensor, number of CTAs); no CTAs: nothing to do."""
+    onto the least loaded.  ``host_buffer(n)``: gives a pinned int32 tensor of at least n elements to write
+    into (default: a fresh one).  Returns (pinned int32 host tensor, number of CTAs); no CTAs: nothing to do."""
     from .native import host_lib
     counts = np.ascontiguousarray(counts, dtype=np.int32)
     starts = np.ascontiguousarray(starts, dtype=np.int32)
     tiles = int(((counts[counts > dec_max] + 127) // 128).sum())
     cap = max_ctas + 1 + 4 * tiles * heads + 4
-    host = torch.empty(cap, dtype=torch.int32).pin_memory()
+    host = host_buffer(cap) if host_buffer is not None else torch.empty(cap, dtype=torch.int32).pin_memory()
     ctas = ctypes.c_int(0)
     used = host_lib().xb_attn_prefill_work(len(counts), counts.ctypes.data, starts.ctypes.data, int(dec_max), int(window or 0),
                                            int(heads), int(kv_heads), int(max_ctas), host.data_ptr(), cap, ctypes.byref(ctas))

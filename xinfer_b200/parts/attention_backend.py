@@ -104,6 +104,34 @@ def _plan(ctx, head_dim: int):
     return plan
 
 
+class _PinnedRing:
+    """A few pinned staging buffers used in turn; one is reused only after the copy that read it has
+    finished (pinning memory anew for every step would synchronise the device)."""
+
+    def __init__(self, depth: int = 4):
+        self.bufs = [None] * depth
+        self.events = [None] * depth
+        self.i = 0
+
+    def take(self, n: int) -> torch.Tensor:
+        self.i = (self.i + 1) % len(self.bufs)
+        if self.events[self.i] is not None:
+            self.events[self.i].synchronize()
+        buf = self.bufs[self.i]
+        if buf is None or buf.numel() < n:
+            buf = torch.empty(max(n, 4096), dtype=torch.int32).pin_memory()
+            self.bufs[self.i] = buf
+        return buf
+
+    def sent(self) -> None:
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[self.i] = ev
+
+
+_work_ring = _PinnedRing()
+
+
 def _prefill_work(ctx, nh: int, nkv: int, window):
     """The step's work list of the tcgen05 prefill kernel for this head layout and window, made once
     per step (natively, on the host) and sent before the step's first kernel; shared by all layers."""
@@ -111,9 +139,10 @@ def _prefill_work(ctx, nh: int, nkv: int, window):
     made = ctx.scratch.get(key)
     if made is None:
         counts = np.diff(ctx.h_q_start[: ctx.real_entries + 1])
-        host, ctas = kernels.attn_prefill_work(counts, ctx.h_start_pos[: ctx.real_entries], DEC_MAX, window, nh, nkv)
-        # the pinned source stays alive until the step is over
+        host, ctas = kernels.attn_prefill_work(counts, ctx.h_start_pos[: ctx.real_entries], DEC_MAX, window, nh, nkv,
+                                               host_buffer=_work_ring.take)
         made = (host.to(ctx.positions.device, non_blocking=True), ctas, host)
+        _work_ring.sent()
         ctx.scratch[key] = made
     return made
 
