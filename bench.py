@@ -4,6 +4,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--shape 8b|0.6b|32b] [--impl ours|reference]
     python bench.py --workload mixed [--shape 0.6b|8b]     # 64 requests, continuous batching
     python bench.py --kernels                               # single kernels at serving sizes
+    python bench.py --ablate                                # a decode step with one kind of kernel left out at a time
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 and the context length
 of the configuration (a "step" is one decode step of the whole batch), timed on the device with
@@ -220,6 +221,8 @@ def main() -> int:
     ap.add_argument("--workload", default="steps", choices=["steps", "mixed"],
                     help="'mixed': 64 requests of 16..2,048 prompt tokens under continuous batching, instead of the step benchmark")
     ap.add_argument("--requests", type=int, default=64, help="requests of the mixed workload")
+    ap.add_argument("--ablate", action="store_true",
+                    help="instead of the step benchmark: a decode step with one kind of kernel left out at a time (what each kind costs in the chain)")
     ap.add_argument("--kernels", action="store_true",
                     help="instead of the step benchmark, time single kernels at serving sizes: one JSON line each")
     args = ap.parse_args()
@@ -229,6 +232,11 @@ def main() -> int:
         print("bench.py: this engine runs on one GPU; --gpus must be 1")
         return 2
     steps, warmup = max(args.steps, 1), max(args.warmup, 3)
+    if args.ablate:
+        from xinfer_b200 import measure
+        for rec in measure.decode_ablation(dict(CONFIG, **SHAPES[args.shape]), layers=args.layers or 12):
+            print(json.dumps(rec), flush=True)
+        return 0
     if args.kernels:
         from xinfer_b200 import measure
         pk = peaks()

@@ -223,3 +223,75 @@ def prefill_elementwise(tokens: int = 2048, *, hidden: int = 4096, heads: int = 
     if int(err):
         raise RuntimeError("a kernel reported an error: " + kernels.describe_error(int(err)))
     return out
+
+
+def decode_ablation(config: Dict, *, layers: int = 12, batches: Sequence[int] = (1, 8), context: int = 3900,
+                    page_size: int = 16, device="cuda:0") -> List[Dict]:
+    """What each kind of kernel costs IN the chain of a decode step: the step is timed whole and with one
+    kind of kernel left out (the numbers it computes are then wrong; its launches are gone, everything
+    else is as in the product: CUDA graph, programmatic dependent launch).  The difference is what
+    that kind really costs, start-up and drain included and whatever it hides of its neighbours
+    excluded; beside it stands what its bytes would take at the measured copy rate."""
+    from .engine.runner import ModelRunner, StepInput
+    from .parts import attention as attention_part
+    from .parts import attention_backend as backend
+    from .parts import norm as norm_part
+    from .parts import swiglu as swiglu_part
+
+    cfg = dict(config, num_hidden_layers=layers)
+    rng = np.random.default_rng(0)
+
+    def timed(batch: int) -> float:
+        runner = ModelRunner.random(cfg, seed=0, dtype="bfloat16", block_size=page_size, device=device,
+                                    num_blocks=batch * (context // page_size + 20), max_num_seqs=batch, max_model_len=context + 256)
+        slots = [runner.open_request() for _ in range(batch)]
+        for s in slots:
+            runner.step([StepInput(s, rng.integers(0, 1000, size=context), [])])
+        one = lambda: runner.step([StepInput(s, rng.integers(0, 1000, size=1), [0]) for s in slots], allow_graph=True)
+        for _ in range(30):
+            one()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(64):
+            one()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / 64 * 1000.0
+
+    keep = (kernels.swiglu, kernels.qk_norm_rope_write, backend.attend, attention_part.linear, swiglu_part.linear,
+            norm_part.RMSNorm.forward)
+
+    def no_norm(self, out, x, ctx, branch=None, sum_out=None, rows=None):
+        return keep[5](self, out, x, ctx, branch, sum_out, rows) if rows is not None else out
+
+    variants = [
+        ("whole step", lambda: None),
+        ("norms (two per layer)", lambda: setattr(norm_part.RMSNorm, "forward", no_norm)),
+        ("q/k norm + rotation + cache write", lambda: setattr(kernels, "qk_norm_rope_write", lambda *a, **k: None)),
+        ("attention", lambda: setattr(backend, "attend", lambda *a, **k: None)),
+        ("q/k/v and output products", lambda: setattr(attention_part, "linear", lambda out, x, w, err=None: out)),
+        ("SiLU gate", lambda: setattr(kernels, "swiglu", lambda out, gu: None)),
+        ("gate/up and down products", lambda: setattr(swiglu_part, "linear", lambda out, x, w, err=None: out)),
+    ]
+    out = []
+    try:
+        for batch in batches:
+            whole = None
+            for name, patch in variants:
+                patch()
+                try:
+                    us = timed(batch)
+                finally:
+                    (kernels.swiglu, kernels.qk_norm_rope_write, backend.attend, attention_part.linear, swiglu_part.linear) = keep[:5]
+                    norm_part.RMSNorm.forward = keep[5]
+                if whole is None:
+                    whole = us
+                    out.append({"kernel": "decode step", "batch": batch, "layers": layers, "us_per_step": round(us, 1)})
+                else:
+                    out.append({"kernel": "decode step without " + name, "batch": batch, "us_per_step": round(us, 1),
+                                "cost_in_chain_us_per_layer": round((whole - us) / layers, 1)})
+    finally:
+        (kernels.swiglu, kernels.qk_norm_rope_write, backend.attend, attention_part.linear, swiglu_part.linear) = keep[:5]
+        norm_part.RMSNorm.forward = keep[5]
+    return out
