@@ -363,3 +363,27 @@ def test_a_failed_step_aborts_what_was_scheduled_and_nothing_else():
     s.add(7, [4] * 3, max_tokens=2)                          # the scheduler goes on
     _, ended = run(s)
     assert list(ended) == [7]
+
+
+def test_stop_sequences_of_several_tokens():
+    """A stop sequence ends a request when the generated tokens end with it; its last token stays out, what
+    came before stays in; the prompt does not count; single ids and sequences mix."""
+    toks = [4, 9, 9, 2, 7, 9, 2, 5, 1]
+
+    def feed(stops, prompt=(9, 2), max_tokens=9):
+        cm, s = make()
+        s.add(0, list(prompt), max_tokens=max_tokens, stop_token_ids=stops)
+        i = [0]
+
+        def tok(e, step):
+            i[0] += 1
+            return toks[i[0] - 1]
+        run(s, tok)
+        return s.output(0), s.finish_reason(0)
+
+    assert feed([[9, 2]]) == ([4, 9, 9], "stop")                 # generated ... 9 then 2: stops, 2 stays out
+    assert feed([[9, 2, 5]]) == ([4, 9, 9, 2, 7, 9, 2], "stop")  # the first 9 2 is followed by 7: no match; the second by 5
+    assert feed([[2, 4]]) == (toks, "length")                    # the prompt's 2 does not count
+    assert feed([7, [9, 9, 9]]) == ([4, 9, 9, 2], "stop")        # a single id beside a sequence that never comes
+    assert feed([[4]]) == ([], "stop")                           # a sequence of one is a stop token
+    assert feed([[1, 1], []]) == (toks, "length")                # never hit; an empty sequence is nothing

@@ -244,8 +244,8 @@ XB_API void* xb_sched_create(void* cm, int max_num_seqs, int max_batched_tokens,
 }
 XB_API void xb_sched_destroy(void* h) { delete static_cast<SchedHandle*>(h); }
 XB_API int xb_sched_add(void* h, long long req_id, const int* prompt, int n, int max_tokens, int ignore_eos,
-                        const int* stop_ids, int n_stop) {
-    return (int)static_cast<SchedHandle*>(h)->sched.add(req_id, prompt, n, max_tokens, ignore_eos != 0, stop_ids, n_stop);
+                        const int* stop_ids, const int* stop_lens, int n_stop) {
+    return (int)static_cast<SchedHandle*>(h)->sched.add(req_id, prompt, n, max_tokens, ignore_eos != 0, stop_ids, stop_lens, n_stop);
 }
 XB_API int xb_sched_abort(void* h, long long req_id) { return static_cast<SchedHandle*>(h)->sched.abort(req_id) ? 1 : 0; }
 

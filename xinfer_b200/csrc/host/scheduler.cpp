@@ -7,7 +7,7 @@ namespace xb {
 Scheduler::Scheduler(CacheManager* cache, const SchedulerConfig& cfg) : cache_(cache), cfg_(cfg) {}
 
 AddStatus Scheduler::add(int64_t req_id, const int32_t* prompt, int n, int max_tokens,
-                         bool ignore_eos, const int32_t* stop_ids, int n_stop) {
+                         bool ignore_eos, const int32_t* stop_ids, const int32_t* stop_lens, int n_stop) {
     if (n <= 0) return ADD_EMPTY_PROMPT;
     if (reqs_.count(req_id)) return ADD_DUPLICATE;
     // the reference refuses prompts longer than max_model_len - 1 and clips max_tokens so that
@@ -32,7 +32,11 @@ AddStatus Scheduler::add(int64_t req_id, const int32_t* prompt, int n, int max_t
     r.prompt_len = n;
     r.max_tokens = max_tokens;
     r.ignore_eos = ignore_eos;
-    if (n_stop > 0) r.stop_ids.assign(stop_ids, stop_ids + n_stop);
+    for (int i = 0, at = 0; i < n_stop; ++i) {
+        const int len = stop_lens ? stop_lens[i] : 1;
+        if (len > 0) r.stop_seqs.emplace_back(stop_ids + at, stop_ids + at + len);
+        at += std::max(len, 0);
+    }
     reqs_[req_id] = std::move(r);
     waiting_.push_back(req_id);
     return ADD_OK;
@@ -162,7 +166,15 @@ std::vector<StepEntry> Scheduler::schedule(std::vector<int32_t>* tokens) {
 bool Scheduler::is_stop(const Request& r, int32_t tok) const {
     if (!r.ignore_eos && std::find(cfg_.eos_token_ids.begin(), cfg_.eos_token_ids.end(), tok) != cfg_.eos_token_ids.end())
         return true;
-    return std::find(r.stop_ids.begin(), r.stop_ids.end(), tok) != r.stop_ids.end();
+    // a stop sequence is hit when the generated tokens, with this one, end with it; the token itself then
+    // stays out, what was generated before it stays (src/core/scheduler.rs:1459-1491, 617-647)
+    const int generated = (int)r.tokens.size() - r.prompt_len;
+    for (const std::vector<int32_t>& stop : r.stop_seqs) {
+        const int before = (int)stop.size() - 1;
+        if (stop.back() != tok || before > generated) continue;
+        if (std::equal(stop.begin(), stop.end() - 1, r.tokens.end() - before)) return true;
+    }
+    return false;
 }
 
 std::vector<int64_t> Scheduler::drain_finished() {

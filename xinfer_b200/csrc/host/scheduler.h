@@ -48,8 +48,11 @@ class Scheduler {
 public:
     Scheduler(CacheManager* cache, const SchedulerConfig& cfg);
 
+    // `stop_ids` holds the request's stop sequences back to back, `stop_lens` the length of each
+    // (n_stop of them): a sequence of one token stops on that token; a longer one stops when the
+    // generated tokens end with it (src/core/scheduler.rs:1459-1491).
     AddStatus add(int64_t req_id, const int32_t* prompt, int n, int max_tokens, bool ignore_eos,
-                  const int32_t* stop_ids, int n_stop);
+                  const int32_t* stop_ids, const int32_t* stop_lens, int n_stop);
     bool abort(int64_t req_id);
 
     // Decide the next step.  Pages for every entry are taken here.  `tokens` receives the entries'
@@ -91,7 +94,7 @@ private:
         int slot = -1;
         int max_tokens = 0;
         bool ignore_eos = false;
-        std::vector<int32_t> stop_ids;
+        std::vector<std::vector<int32_t>> stop_seqs;
         int finish = NOT_FINISHED;
         bool hit_stop_token = false;
     };

@@ -61,11 +61,18 @@ class Scheduler:
             self._lib.xb_sched_destroy(h)
 
     def add(self, req_id: int, prompt: Sequence[int], max_tokens: int, ignore_eos: bool = False,
-            stop_token_ids: Sequence[int] = ()) -> None:
+            stop_token_ids: Sequence = ()) -> None:
+        """``stop_token_ids``: token ids and / or sequences of token ids.  A single id ends the request
+        when it is sampled; a sequence ends it when the generated tokens end with it.  The token that
+        completes a stop stays out of the output (src/core/scheduler.rs:1459-1491, 617-647)."""
         p = np.asarray(list(prompt), dtype=np.int32)
-        s = np.asarray(list(stop_token_ids), dtype=np.int32)
+        seqs = [[int(s)] if isinstance(s, (int, np.integer)) else [int(t) for t in s] for s in stop_token_ids]
+        seqs = [q for q in seqs if q]
+        flat = np.asarray([t for q in seqs for t in q], dtype=np.int32)
+        lens = np.asarray([len(q) for q in seqs], dtype=np.int32)
         rc = self._lib.xb_sched_add(self._h, int(req_id), p.ctypes.data if len(p) else None, len(p), int(max_tokens),
-                                    int(bool(ignore_eos)), s.ctypes.data if len(s) else None, len(s))
+                                    int(bool(ignore_eos)), flat.ctypes.data if len(flat) else None,
+                                    lens.ctypes.data if len(lens) else None, len(lens))
         if rc:
             raise SchedulerError(_ADD_ERRORS.get(rc, f"add failed ({rc})"))
 

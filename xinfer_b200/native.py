@@ -66,7 +66,7 @@ def _declare_host(lib):
           c_void_p, c_void_p, c_longlong, c_void_p])
     _sig(lib, "xb_sched_create", c_void_p, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int])
     _sig(lib, "xb_sched_destroy", None, [c_void_p])
-    _sig(lib, "xb_sched_add", c_int, [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p, c_int])
+    _sig(lib, "xb_sched_add", c_int, [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int])
     _sig(lib, "xb_sched_abort", c_int, [c_void_p, c_longlong])
     _sig(lib, "xb_sched_schedule", c_int,
          [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p])

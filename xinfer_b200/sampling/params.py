@@ -3,7 +3,7 @@
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import List, Optional
+from typing import List, Optional, Sequence, Union
 
 
 @dataclass
@@ -22,7 +22,10 @@ class SamplingParams:
     # it is batched with (the reference draws every request from one engine-wide generator,
     # src/utils/logits_processor.rs:20-36)
     seed: Optional[int] = None
-    stop_token_ids: List[int] = field(default_factory=list)
+    # token ids and / or sequences of token ids that end the request (the reference keeps its stop strings
+    # as sequences of ids, src/utils/config.rs:808-809): a sequence is hit when the generated tokens end with
+    # it; the token that completes a stop stays out of the output
+    stop_token_ids: List[Union[int, Sequence[int]]] = field(default_factory=list)
     session_id: Optional[str] = None
 
     def validate(self) -> None:
