@@ -307,3 +307,31 @@ def test_logits_do_not_change_precision_with_the_number_of_rows():
     # not values of bfloat16: the low 16 bits of the float32 words are in use in both
     for t in (a, b):
         assert (t.view(torch.int32) & 0xFFFF).ne(0).float().mean().item() > 0.9
+
+
+def test_a_stream_can_be_cancelled_and_stop_sequences_end_a_request(model_folders):
+    from xinfer_b200 import SamplingParams
+    folder = model_folders("A", torch.float32)
+    cfg, w = plain.load_folder(folder)
+    p = prompts_for("A", [12], seed=4)[0]
+    free = plain.generate(cfg, w, p, 14)
+    eng = engine(folder, "f32", "A")
+    # a stream that is cancelled after five tokens: what it had stays, its pages come back, the engine goes on
+    seq_id, plen, stream = eng.generate_stream(SamplingParams(max_tokens=14, ignore_eos=True), p)
+    assert (stream.seq_id, stream.prompt_length, stream.finished, stream.cancelled) == (seq_id, 12, False, False)
+    got = []
+    for item in stream:
+        if item.datatype == "TOKEN_ID":
+            got.append(item.data)
+            if len(got) == 5:
+                stream.cancel()
+        else:
+            assert item.datatype == "DONE" and item.data[0] == seq_id
+    assert stream.finished and stream.cancelled
+    assert 5 <= len(got) <= 7 and got == free[: len(got)]      # at most the tokens of steps already queued come after
+    assert eng.runner.cache.live_requests() == 0 and eng.runner.cache.free_pages() == 64 and not eng.has_work()
+    # a stop sequence of two ids: the request ends when the generated tokens end with it; its last token stays out
+    stop = free[6:8]
+    o = eng.generate_sync(SamplingParams(max_tokens=14, ignore_eos=True, stop_token_ids=[[free[2], free[2] + 1], stop]), [p])[0]
+    first = next(i for i in range(1, 14) if free[i - 1:i + 1] == stop)
+    assert o.finish_reason == "stop" and o.decode_output == free[:first]

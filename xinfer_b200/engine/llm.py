@@ -60,7 +60,6 @@ class _Live:
     prompt_len: int
     t_start: float
     t_first: float = 0.0
-    streamed: int = 0
 
 
 def _ms(t: float) -> int:
@@ -74,6 +73,52 @@ class _Flight:
     tokens_dev: Optional[torch.Tensor] = None
     sampler: Optional[Sampler] = None
     penalties: bool = False
+
+
+class EngineStream:
+    """The iterator ``generate_stream`` returns, with the reference's attributes (xinfer.pyi: EngineStream):
+    ``finished``, ``seq_id``, ``prompt_length``, ``cancelled`` and ``cancel()``.  Every ``next`` runs engine
+    steps until the request has new tokens (or has ended) and hands them out one by one."""
+
+    def __init__(self, engine: "Engine", seq_id: int, prompt_length: int):
+        self.engine = engine
+        self.seq_id = seq_id
+        self.prompt_length = prompt_length
+        self.finished = False
+        self.cancelled = False
+        self._queue: List[StreamItem] = []
+        self._streamed = 0
+
+    def cancel(self) -> None:
+        if not self.finished:
+            self.cancelled = self.engine.cancel(self.seq_id) or self.cancelled
+
+    def __iter__(self) -> "EngineStream":
+        return self
+
+    def _pull(self) -> None:
+        eng, seq_id = self.engine, self.seq_id
+        if seq_id in eng._live:
+            eng.step()
+        done = eng._done.get(seq_id)
+        src = done.decode_output if done is not None else eng.scheduler.output(seq_id)
+        self._queue += [StreamItem("TOKEN_ID", int(t)) for t in src[self._streamed:]]
+        self._streamed = len(src)
+        if done is not None:
+            eng._done.pop(seq_id)
+            if done.error is not None:
+                self._queue.append(StreamItem("ERROR", done.error))
+            else:
+                self._queue.append(StreamItem("DONE", (seq_id, done.prompt_length, done.decoded_length,
+                                                       done.decode_finish_time - done.decode_start_time)))
+            self.finished = True
+
+    def __next__(self) -> StreamItem:
+        while not self._queue:
+            if self.finished:
+                raise StopIteration
+            self._pull()
+        return self._queue.pop(0)
 
 
 class Engine:
@@ -156,14 +201,18 @@ class Engine:
         self.stats["preemptions"] = self.scheduler.preemptions
         for seq_id in ended:
             self._finish(seq_id)
+        self._drop_idle_flight()
+        return ended
+
+    def _drop_idle_flight(self) -> None:
+        """A batch queued for requests that have all ended meanwhile: wait for it, keep nothing."""
         if self._flight is not None and not any(e.req_id in self._live for e in self._flight.wanted):
             try:
-                self._retire(self._flight)   # queued for requests that have all ended meanwhile: nothing to keep
+                self._retire(self._flight)
             except RuntimeError as e:
                 for seq_id in self._fail_scheduled(e):
                     self._finish(seq_id)
             self._flight = None
-        return ended
 
     def _fail_scheduled(self, error: Exception) -> List[int]:
         """A step failed.  The requests of every batch that is scheduled and not recorded (the one
@@ -260,26 +309,20 @@ class Engine:
                 break
         return [self._done.pop(i) for i in ids]
 
-    def generate_stream(self, params: SamplingParams, prompt: Sequence[int]) -> Tuple[int, int, Iterator[StreamItem]]:
-        """Returns (seq_id, prompt_length, iterator of StreamItem)."""
+    def generate_stream(self, params: SamplingParams, prompt: Sequence[int]) -> Tuple[int, int, "EngineStream"]:
+        """Returns (seq_id, prompt_length, stream); the stream yields ``StreamItem``s and can be cancelled."""
         seq_id = self.add_request(prompt, params)
-        live = self._live[seq_id]
+        return seq_id, len(prompt), EngineStream(self, seq_id, len(prompt))
 
-        def stream() -> Iterator[StreamItem]:
-            while seq_id in self._live:
-                self.step()
-                src = self._done[seq_id].decode_output if seq_id in self._done else self.scheduler.output(seq_id)
-                for tok in src[live.streamed:]:
-                    yield StreamItem("TOKEN_ID", int(tok))
-                live.streamed = len(src)
-            out = self._done.pop(seq_id)
-            if out.error is not None:
-                yield StreamItem("ERROR", out.error)
-                return
-            yield StreamItem("DONE", (seq_id, out.prompt_length, out.decoded_length,
-                                      out.decode_finish_time - out.decode_start_time))
-
-        return seq_id, len(prompt), stream()
+    def cancel(self, seq_id: int) -> bool:
+        """End a live request now: its pages go back, its output so far stays readable (finish reason "abort")."""
+        if seq_id not in self._live:
+            return False
+        self.scheduler.abort(seq_id)
+        for ended in self.scheduler.drain_finished():
+            self._finish(ended)
+        self._drop_idle_flight()
+        return True
 
     def get_available_kv_tokens(self) -> int:
         return self.runner.available_kv_tokens()
