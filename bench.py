@@ -4,6 +4,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--shape 8b|0.6b|32b] [--impl ours|reference]
     python bench.py --workload mixed [--shape 0.6b|8b]     # 64 requests, continuous batching
     python bench.py --kernels                               # single kernels at serving sizes
+    python bench.py --kernels --attn 16,8,64                # the attention kernels at another head layout
     python bench.py --ablate                                # a decode step with one kind of kernel left out at a time
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 and the context length
@@ -223,6 +224,8 @@ def main() -> int:
     ap.add_argument("--requests", type=int, default=64, help="requests of the mixed workload")
     ap.add_argument("--ablate", action="store_true",
                     help="instead of the step benchmark: a decode step with one kind of kernel left out at a time (what each kind costs in the chain)")
+    ap.add_argument("--attn", default="", metavar="HEADS,KV_HEADS,HEAD_DIM[,PAGE_SIZE]",
+                    help="with --kernels: the attention kernels alone at this head layout, over short and long contexts")
     ap.add_argument("--kernels", action="store_true",
                     help="instead of the step benchmark, time single kernels at serving sizes: one JSON line each")
     args = ap.parse_args()
@@ -236,6 +239,16 @@ def main() -> int:
         from xinfer_b200 import measure
         for rec in measure.decode_ablation(dict(CONFIG, **SHAPES[args.shape]), layers=args.layers or 12):
             print(json.dumps(rec), flush=True)
+        return 0
+    if args.kernels and args.attn:
+        # the attention kernels alone at another head layout: HEADS,KV_HEADS,HEAD_DIM[,PAGE_SIZE]
+        from xinfer_b200 import measure
+        pk = peaks()
+        sizes = [int(x) for x in args.attn.split(",")]
+        lay = dict(heads=sizes[0], kv_heads=sizes[1], head_dim=sizes[2], page_size=sizes[3] if len(sizes) > 3 else PAGE)
+        for rec in (measure.decode_attention(((1, 4096), (8, 4096), (64, 2048), (4, 65536), (16, 512)), hbm_gbs=pk["hbm_gbs"], **lay)
+                    + measure.prefill_attention(((0, 512), (0, 2048), (0, 8192), (30000, 2048)), peak_tflops=pk["bf16_tflops"], **lay)):
+            print(json.dumps(dict(rec, **lay)), flush=True)
         return 0
     if args.kernels:
         from xinfer_b200 import measure

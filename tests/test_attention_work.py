@@ -42,9 +42,9 @@ def test_every_head_of_every_tile_once_and_loads_even():
         assert c == min(max_ctas, len(got)) and offs[0] == 0 and offs[-1] == len(got) and (np.diff(offs) >= 1).all()
         loads = []
         for k in range(c):
-            mine = [cost(b, t, counts, starts, window) * n + 6 for b, t, _, n in got[offs[k]: offs[k + 1]]]
+            mine = [cost(b, t, counts, starts, window) * (6 if n == 2 else 4) + 18 for b, t, _, n in got[offs[k]: offs[k + 1]]]
             loads.append(sum(mine))
-        biggest = max(cost(b, t, counts, starts, window) * n + 6 for b, t, _, n in got)
+        biggest = max(cost(b, t, counts, starts, window) * (6 if n == 2 else 4) + 18 for b, t, _, n in got)
         assert max(loads) - min(loads) <= biggest                    # what longest-first onto the least loaded guarantees
     # few items: single heads, so that the SMs have something to do
     c, offs, items, used = work_list([512], [0], 4, 0, 16, 8, 148)
@@ -54,6 +54,11 @@ def test_every_head_of_every_tile_once_and_loads_even():
     # many items: pairs
     c, offs, items, used = work_list([4096], [0], 4, 0, 32, 8, 148)
     assert c == 148 and (items[:, 3] == 2).all() and len(items) == 32 * 16
+    # two heads per group and a long context: 128 pairs on 128 CTAs end before 256 single heads on 148
+    c, offs, items, used = work_list([2048], [30000], 4, 0, 16, 8, 148)
+    assert c == 128 and (items[:, 3] == 2).all()
+    c, offs, items, used = work_list([2048], [0], 4, 0, 16, 8, 148)       # the same from position 0: short items, single heads
+    assert c == 148 and (items[:, 3] == 1).all()
 
 
 def test_nothing_to_do_and_too_small_a_buffer():

@@ -507,7 +507,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 // decode: few tokens per request, keys split into ranges
 // ------------------------------------------------------------------------------------------------
 constexpr int DEC_ROWS = 16;    // query heads of one key/value head a CTA can hold
-constexpr int DEC_STAGES = 3;   // key/value tiles in flight per CTA
+// key/value tiles in flight per CTA: enough bytes on their way per SM (two CTAs) to cover the memory's
+// latency at full rate, so twice as many where a tile is half as large
+__host__ __device__ constexpr int dec_stages(int dp) { return dp <= 64 ? 6 : 3; }
 constexpr int PLAN_HEADER = 4;  // int32 before the first piece of a plan: [0] = number of pieces
 constexpr int PLAN_ENTRY = 8;   // int32 per piece: token row, request, position, first key, first tile, tiles,
                                 // pieces of the token << 16 | index of this one, rank of the token among the small ones
@@ -637,7 +639,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                       const int* __restrict__ block_table, int table_stride, int nh, int nkv, int d, int ps,
                       int ps_shift, int num_pages, float scale_log2, int dec_max, int splits_max, int page_cap,
                       int* __restrict__ tickets, int* err) {
-    constexpr int HALVES = DP / 64;
+    constexpr int HALVES = DP / 64, DEC_STAGES = dec_stages(DP);
     constexpr uint32_t Q_HALF = DEC_ROWS * 128, Q_BYTES = HALVES * Q_HALF, P_ONE = DEC_ROWS * 128, P_BYTES = 2 * P_ONE;
     constexpr uint32_t KV_HALF = KT * 128, KV_BYTES = HALVES * KV_HALF, STAGE_BYTES = 2 * KV_BYTES;
     constexpr uint32_t BAR_OFF = Q_BYTES + P_BYTES + DEC_STAGES * STAGE_BYTES;
@@ -645,13 +647,15 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const uint32_t base = smem_u32(smem_raw);
     const uint32_t q_sm = base, p_sm = base + Q_BYTES, kv_sm = p_sm + P_BYTES;
     unsigned char* p_ptr = smem_raw + Q_BYTES;
-    // barriers, 8 bytes each: k_full[3] k_empty[3] v_full[3] v_empty[3] s_ready[2] s_free[2] p_ready[2] pv_done[2]
-    // q_full; then four words
+    // barriers, 8 bytes each: k_full k_empty v_full v_empty (one per stage each), s_ready[2] s_free[2] p_ready[2]
+    // pv_done[2] q_full; then four words
+    constexpr uint32_t RING_BARS = 8 * DEC_STAGES;
     const uint32_t bars = base + BAR_OFF;
-    const uint32_t k_full0 = bars, k_empty0 = bars + 24, v_full0 = bars + 48, v_empty0 = bars + 72;
-    const uint32_t s_ready0 = bars + 96, s_free0 = bars + 112, p_ready0 = bars + 128, pv_done0 = bars + 144, q_full = bars + 160;
-    volatile uint32_t* words = reinterpret_cast<volatile uint32_t*>(smem_raw + BAR_OFF + 168);  // tmem, dead, last, skip
-    int* s_pages = reinterpret_cast<int*>(smem_raw + BAR_OFF + 192);   // this range's part of the block table
+    const uint32_t k_full0 = bars, k_empty0 = bars + RING_BARS, v_full0 = bars + 2 * RING_BARS, v_empty0 = bars + 3 * RING_BARS;
+    const uint32_t s_ready0 = bars + 4 * RING_BARS, s_free0 = s_ready0 + 16, p_ready0 = s_ready0 + 32, pv_done0 = s_ready0 + 48,
+                   q_full = s_ready0 + 64;
+    volatile uint32_t* words = reinterpret_cast<volatile uint32_t*>(smem_raw + BAR_OFF + 4 * RING_BARS + 72);  // tmem, dead, last, skip
+    int* s_pages = reinterpret_cast<int*>(smem_raw + BAR_OFF + 4 * RING_BARS + 96);   // this range's part of the block table
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
 
@@ -680,7 +684,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         words[1] = 0;
         words[2] = 0;
         words[3] = (*reinterpret_cast<volatile int*>(err) & XB_ERR_WAIT) ? 1u : 0u;   // an earlier CTA gave up: do not pile on
-        for (int i = 0; i < 14; ++i) mbar_init(bars + 8 * i, 1);   // k_full, k_empty, v_full, v_empty, s_ready
+        for (int i = 0; i < 4 * DEC_STAGES + 2; ++i) mbar_init(bars + 8 * i, 1);   // k_full, k_empty, v_full, v_empty, s_ready
         mbar_init(s_free0, 32);
         mbar_init(s_free0 + 8, 32);
         mbar_init(p_ready0, 32);
@@ -1072,8 +1076,8 @@ int launch_decode(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
                   float* part_ml, const int* plan, int pieces, const int* table, int stride, int nh, int nkv, int d, int ps,
                   int ps_shift, int num_pages, float sl2, int dec_max, int splits_max, int* tickets, int overlap, int* err,
                   cudaStream_t stream) {
-    constexpr size_t smem = (size_t)(DP / 64) * DEC_ROWS * 128 + 2 * DEC_ROWS * 128 + DEC_STAGES * 2 * (size_t)(DP / 64) * KT * 128 + 192 +
-                            (size_t)DEC_PAGE_CAP * 4;
+    constexpr size_t smem = (size_t)(DP / 64) * DEC_ROWS * 128 + 2 * DEC_ROWS * 128 + dec_stages(DP) * 2 * (size_t)(DP / 64) * KT * 128 +
+                            32 * dec_stages(DP) + 96 + (size_t)DEC_PAGE_CAP * 4;
     cudaFuncSetAttribute(attn_decode_tc_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaFuncSetAttribute(attn_decode_tc_kernel<DP>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     return xb_launch_opt(overlap != 0, attn_decode_tc_kernel<DP>, dim3(nkv, pieces), dim3(128), smem, stream, mq, mk, mv,

@@ -154,18 +154,20 @@ XB_API long long xb_assemble(void* h, int B, const int* slots, const int* counts
 // ---- work lists of the prefill attention kernel ---------------------------------------------------
 // The step's portions of more than dec_max tokens are cut into items of 128 queries (a query tile) of
 // two query heads that share a key/value head (one head where a group has an odd head left); an item's
-// cost is its number of 64-key tiles (half of it for an item of one head) plus a fixed start-up.  Where
-// two-head items would not give every one of max_ctas CTAs an item (short portions, few heads), every
-// item takes one head instead: twice the items of half the length.  The items go, longest first, each onto
-// the CTA with the least work so far, so that all CTAs end together whatever the portions' lengths
-// are; items of equal cost - the heads of one query tile, which read the same keys - land on different
-// CTAs and run at the same time.
+// cost is its number of 64-key tiles times the cost of a tile (of two heads, or of one) plus a fixed
+// start-up.  The items go, longest first, each onto the CTA with the least work so far, so that all CTAs
+// end together whatever the portions' lengths are; items of equal cost - the heads of one query tile,
+// which read the same keys - land on different CTAs and run at the same time.  The same is tried with
+// one head per item (twice the items, each two thirds as long), and the cut that ends earlier is taken:
+// one head where two-head items would leave CTAs idle (short portions, few heads), two otherwise.
 // out: [ctas + 1] offsets (in items) then 4 int32 per item: portion, query tile, first query head, heads.
 // Returns the number of int32 written (-1: capacity too small) and the number of CTAs in *ctas_out.
 XB_API long long xb_attn_prefill_work(int B, const int* counts, const int* starts, int dec_max, int window,
                                       int heads, int kv_heads, int max_ctas, int32_t* out, long long capacity,
                                       int* ctas_out) {
-    constexpr int QT = 128, KT = 64, START_UP = 6, INTS = 4;   // costs in half tiles of two heads
+    // costs in sixths of a key tile of two heads: a tile of one head takes about two thirds of the time of a tile
+    // of two (measured at long contexts: 0.76 us against 1.15 us), an item's start about three tiles
+    constexpr int QT = 128, KT = 64, TILE_OF_TWO = 6, TILE_OF_ONE = 4, START_UP = 18, INTS = 4;
     struct Tile { int tiles, b, tile; };
     std::vector<Tile> tiles;
     for (int b = 0; b < B; ++b) {
@@ -181,37 +183,50 @@ XB_API long long xb_attn_prefill_work(int B, const int* counts, const int* start
     if (tiles.empty() || heads <= 0 || kv_heads <= 0 || heads % kv_heads) return 0;
     std::stable_sort(tiles.begin(), tiles.end(), [](const Tile& x, const Tile& y) { return x.tiles > y.tiles; });
     const int G = heads / kv_heads, per_group = (G + 1) / 2;
-    // pairs that would not even give every CTA an item leave SMs idle while the longest item runs alone; a
-    // tile of one head takes more than half the time of a tile of two, so pairs stay wherever they fill the CTAs
-    const bool singles = G >= 2 && (long long)tiles.size() * kv_heads * per_group <= max_ctas;
     struct Head { int h0, nhd; };
-    std::vector<Head> head_items;
-    for (int g = 0; g < kv_heads; ++g) {
-        if (singles) {
-            for (int h = 0; h < G; ++h) head_items.push_back({g * G + h, 1});
-        } else {
-            for (int pr = 0; pr < per_group; ++pr) head_items.push_back({g * G + 2 * pr, 2 * pr + 1 < G ? 2 : 1});
+    struct Shared { std::vector<std::vector<int32_t>> lists; long long longest = 0, n_items = 0; };
+    // items of two heads (`singles` false) or of one, shared out: least loaded CTA first, ties to the lower index
+    auto share_out = [&](bool singles, Shared& made) {
+        std::vector<Head> head_items;
+        for (int g = 0; g < kv_heads; ++g) {
+            if (singles) {
+                for (int h = 0; h < G; ++h) head_items.push_back({g * G + h, 1});
+            } else {
+                for (int pr = 0; pr < per_group; ++pr) head_items.push_back({g * G + 2 * pr, 2 * pr + 1 < G ? 2 : 1});
+            }
         }
+        made.n_items = (long long)tiles.size() * (long long)head_items.size();
+        const int ctas = (int)std::min<long long>(max_ctas, made.n_items);
+        std::vector<std::pair<long long, int>> heap;
+        for (int c = 0; c < ctas; ++c) heap.emplace_back(0, c);
+        auto later = [](const std::pair<long long, int>& x, const std::pair<long long, int>& y) { return x > y; };
+        std::make_heap(heap.begin(), heap.end(), later);
+        made.lists.assign(ctas, {});
+        for (const Tile& t : tiles) {
+            for (const Head& h : head_items) {
+                std::pop_heap(heap.begin(), heap.end(), later);
+                auto& top = heap.back();
+                made.lists[top.second].insert(made.lists[top.second].end(), {t.b, t.tile, h.h0, h.nhd});
+                top.first += (long long)t.tiles * (h.nhd == 2 ? TILE_OF_TWO : TILE_OF_ONE) + START_UP;
+                made.longest = std::max(made.longest, top.first);
+                std::push_heap(heap.begin(), heap.end(), later);
+            }
+        }
+    };
+    // two heads per item load a key/value tile once for both; one head per item gives twice as many items to
+    // fill the CTAs with.  Whichever ends earlier by these costs is taken (a few thousand items at most).
+    Shared made;
+    share_out(false, made);
+    if (G >= 2) {
+        Shared ones;
+        share_out(true, ones);
+        if (ones.longest < made.longest) made = std::move(ones);
     }
-    const long long n_items = (long long)tiles.size() * (long long)head_items.size();
-    const int ctas = (int)std::min<long long>(max_ctas, n_items);
+    const std::vector<std::vector<int32_t>>& lists = made.lists;
+    const long long n_items = made.n_items;
+    const int ctas = (int)lists.size();
     *ctas_out = ctas;
     if ((long long)ctas + 1 + INTS * n_items > capacity) return -1;
-    // least loaded CTA first; ties go to the lower index
-    std::vector<std::pair<long long, int>> heap;
-    for (int c = 0; c < ctas; ++c) heap.emplace_back(0, c);
-    auto later = [](const std::pair<long long, int>& x, const std::pair<long long, int>& y) { return x > y; };
-    std::make_heap(heap.begin(), heap.end(), later);
-    std::vector<std::vector<int32_t>> lists(ctas);
-    for (const Tile& t : tiles) {
-        for (const Head& h : head_items) {
-            std::pop_heap(heap.begin(), heap.end(), later);
-            auto& top = heap.back();
-            lists[top.second].insert(lists[top.second].end(), {t.b, t.tile, h.h0, h.nhd});
-            top.first += t.tiles * h.nhd + START_UP;
-            std::push_heap(heap.begin(), heap.end(), later);
-        }
-    }
     int32_t* items = out + ctas + 1;
     int at = 0;
     for (int c = 0; c < ctas; ++c) {
