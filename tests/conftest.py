@@ -19,7 +19,7 @@ def model_folders(tmp_path_factory):
     """Random-weight model folders of the tiny configurations, made once per session in a
     temporary place: ``model_folders(name, store_dtype)`` -> path."""
     import torch
-    from helpers import TINY, sharpen
+    from helpers import TINY, sharpen_for
     from xinfer_b200.weights import write_random_model
     made = {}
 
@@ -28,7 +28,7 @@ def model_folders(tmp_path_factory):
         if key not in made:
             d = tmp_path_factory.mktemp(f"model_{name}_{str(store_dtype).split('.')[-1]}")
             cfg, seed = TINY[name]
-            write_random_model(str(d), cfg, seed, dtype=store_dtype, override=sharpen)
+            write_random_model(str(d), cfg, seed, dtype=store_dtype, override=sharpen_for(cfg))
             made[key] = str(d)
         return made[key]
 

@@ -40,6 +40,22 @@ def sharpen(name: str, t: torch.Tensor):
     return None
 
 
+def sharpen_for(cfg: dict):
+    """``sharpen`` for a configuration.  Where the output head is the embedding table, the most likely
+    next token of a random model is the token it was given (a row's product with itself stands far above
+    its products with other rows), and greedy generation repeats one token whatever the cache holds; a
+    smaller table lets the layers' outputs decide, so that a generated sequence shows a wrong step."""
+    if not cfg.get("tie_word_embeddings"):
+        return sharpen
+
+    def override(name: str, t: torch.Tensor):
+        if name.endswith("embed_tokens.weight"):
+            return t.float() * 0.125
+        return sharpen(name, t)
+
+    return override
+
+
 def prompts_for(name: str, lengths: Sequence[int], seed: int = 0) -> List[List[int]]:
     cfg, _ = TINY[name]
     rng = np.random.default_rng(1000 + seed)

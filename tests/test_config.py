@@ -193,3 +193,32 @@ def test_nvtx_ranges_follow_the_flag():
         tracing.enable(was)
     assert tracing.step_kind([1, 1, 1]) == "decode" and tracing.step_kind([5, 9]) == "prefill"
     assert tracing.step_kind([1, 7]) == "mixed"
+
+
+def test_generation_config_reads_merges_and_fills(tmp_path):
+    import json
+    from xinfer_b200 import GenerationConfig, SamplingParams
+    from xinfer_b200.config.generation import join_eos
+    assert GenerationConfig.load(str(tmp_path)) is None                      # a folder without the file
+    (tmp_path / "generation_config.json").write_text(json.dumps(
+        {"temperature": 0.6, "top_k": 20, "top_p": 0.95, "eos_token_id": [7, 3], "do_sample": True, "bos_token_id": 1}))
+    g = GenerationConfig.load(str(tmp_path))
+    assert (g.temperature, g.top_k, g.top_p, g.frequency_penalty, g.bos_token_id, g.eos_token_id) == (0.6, 20, 0.95, None, 1, (7, 3))
+    # the engine's own options come first, field by field
+    m = GenerationConfig(temperature=0.0, presence_penalty=1.5).over(g)
+    assert (m.temperature, m.top_k, m.top_p, m.presence_penalty, m.eos_token_id) == (0.0, 20, 0.95, 1.5, (7, 3))
+    assert GenerationConfig(top_k=5).over(None).top_k == 5
+    # a request keeps what it sets, and is not changed in place
+    p = SamplingParams(temperature=1.0, max_tokens=9)
+    f = g.fill(p)
+    assert (f.temperature, f.top_k, f.top_p, f.max_tokens) == (1.0, 20, 0.95, 9) and p.top_k is None
+    assert GenerationConfig().fill(p) is p
+    # EOS ids: config.json's first, then what only the generation config names
+    assert join_eos((3,), g) == (3, 7) and join_eos((), g) == (7, 3) and join_eos((4,), None) == (4,)
+    for bad in ({"temperature": "hot"}, {"top_k": 2.5}, {"eos_token_id": "x"}, {"top_p": True}):
+        (tmp_path / "generation_config.json").write_text(json.dumps(bad))
+        with pytest.raises(ConfigError):
+            GenerationConfig.load(str(tmp_path))
+    (tmp_path / "generation_config.json").write_text("{ not json")
+    with pytest.raises(ConfigError):
+        GenerationConfig.load(str(tmp_path))

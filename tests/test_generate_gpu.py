@@ -332,6 +332,37 @@ def test_a_stream_can_be_cancelled_and_stop_sequences_end_a_request(model_folder
     assert eng.runner.cache.live_requests() == 0 and eng.runner.cache.free_pages() == 64 and not eng.has_work()
     # a stop sequence of two ids: the request ends when the generated tokens end with it; its last token stays out
     stop = free[6:8]
-    o = eng.generate_sync(SamplingParams(max_tokens=14, ignore_eos=True, stop_token_ids=[[free[2], free[2] + 1], stop]), [p])[0]
+    o = eng.generate_sync(SamplingParams(max_tokens=14, ignore_eos=True, stop_token_ids=[[free[2], (free[2] + 1) % 256], stop]), [p])[0]
     first = next(i for i in range(1, 14) if free[i - 1:i + 1] == stop)
     assert o.finish_reason == "stop" and o.decode_output == free[:first]
+
+
+def test_generation_config_of_the_folder_and_of_the_engine(model_folders, tmp_path):
+    import json
+    import shutil
+    from xinfer_b200 import GenerationConfig, SamplingParams
+    src = model_folders("A", torch.float32)
+    cfg, w = plain.load_folder(src)
+    p = prompts_for("A", [9], seed=11)[0]
+    free = plain.generate(cfg, w, p, 12)
+    folder = str(tmp_path / "with_generation_config")
+    shutil.copytree(src, folder)
+    stop_at = next(i for i in range(3, 12) if free[i] not in free[:i])      # a token that generation meets there first
+    with open(folder + "/generation_config.json", "w") as f:
+        json.dump({"temperature": 5.0, "top_k": 1, "eos_token_id": [free[stop_at]]}, f)
+    eng = engine(folder, "f32", "A")
+    assert eng.eos_token_ids[-1] == free[stop_at] and eng.generation_cfg.top_k == 1
+    # a request that sets nothing takes the folder's options: the one most likely token at any temperature,
+    # until the folder's extra EOS id comes (it stays out of the output)
+    o = eng.generate_sync(SamplingParams(max_tokens=12), [p])[0]
+    assert o.decode_output == free[:stop_at] and o.finish_reason == "stop"
+    o = eng.generate_sync(SamplingParams(max_tokens=12, ignore_eos=True), [p])[0]
+    assert o.decode_output == free
+    # the engine's own options come before the folder's: top-k off, so temperature 5 draws from nearly all tokens
+    eng2 = engine(folder, "f32", "A", generation_cfg=GenerationConfig(top_k=0))
+    assert (eng2.generation_cfg.temperature, eng2.generation_cfg.top_k) == (5.0, 0)
+    o = eng2.generate_sync(SamplingParams(max_tokens=12, ignore_eos=True, seed=3), [p])[0]
+    assert o.decode_output != free
+    # and a request's own options before both
+    o = eng2.generate_sync(SamplingParams(max_tokens=12, ignore_eos=True, temperature=0.0), [p])[0]
+    assert o.decode_output == free

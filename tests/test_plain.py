@@ -63,8 +63,9 @@ def _weights(name, dtype):
     from xinfer_b200.config import Qwen3Config
     from xinfer_b200.models import model_weight_specs
     from xinfer_b200.weights import draw
-    from helpers import sharpen
+    from helpers import sharpen_for
     cfg, seed = TINY[name]
+    sharpen = sharpen_for(cfg)
     w = {}
     for s in model_weight_specs(Qwen3Config.from_dict(cfg).plan()):
         t = draw(s, seed, 0.02, 0.1, torch.float32)

@@ -4,7 +4,7 @@ Public entry points, in the manner of the reference's Python package (xinfer.pyi
 ``Engine(EngineConfig, dtype)`` with ``generate_sync`` / ``generate_stream``, ``SamplingParams``,
 ``GenerationOutput``; plus ``ModelRunner.step`` for callers that drive steps themselves.
 """
-from .config import EngineConfig, Qwen3Config, ConfigError, register_architecture
+from .config import EngineConfig, GenerationConfig, Qwen3Config, ConfigError, register_architecture
 
 __version__ = "0.1.0"
 
@@ -23,5 +23,5 @@ def __getattr__(name):
     raise AttributeError(f"module 'xinfer_b200' has no attribute '{name}'")
 
 
-__all__ = ["EngineConfig", "Qwen3Config", "ConfigError", "register_architecture", "Engine",
+__all__ = ["EngineConfig", "GenerationConfig", "Qwen3Config", "ConfigError", "register_architecture", "Engine",
            "GenerationOutput", "StreamItem", "SamplingParams", "ModelRunner", "StepInput", "StepError"]

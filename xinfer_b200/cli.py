@@ -80,7 +80,7 @@ def main(argv: Optional[List[str]] = None) -> int:
         return 0
 
     import numpy as np
-    from . import Engine, EngineConfig, SamplingParams
+    from . import Engine, EngineConfig, GenerationConfig, SamplingParams
     from .config import load_config
 
     if args.prompts:
@@ -91,8 +91,13 @@ def main(argv: Optional[List[str]] = None) -> int:
         prompts = [rng.integers(0, cfg.vocab_size, size=args.prompt_len or 16).tolist()]
     if args.batch:
         prompts = [prompts[0]] * args.batch
+    # sampling flags make the engine's default options, as in the reference (src/main.rs:117-135); they come
+    # before those of the folder's generation_config.json
+    flags = dict(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
+                 frequency_penalty=args.frequency_penalty, presence_penalty=args.presence_penalty)
+    generation_cfg = GenerationConfig(**flags) if any(v is not None for v in flags.values()) else None
     econfig = EngineConfig(
-        weight_path=folder, block_size=args.block_size, num_blocks=args.num_blocks,
+        weight_path=folder, generation_cfg=generation_cfg, block_size=args.block_size, num_blocks=args.num_blocks,
         kv_fraction=args.kv_fraction, max_num_seqs=args.max_num_seqs or max(len(prompts), 1),
         max_num_batched_tokens=args.max_num_batched_tokens, prefill_chunk_size=args.prefill_chunk_size,
         max_model_len=args.max_model_len, max_tokens=args.max_tokens, seed=args.seed,
@@ -101,9 +106,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     t0 = time.time()
     engine = Engine(econfig, args.dtype)
     print(f"model loaded in {time.time() - t0:.1f} s; cache holds {engine.runner.kv_cache_tokens()} tokens", file=sys.stderr)
-    params = SamplingParams(temperature=args.temperature, max_tokens=args.max_tokens, ignore_eos=args.ignore_eos,
-                            top_k=args.top_k, top_p=args.top_p, frequency_penalty=args.frequency_penalty,
-                            presence_penalty=args.presence_penalty)
+    params = SamplingParams(max_tokens=args.max_tokens, ignore_eos=args.ignore_eos)
     outs = engine.generate_sync(params, prompts)
     for o in outs:
         print(f"[seq {o.seq_id}] prompt {o.prompt_length} tokens -> {o.decoded_length} tokens ({o.finish_reason}): "

@@ -5,6 +5,8 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Optional
 
+from .generation import GenerationConfig
+
 
 @dataclass
 class EngineConfig:
@@ -27,6 +29,9 @@ class EngineConfig:
     # default for SamplingParams.max_tokens
     max_tokens: Optional[int] = None
     seed: Optional[int] = None
+    # defaults for the sampling options a request leaves unset; they come before those of the model folder's
+    # generation_config.json, field by field (the reference's `generation_cfg`)
+    generation_cfg: Optional[GenerationConfig] = None
     disable_cuda_graph: bool = False
     # decide and queue the next decode step while the current one runs (the device then does not
     # wait for the host between steps); off: every step waits for its tokens before the next is decided

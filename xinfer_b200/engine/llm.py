@@ -14,6 +14,7 @@ the reason and keeps its loop alive (src/core/engine.rs:2392-2408).
 """
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import dataclass
 from typing import Dict, Iterator, List, Optional, Sequence, Tuple, Union
@@ -22,6 +23,7 @@ import numpy as np
 import torch
 
 from ..config import EngineConfig
+from ..config.generation import GenerationConfig, join_eos
 from ..sampling import SamplingParams
 from ..sampling.sampler import PENALTY_HISTORY, Sampler
 from .runner import ModelRunner, StepError, StepInput
@@ -132,11 +134,16 @@ class Engine:
             max_num_seqs=econfig.max_num_seqs, kv_fraction=econfig.kv_fraction, device=econfig.device,
             max_model_len=econfig.max_model_len, poison_freed_pages=econfig.poison_freed_pages)
         self.max_model_len = self.runner.max_model_len
+        # defaults for what a request leaves unset: the engine's own, then the model folder's generation_config.json
+        folder = econfig.weight_path or econfig.model_id
+        from_folder = GenerationConfig.load(folder) if folder and os.path.isdir(folder) else None
+        self.generation_cfg = econfig.generation_cfg.over(from_folder) if econfig.generation_cfg is not None else from_folder
+        self.eos_token_ids = join_eos(self.runner.plan.eos_token_ids, from_folder)
         budget = min(econfig.max_num_batched_tokens, max(self.runner.kv_cache_tokens(), 1))
         self.scheduler = Scheduler(
             self.runner.cache, max_num_seqs=econfig.max_num_seqs, max_num_batched_tokens=budget,
             prefill_chunk_size=econfig.prefill_chunk_size, max_model_len=self.max_model_len,
-            eos_token_ids=self.runner.plan.eos_token_ids)
+            eos_token_ids=self.eos_token_ids)
         # two sets of pinned buffers (two batches can be in flight); both leave their ids in the runner's
         # buffer, where the step after reads them on the device
         self.samplers = [Sampler(self.runner.device, econfig.max_num_seqs, out_dev=self.runner.sampled_tokens,
@@ -158,6 +165,8 @@ class Engine:
     # ---- admission ------------------------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
         params = params or SamplingParams()
+        if self.generation_cfg is not None:
+            params = self.generation_cfg.fill(params)
         params.validate()
         prompt = [int(t) for t in prompt]
         V = self.runner.plan.vocab_size
