@@ -47,3 +47,38 @@ def test_random_workload_equals_plain(trial, model_folders):
         assert out.error is None and out.decode_output == want, (name, i, out.finish_reason)
     eng.runner.cache.check_consistent()
     assert eng.runner.cache.free_pages() == pages and eng.runner.cache.live_requests() == 0
+
+
+def test_the_same_wave_again_gives_the_same_tokens_and_holds_no_more_memory(model_folders):
+    # bfloat16 with CUDA graphs and steps decided ahead: five times the same twelve requests (temperature and
+    # greedy, arriving while others run) through one engine.  From the second wave on everything is reused -
+    # pages that others have held, captured graphs, workspaces, samplers' buffers - so the tokens must be those
+    # of the first wave, and the device memory in use must stay where the first wave left it.
+    from xinfer_b200 import Engine, EngineConfig, SamplingParams
+    cfg, _ = TINY["B"]
+    folder = model_folders("B", torch.bfloat16)
+    page = PAGE_SIZE["B"]
+    eng = Engine(EngineConfig(weight_path=folder, block_size=page, num_blocks=24, max_num_seqs=4, max_num_batched_tokens=64,
+                              prefill_chunk_size=24), "bf16")
+    waves, held = [], []
+    for wave in range(5):
+        rng = np.random.default_rng(99)
+        prompts = [rng.integers(0, cfg["vocab_size"], size=int(rng.integers(1, 70))).tolist() for _ in range(12)]
+        params = [SamplingParams(temperature=float(rng.choice([0.0, 0.9])), max_tokens=int(rng.integers(2, 40)), ignore_eos=True,
+                                 seed=int(rng.integers(0, 1000))) for _ in range(12)]
+        pending, ids = list(range(12)), {}
+        while pending or eng.has_work():
+            while pending and (rng.random() < 0.4 or not eng.has_work()):
+                i = pending.pop(0)
+                ids[eng.add_request(prompts[i], params[i])] = i
+            eng.step()
+        outs = {i: eng._done.pop(sid) for sid, i in ids.items()}
+        assert all(o.error is None and o.decoded_length == params[i].max_tokens for i, o in outs.items())
+        waves.append([outs[i].decode_output for i in range(12)])
+        torch.cuda.synchronize()
+        held.append(torch.cuda.memory_allocated())
+        eng.runner.cache.check_consistent()
+        assert eng.runner.cache.free_pages() == 24 and eng.runner.cache.live_requests() == 0
+    assert all(w == waves[0] for w in waves[1:])
+    assert held[1:] == [held[1]] * 4 and held[1] <= held[0] + (1 << 20), held
+    assert eng.stats["preemptions"] > 0 and eng.stats["steps_decided_ahead"] > 0, eng.stats     # the waves met both
