@@ -226,6 +226,8 @@ def main() -> int:
                     help="instead of the step benchmark: a decode step with one kind of kernel left out at a time (what each kind costs in the chain)")
     ap.add_argument("--attn", default="", metavar="HEADS,KV_HEADS,HEAD_DIM[,PAGE_SIZE]",
                     help="with --kernels: the attention kernels alone at this head layout, over short and long contexts")
+    ap.add_argument("--case", default="", metavar="decode:BATCHxCONTEXT | prefill:CACHED+NEW",
+                    help="with --kernels --attn: this one case instead of the standard ones")
     ap.add_argument("--kernels", action="store_true",
                     help="instead of the step benchmark, time single kernels at serving sizes: one JSON line each")
     args = ap.parse_args()
@@ -246,8 +248,17 @@ def main() -> int:
         pk = peaks()
         sizes = [int(x) for x in args.attn.split(",")]
         lay = dict(heads=sizes[0], kv_heads=sizes[1], head_dim=sizes[2], page_size=sizes[3] if len(sizes) > 3 else PAGE)
-        for rec in (measure.decode_attention(((1, 4096), (8, 4096), (64, 2048), (4, 65536), (16, 512)), hbm_gbs=pk["hbm_gbs"], **lay)
-                    + measure.prefill_attention(((0, 512), (0, 2048), (0, 8192), (30000, 2048)), peak_tflops=pk["bf16_tflops"], **lay)):
+        decode_cases, prefill_cases = ((1, 4096), (8, 4096), (64, 2048), (4, 65536), (16, 512)), ((0, 512), (0, 2048), (0, 8192), (30000, 2048))
+        if args.case:      # one case alone (its first launch is a plain one: what a profiler is pointed at)
+            kind, _, size = args.case.partition(":")
+            if kind == "decode":
+                decode_cases, prefill_cases = (tuple(int(x) for x in size.split("x")),), ()
+            elif kind == "prefill":
+                decode_cases, prefill_cases = (), (tuple(int(x) for x in size.split("+")),)
+            else:
+                raise SystemExit("bench.py: --case is decode:BATCHxCONTEXT or prefill:CACHED+NEW")
+        for rec in (measure.decode_attention(decode_cases, hbm_gbs=pk["hbm_gbs"], **lay)
+                    + measure.prefill_attention(prefill_cases, peak_tflops=pk["bf16_tflops"], **lay)):
             print(json.dumps(dict(rec, **lay)), flush=True)
         return 0
     if args.kernels:
