@@ -387,8 +387,9 @@ def main() -> int:
     # the prompts' prefill leaves the device at its power cap for some tens of milliseconds: decode steps
     # run untimed until the clocks have come back
     e2e_warmup = warmup + SETTLE
-    prompt_len = args.context - n_e2e - e2e_warmup - 16
-    sp = SamplingParams(temperature=0.0, max_tokens=n_e2e + e2e_warmup + 64, ignore_eos=True)
+    margin = B // 2 + 8
+    prompt_len = args.context - n_e2e - e2e_warmup - margin - 8     # prompt + max_tokens stays inside a request's pages
+    sp = SamplingParams(temperature=0.0, max_tokens=n_e2e + e2e_warmup + margin, ignore_eos=True)
     for _ in range(B):
         engine.add_request(rng.integers(0, V, size=prompt_len).tolist(), sp)
     while any(engine.scheduler.output(i) == [] for i in list(engine._live)):   # prompts, first tokens
