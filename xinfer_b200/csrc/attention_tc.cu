@@ -156,7 +156,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const bool is_v = warp == 10;
         const uint32_t full0 = is_v ? v_full0 : k_full0, empty0 = is_v ? v_empty0 : k_empty0;
         const CUtensorMap* map = is_v ? &map_v : &map_k;
-        int T = 0;   // tiles of the items before this one
+        int s = 0;            // the ring stage of the next tile, over all items
+        uint32_t ph = 0;      // parity of the number of times the ring has been gone round
+        bool rounds = false;  // it has been gone round at least once
         bool ok = true;
         for (int k = item_begin; k < item_end && ok; ++k) {
             const PrefillItem w = item_at(k);
@@ -174,9 +176,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             };
             int page_next = page_of(0);
             for (int it = 0; it < w.iters; ++it) {
-                const int gt = T + it, s = gt % NS;
                 const int page = page_next;
-                if (gt >= NS && !__all_sync(0xffffffffu, mbar_wait(empty0 + 8 * s, ((gt / NS) - 1) & 1, err))) {
+                // s = (tiles so far) % NS and the parity of their quotient run along: no division per tile
+                if (rounds && !__all_sync(0xffffffffu, mbar_wait(empty0 + 8 * s, ph ^ 1u, err))) {
                     words[3] = 1;
                     ok = false;
                     break;
@@ -190,8 +192,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     tma_load_2d(dst, map, hf * 64, (page * nkv + w.g) * ps + (j & (ps - 1)), full0 + 8 * s);
                 }
                 page_next = page_of(it + 1);
+                if (++s == NS) {
+                    s = 0;
+                    ph ^= 1u;
+                    rounds = true;
+                }
             }
-            T += w.iters;
         }
     } else if (warp == 9) {
         // ---- Q loads and S = Q K^T, both heads, tile after tile, item after item -----------------------------
@@ -205,7 +211,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     for (int hf = 0; hf < HALVES; ++hf)
                         tma_load_3d(q_sm + hd * Q_ONE + hf * QT * 128, &map_q, hf * 64, w.h0 + hd, w.t0, q_full);
             };
-            int T = 0, Th[2] = {0, 0};
+            int s = 0, Th[2] = {0, 0};   // ring stage of the next tile (over all items), tiles of each head so far
+            uint32_t ph = 0;               // parity of the times the ring has been gone round
             bool ok = true;
             PrefillItem w = item_at(item_begin);
             load_q(w);
@@ -213,8 +220,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 const int I = k - item_begin;
                 ok = mbar_wait(q_full, (uint32_t)I & 1u, err, true);
                 for (int it = 0; it < w.iters && ok; ++it) {
-                    const int gt = T + it, s = gt % NS;
-                    ok = mbar_wait(k_full0 + 8 * s, (gt / NS) & 1, err, true);
+                    ok = mbar_wait(k_full0 + 8 * s, ph, err, true);
                     const uint64_t dk = dk0 + (uint64_t)((s * STAGE_BYTES) >> 4);
 #pragma unroll
                     for (int hd = 0; hd < 2; ++hd) {
@@ -235,9 +241,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     }
                     if (!ok) break;
                     umma_commit(k_empty0 + 8 * s);   // the key stage is free once both products have completed
+                    if (++s == NS) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
                 }
                 if (!ok) break;
-                T += w.iters;
                 Th[0] += w.iters;
                 if (w.nhd == 2) Th[1] += w.iters;
                 if (k + 1 < item_end) {
@@ -257,13 +266,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (lane == 0) {
             const uint32_t idesc_o = umma_idesc(DP, 1);
             const uint64_t dv0 = umma_desc(kv_sm + KV_BYTES, KV_HALF, 1024);
-            int T = 0, Th[2] = {0, 0};
+            int s = 0, Th[2] = {0, 0};   // ring stage of the next tile (over all items), tiles of each head so far
+            uint32_t ph = 0;               // parity of the times the ring has been gone round
             bool ok = true;
             for (int k = item_begin; k < item_end && ok; ++k) {
                 const PrefillItem w = item_at(k);
                 for (int it = 0; it < w.iters && ok; ++it) {
-                    const int gt = T + it, s = gt % NS;
-                    ok = mbar_wait(v_full0 + 8 * s, (gt / NS) & 1, err, true);
+                    ok = mbar_wait(v_full0 + 8 * s, ph, err, true);
                     const uint64_t dv = dv0 + (uint64_t)((s * STAGE_BYTES) >> 4);
 #pragma unroll
                     for (int hd = 0; hd < 2; ++hd) {
@@ -284,8 +293,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     if (!ok) break;
                     umma_commit(v_empty0 + 8 * s);           // and so is the value stage
                     if (it + 1 == w.iters) umma_commit(bar_o);
+                    if (++s == NS) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
                 }
-                T += w.iters;
                 Th[0] += w.iters;
                 if (w.nhd == 2) Th[1] += w.iters;
             }

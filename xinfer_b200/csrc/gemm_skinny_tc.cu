@@ -130,21 +130,28 @@ gemm_skinny_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         pdl_wait();
         for (int it = 0; it < pre; ++it)
             tma_load_2d(base + it * stage_bytes + w_bytes, &map_x, k_begin + it * TILE_K, 0, full0 + 8 * it);
+        // stage and phase run along with `it` (it % stages, (it / stages) & 1): no division in this thread's loop
+        int s = pre == stages ? 0 : pre;
+        uint32_t phase = pre == stages ? 1u : 0u;
         for (int it = pre; it < iters; ++it) {
-            const int s = it % stages;
-            if (!mbar_wait(empty0 + 8 * s, ((it / stages) & 1) ^ 1, err)) break;
+            if (!mbar_wait(empty0 + 8 * s, phase ^ 1u, err)) break;
             const uint32_t dst = base + s * stage_bytes;
             mbar_expect_tx(full0 + 8 * s, stage_bytes);
             load_w(dst, k_begin + it * TILE_K, full0 + 8 * s);
             tma_load_2d(dst + w_bytes, &map_x, k_begin + it * TILE_K, 0, full0 + 8 * s);
+            if (++s == stages) {
+                s = 0;
+                phase ^= 1u;
+            }
         }
     } else if (threadIdx.x == 32) {
         // ---- MMA issuer -------------------------------------------------------------------------------
         const uint32_t idesc = umma_idesc(mp);
         bool ok = true;
+        int s = 0;
+        uint32_t phase = 0;
         for (int it = 0; it < iters && ok; ++it) {
-            const int s = it % stages;
-            ok = mbar_wait(full0 + 8 * s, (it / stages) & 1, err);
+            ok = mbar_wait(full0 + 8 * s, phase, err);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t a = base + s * stage_bytes;
@@ -153,6 +160,10 @@ gemm_skinny_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             for (int kk = 0; kk < TILE_K / 16; ++kk)   // 16 K elements = 32 bytes further along the swizzle row
                 umma_bf16(tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc, (it | kk) ? 1u : 0u);
             umma_commit(empty0 + 8 * s);   // the stage is free once these MMAs have read it
+            if (++s == stages) {
+                s = 0;
+                phase ^= 1u;
+            }
         }
         umma_commit(accum);                 // arrives when every MMA issued so far is complete
     }
