@@ -283,10 +283,13 @@ def main() -> int:
     if args.workload == "mixed":
         return mixed_workload(args, cfg, full, pk)
     max_b = args.batch if args.no_points else max(args.batch, 64)
-    pages_per_req = (args.context + PAGE - 1) // PAGE + 1
+    if args.context < 256:
+        raise SystemExit("bench.py: --context must be at least 256")
+    longest = max(args.context, PREFILL_TOKENS + 256)     # the prefill measurement and the reference's decode setting need their room
+    pages_per_req = (longest + PAGE - 1) // PAGE + 1
     t_load = time.time()
     runner = ModelRunner.random(cfg, seed=0, dtype="bfloat16", block_size=PAGE, num_blocks=max_b * pages_per_req,
-                                max_num_seqs=max_b, max_model_len=args.context + 64)
+                                max_num_seqs=max_b, max_model_len=longest + 64)
     torch.cuda.synchronize()
     load_s = time.time() - t_load
     rng = np.random.default_rng(0)
@@ -379,7 +382,7 @@ def main() -> int:
 
     # ---- the same through the Python entry point ----------------------------------------------------------
     econfig = EngineConfig(weight_path="(random)", block_size=PAGE, max_num_seqs=max_b, max_num_batched_tokens=8192,
-                           prefill_chunk_size=4096, max_model_len=args.context + 64, disable_cuda_graph=not use_graph)
+                           prefill_chunk_size=4096, max_model_len=longest + 64, disable_cuda_graph=not use_graph)
     engine = Engine(econfig, "bf16", runner=runner)
     n_e2e = min(steps, 64)
     # prompts are prefilled two per step, so requests start decoding a few steps apart: leave room
