@@ -98,3 +98,33 @@ def test_one_sampler_over_shrinking_and_growing_batches(mode):
         want = [plain.sample(logits[r], p.temperature or 0.0, top_k=p.top_k or 0,
                              top_p=p.top_p if p.top_p is not None else 1.0, seed=seeds[r], draw=draw) for r in range(R)]
         assert got == want, (R, got, want)
+
+
+@pytest.mark.parametrize("rows", [3, 40])
+def test_top_k_on_shapes_of_logits_that_defeat_a_threshold(rows):
+    # the chunk's largest are found through a threshold taken from the threads' maxima; these rows make that
+    # threshold useless or the gathered set huge (plateaus, sorted rows, nearly everything minus infinity, all large values behind one thread),
+    # in chunks that fit the shared memory (3 rows) and in chunks that do not (40 rows)
+    from xinfer_b200.sampling import SamplingParams
+    vocab = 151936
+    rng = np.random.default_rng(rows)
+    base = (rng.normal(size=vocab) * 3).astype(np.float32)
+    shapes = [
+        np.zeros(vocab, dtype=np.float32),                                   # all equal: the lowest indices win
+        np.sort(base),                                                        # ascending
+        np.sort(base)[::-1].copy(),                                           # descending
+        np.where(rng.random(vocab) < 0.05, np.float32(9.0), base),            # a plateau of 7,600 equal maxima
+        np.where(rng.random(vocab) < 0.0002, base, np.float32(-np.inf)),      # about 30 finite values
+        np.where(np.arange(vocab) % 1024 == 5, base + 30, base),              # every large value in one thread's elements
+        np.round(base),                                                       # seven or so distinct values
+    ]
+    combos = [(20, 0.95), (1, None), (256, None), (257, 0.9), (None, 0.8), (1000, None), (64, 0.5)]
+    logits = np.stack([shapes[r % len(shapes)] for r in range(rows)]).astype(np.float32)
+    for shift in range(len(combos) if rows == 3 else 2):
+        use = [combos[(r + shift) % len(combos)] for r in range(rows)]
+        params = [SamplingParams(temperature=0.8, top_k=k, top_p=p) for k, p in use]
+        seeds = list(range(7, 7 + rows))
+        got = run(logits, params, seeds, [shift] * rows)
+        want = [plain.sample(logits[r], 0.8, top_k=use[r][0] or 0, top_p=use[r][1] if use[r][1] is not None else 1.0,
+                             seed=seeds[r], draw=shift) for r in range(rows)]
+        assert got == want, (shift, got, want)

@@ -125,8 +125,132 @@ __device__ __forceinline__ unsigned long long key_of(float v, int i) {
     return ((unsigned long long)float_key(v) << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)i);
 }
 
-#define XB_SAMPLE_CHUNK_SMEM 8192   // values of a chunk that are kept in shared memory
+#define XB_SAMPLE_CHUNK_SMEM 6144   // values of a chunk that are kept in shared memory
+#define XB_SAMPLE_POOL 1024         // keys above a chunk's first threshold that are kept in shared memory
 #define XB_SAMPLE_CHUNKS_MAX 64
+
+// The `need`-th largest of the n unique 64-bit keys key_at(0) .. key_at(n - 1), or a lower bound of it
+// above the next smaller key: `key >= result` holds for exactly the `need` largest (need <= n).  A radix
+// select from the top byte down; the whole block takes part (blockDim.x a multiple of 32).  The
+// passes end as soon as a bin is needed whole, which for float keys with an index below them is after
+// the float's bytes at the latest in practice.
+struct SelectShared {
+    unsigned int hist[256];
+    unsigned long long prefix;
+    int need, done;
+};
+template <typename KeyAt>
+__device__ __forceinline__ unsigned long long select_kth(int n, int need, KeyAt key_at, SelectShared& sh) {
+    const int tid = threadIdx.x, lane = tid & 31;
+    if (tid == 0) {
+        sh.prefix = 0ull;
+        sh.need = need;
+        sh.done = 0;
+    }
+    __syncthreads();
+    for (int pass = 7; pass >= 0; --pass) {
+        if (tid < 256) sh.hist[tid] = 0u;
+        __syncthreads();
+        const unsigned long long prefix = sh.prefix;
+        const int shift = pass * 8;
+        for (int base = 0; base < n; base += blockDim.x) {   // the same trips for every thread: the match below is warp-wide
+            const int i = base + tid;
+            unsigned int bin = 256u + (unsigned)lane;        // matches no other lane
+            if (i < n) {
+                const unsigned long long key = key_at(i);
+                if (pass == 7 || (key >> (shift + 8)) == (prefix >> (shift + 8))) bin = (unsigned)(key >> shift) & 255u;
+            }
+            // the lanes that share the first lane's bin add as one; the others each for themselves
+            const unsigned int first = __shfl_sync(0xffffffffu, bin, 0);
+            const unsigned int same = __ballot_sync(0xffffffffu, bin == first);
+            if (bin == first) {
+                if (lane == 0 && bin < 256u) atomicAdd(&sh.hist[bin], (unsigned)__popc(same));
+            } else if (bin < 256u) {
+                atomicAdd(&sh.hist[bin], 1u);
+            }
+        }
+        __syncthreads();
+        if (tid < 32) {
+            // the bin in which the count, summed from the top bin down, reaches what is still needed:
+            // lane l holds bins 255 - 8l down to 248 - 8l
+            unsigned int c[8], sum = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                c[j] = sh.hist[255 - (8 * lane + j)];
+                sum += c[j];
+            }
+            unsigned int incl = sum;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned int t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t;
+            }
+            const unsigned int want = (unsigned int)sh.need, excl = incl - sum;
+            const bool here = excl < want && (incl >= want || lane == 31);
+            __syncwarp();
+            if (here) {
+                unsigned int rem = want - excl;
+                int bin = 0;
+                bool whole = false;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int b = 255 - (8 * lane + j);
+                    if (c[j] >= rem || b == 0) {
+                        bin = b;
+                        whole = c[j] == rem;   // every key of this bin is wanted: the bytes below decide nothing
+                        break;
+                    }
+                    rem -= c[j];
+                }
+                sh.need = (int)rem;
+                sh.prefix = prefix | ((unsigned long long)bin << shift);
+                sh.done = whole ? 1 : 0;
+            }
+        }
+        __syncthreads();
+        if (sh.done) break;
+    }
+    return sh.prefix;
+}
+
+#define XB_SAMPLE_FEW 64   // up to this many wanted keys are found through the maxima of groups of four threads
+
+// A threshold that at least n of the block's keys reach (one key per thread, 0: none), found without
+// counting them all: the n-th largest of the maxima of the 256 groups of four adjacent threads (each is
+// one of the keys, so n keys are >= it; and a group's maximum is a rare value, so not many more are).
+// 0 when fewer than n groups hold a key: then every key is wanted.  blockDim.x must be 1024.
+__device__ __forceinline__ unsigned long long group_threshold(unsigned long long mine, int n, unsigned long long* gmax /* [256] */,
+                                                              unsigned long long* s_t) {
+    unsigned long long g = mine, o;
+    o = __shfl_xor_sync(0xffffffffu, g, 1);
+    g = o > g ? o : g;
+    o = __shfl_xor_sync(0xffffffffu, g, 2);
+    g = o > g ? o : g;
+    __syncthreads();   // whoever read gmax or s_t before is done
+    if ((threadIdx.x & 3) == 0) gmax[threadIdx.x >> 2] = g;
+    if (threadIdx.x == 0) *s_t = 0ull;
+    __syncthreads();
+    if (threadIdx.x < 256) {
+        const unsigned long long me = gmax[threadIdx.x];
+        int larger = 0;
+#pragma unroll 8
+        for (int j = 0; j < 256; ++j) larger += gmax[j] > me ? 1 : 0;
+        if (me != 0ull && larger == n - 1) *s_t = me;   // keys are unique: one group at most
+    }
+    __syncthreads();
+    return *s_t;
+}
+
+// The `n` largest of pool[0 .. m), in descending order, to dst[0 .. n): every key is placed by the number of
+// keys above it (m is small: a few times n).  Keys are unique.
+__device__ __forceinline__ void place_largest(const unsigned long long* pool, int m, int n, unsigned long long* dst, bool write) {
+    for (int i = threadIdx.x; i < m; i += blockDim.x) {
+        const unsigned long long me = pool[i];
+        int larger = 0;
+        for (int j = 0; j < m; ++j) larger += pool[j] > me ? 1 : 0;
+        if (write && larger < n) dst[larger] = me;
+    }
+}
 
 // Scratch of the sampler, per row: a candidate counter and a ticket (both zero between launches),
 // candidate keys, partial results of the chunks.  The arrays are laid out for the buffer's capacity
@@ -150,11 +274,13 @@ sample_kernel(int* __restrict__ out_tokens, const float* __restrict__ logits, co
     // itself reports reaches the host with the next one)
     if (err_word != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) out_tokens[gridDim.y] = *err_word;
     __shared__ Best sbest[32];
-    __shared__ unsigned int hist[256];
+    __shared__ SelectShared sel;
     __shared__ unsigned long long cand_key[XB_TOPK_MAX];
     __shared__ float cand_p[XB_TOPK_MAX];
-    __shared__ float s_vals[XB_SAMPLE_CHUNK_SMEM];
-    __shared__ unsigned long long s_prefix;
+    __shared__ __align__(8) float s_vals[XB_SAMPLE_CHUNK_SMEM];
+    __shared__ unsigned long long pool[XB_SAMPLE_POOL];
+    __shared__ unsigned long long gmax[256];
+    __shared__ unsigned long long s_t;
     __shared__ int s_need, s_base, s_keep, s_last;
 
     const int r = blockIdx.y;
@@ -194,66 +320,54 @@ sample_kernel(int* __restrict__ out_tokens, const float* __restrict__ logits, co
         b = block_best(b, sbest);
         if (threadIdx.x == 0) sc.part[(size_t)r * XB_SAMPLE_CHUNKS_MAX + blockIdx.x] = b;
     } else {
-        // ---- the chunk's k largest by (value, then lower index): radix select on 64-bit keys ------------
+        // ---- the chunk's k largest by (value, then lower index) --------------------------------------------
+        // Few wanted among many: every thread keeps the largest key of the elements it reads; the kc-th
+        // largest of those 1024 maxima is a threshold T that at least kc elements reach, so the chunk's kc
+        // largest are among the elements >= T - about kc of them, since a thread's maximum is a rare value.
+        // They are gathered in shared memory and the kc-th is selected among them.  The chunk is read
+        // twice and counted once.  Otherwise (many wanted, or more than the pool holds reached T): a radix
+        // select over the whole chunk.
         const int n_chunk = hi - lo;
         const bool cached = n_chunk <= XB_SAMPLE_CHUNK_SMEM;
-        if (cached)
-            for (int i = threadIdx.x; i < n_chunk; i += blockDim.x) s_vals[i] = row[lo + i];
         const int kc = min(k, n_chunk);
-        if (threadIdx.x == 0) {
-            s_prefix = 0ull;
-            s_need = kc;
+        unsigned long long mine = 0ull;   // below every key: a key's low half is 2^32 - 1 - index > 0
+        for (int i = threadIdx.x; i < n_chunk; i += blockDim.x) {
+            const float v = row[lo + i];
+            if (cached) s_vals[i] = v;
+            const unsigned long long key = key_of(v, lo + i);
+            mine = key > mine ? key : mine;
         }
+        auto key_at = [&](int i) { return key_of(cached ? s_vals[i] : row[lo + i], lo + i); };
+        const int holders = min(n_chunk, (int)blockDim.x);   // threads that read an element
+        bool gathered = kc <= XB_SAMPLE_POOL / 4 && holders >= 4 * kc;
+        const bool few = gathered && kc <= XB_SAMPLE_FEW;
+        unsigned long long kth = 0ull;
+        int pooled = 0;
+        if (gathered) {
+            unsigned long long T;
+            if (few) {
+                T = group_threshold(mine, kc, gmax, &s_t);
+                if (T == 0ull) T = 1ull;    // fewer groups than wanted keys hold any: every element (keys are >= 1)
+            } else {
+                cand_key[threadIdx.x] = mine;   // (free until the row's last CTA needs it)
+                T = select_kth(holders, kc, [&](int i) { return cand_key[i]; }, sel);
+            }
+            if (threadIdx.x == 0) s_need = 0;
+            __syncthreads();
+            for (int i = threadIdx.x; i < n_chunk; i += blockDim.x) {
+                const unsigned long long key = key_at(i);
+                if (key >= T) {
+                    const int at = atomicAdd(&s_need, 1);
+                    if (at < XB_SAMPLE_POOL) pool[at] = key;
+                }
+            }
+            __syncthreads();
+            pooled = s_need;
+            gathered = pooled <= XB_SAMPLE_POOL;
+            if (gathered && !few) kth = pooled > kc ? select_kth(pooled, kc, [&](int i) { return pool[i]; }, sel) : T;
+        }
+        if (!gathered) kth = select_kth(n_chunk, kc, key_at, sel);   // keys of the chunk's kc largest are >= kth; keys are unique
         __syncthreads();
-        for (int pass = 7; pass >= 0; --pass) {
-            if (threadIdx.x < 256) hist[threadIdx.x] = 0u;
-            __syncthreads();
-            const unsigned long long prefix = s_prefix;
-            const int shift = pass * 8;
-            for (int i = lo + (int)threadIdx.x; i < hi; i += blockDim.x) {
-                const unsigned long long key = key_of(cached ? s_vals[i - lo] : row[i], i);
-                if (pass == 7 || (key >> (shift + 8)) == (prefix >> (shift + 8)))
-                    atomicAdd(&hist[(unsigned)(key >> shift) & 255u], 1u);
-            }
-            __syncthreads();
-            if (threadIdx.x < 32) {
-                // the bin in which the count, summed from the top bin down, reaches what is still needed:
-                // lane l holds bins 255 - 8l down to 248 - 8l
-                const int lane = threadIdx.x;
-                unsigned int c[8], sum = 0;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    c[j] = hist[255 - (8 * lane + j)];
-                    sum += c[j];
-                }
-                unsigned int incl = sum;
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const unsigned int t = __shfl_up_sync(0xffffffffu, incl, o);
-                    if (lane >= o) incl += t;
-                }
-                const unsigned int need = (unsigned int)s_need, excl = incl - sum;
-                const bool here = excl < need && (incl >= need || lane == 31);
-                __syncwarp();
-                if (here) {
-                    unsigned int rem = need - excl;
-                    int bin = 0;
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int b = 255 - (8 * lane + j);
-                        if (c[j] >= rem || b == 0) {
-                            bin = b;
-                            break;
-                        }
-                        rem -= c[j];
-                    }
-                    s_need = (int)rem;
-                    s_prefix = prefix | ((unsigned long long)bin << shift);
-                }
-            }
-            __syncthreads();
-        }
-        const unsigned long long kth = s_prefix;  // the chunk's kc-th largest key; keys are unique
         if (threadIdx.x == 0) s_base = atomicAdd(&sc.count[r], kc);   // room for this chunk's candidates
         __syncthreads();
         // a counter that was not zero at launch (scratch shared with something else) must not turn
@@ -263,11 +377,16 @@ sample_kernel(int* __restrict__ out_tokens, const float* __restrict__ logits, co
         unsigned long long* dst = sc.cand + (size_t)r * XB_TOPK_MAX + (room ? s_base : 0);
         if (threadIdx.x == 0) s_need = 0;
         __syncthreads();
-        for (int i = lo + (int)threadIdx.x; i < hi; i += blockDim.x) {
-            const unsigned long long key = key_of(cached ? s_vals[i - lo] : row[i], i);
-            if (key >= kth) {
-                const int at = atomicAdd(&s_need, 1);
-                if (room && at < kc) dst[at] = key;
+        if (gathered && few) {
+            place_largest(pool, pooled, kc, dst, room);
+        } else {
+            const int from = gathered ? pooled : n_chunk;
+            for (int i = threadIdx.x; i < from; i += blockDim.x) {
+                const unsigned long long key = gathered ? pool[i] : key_at(i);
+                if (key >= kth) {
+                    const int at = atomicAdd(&s_need, 1);
+                    if (room && at < kc) dst[at] = key;
+                }
             }
         }
     }
@@ -304,12 +423,46 @@ sample_kernel(int* __restrict__ out_tokens, const float* __restrict__ logits, co
         sc.count[r] = 0;
     }
     const int n = total < k ? total : k;
-    // bitonic sort, descending: the first n keys are the row's n largest
-    for (int size = 2; size <= XB_TOPK_MAX; size <<= 1) {
+    if (n <= XB_SAMPLE_FEW && total > n) {
+        // few wanted: a threshold from the groups' maxima, the candidates that reach it gathered and placed in order
+        const unsigned long long my_key = (int)threadIdx.x < total ? cand_key[threadIdx.x] : 0ull;
+        unsigned long long T = group_threshold(my_key, n, gmax, &s_t);
+        if (T == 0ull) T = 1ull;
+        if (threadIdx.x == 0) s_need = 0;
+        __syncthreads();
+        if (my_key >= T) pool[atomicAdd(&s_need, 1)] = my_key;   // at most `total` <= 1024 of them
+        __syncthreads();
+        const int m = s_need;
+        for (int i = threadIdx.x; i < XB_TOPK_MAX; i += blockDim.x) cand_key[i] = 0ull;
+        __syncthreads();
+        place_largest(pool, m, n, cand_key, true);
+        __syncthreads();
+    } else {
+    // the row's n largest among the chunks' candidates (a select, as above), moved to the front ...
+    if (total > n) {
+        unsigned long long* top = reinterpret_cast<unsigned long long*>(s_vals);   // the chunk's values are done with
+        const unsigned long long kth = select_kth(total, n, [&](int i) { return cand_key[i]; }, sel);
+        if (threadIdx.x == 0) s_need = 0;
+        __syncthreads();
+        for (int i = threadIdx.x; i < total; i += blockDim.x) {
+            const unsigned long long key = cand_key[i];
+            if (key >= kth) {
+                const int at = atomicAdd(&s_need, 1);
+                if (at < n) top[at] = key;
+            }
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < XB_TOPK_MAX; i += blockDim.x) cand_key[i] = i < n ? top[i] : 0ull;
+        __syncthreads();
+    }
+    // ... and put in descending order: a bitonic sort over the next power of two
+    int sort_n = 2;
+    while (sort_n < n) sort_n <<= 1;
+    for (int size = 2; size <= sort_n; size <<= 1) {
         for (int stride = size >> 1; stride > 0; stride >>= 1) {
             const int i = threadIdx.x;
             const int j = i ^ stride;
-            if (j > i) {
+            if (i < sort_n && j > i) {
                 const bool desc = (i & size) == 0;
                 const unsigned long long a = cand_key[i], b = cand_key[j];
                 if (desc ? (a < b) : (a > b)) {
@@ -319,6 +472,7 @@ sample_kernel(int* __restrict__ out_tokens, const float* __restrict__ logits, co
             }
             __syncthreads();
         }
+    }
     }
     // ---- probabilities of the candidates, renormalised; nucleus cut ---------------------------
     {
@@ -378,7 +532,7 @@ XB_EXPORT int xb_sample(int* out_tokens, float* logits, const void* params, cons
     sc.cand = (unsigned long long*)base;
     base += (size_t)capacity * XB_TOPK_MAX * 8;
     sc.part = (Best*)base;
-    int chunks = 296 / rows;   // two CTAs of 1024 threads per SM of a 148-SM part
+    int chunks = 148 / rows;   // one CTA of 1024 threads per SM of a 148-SM part (its registers fill the SM): one wave
     if (chunks < 1) chunks = 1;
     if (chunks > XB_SAMPLE_CHUNKS_MAX) chunks = XB_SAMPLE_CHUNKS_MAX;
     sample_kernel<<<dim3(chunks, rows), 1024, 0, stream>>>(out_tokens, logits, (const SampleParams*)params, vocab, chunks, sc, err_word);
