@@ -581,11 +581,15 @@ attn_decode_plan_kernel(int* __restrict__ plan, int capacity, const int* __restr
         sum += tiles[i];
     }
     const long long all_tiles = (long long)block_scan(sum, unused) * nkv;
-    long long share = (all_tiles + target_ctas - 1) / target_ctas;
-    if (share < min_tiles) share = min_tiles;
+    // the share as an int (a larger one would cut nothing anyway), so that the divisions below are short ones:
+    // every thread of the block goes through them, most with nothing to divide
+    const int share = (int)max((long long)min_tiles, min((all_tiles + target_ctas - 1) / target_ctas, (long long)INT_MAX));
     int pieces = 0, at;
 #pragma unroll
-    for (int i = 0; i < EACH_MAX; ++i) pieces += tiles[i] ? max(1, (int)(tiles[i] / share)) : 0;
+    for (int i = 0; i < EACH_MAX; ++i) {
+        if (tiles[i] == 0) continue;
+        pieces += max(1, tiles[i] / share);
+    }
     const int total = block_scan(pieces, at);
     if (threadIdx.x == 0) {
         plan[0] = total <= capacity ? total : 0;
@@ -599,7 +603,7 @@ attn_decode_plan_kernel(int* __restrict__ plan, int capacity, const int* __restr
 #pragma unroll
         for (int i = 0; i < EACH_MAX; ++i) {
             if (!tiles[i]) continue;
-            const int n = tiles[i], cz = max(1, (int)(n / share)), sz = (n + cz - 1) / cz;
+            const int n = tiles[i], cz = max(1, n / share), sz = (n + cz - 1) / cz;
             for (int j = 0; j < cz; ++j, ++a) piece_tiles[a] = j * sz < n ? min(sz, n - j * sz) : 0;
         }
         __syncthreads();
@@ -608,7 +612,7 @@ attn_decode_plan_kernel(int* __restrict__ plan, int capacity, const int* __restr
     for (int i = 0; i < EACH_MAX; ++i) {
         if (!tiles[i]) continue;
         const int z = (int)threadIdx.x * each + i, t = tok[i], n = tiles[i];
-        const int cz = max(1, (int)(n / share));
+        const int cz = max(1, n / share);
         const int sz = (n + cz - 1) / cz, ns = (n + sz - 1) / sz;   // tiles per piece; pieces that hold any
         const int pos = positions[t];
         const int lo = window > 0 ? max(0, pos - window + 1) : 0;
