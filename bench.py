@@ -265,7 +265,8 @@ def main() -> int:
         from xinfer_b200 import measure
         pk = peaks()
         for rec in (measure.decode_gemms(hbm_gbs=pk["hbm_gbs"]) + measure.decode_attention(hbm_gbs=pk["hbm_gbs"])
-                    + measure.prefill_attention(peak_tflops=pk["bf16_tflops"]) + measure.prefill_elementwise(hbm_gbs=pk["hbm_gbs"])):
+                    + measure.prefill_attention(peak_tflops=pk["bf16_tflops"]) + measure.prefill_elementwise(hbm_gbs=pk["hbm_gbs"])
+                    + measure.sampling()):
             print(json.dumps(rec), flush=True)
         return 0
 

@@ -225,6 +225,26 @@ def prefill_elementwise(tokens: int = 2048, *, hidden: int = 4096, heads: int = 
     return out
 
 
+def sampling(rows: Sequence[int] = (1, 8, 64), *, vocab: int = 151936, device="cuda:0") -> List[Dict]:
+    """The sampling kernel alone (no host work, no copies) over float32 logits, per way of sampling."""
+    from .sampling import SamplingParams
+    from .sampling.sampler import Sampler
+    ways = (("greedy", SamplingParams(temperature=0.0)), ("temperature", SamplingParams(temperature=0.8)),
+            ("top-k 20, top-p 0.95", SamplingParams(temperature=0.6, top_k=20, top_p=0.95)),
+            ("top-p 0.9", SamplingParams(temperature=0.8, top_p=0.9)), ("top-k 1000", SamplingParams(temperature=0.8, top_k=1000)))
+    out = []
+    for r in rows:
+        logits = torch.randn(r, vocab, device=device) * 3
+        s = Sampler(device, r)
+        rec = {"kernel": "sampling", "rows": r, "vocab": vocab}
+        for name, sp in ways:
+            s.sample(logits, [sp] * r, [1] * r, [0] * r, None)     # leaves the rows' parameters on the device
+            rec[name + " us"] = round(_graph_time_us(lambda: [kernels.sample(s._out_dev, logits, s._params_dev, s._hist_dev, False,
+                                                                             s._scratch, None, capacity=r) for _ in range(8)], 8), 1)
+        out.append(rec)
+    return out
+
+
 def decode_ablation(config: Dict, *, layers: int = 12, batches: Sequence[int] = (1, 8), context: int = 3900,
                     page_size: int = 16, device="cuda:0") -> List[Dict]:
     """What each kind of kernel costs IN the chain of a decode step: the step is timed whole and with one
