@@ -222,3 +222,12 @@ def test_generation_config_reads_merges_and_fills(tmp_path):
     (tmp_path / "generation_config.json").write_text("{ not json")
     with pytest.raises(ConfigError):
         GenerationConfig.load(str(tmp_path))
+
+
+def test_command_line_refuses_what_the_engine_does_not_do():
+    from xinfer_b200.cli import main
+    for argv, word in ((["--m", "x", "--cpu"], "no CPU path"), (["--m", "x", "--d", "0,1"], "one GPU"),
+                       (["--m", "x", "--d", "gpu"], "one GPU"), (["--m", "x", "--w", "y"], "either"), ([], "required")):
+        with pytest.raises(SystemExit) as e:
+            main(argv)
+        assert word in str(e.value)

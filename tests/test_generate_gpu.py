@@ -158,10 +158,14 @@ def test_command_line(model_folders, capsys):
     folder = model_folders("A", torch.float32)
     cfg, w = plain.load_folder(folder)
     assert main(["--m", folder, "--dtype", "f32", "--prompts", "5,6,7|9,10", "--max-tokens", "4", "--ignore-eos",
-                 "--disable-cuda-graph", "--num-blocks", "16"]) == 0
+                 "--disable-cuda-graph", "--num-blocks", "16", "--d", "0"]) == 0
     out = capsys.readouterr().out
     want = ",".join(str(t) for t in plain.generate(cfg, w, [5, 6, 7], 4))
     assert want in out and "Prompt tokens: 5" in out and "Decoded tokens: 8" in out
+    # the sampling flags are the engine's defaults for requests that set nothing (top-k 1: the best token whatever the temperature)
+    assert main(["--m", folder, "--dtype", "f32", "--prompts", "5,6,7", "--max-tokens", "4", "--ignore-eos", "--num-blocks", "16",
+                 "--temperature", "3.0", "--top-k", "1", "--seed", "5"]) == 0
+    assert want in capsys.readouterr().out
 
 
 @pytest.mark.parametrize("dtype,graphs", [("f32", False), ("bf16", True), ("bf16", False)])

@@ -24,6 +24,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--m", dest="model_id", help="model folder (config.json and model.safetensors)")
     ap.add_argument("--w", dest="weight_path", help="same as --m (the reference's older spelling)")
     ap.add_argument("--dtype", default="bf16", help="bf16 (default) or f32")
+    ap.add_argument("--d", dest="device_ids", help="the GPU to run on, by index (the reference takes a list: one device here)")
+    ap.add_argument("--cpu", action="store_true", help="refused: this engine has no CPU path")
     ap.add_argument("--prompts", help="token ids: '1,2,3|4,5,6' ('|' between prompts)")
     ap.add_argument("--batch", type=int, help="repeat one prompt this many times (batch performance test)")
     ap.add_argument("--prompt-len", type=int, help="make a prompt of this many seeded random token ids")
@@ -69,6 +71,14 @@ def main(argv: Optional[List[str]] = None) -> int:
     folder = args.model_id or args.weight_path
     if not folder:
         raise SystemExit("--m <model folder> is required")
+    if args.cpu:
+        raise SystemExit("--cpu: this engine runs on a B200 only; there is no CPU path")
+    device = "cuda:0"
+    if args.device_ids:
+        ids = [x for x in args.device_ids.split(",") if x != ""]
+        if len(ids) != 1 or not ids[0].isdigit():
+            raise SystemExit(f"--d {args.device_ids}: this engine runs on one GPU; give one device index")
+        device = f"cuda:{ids[0]}"
     if args.random:
         import torch
         from .weights import write_random_model
@@ -97,7 +107,7 @@ def main(argv: Optional[List[str]] = None) -> int:
                  frequency_penalty=args.frequency_penalty, presence_penalty=args.presence_penalty)
     generation_cfg = GenerationConfig(**flags) if any(v is not None for v in flags.values()) else None
     econfig = EngineConfig(
-        weight_path=folder, generation_cfg=generation_cfg, block_size=args.block_size, num_blocks=args.num_blocks,
+        weight_path=folder, generation_cfg=generation_cfg, device=device, block_size=args.block_size, num_blocks=args.num_blocks,
         kv_fraction=args.kv_fraction, max_num_seqs=args.max_num_seqs or max(len(prompts), 1),
         max_num_batched_tokens=args.max_num_batched_tokens, prefill_chunk_size=args.prefill_chunk_size,
         max_model_len=args.max_model_len, max_tokens=args.max_tokens, seed=args.seed,
