@@ -116,7 +116,7 @@ def test_top_k_on_shapes_of_logits_that_defeat_a_threshold(rows):
         np.where(rng.random(vocab) < 0.05, np.float32(9.0), base),            # a plateau of 7,600 equal maxima
         np.where(rng.random(vocab) < 0.0002, base, np.float32(-np.inf)),      # about 30 finite values
         np.where(np.arange(vocab) % 1024 == 5, base + 30, base),              # every large value in one thread's elements
-        np.round(base),                                                       # seven or so distinct values
+        np.round(base * 0.05),                                                # zeros of both signs, and little else
     ]
     combos = [(20, 0.95), (1, None), (256, None), (257, 0.9), (None, 0.8), (1000, None), (64, 0.5)]
     logits = np.stack([shapes[r % len(shapes)] for r in range(rows)]).astype(np.float32)

@@ -32,10 +32,11 @@ __device__ __forceinline__ float gumbel_of(uint32_t seed_lo, uint32_t seed_hi, u
     return -logf(-logf(u));
 }
 
-// order-preserving map float -> uint32 (larger float, larger key); NaN sorts lowest
+// order-preserving map float -> uint32 (larger float, larger key); NaN sorts lowest; the two zeros get one
+// key (-0 + 0 is +0), as they compare equal everywhere else
 __device__ __forceinline__ uint32_t float_key(float v) {
     if (v != v) return 0u;
-    const uint32_t b = __float_as_uint(v);
+    const uint32_t b = __float_as_uint(v + 0.f);
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 
