@@ -168,6 +168,22 @@ def test_abort_frees_pages():
     assert cm.free_pages() == 64 and s.finish_reason(0) == "abort" and s.drain_finished() == [0]
 
 
+def test_abort_of_a_waiting_request_and_of_one_whose_step_is_not_recorded_yet():
+    cm, s = make(seqs=1)
+    s.add(0, [1] * 10, max_tokens=4)
+    s.add(1, [2] * 10, max_tokens=4)          # waits: one request slot
+    assert s.abort(1) and s.finish_reason(1) == "abort" and s.drain_finished() == [1] and s.output(1) == []
+    entries = s.schedule()                     # request 0's prompt, scheduled ...
+    assert [e.req_id for e in entries] == [0]
+    assert s.abort(0) and cm.free_pages() == 64   # ... and aborted before its token is recorded
+    assert s.commit([9]) == [0] and s.output(0) == []   # reported as ended; the token of a request that is gone is dropped
+    assert s.drain_finished() == [] and not s.has_work()
+    cm.check_consistent()
+    s.add(2, [3] * 5, max_tokens=2)            # the scheduler goes on
+    batches, ended = run(s)
+    assert s.output(2) == [7, 7] and cm.free_pages() == 64
+
+
 @pytest.mark.parametrize("seed", range(5))
 def test_random_workloads_finish_and_leave_the_pool_whole(seed):
     rng = random.Random(seed)
