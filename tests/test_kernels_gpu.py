@@ -529,3 +529,30 @@ def test_swiglu_many_rows_equals_few_rows(tokens, inter):
     assert torch.equal(o1, o2)
     gate, up = gu[:, :inter].float(), gu[:, inter:].float()
     assert (o2.float() - torch.nn.functional.silu(gate) * up).abs().max().item() <= 0.02 * (gate.abs() * up.abs()).max().item()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("seed", range(4))
+def test_attention_tiled_random_layouts_and_batches(seed):
+    """Random head layouts (1 to 16 query heads per key/value head), head sizes, page sizes, windows and
+    mixed batches of decode tokens and prompt portions, through the backend's choice of kernels."""
+    rng = np.random.default_rng(500 + seed)
+    for case in range(10):
+        nkv = int(rng.choice([1, 2, 3, 4, 8]))
+        G = int(rng.choice([1, 2, 3, 4, 5, 8, 16]))
+        if nkv * G > 40:
+            nkv = max(1, 40 // G)
+        d = int(rng.choice([16, 32, 48, 64, 80, 96, 112, 128]))
+        ps = int(rng.choice([8, 16, 32, 64, 128]))
+        window = None if rng.random() < 0.6 else int(rng.integers(3, 900))
+        entries = []
+        for _ in range(int(rng.integers(1, 6))):
+            kind = rng.random()
+            if kind < 0.45:
+                entries.append((int(rng.integers(0, 1500)), int(rng.integers(1, 5))))      # decode tokens behind a context
+            elif kind < 0.9:
+                entries.append((int(rng.integers(0, 700)), int(rng.integers(5, 400))))      # a portion behind a prefix
+            else:
+                entries.append((0, int(rng.integers(1, 300))))                              # the start of a prompt
+        worst = attention_case(tiled_kernel, torch.bfloat16, nkv * G, nkv, d, ps, entries, window, seed=case)
+        assert worst <= tol(torch.bfloat16, 2), (nkv * G, nkv, d, ps, window, entries, worst)

@@ -128,3 +128,27 @@ def test_top_k_on_shapes_of_logits_that_defeat_a_threshold(rows):
         want = [plain.sample(logits[r], 0.8, top_k=use[r][0] or 0, top_p=use[r][1] if use[r][1] is not None else 1.0,
                              seed=seeds[r], draw=shift) for r in range(rows)]
         assert got == want, (shift, got, want)
+
+
+@pytest.mark.parametrize("seed", range(3))
+def test_random_rows_and_options(seed):
+    # random vocabularies, row counts, scales (coarse values, halves of minus infinity) and options per row
+    from xinfer_b200.sampling import SamplingParams
+    rng = np.random.default_rng(2024 + seed)
+    for trial in range(10):
+        vocab = int(rng.choice([7, 64, 257, 1000, 4097, 32000, 151936]))
+        rows = int(rng.choice([1, 2, 5, 8, 17, 40, 64, 150]))
+        rows = max(1, min(rows, int(3e6 // vocab)))
+        logits = (rng.normal(size=(rows, vocab)) * float(rng.choice([0.1, 1, 3, 10]))).astype(np.float32)
+        if rng.random() < 0.5:
+            logits = np.round(logits * 4) / 4
+        if rng.random() < 0.2:
+            logits[:, : vocab // 2] = -np.inf
+        params = [SamplingParams(temperature=float(rng.choice([0.0, 0.3, 0.8, 1.0, 2.0])),
+                                 top_k=int(rng.choice([0, 1, 2, 20, 50, 64, 65, 100, 256, 300, 1024, 5000])),
+                                 top_p=float(rng.choice([1.0, 0.0, 0.1, 0.5, 0.9, 0.95, 0.999]))) for _ in range(rows)]
+        seeds = [int(rng.integers(0, 2 ** 40)) for _ in range(rows)]
+        got = run(logits, params, seeds, [trial] * rows)
+        want = [plain.sample(logits[r], params[r].temperature, top_k=params[r].top_k, top_p=params[r].top_p, seed=seeds[r], draw=trial)
+                for r in range(rows)]
+        assert got == want, (trial, vocab, rows, [(r, params[r]) for r in range(rows) if got[r] != want[r]][:3])
