@@ -200,16 +200,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
         }
     } else if (warp == 9) {
-        // ---- Q loads and S = Q K^T, both heads, tile after tile, item after item -----------------------------
-        if (lane == 0) {
+        // ---- Q loads and S = Q K^T, both heads, tile after tile, item after item: the whole warp walks the loop
+        // (its values stay uniform), one lane issues -----------------------------------------------------------
+        {
+            const bool leader = lane == 0;
             const uint32_t idesc_s = umma_idesc(KT, 0);
             const uint64_t dq0 = umma_desc(q_sm, 16, 1024), dk0 = umma_desc(kv_sm, 16, 1024);
             auto load_q = [&](const PrefillItem& w) {
-                mbar_expect_tx(q_full, (uint32_t)w.nhd * Q_ONE);
-                for (int hd = 0; hd < w.nhd; ++hd)
+                if (leader) {
+                    mbar_expect_tx(q_full, (uint32_t)w.nhd * Q_ONE);
+                    for (int hd = 0; hd < w.nhd; ++hd)
 #pragma unroll
-                    for (int hf = 0; hf < HALVES; ++hf)
-                        tma_load_3d(q_sm + hd * Q_ONE + hf * QT * 128, &map_q, hf * 64, w.h0 + hd, w.t0, q_full);
+                        for (int hf = 0; hf < HALVES; ++hf)
+                            tma_load_3d(q_sm + hd * Q_ONE + hf * QT * 128, &map_q, hf * 64, w.h0 + hd, w.t0, q_full);
+                }
+                __syncwarp();
             };
             int s = 0, Th[2] = {0, 0};   // ring stage of the next tile (over all items), tiles of each head so far
             uint32_t ph = 0;               // parity of the times the ring has been gone round
@@ -218,29 +223,33 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             load_q(w);
             for (int k = item_begin; k < item_end && ok; ++k) {
                 const int I = k - item_begin;
-                ok = mbar_wait(q_full, (uint32_t)I & 1u, err, true);
+                ok = __all_sync(0xffffffffu, mbar_wait(q_full, (uint32_t)I & 1u, err, true));
                 for (int it = 0; it < w.iters && ok; ++it) {
-                    ok = mbar_wait(k_full0 + 8 * s, ph, err, true);
+                    ok = __all_sync(0xffffffffu, mbar_wait(k_full0 + 8 * s, ph, err, true));
                     const uint64_t dk = dk0 + (uint64_t)((s * STAGE_BYTES) >> 4);
 #pragma unroll
                     for (int hd = 0; hd < 2; ++hd) {
                         if (hd >= w.nhd) break;
                         const int th = Th[hd] + it, sb = th & 1;
                         // S[sb] of this head held the scores and then P of its tile th - 2: that P V must have read it
-                        ok = ok && (th < 2 || mbar_wait(pv_done0 + 8 * (2 * hd + sb), ((th >> 1) - 1) & 1, err, true));
+                        ok = ok && (th < 2 || __all_sync(0xffffffffu, mbar_wait(pv_done0 + 8 * (2 * hd + sb), ((th >> 1) - 1) & 1, err, true)));
                         if (!ok) break;
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         const uint64_t dq = dq0 + (uint64_t)((hd * Q_ONE) >> 4);
+                        if (leader) {
 #pragma unroll
-                        for (int kk = 0; kk < DP / 16; ++kk) {
-                            const uint32_t off = (kk >> 2), inner = (kk & 3) * 32;
-                            umma_bf16(tmem + (uint32_t)(hd * 128 + sb * 64), dq + (uint64_t)((off * QT * 128 + inner) >> 4),
-                                      dk + (uint64_t)((off * KV_HALF + inner) >> 4), idesc_s, kk ? 1u : 0u);
+                            for (int kk = 0; kk < DP / 16; ++kk) {
+                                const uint32_t off = (kk >> 2), inner = (kk & 3) * 32;
+                                umma_bf16(tmem + (uint32_t)(hd * 128 + sb * 64), dq + (uint64_t)((off * QT * 128 + inner) >> 4),
+                                          dk + (uint64_t)((off * KV_HALF + inner) >> 4), idesc_s, kk ? 1u : 0u);
+                            }
+                            umma_commit(s_ready0 + 8 * (2 * hd + sb));
                         }
-                        umma_commit(s_ready0 + 8 * (2 * hd + sb));
+                        __syncwarp();
                     }
                     if (!ok) break;
-                    umma_commit(k_empty0 + 8 * s);   // the key stage is free once both products have completed
+                    if (leader) umma_commit(k_empty0 + 8 * s);   // the key stage is free once both products have completed
+                    __syncwarp();
                     if (++s == NS) {
                         s = 0;
                         ph ^= 1u;
@@ -251,8 +260,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (w.nhd == 2) Th[1] += w.iters;
                 if (k + 1 < item_end) {
                     // the next item's Q goes where this one's lies: once every product that reads it has completed
-                    umma_commit(q_empty);
-                    ok = mbar_wait(q_empty, (uint32_t)I & 1u, err, true);
+                    if (leader) umma_commit(q_empty);
+                    __syncwarp();
+                    ok = __all_sync(0xffffffffu, mbar_wait(q_empty, (uint32_t)I & 1u, err, true));
                     if (ok) {
                         w = item_at(k + 1);
                         load_q(w);
@@ -262,8 +272,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (!ok) words[3] = 1;
         }
     } else if (warp == 11) {
-        // ---- issuer of O += P V, both heads, tile after tile, item after item ---------------------------------
-        if (lane == 0) {
+        // ---- issuer of O += P V, both heads, tile after tile, item after item (the whole warp walks, one lane issues)
+        {
+            const bool leader = lane == 0;
             const uint32_t idesc_o = umma_idesc(DP, 1);
             const uint64_t dv0 = umma_desc(kv_sm + KV_BYTES, KV_HALF, 1024);
             int s = 0, Th[2] = {0, 0};   // ring stage of the next tile (over all items), tiles of each head so far
@@ -272,27 +283,33 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             for (int k = item_begin; k < item_end && ok; ++k) {
                 const PrefillItem w = item_at(k);
                 for (int it = 0; it < w.iters && ok; ++it) {
-                    ok = mbar_wait(v_full0 + 8 * s, ph, err, true);
+                    ok = __all_sync(0xffffffffu, mbar_wait(v_full0 + 8 * s, ph, err, true));
                     const uint64_t dv = dv0 + (uint64_t)((s * STAGE_BYTES) >> 4);
 #pragma unroll
                     for (int hd = 0; hd < 2; ++hd) {
                         if (hd >= w.nhd) break;
                         const int th = Th[hd] + it, sb = th & 1;
-                        ok = ok && mbar_wait(p_ready0 + 8 * hd, th & 1, err, true);   // P written, V rows zeroed, O rescaled
+                        ok = ok && __all_sync(0xffffffffu, mbar_wait(p_ready0 + 8 * hd, th & 1, err, true));   // P written, V rows zeroed, O rescaled
                         if (!ok) break;
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         // A = P [128 x 64 keys] in tensor memory (over the scores it came from), B = V [64 keys x DP]
                         // MN-major (halves 64 columns apart); the item's first tile overwrites O
                         const uint32_t tp = tmem + (uint32_t)(hd * 128 + sb * 64);
+                        if (leader) {
 #pragma unroll
-                        for (int kk = 0; kk < KT / 16; ++kk)
-                            umma_bf16_ta(tmem + (uint32_t)(256 + hd * 128), tp + (uint32_t)(kk * 8), dv + (uint64_t)((kk * 2048) >> 4),
-                                         idesc_o, (it | kk) ? 1u : 0u);
-                        umma_commit(pv_done0 + 8 * (2 * hd + sb));   // P, its score buffer and O of this head are free again
+                            for (int kk = 0; kk < KT / 16; ++kk)
+                                umma_bf16_ta(tmem + (uint32_t)(256 + hd * 128), tp + (uint32_t)(kk * 8), dv + (uint64_t)((kk * 2048) >> 4),
+                                             idesc_o, (it | kk) ? 1u : 0u);
+                            umma_commit(pv_done0 + 8 * (2 * hd + sb));   // P, its score buffer and O of this head are free again
+                        }
+                        __syncwarp();
                     }
                     if (!ok) break;
-                    umma_commit(v_empty0 + 8 * s);           // and so is the value stage
-                    if (it + 1 == w.iters) umma_commit(bar_o);
+                    if (leader) {
+                        umma_commit(v_empty0 + 8 * s);           // and so is the value stage
+                        if (it + 1 == w.iters) umma_commit(bar_o);
+                    }
+                    __syncwarp();
                     if (++s == NS) {
                         s = 0;
                         ph ^= 1u;
