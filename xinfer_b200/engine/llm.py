@@ -101,7 +101,10 @@ class EngineStream:
     def _pull(self) -> None:
         eng, seq_id = self.engine, self.seq_id
         if seq_id in eng._live:
+            before = (eng.stats["steps"], len(eng._live))
             eng.step()
+            if (eng.stats["steps"], len(eng._live)) == before and not eng.has_work() and seq_id in eng._live:
+                eng.cancel(seq_id)     # nothing can move this request any further: end it instead of spinning
         done = eng._done.get(seq_id)
         src = done.decode_output if done is not None else eng.scheduler.output(seq_id)
         self._queue += [StreamItem("TOKEN_ID", int(t)) for t in src[self._streamed:]]
