@@ -5,7 +5,12 @@ per part, on the CPU.  It shares no code with the engine (it reads safetensors t
 It rests on the formulas of the reference's sources (cited per function as file:line inside the
 reference project): the reference's own model code cannot be imported or compiled here (a Rust
 crate whose tensor and kernel layers are external git crates; no Rust toolchain, no network), so
-no golden output of the reference exists under tests/golden.
+no output of the reference's model exists under tests/golden.  What can be run of the reference
+on the CPU are the Python golden functions of its differential probes - rotation, SiLU gate,
+causal attention with grouped heads after a prefix; their outputs on small seeded inputs are in
+tests/golden/probe_parts.safetensors (written by tests/golden/make_golden.py), and
+tests/test_golden.py holds ``apply_rope``, ``swiglu`` and ``causal_attention`` against them.  RMSNorm, the
+order of q/k norm and rotation, the residual structure and the output head are pinned by reading alone.
 
 ``dtype`` float64 gives a high-precision run whose rotation angles are still the float32 values
 the reference computes; float32 is the like-for-like run.  ``round_to`` = torch.bfloat16 rounds
