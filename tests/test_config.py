@@ -231,3 +231,18 @@ def test_command_line_refuses_what_the_engine_does_not_do():
         with pytest.raises(SystemExit) as e:
             main(argv)
         assert word in str(e.value)
+
+
+def test_engine_config_takes_the_references_options_and_refuses_what_is_not_built():
+    # the options of the reference's Python example, none of them asking for an unbuilt feature
+    ec = EngineConfig(model_id=None, weight_path="/m", weight_file=None, max_num_seqs=2, max_model_len=512, max_tokens=64, isq=None,
+                      device_ids=[0], generation_cfg=None, disable_prefix_cache=True, prefix_cache_max_tokens=None,
+                      kvcache_dtype=None, server_mode=False, cpu_mem_fold=None, kv_fraction=0.5, disable_reasoning=True,
+                      disable_cuda_graph=False, prefill_chunk_size=8192)
+    ec.validate()
+    assert ec.device == "cuda:0"
+    for kw, word in ((dict(isq="q4k"), "isq"), (dict(kvcache_dtype="fp8"), "kvcache_dtype"), (dict(device_ids=[0, 1]), "device_ids"),
+                     (dict(num_shards=2), "num_shards"), (dict(weight_file="m.gguf"), "weight_file"), (dict(server_mode=True), "server_mode"),
+                     (dict(cpu_mem_fold=0.5), "cpu_mem_fold"), (dict(mtp_num_speculative_tokens=2), "speculative")):
+        with pytest.raises(ValueError, match=word):
+            EngineConfig(weight_path="/m", **kw).validate()

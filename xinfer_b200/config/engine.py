@@ -3,7 +3,7 @@
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional
+from typing import List, Optional
 
 from .generation import GenerationConfig
 
@@ -39,6 +39,23 @@ class EngineConfig:
     device: str = "cuda:0"
     # debug: fill every page that goes back to its pool with NaN before the next step runs
     poison_freed_pages: bool = False
+    # ---- options of the reference's EngineConfig for what this engine does not build.  They are accepted so
+    # that a script written for the reference constructs its configuration unchanged; a value that asks for the
+    # feature is refused by validate() with the feature's name, a value that switches it off is ignored. ----
+    device_ids: Optional[List[int]] = None        # one GPU: [i] selects cuda:i
+    weight_file: Optional[str] = None             # GGUF files
+    isq: Optional[str] = None                     # in-situ quantization
+    kvcache_dtype: Optional[str] = None           # quantized caches ("auto" / None: the engine's dtype)
+    num_shards: Optional[int] = 1                 # tensor parallelism
+    num_nodes: int = 1
+    server_mode: Optional[bool] = None
+    cpu_mem_fold: Optional[float] = None          # cache pages swapped to host memory
+    disable_prefix_cache: bool = False            # there is no prefix cache to disable
+    prefix_cache_max_tokens: Optional[int] = None
+    disable_reasoning: bool = False               # chat templates are outside this engine
+    mtp_num_speculative_tokens: Optional[int] = None
+    hf_token: Optional[str] = None
+    hf_token_path: Optional[str] = None
 
     def model_dir(self) -> str:
         path = self.weight_path or self.model_id
@@ -55,3 +72,24 @@ class EngineConfig:
             raise ValueError(f"EngineConfig.num_blocks must be positive, got {self.num_blocks}")
         if not (0.0 < self.kv_fraction <= 1.0):
             raise ValueError(f"EngineConfig.kv_fraction must lie in (0, 1], got {self.kv_fraction}")
+        not_built = []
+        if self.weight_file:
+            not_built.append("weight_file (GGUF weights)")
+        if self.isq:
+            not_built.append("isq (quantized weights)")
+        if self.kvcache_dtype not in (None, "", "auto"):
+            not_built.append("kvcache_dtype (quantized caches)")
+        if self.num_shards not in (None, 1) or self.num_nodes != 1:
+            not_built.append("num_shards / num_nodes (more than one GPU)")
+        if self.device_ids is not None and len(self.device_ids) != 1:
+            not_built.append("device_ids with more than one GPU")
+        if self.server_mode:
+            not_built.append("server_mode")
+        if self.cpu_mem_fold:
+            not_built.append("cpu_mem_fold (cache pages in host memory)")
+        if self.mtp_num_speculative_tokens:
+            not_built.append("mtp_num_speculative_tokens (speculative decoding)")
+        if not_built:
+            raise ValueError("EngineConfig asks for what this engine does not build: " + "; ".join(not_built))
+        if self.device_ids is not None:
+            self.device = f"cuda:{int(self.device_ids[0])}"
