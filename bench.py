@@ -367,6 +367,9 @@ def main() -> int:
     # ---- decode at the headline batch --------------------------------------------------------------------
     B = args.batch
     ctx0 = args.context - steps - warmup - SETTLE - 2
+    if ctx0 < 16:
+        raise SystemExit(f"bench.py: --steps {steps} with --warmup {warmup} does not fit a context of {args.context} "
+                         f"(the timed steps end at the context length): give a larger --context or fewer steps")
     slots = fill(B, ctx0)
     ms, launches, (t0, t1) = decode_device(slots, steps, warmup)
     ck = clocks.summary(t0, t1)
